@@ -1,0 +1,101 @@
+"""ctypes binding of libgufo_cuda.so, the C ABI declared in include/gufo_cuda.h.
+
+There is no fallback: if the library is missing or no sm_100 device is usable,
+loading or context creation raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgufo_cuda.so")
+
+OK = 0
+STATUS_NAMES = {1: "bad argument", 2: "shape", 3: "unsupported type", 4: "CUDA runtime",
+                5: "out of memory", 6: "timeout", 7: "too large"}
+
+_f32p = C.POINTER(C.c_float)
+
+
+class GufoCudaError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"gufo_cuda status {status} ({STATUS_NAMES.get(status, '?')}): {text}")
+        self.status = status
+
+
+class Rows(C.Structure):
+    """gufo_cuda_rows: rows [first, first + rows) of a matrix handle."""
+    _fields_ = [("w", C.c_int64), ("first", C.c_int64), ("rows", C.c_int64)]
+
+
+class DeltaSeq(C.Structure):
+    _fields_ = [("state", C.c_void_p), ("state_out", C.c_void_p), ("q", C.c_void_p), ("k", C.c_void_p),
+                ("v", C.c_void_p), ("decay", C.c_void_p), ("beta", C.c_void_p), ("y", C.c_void_p)]
+
+
+class LinearSeq(C.Structure):
+    _fields_ = [("in_", C.c_void_p), ("conv_in", C.c_void_p), ("conv_out", C.c_void_p),
+                ("ssm", C.c_void_p), ("ssm_out", C.c_void_p), ("y", C.c_void_p)]
+
+
+class DeltaNetParams(C.Structure):
+    _fields_ = [("key_heads", C.c_int), ("value_heads", C.c_int), ("head_dim", C.c_int),
+                ("conv_kernel", C.c_int), ("rms_eps", C.c_float), ("conv", _f32p), ("ssm_a", _f32p),
+                ("dt_bias", _f32p), ("ssm_norm", _f32p)]
+
+
+# name -> (restype, argtypes); every symbol include/gufo_cuda.h declares.
+SIGNATURES = {
+    "gufo_cuda_ctx_create": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "gufo_cuda_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "gufo_cuda_ctx_synchronize": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_last_error": (C.c_char_p, [C.c_void_p]),
+    "gufo_cuda_launch_count": (C.c_int64, [C.c_void_p]),
+    "gufo_cuda_malloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "gufo_cuda_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "gufo_cuda_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "gufo_cuda_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "gufo_cuda_memset_zero": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t]),
+    "gufo_cuda_matrix_upload": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64,
+                                          C.POINTER(C.c_int64)]),
+    "gufo_cuda_matrix_from_device": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_int64,
+                                               C.POINTER(C.c_int64)]),
+    "gufo_cuda_matrix_free": (C.c_int, [C.c_void_p, C.c_int64]),
+    "gufo_cuda_dequantize": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "gufo_cuda_dequantize_device": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "gufo_cuda_matmul": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "gufo_cuda_matmul_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int,
+                                          C.c_void_p]),
+    "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,
+                                              C.c_int]),
+    "gufo_cuda_deltanet_layer_create": (C.c_int, [C.c_void_p, C.POINTER(DeltaNetParams),
+                                                  C.POINTER(C.c_int64)]),
+    "gufo_cuda_deltanet_layer_free": (C.c_int, [C.c_void_p, C.c_int64]),
+    "gufo_cuda_deltanet_linear_device": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(LinearSeq), C.c_int]),
+}
+
+_lib = None
+
+
+def load(path: str = LIB_PATH) -> C.CDLL:
+    """Loads the library and declares every entry point; raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(path):
+        raise FileNotFoundError(
+            f"{path} is not built: run `python -m gufo_npu_b200.build` (this backend has no CPU path)")
+    lib = C.CDLL(path)
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def check(lib: C.CDLL, ctx, status: int) -> None:
+    if status != OK:
+        raise GufoCudaError(status, (lib.gufo_cuda_last_error(ctx) or b"").decode())

@@ -1,0 +1,376 @@
+"""Host side of the CUDA backend: the reference's operator interface over the C ABI.
+
+`CudaProjections` mirrors `qwen35::Projections` / `GgufProjections`
+(src/models/qwen35/projections.hpp:45-59, gguf_projections.hpp:19-58 in the
+reference): the same stages, argument meaning and errors, with the matrix
+products on the device. `CudaMixer.Linear` mirrors `Mixer::Linear`
+(src/models/qwen35/decoder.hpp:78-84). Everything computes through
+libgufo_cuda.so; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from . import _capi
+from .synth import ModelConfig, Tensor
+
+
+class Stage(enum.IntEnum):
+    """qwen35::Stage (src/models/qwen35/projections.hpp:14-39)."""
+    kLinearIn = 0
+    kAttentionIn = 1
+    kMixerOut = 2
+    kFfnIn = 3
+    kFfnDown = 4
+    kLmHead = 5
+    kRouter = 6
+    kExpertIn = 7
+    kExpertDown = 8
+    kMtpIn = 9
+
+
+def stage_inputs(c: ModelConfig, stage: Stage, layer: int) -> int:
+    """StageInputs (src/models/qwen35/reference.cpp:609-623)."""
+    if stage == Stage.kMixerOut:
+        return c.heads * c.head_dim if c.is_full_attention(layer) else c.value_dim
+    if stage == Stage.kFfnDown:
+        return c.ffn_width
+    if stage == Stage.kExpertDown:
+        return c.expert_ffn
+    if stage == Stage.kMtpIn:
+        return 2 * c.hidden
+    return c.hidden
+
+
+def stage_outputs(c: ModelConfig, stage: Stage, layer: int) -> int:
+    """StageOutputs (src/models/qwen35/reference.cpp:625-648)."""
+    if stage == Stage.kLinearIn:
+        return c.conv_channels + c.value_dim + 2 * c.linear_value_heads
+    if stage == Stage.kAttentionIn:
+        return 2 * c.heads * c.head_dim + 2 * c.kv_heads * c.head_dim
+    if stage in (Stage.kMixerOut, Stage.kFfnDown, Stage.kExpertDown, Stage.kMtpIn):
+        return c.hidden
+    if stage == Stage.kFfnIn:
+        return 2 * c.ffn_width
+    if stage == Stage.kLmHead:
+        return c.vocab
+    if stage == Stage.kRouter:
+        return c.experts + 1
+    if stage == Stage.kExpertIn:
+        return 2 * c.expert_ffn
+    raise ValueError(stage)
+
+
+def _ptr(buf) -> int:
+    """Device or host address of a torch tensor, numpy array or raw integer."""
+    if buf is None:
+        return 0
+    if isinstance(buf, int):
+        return buf
+    if isinstance(buf, np.ndarray):
+        return buf.ctypes.data
+    return buf.data_ptr()
+
+
+class Context:
+    """One gufo_cuda_ctx: a device, a stream, its weights and scratch."""
+
+    def __init__(self, device: int = 0, stream: Optional[int] = None):
+        self.lib = _capi.load()
+        handle = C.c_void_p()
+        status = self.lib.gufo_cuda_ctx_create(device, C.c_void_p(stream or 0), C.byref(handle))
+        _capi.check(self.lib, None, status)
+        self.handle = handle
+        self.device = device
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.gufo_cuda_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, status: int) -> None:
+        _capi.check(self.lib, self.handle, status)
+
+    def set_stream(self, stream: int) -> None:
+        self._check(self.lib.gufo_cuda_ctx_set_stream(self.handle, C.c_void_p(stream)))
+
+    def synchronize(self) -> None:
+        self._check(self.lib.gufo_cuda_ctx_synchronize(self.handle))
+
+    def launch_count(self) -> int:
+        return int(self.lib.gufo_cuda_launch_count(self.handle))
+
+    # -- device memory ----------------------------------------------------
+    def malloc(self, nbytes: int) -> int:
+        out = C.c_void_p()
+        self._check(self.lib.gufo_cuda_malloc(self.handle, nbytes, C.byref(out)))
+        return int(out.value)
+
+    def free(self, ptr: int) -> None:
+        self._check(self.lib.gufo_cuda_free(self.handle, C.c_void_p(ptr)))
+
+    def upload(self, dst: int, src: np.ndarray) -> None:
+        src = np.ascontiguousarray(src)
+        self._check(self.lib.gufo_cuda_upload(self.handle, C.c_void_p(dst), C.c_void_p(src.ctypes.data), src.nbytes))
+
+    def download(self, src: int, shape, dtype=np.float32) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        self._check(self.lib.gufo_cuda_download(self.handle, C.c_void_p(out.ctypes.data), C.c_void_p(src), out.nbytes))
+        return out
+
+    def memset_zero(self, ptr: int, nbytes: int) -> None:
+        self._check(self.lib.gufo_cuda_memset_zero(self.handle, C.c_void_p(ptr), nbytes))
+
+    # -- weights ------------------------------------------------------------
+    def matrix_upload(self, ggml_type: int, host_bytes: np.ndarray, rows: int, cols: int) -> int:
+        host_bytes = np.ascontiguousarray(host_bytes)
+        out = C.c_int64()
+        self._check(self.lib.gufo_cuda_matrix_upload(self.handle, ggml_type, C.c_void_p(host_bytes.ctypes.data),
+                                                     rows, cols, C.byref(out)))
+        return int(out.value)
+
+    def matrix_from_device(self, ggml_type: int, device_ptr: int, rows: int, cols: int) -> int:
+        out = C.c_int64()
+        self._check(self.lib.gufo_cuda_matrix_from_device(self.handle, ggml_type, C.c_void_p(device_ptr), rows,
+                                                          cols, C.byref(out)))
+        return int(out.value)
+
+    def matrix_free(self, matrix: int) -> None:
+        self._check(self.lib.gufo_cuda_matrix_free(self.handle, matrix))
+
+    def dequantize(self, matrix: int, first: int, rows: int, cols: int) -> np.ndarray:
+        out = np.empty((rows, cols), dtype=np.float32)
+        self._check(self.lib.gufo_cuda_dequantize(self.handle, matrix, first, rows, C.c_void_p(out.ctypes.data)))
+        return out
+
+    def dequantize_device(self, matrix: int, first: int, rows: int, dst) -> None:
+        self._check(self.lib.gufo_cuda_dequantize_device(self.handle, matrix, first, rows, C.c_void_p(_ptr(dst))))
+
+    # -- products -----------------------------------------------------------
+    @staticmethod
+    def _parts(parts: Sequence) -> "C.Array":
+        arr = (_capi.Rows * max(len(parts), 1))()
+        for i, (w, first, rows) in enumerate(parts):
+            arr[i] = _capi.Rows(w, first, rows)
+        return arr
+
+    def matmul(self, parts: Sequence, x: np.ndarray, tokens: int, out_width: int) -> np.ndarray:
+        """Host pointers: copies x up, runs, copies y down. parts: [(matrix, first, rows)]."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty((tokens, out_width), dtype=np.float32)
+        self._check(self.lib.gufo_cuda_matmul(self.handle, self._parts(parts), len(parts),
+                                              C.c_void_p(x.ctypes.data), tokens, C.c_void_p(y.ctypes.data)))
+        return y
+
+    def matmul_host(self, parts_arr, nparts: int, x_ptr: int, tokens: int, y_ptr: int) -> None:
+        """The same on caller-owned (for example pinned) host buffers, no allocation."""
+        self._check(self.lib.gufo_cuda_matmul(self.handle, parts_arr, nparts, C.c_void_p(x_ptr), tokens,
+                                              C.c_void_p(y_ptr)))
+
+    def matmul_device(self, parts_arr, nparts: int, x, tokens: int, y) -> None:
+        self._check(self.lib.gufo_cuda_matmul_device(self.handle, parts_arr, nparts, C.c_void_p(_ptr(x)), tokens,
+                                                     C.c_void_p(_ptr(y))))
+
+    # -- DeltaNet -----------------------------------------------------------
+    def delta_rule_device(self, seqs: List[dict], key_heads: int, value_heads: int, head_dim: int) -> None:
+        arr = (_capi.DeltaSeq * max(len(seqs), 1))()
+        for i, s in enumerate(seqs):
+            arr[i] = _capi.DeltaSeq(_ptr(s["state"]), _ptr(s.get("state_out")), _ptr(s["q"]), _ptr(s["k"]),
+                                    _ptr(s["v"]), _ptr(s["decay"]), _ptr(s["beta"]), _ptr(s["y"]))
+        self._check(self.lib.gufo_cuda_delta_rule_device(self.handle, arr, len(seqs), key_heads, value_heads,
+                                                         head_dim))
+
+    def deltanet_layer_create(self, key_heads: int, value_heads: int, head_dim: int, conv_kernel: int,
+                              rms_eps: float, conv, ssm_a, dt_bias, ssm_norm) -> int:
+        keep = [np.ascontiguousarray(a, dtype=np.float32) for a in (conv, ssm_a, dt_bias, ssm_norm)]
+        f32p = C.POINTER(C.c_float)
+        params = _capi.DeltaNetParams(key_heads, value_heads, head_dim, conv_kernel, rms_eps,
+                                      *(a.ctypes.data_as(f32p) for a in keep))
+        out = C.c_int64()
+        self._check(self.lib.gufo_cuda_deltanet_layer_create(self.handle, C.byref(params), C.byref(out)))
+        return int(out.value)
+
+    def deltanet_layer_free(self, layer: int) -> None:
+        self._check(self.lib.gufo_cuda_deltanet_layer_free(self.handle, layer))
+
+    def deltanet_linear_device(self, layer: int, seqs: List[dict]) -> None:
+        arr = (_capi.LinearSeq * max(len(seqs), 1))()
+        for i, s in enumerate(seqs):
+            arr[i] = _capi.LinearSeq(_ptr(s["in"]), _ptr(s["conv_in"]), _ptr(s["conv_out"]), _ptr(s["ssm"]),
+                                     _ptr(s.get("ssm_out")), _ptr(s["y"]))
+        self._check(self.lib.gufo_cuda_deltanet_linear_device(self.handle, layer, arr, len(seqs)))
+
+
+def _shape_error(name: str, shape, want) -> RuntimeError:
+    return RuntimeError(f"qwen35: tensor {name} has shape {list(shape)}, expected {list(want)}")
+
+
+class CudaProjections:
+    """The matrix products of a Qwen3.5 forward pass on the device.
+
+    Construction uploads every projection tensor once and checks its shape as
+    GgufProjections does (src/models/qwen35/gguf_projections.cpp:27-46,100-175):
+    a wrong shape raises RuntimeError. Apply / ApplyExpert take and return host
+    arrays like the reference's interface; apply_device is the same product on
+    device-resident activations.
+    """
+
+    def __init__(self, ctx: Context, cfg: ModelConfig, tensors: Dict[str, Tensor]):
+        self.ctx = ctx
+        self.config = cfg
+        self._matrices: Dict[str, int] = {}
+        self._tensors = tensors
+        c = cfg
+        lm = "token_embd.weight" if c.tied_embeddings else "output.weight"
+        self._check_shape(lm, (c.hidden, c.vocab))
+        self.lm_head = [(self._matrix(lm), 0, c.vocab)]
+        self.embed = self._matrix("token_embd.weight")
+        attn_dim = c.heads * c.head_dim
+        kv_dim = c.kv_heads * c.head_dim
+        self.layers: List[dict] = []
+        for il in range(c.layers):
+            p = f"blk.{il}."
+            layer: dict = {}
+            if c.is_moe:
+                self._check_shape(p + "ffn_gate_inp.weight", (c.hidden, c.experts))
+                self._check_shape(p + "ffn_gate_inp_shexp.weight", (c.hidden, 1))
+                layer[Stage.kRouter] = [self._all(p + "ffn_gate_inp.weight"),
+                                        self._all(p + "ffn_gate_inp_shexp.weight")]
+                for name, cols, rows in (("ffn_gate_exps.weight", c.hidden, c.expert_ffn),
+                                         ("ffn_up_exps.weight", c.hidden, c.expert_ffn),
+                                         ("ffn_down_exps.weight", c.expert_ffn, c.hidden)):
+                    self._check_shape(p + name, (cols, rows, c.experts))
+                layer["gate_exps"] = self._matrix(p + "ffn_gate_exps.weight")
+                layer["up_exps"] = self._matrix(p + "ffn_up_exps.weight")
+                layer["down_exps"] = self._matrix(p + "ffn_down_exps.weight")
+            suffix = "_shexp.weight" if c.is_moe else ".weight"
+            self._check_shape(p + "ffn_gate" + suffix, (c.hidden, c.ffn_width))
+            self._check_shape(p + "ffn_up" + suffix, (c.hidden, c.ffn_width))
+            self._check_shape(p + "ffn_down" + suffix, (c.ffn_width, c.hidden))
+            layer[Stage.kFfnIn] = [self._all(p + "ffn_gate" + suffix), self._all(p + "ffn_up" + suffix)]
+            layer[Stage.kFfnDown] = [self._all(p + "ffn_down" + suffix)]
+            if c.is_full_attention(il):
+                self._check_shape(p + "attn_q.weight", (c.hidden, 2 * attn_dim))
+                self._check_shape(p + "attn_k.weight", (c.hidden, kv_dim))
+                self._check_shape(p + "attn_v.weight", (c.hidden, kv_dim))
+                self._check_shape(p + "attn_output.weight", (attn_dim, c.hidden))
+                layer[Stage.kAttentionIn] = [self._all(p + n) for n in
+                                             ("attn_q.weight", "attn_k.weight", "attn_v.weight")]
+                layer[Stage.kMixerOut] = [self._all(p + "attn_output.weight")]
+            else:
+                self._check_shape(p + "attn_qkv.weight", (c.hidden, c.conv_channels))
+                self._check_shape(p + "attn_gate.weight", (c.hidden, c.value_dim))
+                self._check_shape(p + "ssm_alpha.weight", (c.hidden, c.linear_value_heads))
+                self._check_shape(p + "ssm_beta.weight", (c.hidden, c.linear_value_heads))
+                self._check_shape(p + "ssm_out.weight", (c.value_dim, c.hidden))
+                layer[Stage.kLinearIn] = [self._all(p + n) for n in
+                                          ("attn_qkv.weight", "attn_gate.weight", "ssm_alpha.weight",
+                                           "ssm_beta.weight")]
+                layer[Stage.kMixerOut] = [self._all(p + "ssm_out.weight")]
+            self.layers.append(layer)
+        self._tensors = None  # host bytes are not referenced after upload
+
+    # -- construction helpers ------------------------------------------------
+    def _check_shape(self, name: str, want) -> None:
+        if name not in self._tensors:
+            raise RuntimeError(f"GGUF: missing tensor {name}")
+        shape = tuple(self._tensors[name].shape)
+        want = tuple(want)
+        if len(want) == 2 and want[1] == 1 and len(shape) == 1:
+            want = want[:1]
+        if shape != want:
+            raise _shape_error(name, shape, want)
+
+    def _matrix(self, name: str) -> int:
+        if name not in self._matrices:
+            t = self._tensors[name]
+            if t.data.is_cuda:
+                # Weights generated on the device stay where they are; the tensor is kept alive here.
+                self._keep = getattr(self, "_keep", [])
+                self._keep.append(t.data)
+                handle = self.ctx.matrix_from_device(t.ggml_type, t.data.data_ptr(), t.rows, t.cols)
+            else:
+                handle = self.ctx.matrix_upload(t.ggml_type, t.data.numpy(), t.rows, t.cols)
+            self._matrices[name] = handle
+        return self._matrices[name]
+
+    def _all(self, name: str):
+        return (self._matrix(name), 0, self._tensors[name].rows)
+
+    # -- the reference's interface ---------------------------------------------
+    def parts(self, stage: Stage, layer: int):
+        if stage == Stage.kLmHead:
+            return self.lm_head
+        if layer < 0 or layer >= len(self.layers):
+            raise IndexError("qwen35: no such layer")
+        parts = self.layers[layer].get(stage)
+        if not parts:
+            raise LookupError("qwen35: no weights for this stage and layer")
+        return parts
+
+    def expert_parts(self, stage: Stage, layer: int, expert: int):
+        c = self.config
+        l = self.layers[layer]
+        if "gate_exps" not in l or expert < 0 or expert >= c.experts:
+            raise LookupError("qwen35: no such expert")
+        if stage == Stage.kExpertIn:
+            return [(l["gate_exps"], expert * c.expert_ffn, c.expert_ffn),
+                    (l["up_exps"], expert * c.expert_ffn, c.expert_ffn)]
+        if stage == Stage.kExpertDown:
+            return [(l["down_exps"], expert * c.hidden, c.hidden)]
+        raise LookupError("qwen35: ApplyExpert takes expert stages only")
+
+    def Apply(self, stage: Stage, layer: int, x: np.ndarray, tokens: int) -> np.ndarray:
+        """y[t] = W x[t]: `tokens` rows of StageInputs in, rows of StageOutputs out (host arrays)."""
+        parts = self.parts(stage, layer)
+        return self.ctx.matmul(parts, x, tokens, sum(p[2] for p in parts))
+
+    def ApplyExpert(self, stage: Stage, layer: int, expert: int, x: np.ndarray, tokens: int) -> np.ndarray:
+        parts = self.expert_parts(stage, layer, expert)
+        return self.ctx.matmul(parts, x, tokens, sum(p[2] for p in parts))
+
+    def apply_device(self, stage: Stage, layer: int, x, tokens: int, y) -> None:
+        parts = self.parts(stage, layer)
+        self.ctx.matmul_device(Context._parts(parts), len(parts), x, tokens, y)
+
+
+class CudaMixer:
+    """Gated DeltaNet decode step with the state resident on the device (Mixer::Linear)."""
+
+    def __init__(self, ctx: Context, cfg: ModelConfig, tensors: Dict[str, Tensor]):
+        self.ctx = ctx
+        self.config = cfg
+        self.layers: Dict[int, int] = {}
+        for il in range(cfg.layers):
+            if cfg.is_full_attention(il):
+                continue
+            p = f"blk.{il}."
+
+            def f32(name):
+                return tensors[p + name].data.cpu().numpy().view(np.float32)
+            self.layers[il] = ctx.deltanet_layer_create(
+                cfg.linear_key_heads, cfg.linear_value_heads, cfg.linear_head_dim, cfg.conv_kernel, cfg.rms_eps,
+                f32("ssm_conv1d.weight"), f32("ssm_a"), f32("ssm_dt.bias"), f32("ssm_norm.weight"))
+
+    def conv_values(self) -> int:
+        return (self.config.conv_kernel - 1) * self.config.conv_channels
+
+    def ssm_values(self) -> int:
+        c = self.config
+        return c.linear_value_heads * c.linear_head_dim * c.linear_head_dim
+
+    def Linear(self, layer: int, seqs: List[dict]) -> None:
+        """One step for each sequence in `seqs` (device pointers: in, conv_in, conv_out, ssm, ssm_out?, y)."""
+        if layer not in self.layers:
+            raise ValueError(f"deltanet: layer {layer} is not a DeltaNet layer")
+        self.ctx.deltanet_linear_device(self.layers[layer], seqs)

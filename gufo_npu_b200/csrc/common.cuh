@@ -1,0 +1,122 @@
+// Shared declarations of the backend's translation units: the context, status
+// helpers and the GGUF block decoders used by more than one kernel file.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+#include "gufo_cuda.h"
+
+namespace gufo {
+
+constexpr int kSuperBlock = 256;   // values per K-quant super-block
+constexpr int kQ4KBytes = 144;     // d, dmin (fp16), 12 scale bytes, 128 nibble bytes
+constexpr int kQ6KBytes = 210;     // 128 ql, 64 qh, 16 int8 scales, d (fp16)
+
+struct Matrix {
+  int type = 0;
+  const uint8_t* data = nullptr;  // device
+  int64_t rows = 0;
+  int64_t cols = 0;
+  size_t row_bytes = 0;
+  bool owned = false;
+};
+
+struct DeltaNetLayer {
+  int key_heads = 0;
+  int value_heads = 0;
+  int head_dim = 0;
+  int conv_kernel = 0;
+  float rms_eps = 0;
+  float* conv = nullptr;      // device copies
+  float* ssm_a = nullptr;
+  float* dt_bias = nullptr;
+  float* ssm_norm = nullptr;
+};
+
+void SetError(const std::string& text);
+int Fail(int status, const std::string& text);
+int CudaFail(cudaError_t e, const char* what);
+
+// Bytes of a row of `cols` values of `type`; 0 when the type is not run here or
+// cols is not a whole number of blocks.
+size_t RowBytes(int type, int64_t cols);
+
+}  // namespace gufo
+
+struct gufo_cuda_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 0;
+  std::mutex mu;
+  std::unordered_map<int64_t, gufo::Matrix> matrices;
+  std::unordered_map<int64_t, gufo::DeltaNetLayer> deltanet_layers;
+  int64_t next_id = 1;
+  // Staging for the host-pointer entry points.
+  float* stage_x = nullptr;
+  size_t stage_x_bytes = 0;
+  float* stage_y = nullptr;
+  size_t stage_y_bytes = 0;
+  std::atomic<int64_t> launches{0};
+
+  const gufo::Matrix* FindMatrix(int64_t id) const {
+    auto it = matrices.find(id);
+    return it == matrices.end() ? nullptr : &it->second;
+  }
+  int Reserve(float** buffer, size_t* have, size_t want);
+};
+
+#define GUFO_CUDA_TRY(expr)                                 \
+  do {                                                      \
+    cudaError_t gufo_e_ = (expr);                           \
+    if (gufo_e_ != cudaSuccess) {                           \
+      return gufo::CudaFail(gufo_e_, #expr);                \
+    }                                                       \
+  } while (0)
+
+namespace gufo {
+
+// ---- device helpers ------------------------------------------------------
+
+// fp16 bits to fp32, exact for every input including subnormals (the
+// conversion quant::HalfToFloat spells out, src/core/quant.cpp:129-155).
+__device__ __forceinline__ float HalfBitsToFloat(uint16_t h) {
+  float f;
+  asm("{ .reg .b16 t; mov.b16 t, %1; cvt.f32.f16 %0, t; }" : "=f"(f) : "h"(h));
+  return f;
+}
+
+// The 6-bit scale and min of sub-block j of a Q4_K block from its 12 packed
+// bytes held as three little-endian words (quant::ScaleMinK4,
+// src/core/quant.cpp:158-167).
+__device__ __forceinline__ void ScaleMinK4(int j, uint32_t s0, uint32_t s1,
+                                           uint32_t s2, int* sc, int* m) {
+  const int shift = 8 * (j & 3);
+  const uint32_t a = (s0 >> shift) & 0xFFu;  // bytes 0..3
+  const uint32_t b = (s1 >> shift) & 0xFFu;  // bytes 4..7
+  if (j < 4) {
+    *sc = a & 63;
+    *m = b & 63;
+  } else {
+    const uint32_t c = (s2 >> shift) & 0xFFu;  // bytes 8..11
+    *sc = (c & 0x0F) | ((a >> 6) << 4);
+    *m = (c >> 4) | ((b >> 6) << 4);
+  }
+}
+
+__device__ __forceinline__ float WarpSum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  }
+  return v;
+}
+
+}  // namespace gufo

@@ -1,0 +1,313 @@
+// Context, device memory and weight handles of the C ABI (include/gufo_cuda.h).
+#include "common.cuh"
+
+#include <cstring>
+#include <new>
+
+namespace gufo {
+
+namespace {
+thread_local std::string g_last_error;
+}
+
+void SetError(const std::string& text) { g_last_error = text; }
+
+int Fail(int status, const std::string& text) {
+  g_last_error = text;
+  return status;
+}
+
+int CudaFail(cudaError_t e, const char* what) {
+  g_last_error = std::string(what) + ": " + cudaGetErrorString(e);
+  return e == cudaErrorMemoryAllocation ? GUFO_CUDA_OUT_OF_MEMORY
+                                        : GUFO_CUDA_RUNTIME;
+}
+
+size_t RowBytes(int type, int64_t cols) {
+  if (cols <= 0) {
+    return 0;
+  }
+  switch (type) {
+    case GUFO_CUDA_F32:
+      return static_cast<size_t>(cols) * 4;
+    case GUFO_CUDA_Q4_K:
+      return cols % kSuperBlock ? 0 : static_cast<size_t>(cols / kSuperBlock) * kQ4KBytes;
+    case GUFO_CUDA_Q6_K:
+      return cols % kSuperBlock ? 0 : static_cast<size_t>(cols / kSuperBlock) * kQ6KBytes;
+    default:
+      return 0;
+  }
+}
+
+}  // namespace gufo
+
+int gufo_cuda_ctx::Reserve(float** buffer, size_t* have, size_t want) {
+  if (*have >= want) {
+    return GUFO_CUDA_OK;
+  }
+  if (*buffer != nullptr) {
+    GUFO_CUDA_TRY(cudaStreamSynchronize(stream));
+    GUFO_CUDA_TRY(cudaFree(*buffer));
+    *buffer = nullptr;
+    *have = 0;
+  }
+  const size_t grown = want + want / 2;
+  GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(buffer), grown));
+  *have = grown;
+  return GUFO_CUDA_OK;
+}
+
+using gufo::Fail;
+
+extern "C" {
+
+const char* gufo_cuda_last_error(const gufo_cuda_ctx*) {
+  return gufo::g_last_error.c_str();
+}
+
+int64_t gufo_cuda_launch_count(const gufo_cuda_ctx* ctx) {
+  return ctx == nullptr ? 0 : ctx->launches.load();
+}
+
+int gufo_cuda_ctx_create(int device, void* stream, gufo_cuda_ctx** out) {
+  if (out == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "ctx_create: out is null");
+  }
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0) {
+    return Fail(GUFO_CUDA_RUNTIME,
+                std::string("no CUDA device: this backend has no CPU path (") +
+                    cudaGetErrorString(e) + ")");
+  }
+  if (device < 0 || device >= count) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "ctx_create: no such device");
+  }
+  GUFO_CUDA_TRY(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  GUFO_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    return Fail(GUFO_CUDA_RUNTIME,
+                "device is not sm_100: the kernels are built for sm_100a only");
+  }
+  auto* ctx = new (std::nothrow) gufo_cuda_ctx();
+  if (ctx == nullptr) {
+    return Fail(GUFO_CUDA_OUT_OF_MEMORY, "ctx_create: host allocation failed");
+  }
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (stream != nullptr) {
+    ctx->stream = static_cast<cudaStream_t>(stream);
+  } else {
+    e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) {
+      delete ctx;
+      return gufo::CudaFail(e, "cudaStreamCreate");
+    }
+    ctx->own_stream = true;
+  }
+  *out = ctx;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx) {
+  if (ctx == nullptr) {
+    return GUFO_CUDA_OK;
+  }
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& kv : ctx->matrices) {
+    if (kv.second.owned) {
+      cudaFree(const_cast<uint8_t*>(kv.second.data));
+    }
+  }
+  for (auto& kv : ctx->deltanet_layers) {
+    cudaFree(kv.second.conv);
+    cudaFree(kv.second.ssm_a);
+    cudaFree(kv.second.dt_bias);
+    cudaFree(kv.second.ssm_norm);
+  }
+  cudaFree(ctx->stage_x);
+  cudaFree(ctx->stage_y);
+  if (ctx->own_stream) {
+    cudaStreamDestroy(ctx->stream);
+  }
+  delete ctx;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_ctx_set_stream(gufo_cuda_ctx* ctx, void* stream) {
+  if (ctx == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "set_stream: ctx is null");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (ctx->own_stream) {
+    cudaStreamSynchronize(ctx->stream);
+    cudaStreamDestroy(ctx->stream);
+    ctx->own_stream = false;
+  }
+  ctx->stream = static_cast<cudaStream_t>(stream);
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx) {
+  if (ctx == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "synchronize: ctx is null");
+  }
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_malloc(gufo_cuda_ctx* ctx, size_t bytes, void** device_ptr) {
+  if (ctx == nullptr || device_ptr == nullptr || bytes == 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "malloc: bad argument");
+  }
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(cudaMalloc(device_ptr, bytes));
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_free(gufo_cuda_ctx* ctx, void* device_ptr) {
+  if (ctx == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "free: ctx is null");
+  }
+  if (device_ptr != nullptr) {
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    GUFO_CUDA_TRY(cudaFree(device_ptr));
+  }
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_upload(gufo_cuda_ctx* ctx, void* device_dst, const void* host_src,
+                     size_t bytes) {
+  if (ctx == nullptr || device_dst == nullptr || host_src == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "upload: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaMemcpyAsync(device_dst, host_src, bytes,
+                                cudaMemcpyHostToDevice, ctx->stream));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_download(gufo_cuda_ctx* ctx, void* host_dst,
+                       const void* device_src, size_t bytes) {
+  if (ctx == nullptr || host_dst == nullptr || device_src == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "download: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaMemcpyAsync(host_dst, device_src, bytes,
+                                cudaMemcpyDeviceToHost, ctx->stream));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_memset_zero(gufo_cuda_ctx* ctx, void* device_ptr, size_t bytes) {
+  if (ctx == nullptr || device_ptr == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "memset_zero: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaMemsetAsync(device_ptr, 0, bytes, ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+static int AddMatrix(gufo_cuda_ctx* ctx, int type, const uint8_t* data,
+                     int64_t rows, int64_t cols, bool owned,
+                     gufo_cuda_matrix* out) {
+  gufo::Matrix m;
+  m.type = type;
+  m.data = data;
+  m.rows = rows;
+  m.cols = cols;
+  m.row_bytes = gufo::RowBytes(type, cols);
+  m.owned = owned;
+  const int64_t id = ctx->next_id++;
+  ctx->matrices.emplace(id, m);
+  *out = id;
+  return GUFO_CUDA_OK;
+}
+
+static int CheckMatrixArgs(const gufo_cuda_ctx* ctx, int type, const void* bytes,
+                           int64_t rows, int64_t cols,
+                           const gufo_cuda_matrix* out) {
+  if (ctx == nullptr || bytes == nullptr || out == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matrix: null pointer");
+  }
+  if (type != GUFO_CUDA_F32 && type != GUFO_CUDA_Q4_K && type != GUFO_CUDA_Q6_K) {
+    return Fail(GUFO_CUDA_UNSUPPORTED_TYPE,
+                "matrix: ggml type " + std::to_string(type) +
+                    " is not run by this backend (Q4_K, Q6_K, F32)");
+  }
+  if (rows <= 0 || cols <= 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matrix: rows and cols must be positive");
+  }
+  if (gufo::RowBytes(type, cols) == 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matrix: row is not a whole number of blocks");
+  }
+  if (type == GUFO_CUDA_F32 && cols % 4 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matrix: F32 rows must be a multiple of 4 wide");
+  }
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_matrix_upload(gufo_cuda_ctx* ctx, int ggml_type,
+                            const void* host_bytes, int64_t rows, int64_t cols,
+                            gufo_cuda_matrix* out) {
+  int rc = CheckMatrixArgs(ctx, ggml_type, host_bytes, rows, cols, out);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  const size_t bytes = gufo::RowBytes(ggml_type, cols) * static_cast<size_t>(rows);
+  // 16 spare bytes: kernels may read whole 16-byte vectors up to the end.
+  void* dev = nullptr;
+  GUFO_CUDA_TRY(cudaMalloc(&dev, bytes + 16));
+  cudaError_t e = cudaMemcpyAsync(dev, host_bytes, bytes, cudaMemcpyHostToDevice,
+                                  ctx->stream);
+  if (e == cudaSuccess) {
+    e = cudaStreamSynchronize(ctx->stream);
+  }
+  if (e != cudaSuccess) {
+    cudaFree(dev);
+    return gufo::CudaFail(e, "matrix_upload copy");
+  }
+  return AddMatrix(ctx, ggml_type, static_cast<const uint8_t*>(dev), rows, cols,
+                   true, out);
+}
+
+int gufo_cuda_matrix_from_device(gufo_cuda_ctx* ctx, int ggml_type,
+                                 const void* device_bytes, int64_t rows,
+                                 int64_t cols, gufo_cuda_matrix* out) {
+  int rc = CheckMatrixArgs(ctx, ggml_type, device_bytes, rows, cols, out);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (reinterpret_cast<uintptr_t>(device_bytes) % 16 != 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                "matrix_from_device: bytes must be 16-byte aligned");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return AddMatrix(ctx, ggml_type, static_cast<const uint8_t*>(device_bytes), rows,
+                   cols, false, out);
+}
+
+int gufo_cuda_matrix_free(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix) {
+  if (ctx == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matrix_free: ctx is null");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->matrices.find(matrix);
+  if (it == ctx->matrices.end()) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matrix_free: unknown handle");
+  }
+  if (it->second.owned) {
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    GUFO_CUDA_TRY(cudaFree(const_cast<uint8_t*>(it->second.data)));
+  }
+  ctx->matrices.erase(it);
+  return GUFO_CUDA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,219 @@
+/* gufo_cuda.h - C ABI of the B200 (sm_100a) backend for gufo-npu's decode hot
+ * path: GGUF Q4_K / Q6_K dequant-fused GEMV and small-M GEMM behind every
+ * projection, bit-exact dequantization, the Gated DeltaNet decode step and the
+ * routed-expert FFN of the MoE models.
+ *
+ * This is the boundary a `src/cuda` backend binds beside the reference's
+ * `src/npu`: plain pointers and sizes, no C++ types, no exceptions. Each entry
+ * point names the reference interface it stands behind (paths are relative to
+ * the reference project's root).
+ *
+ * Conventions
+ *  - Every function returns a gufo_cuda_status (0 = ok) and never throws or
+ *    aborts; gufo_cuda_last_error() gives the text of the calling thread's last
+ *    failure on that context.
+ *  - A context belongs to one CUDA device and one stream. Calls on one context
+ *    are serialised by an internal mutex, as the reference serialises products
+ *    on its shared pool (src/models/qwen35/gguf_projections.cpp:253).
+ *  - `_device` variants take device pointers and only enqueue work on the
+ *    context's stream; the plain variants take host pointers, copy inputs up and
+ *    results down, and return after the stream has drained.
+ *  - All activations and outputs are fp32. Matrices are row-major GGUF blocks:
+ *    `rows` rows of `cols` values, cols contiguous (ggml shape [cols, rows]).
+ *  - There is no CPU fallback: without a usable device, context creation fails.
+ */
+#ifndef GUFO_CUDA_H_
+#define GUFO_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum gufo_cuda_status {
+  GUFO_CUDA_OK = 0,
+  GUFO_CUDA_BAD_ARGUMENT = 1,     /* null pointer, bad count, unknown handle   */
+  GUFO_CUDA_SHAPE = 2,            /* widths or row ranges that do not fit      */
+  GUFO_CUDA_UNSUPPORTED_TYPE = 3, /* a ggml type this backend does not run     */
+  GUFO_CUDA_RUNTIME = 4,          /* a CUDA call failed; see last_error        */
+  GUFO_CUDA_OUT_OF_MEMORY = 5,
+  GUFO_CUDA_TIMEOUT = 6,          /* a bounded device-side wait ran out        */
+  GUFO_CUDA_TOO_LARGE = 7         /* beyond a fixed capacity of the entry point */
+} gufo_cuda_status;
+
+/* ggml tensor type ids, as in the reference's gguf::GgmlType
+ * (src/core/gguf.hpp:16-24). */
+enum {
+  GUFO_CUDA_F32 = 0,
+  GUFO_CUDA_Q4_K = 12,
+  GUFO_CUDA_Q6_K = 14
+};
+
+typedef struct gufo_cuda_ctx gufo_cuda_ctx;
+/* Opaque matrix handle (> 0). */
+typedef int64_t gufo_cuda_matrix;
+/* Opaque handle of one DeltaNet layer's small weights (> 0). */
+typedef int64_t gufo_cuda_deltanet_layer;
+
+/* ---- context ---------------------------------------------------------- */
+
+/* Creates a context on CUDA device `device`. `stream` is a cudaStream_t to
+ * enqueue on, or NULL for a stream the context creates and owns. Stands where
+ * the reference opens its accelerator (npu::GemvRuntime, src/npu/gemv.hpp:82-
+ * 100); fails with GUFO_CUDA_RUNTIME when no sm_100 device is usable, as the
+ * reference's stub runtime throws (src/npu/gemv_stub.cpp:8-10). */
+int gufo_cuda_ctx_create(int device, void* stream, gufo_cuda_ctx** out);
+int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx);
+/* Replaces the stream later work is enqueued on (not owned). */
+int gufo_cuda_ctx_set_stream(gufo_cuda_ctx* ctx, void* stream);
+int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx);
+/* Text of the last failure of a call on `ctx` (or of ctx_create when ctx is
+ * NULL) made by this thread; valid until that thread's next failing call. */
+const char* gufo_cuda_last_error(const gufo_cuda_ctx* ctx);
+/* Number of kernels this context has launched so far. */
+int64_t gufo_cuda_launch_count(const gufo_cuda_ctx* ctx);
+
+/* ---- device memory (decode state lives on the device between steps) ---- */
+
+/* Plain device buffers for activations, DeltaNet states and conv windows.
+ * States are raw fp32 in the reference's layout (DecodeState::Layer,
+ * src/models/qwen35/decoder.hpp:26-37), so upload/download are the checkpoint
+ * and rollback primitives (src/models/qwen35/state_capture.hpp:8-14). */
+int gufo_cuda_malloc(gufo_cuda_ctx* ctx, size_t bytes, void** device_ptr);
+int gufo_cuda_free(gufo_cuda_ctx* ctx, void* device_ptr);
+int gufo_cuda_upload(gufo_cuda_ctx* ctx, void* device_dst, const void* host_src,
+                     size_t bytes);
+int gufo_cuda_download(gufo_cuda_ctx* ctx, void* host_dst,
+                       const void* device_src, size_t bytes);
+int gufo_cuda_memset_zero(gufo_cuda_ctx* ctx, void* device_ptr, size_t bytes);
+
+/* ---- weights ---------------------------------------------------------- */
+
+/* Copies a GGUF tensor's rows to the device once, as the reference's NPU
+ * GEMV uploads at construction (npu::Q4nxGemv, src/npu/gemv.hpp:136-144). The
+ * host bytes are not referenced after the call. `cols` must be a whole number
+ * of blocks of `ggml_type` (quant::RowBytes, src/core/quant.cpp:221-227).
+ * Types: Q4_K, Q6_K and F32 (the alpha/beta and router rows,
+ * src/models/qwen35/gguf_projections.cpp:126-131,162-170). */
+int gufo_cuda_matrix_upload(gufo_cuda_ctx* ctx, int ggml_type,
+                            const void* host_bytes, int64_t rows, int64_t cols,
+                            gufo_cuda_matrix* out);
+/* The same over bytes already on the device; they are borrowed, not copied,
+ * and must outlive the handle (GgufProjections keeps pointers into the mapped
+ * file the same way, src/models/qwen35/gguf_projections.hpp:28). */
+int gufo_cuda_matrix_from_device(gufo_cuda_ctx* ctx, int ggml_type,
+                                 const void* device_bytes, int64_t rows,
+                                 int64_t cols, gufo_cuda_matrix* out);
+int gufo_cuda_matrix_free(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix);
+
+/* ---- dequantization ---------------------------------------------------- */
+
+/* quant::Dequantize (src/core/quant.cpp:33-59 Q4_K, 98-125 Q6_K, 221-260):
+ * rows [first, first + rows) of `matrix` to fp32, bit for bit the reference's
+ * values. Used for embedding rows (src/models/qwen35/decoder.cpp:486-489). */
+int gufo_cuda_dequantize(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix,
+                         int64_t first, int64_t rows, float* host_dst);
+int gufo_cuda_dequantize_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix,
+                                int64_t first, int64_t rows, float* device_dst);
+
+/* ---- projections ------------------------------------------------------- */
+
+/* Rows [first, first + rows) of a matrix: GgufProjections::Rows
+ * (src/models/qwen35/gguf_projections.hpp:40-44). */
+typedef struct gufo_cuda_rows {
+  gufo_cuda_matrix w;
+  int64_t first;
+  int64_t rows;
+} gufo_cuda_rows;
+
+/* GgufProjections::MatMul (src/models/qwen35/gguf_projections.cpp:239-286),
+ * the product behind Projections::Apply and ApplyExpert
+ * (src/models/qwen35/projections.hpp:45-59):
+ *   y[t] = [W_0 x[t] | W_1 x[t] | ...]  for t in [0, tokens)
+ * x is `tokens` rows of `cols` fp32 (all parts share cols), y is `tokens` rows
+ * of sum(parts[p].rows) fp32. Each output is one row dot, so results do not
+ * depend on how rows are stacked or how many tokens come together. */
+int gufo_cuda_matmul(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
+                     int nparts, const float* host_x, int tokens, float* host_y);
+int gufo_cuda_matmul_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
+                            int nparts, const float* device_x, int tokens,
+                            float* device_y);
+
+/* ---- Gated DeltaNet decode step ---------------------------------------- */
+
+/* One sequence's inputs to the delta rule with the gates already evaluated
+ * (the arithmetic of src/models/qwen35/decoder.cpp:234-257 per value head):
+ *   u = (decay S)^T k; delta = beta (v - u); S' = decay S + k delta^T; y = S'^T q
+ * `state` is [value_heads][head_dim (key i)][head_dim (value j)] fp32 on the
+ * device. With `state_out` the new state goes there and `state` is left
+ * unchanged (a draft token that may be rolled back: the ssm_out argument of
+ * Mixer::Linear, src/models/qwen35/decoder.hpp:78-84); NULL updates in place.
+ * q, k: [key_heads][head_dim], already normalised; v, y: [value_heads]
+ * [head_dim]; decay, beta: [value_heads]. Value head h reads key head
+ * h % key_heads (src/models/qwen35/decoder.cpp:221). All device pointers. */
+typedef struct gufo_cuda_delta_seq {
+  float* state;
+  float* state_out;
+  const float* q;
+  const float* k;
+  const float* v;
+  const float* decay;
+  const float* beta;
+  float* y;
+} gufo_cuda_delta_seq;
+
+/* Applies the delta rule to `nseq` independent sequences in one launch.
+ * `seqs` is a host array of `nseq` descriptors (device pointers inside). */
+int gufo_cuda_delta_rule_device(gufo_cuda_ctx* ctx,
+                                const gufo_cuda_delta_seq* seqs, int nseq,
+                                int key_heads, int value_heads, int head_dim);
+
+/* The small weights Mixer loads per DeltaNet layer
+ * (src/models/qwen35/decoder.cpp:40-47,76-80): host pointers, copied. */
+typedef struct gufo_cuda_deltanet_params {
+  int key_heads;
+  int value_heads;
+  int head_dim;
+  int conv_kernel;
+  float rms_eps;
+  const float* conv;     /* [2 key_dim + value_dim][conv_kernel] */
+  const float* ssm_a;    /* [value_heads] */
+  const float* dt_bias;  /* [value_heads] */
+  const float* ssm_norm; /* [head_dim] */
+} gufo_cuda_deltanet_params;
+
+int gufo_cuda_deltanet_layer_create(gufo_cuda_ctx* ctx,
+                                    const gufo_cuda_deltanet_params* params,
+                                    gufo_cuda_deltanet_layer* out);
+int gufo_cuda_deltanet_layer_free(gufo_cuda_ctx* ctx,
+                                  gufo_cuda_deltanet_layer layer);
+
+/* One sequence's step through Mixer::Linear
+ * (src/models/qwen35/decoder.cpp:161-265): causal conv + SiLU, q/k L2 norm,
+ * gates, delta rule, gated RMSNorm. `in` is the kLinearIn row
+ * [qkv | z | alpha | beta]; y gets value_dim values. The conv window is read
+ * from conv_in and the advanced window written to conv_out, two distinct
+ * [conv_kernel - 1][channels] buffers (the reference's fused step also writes
+ * a second window and swaps, src/models/qwen35_2b/deltanet.cpp:236-247,355);
+ * keeping conv_in is the rollback of a draft token. ssm / ssm_out as `state` /
+ * `state_out` above. All device pointers. */
+typedef struct gufo_cuda_linear_seq {
+  const float* in;
+  const float* conv_in;
+  float* conv_out;
+  float* ssm;
+  float* ssm_out;
+  float* y;
+} gufo_cuda_linear_seq;
+
+int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
+                                     gufo_cuda_deltanet_layer layer,
+                                     const gufo_cuda_linear_seq* seqs,
+                                     int nseq);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GUFO_CUDA_H_ */

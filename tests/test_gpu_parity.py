@@ -1,0 +1,362 @@
+"""GPU parity: the CUDA path through the C ABI against the CPU oracle and the committed
+reference outputs. Tolerances: dequantization bit-exact; GEMV / GEMM outputs <= 1e-3
+relative L2 (fp32); DeltaNet state and output <= 1e-4 relative L2."""
+import numpy as np
+import pytest
+import torch
+
+from gufo_npu_b200 import quantize as Q
+from gufo_npu_b200 import synth
+from gufo_npu_b200.backend import Context, CudaMixer, CudaProjections, Stage, stage_inputs
+from tests.golden import make_golden as G
+
+pytestmark = pytest.mark.gpu
+
+GEMV_TOL = 1e-3      # relative L2, fp32 outputs
+DELTA_TOL = 1e-4     # relative L2, DeltaNet state and output
+TYPES = {"q4k": Q.GGML_Q4_K, "q6k": Q.GGML_Q6_K}
+
+
+def rel_l2(got, want):
+    got = np.asarray(got, dtype=np.float64).ravel()
+    want = np.asarray(want, dtype=np.float64).ravel()
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = Context(0)
+    yield c
+    c.close()
+
+
+# ---- dequantization -------------------------------------------------------
+
+@pytest.mark.parametrize("name,ggml_type", [("Q4_K", Q.GGML_Q4_K), ("Q6_K", Q.GGML_Q6_K)])
+def test_dequantize_reference_fixtures_bit_exact(ctx, golden, name, ggml_type):
+    raw = np.fromfile(golden.path("quant", name + ".bin"), dtype=np.uint8)
+    want = np.fromfile(golden.path("quant", name + ".f32"), dtype=np.float32)
+    m = ctx.matrix_upload(ggml_type, raw, 1, want.size)
+    got = ctx.dequantize(m, 0, 1, want.size)
+    assert np.array_equal(bits(got.ravel()), bits(want))
+    ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("name", ["q4k", "q6k"])
+def test_dequantize_matches_oracle_bit_exact(ctx, oracle, name):
+    t = TYPES[name]
+    rows, cols = 37, 1024
+    for raw in (Q.random_blocks(t, rows, cols, seed=21).numpy(),
+                Q.quantize(t, torch.from_numpy(G.normal(22, rows, cols) * 0.02)).numpy()):
+        m = ctx.matrix_upload(t, raw, rows, cols)
+        got = ctx.dequantize(m, 0, rows, cols)
+        want = oracle.dequantize(t, raw, rows * cols).reshape(rows, cols)
+        assert np.array_equal(bits(got), bits(want))
+        # A row range, as the embedding lookup reads one row.
+        got = ctx.dequantize(m, 5, 2, cols)
+        assert np.array_equal(bits(got), bits(want[5:7]))
+        ctx.matrix_free(m)
+
+
+def test_dequantize_subnormal_and_extreme_scales(ctx, oracle):
+    """fp16 d / dmin that are subnormal, zero or the largest finite half."""
+    for t, offs in ((Q.GGML_Q4_K, (0, 2)), (Q.GGML_Q6_K, (208,))):
+        raw = Q.random_blocks(t, 1, 256 * 6, seed=31).numpy().reshape(6, -1)
+        for b, half in enumerate((0x0001, 0x03FF, 0x0000, 0x7BFF, 0x8001, 0xFBFF)):
+            for at in offs:
+                raw[b, at] = half & 0xFF
+                raw[b, at + 1] = half >> 8
+        m = ctx.matrix_upload(t, raw.reshape(-1), 1, 256 * 6)
+        got = ctx.dequantize(m, 0, 1, 256 * 6)
+        want = oracle.dequantize(t, raw.reshape(-1), 256 * 6)
+        assert np.array_equal(bits(got.ravel()), bits(want))
+        ctx.matrix_free(m)
+
+
+def test_dequantize_full_size_bit_exact(ctx, oracle):
+    """The 6144 x 2048 Q4_K matrix of the headline GEMV: every value, bit for bit."""
+    gen = torch.Generator().manual_seed(1)
+    w = torch.randn(6144, 2048, generator=gen) * 0.02
+    raw = Q.quantize_q4_k(w).numpy()
+    m = ctx.matrix_upload(Q.GGML_Q4_K, raw, 6144, 2048)
+    got = ctx.dequantize(m, 0, 6144, 2048)
+    want = oracle.dequantize(Q.GGML_Q4_K, raw, 6144 * 2048).reshape(6144, 2048)
+    assert np.array_equal(bits(got), bits(want))
+    # The packer's codes reproduce the weights to within one quantization step.
+    assert rel_l2(got, w.numpy()) < 0.1
+    ctx.matrix_free(m)
+
+
+# ---- GEMV / small-M GEMM ----------------------------------------------------
+
+def test_headline_gemv_q4k_6144x2048(ctx, oracle):
+    """W 6144 x 2048 from N(0, 0.02) seed 1, x N(0, 1) seed 2, batch 1."""
+    w = torch.randn(6144, 2048, generator=torch.Generator().manual_seed(1)) * 0.02
+    raw = Q.quantize_q4_k(w).numpy()
+    x = torch.randn(2048, generator=torch.Generator().manual_seed(2)).numpy()
+    m = ctx.matrix_upload(Q.GGML_Q4_K, raw, 6144, 2048)
+    got = ctx.matmul([(m, 0, 6144)], x, 1, 6144)
+    want = oracle.matmul([(raw, Q.GGML_Q4_K, 0, 6144)], 2048, x)
+    exact = oracle.matmul([(raw, Q.GGML_Q4_K, 0, 6144)], 2048, x, exact=True)
+    assert rel_l2(got, want) <= GEMV_TOL
+    assert rel_l2(got, exact) < 1e-5          # fp32 accumulation sits far inside the tolerance
+    ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("name", ["q4k", "q6k"])
+@pytest.mark.parametrize("rows,cols", [(1, 256), (16, 256), (1000, 512), (2048, 6144), (257, 2560)])
+def test_gemv_shapes_random_blocks(ctx, oracle, name, rows, cols):
+    """Ragged row counts and every block pattern; error bound of the reference's fused-dot
+    test (2e-5 of sum |w x|, tests/models/qwen35/gguf_dot_test.cpp:114-116)."""
+    t = TYPES[name]
+    raw = Q.random_blocks(t, rows, cols, seed=rows + cols).numpy()
+    x = G.normal(rows * 3 + cols, cols)
+    m = ctx.matrix_upload(t, raw, rows, cols)
+    got = ctx.matmul([(m, 0, rows)], x, 1, rows)[0]
+    want = oracle.matmul([(raw, t, 0, rows)], cols, x)[0]
+    assert rel_l2(got, want) <= GEMV_TOL
+    wabs = np.abs(oracle.dequantize(t, raw[:64], min(rows, 64) * cols).reshape(-1, cols))
+    magnitude = wabs @ np.abs(x)
+    n = magnitude.size
+    exact = oracle.matmul([(raw, t, 0, n)], cols, x, exact=True)[0]
+    assert np.all(np.abs(got[:n] - exact) < 2e-5 * magnitude)
+    ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8, 9, 19])
+def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
+    """Results do not depend on how many tokens come together
+    (src/models/qwen35/gguf_projections.cpp:241-243)."""
+    rows, cols = 96, 768
+    x = G.normal(50 + tokens, tokens, cols)
+    for name, t in TYPES.items():
+        raw = Q.quantize(t, torch.from_numpy(G.normal(60, rows, cols) * 0.02)).numpy()
+        m = ctx.matrix_upload(t, raw, rows, cols)
+        got = ctx.matmul([(m, 0, rows)], x, tokens, rows)
+        want = oracle.matmul([(raw, t, 0, rows)], cols, x)
+        assert rel_l2(got, want) <= 1e-5
+        single = np.stack([ctx.matmul([(m, 0, rows)], x[i], 1, rows)[0] for i in range(tokens)])
+        assert rel_l2(got, single) <= 1e-6
+        ctx.matrix_free(m)
+
+
+def test_empty_and_bad_products(ctx):
+    from gufo_npu_b200._capi import GufoCudaError
+    raw = Q.random_blocks(Q.GGML_Q4_K, 8, 256, seed=1).numpy()
+    m = ctx.matrix_upload(Q.GGML_Q4_K, raw, 8, 256)
+    other = ctx.matrix_upload(Q.GGML_Q4_K, Q.random_blocks(Q.GGML_Q4_K, 8, 512, seed=1).numpy(), 8, 512)
+    x = np.zeros(256, dtype=np.float32)
+    assert ctx.matmul([(m, 0, 8)], np.zeros((0, 256), dtype=np.float32), 0, 8).shape == (0, 8)
+    for bad, status in (([(m, 4, 8)], 2), ([(m, -1, 2)], 2), ([(m, 0, 0)], 2), ([(999, 0, 1)], 1),
+                        ([(m, 0, 8), (other, 0, 8)], 2), ([], 1)):
+        with pytest.raises(GufoCudaError) as e:
+            ctx.matmul(bad, x, 1, 8)
+        assert e.value.status == status
+    with pytest.raises(GufoCudaError) as e:
+        ctx.matrix_upload(13, raw, 8, 256)          # Q5_K: not run by this backend
+    assert e.value.status == 3
+    with pytest.raises(GufoCudaError) as e:
+        ctx.matrix_upload(Q.GGML_Q4_K, raw, 8, 250)
+    assert e.value.status == 2
+    ctx.matrix_free(m)
+    ctx.matrix_free(other)
+    with pytest.raises(GufoCudaError):
+        ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("tag,kwargs,seed", [("dense", G.DENSE, G.DENSE_SEED), ("moe", G.MOE, G.MOE_SEED)])
+def test_projections_match_reference_outputs(ctx, golden, tag, kwargs, seed):
+    """CudaProjections.Apply / ApplyExpert against the committed outputs of the reference's
+    GgufProjections (fp32 and double) on the same synthetic models: every stage, 1 and 3 tokens."""
+    cfg = synth.ModelConfig(**kwargs)
+    tensors = synth.build_model(cfg, seed)
+    proj = CudaProjections(ctx, cfg, tensors)
+    g = golden("projections")
+    worst = 0.0
+    for il in range(cfg.layers):
+        stages = [Stage.kMixerOut, Stage.kFfnIn, Stage.kFfnDown,
+                  Stage.kAttentionIn if cfg.is_full_attention(il) else Stage.kLinearIn]
+        if cfg.is_moe:
+            stages.append(Stage.kRouter)
+        names = {Stage.kMixerOut: "mixer_out", Stage.kFfnIn: "ffn_in", Stage.kFfnDown: "ffn_down",
+                 Stage.kAttentionIn: "attention_in", Stage.kLinearIn: "linear_in", Stage.kRouter: "router"}
+        for stage in stages:
+            for tokens in (1, 3):
+                x = G.normal(1000 + 10 * il + tokens, tokens, stage_inputs(cfg, stage, il))
+                got = proj.Apply(stage, il, x, tokens)
+                for prec in ("f32", "f64"):
+                    err = rel_l2(got, g[f"{tag}_{prec}_{names[stage]}_{il}_{tokens}"])
+                    worst = max(worst, err)
+                    assert err <= GEMV_TOL, (stage, il, tokens, prec, err)
+        if cfg.is_moe:
+            for expert in (0, 5, cfg.experts - 1):
+                for stage, name in ((Stage.kExpertIn, "expert_in"), (Stage.kExpertDown, "expert_down")):
+                    x = G.normal(2000 + expert, 2, stage_inputs(cfg, stage, il))
+                    got = proj.ApplyExpert(stage, il, expert, x, 2)
+                    assert rel_l2(got, g[f"{tag}_f32_{name}_{il}_e{expert}"]) <= GEMV_TOL
+    got = proj.Apply(Stage.kLmHead, -1, G.normal(3000, 2, cfg.hidden), 2)
+    assert rel_l2(got, g[f"{tag}_f32_lm_head"]) <= GEMV_TOL
+    assert worst < 1e-5
+    with pytest.raises(LookupError):
+        proj.Apply(Stage.kExpertIn, 0, np.zeros(cfg.hidden, dtype=np.float32), 1)
+    if not cfg.is_moe:
+        with pytest.raises(LookupError):
+            proj.ApplyExpert(Stage.kExpertIn, 0, 0, np.zeros(cfg.hidden, dtype=np.float32), 1)
+
+
+def test_projection_shape_check_at_construction(ctx):
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    bad = dict(tensors)
+    t = bad["blk.0.ffn_down.weight"]
+    bad["blk.0.ffn_down.weight"] = synth.Tensor((t.shape[1], t.shape[0]), t.ggml_type, t.data)
+    with pytest.raises(RuntimeError, match="has shape"):
+        CudaProjections(ctx, cfg, bad)
+
+
+# ---- Gated DeltaNet -----------------------------------------------------------
+
+def _delta_inputs(seed, hk, hv, dk):
+    rng = np.random.default_rng(seed)
+    q = rng.standard_normal((hk, dk)).astype(np.float32)
+    k = rng.standard_normal((hk, dk)).astype(np.float32)
+    q /= np.linalg.norm(q, axis=1, keepdims=True)
+    k /= np.linalg.norm(k, axis=1, keepdims=True)
+    v = rng.standard_normal((hv, dk)).astype(np.float32)
+    beta = (1.0 / (1.0 + np.exp(-rng.standard_normal(hv)))).astype(np.float32)
+    g = rng.standard_normal(hv)
+    decay = np.exp(-np.log1p(np.exp(g))).astype(np.float32)
+    return q, k, v, decay, beta
+
+
+@pytest.mark.parametrize("hk,hv,dk", [(16, 16, 128), (2, 4, 128), (1, 2, 64), (2, 2, 32)])
+def test_delta_rule_matches_oracle_over_steps(ctx, oracle, hk, hv, dk):
+    """8 sequences of ragged context lengths: each state is advanced by its own number of
+    steps; state and output are checked after step 1, mid-way and after the last step."""
+    dev = torch.device("cuda:0")
+    nseq = 8
+    lengths = np.random.default_rng(7).integers(1, 25, size=nseq)
+    states = torch.zeros(nseq, hv, dk, dk, device=dev)
+    ref_states = np.zeros((nseq, hv, dk, dk), dtype=np.float32)
+    checked = 0
+    for step in range(int(lengths.max())):
+        live = [s for s in range(nseq) if step < lengths[s]]
+        bufs, seqs = [], []
+        for s in live:
+            q, k, v, decay, beta = _delta_inputs(1000 * s + step, hk, hv, dk)
+            d = {n: torch.from_numpy(a).to(dev) for n, a in
+                 (("q", q), ("k", k), ("v", v), ("decay", decay), ("beta", beta))}
+            d["y"] = torch.empty(hv, dk, device=dev)
+            d["state"] = states[s]
+            bufs.append((s, d, (q, k, v, decay, beta)))
+            seqs.append(d)
+        torch.cuda.synchronize()
+        ctx.delta_rule_device(seqs, hk, hv, dk)
+        ctx.synchronize()
+        for s, d, (q, k, v, decay, beta) in bufs:
+            want_y = np.empty((hv, dk), dtype=np.float32)
+            for h in range(hv):
+                ref_states[s, h], want_y[h] = oracle.delta_rule(ref_states[s, h], k[h % hk], q[h % hk], v[h],
+                                                                float(decay[h]), float(beta[h]))
+            if step in (0, lengths[s] // 2, lengths[s] - 1):
+                assert rel_l2(d["y"].cpu().numpy(), want_y) <= DELTA_TOL
+                assert rel_l2(states[s].cpu().numpy(), ref_states[s]) <= DELTA_TOL
+                checked += 1
+    assert checked >= nseq
+
+
+def test_delta_rule_alternate_output_leaves_state(ctx, oracle):
+    dev = torch.device("cuda:0")
+    hk = hv = 4
+    dk = 128
+    state = torch.randn(hv, dk, dk, device=dev, generator=torch.Generator(device=dev).manual_seed(3))
+    before = state.clone()
+    out = torch.zeros_like(state)
+    q, k, v, decay, beta = _delta_inputs(5, hk, hv, dk)
+    d = {n: torch.from_numpy(a).to(dev) for n, a in (("q", q), ("k", k), ("v", v), ("decay", decay), ("beta", beta))}
+    d.update(state=state, state_out=out, y=torch.empty(hv, dk, device=dev))
+    torch.cuda.synchronize()
+    ctx.delta_rule_device([d], hk, hv, dk)
+    ctx.synchronize()
+    assert torch.equal(state, before)
+    for h in range(hv):
+        want, want_y = oracle.delta_rule(before[h].cpu().numpy(), k[h], q[h], v[h], float(decay[h]), float(beta[h]))
+        assert rel_l2(out[h].cpu().numpy(), want) <= DELTA_TOL
+        assert rel_l2(d["y"][h].cpu().numpy(), want_y) <= DELTA_TOL
+
+
+def test_deltanet_linear_matches_reference_outputs(ctx, golden):
+    """Mixer::Linear over 12 steps with speculative states kept or dropped, against the
+    committed outputs of the reference (tests/golden/deltanet.npz)."""
+    dev = torch.device("cuda:0")
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    mixer = CudaMixer(ctx, cfg, tensors)
+    g = golden("deltanet")
+    width = cfg.conv_channels + cfg.value_dim + 2 * cfg.linear_value_heads
+    conv = [torch.zeros(mixer.conv_values(), device=dev), torch.zeros(mixer.conv_values(), device=dev)]
+    ssm = torch.zeros(mixer.ssm_values(), device=dev)
+    spec = torch.zeros_like(ssm)
+    y = torch.empty(cfg.value_dim, device=dev)
+    cur = 0
+    for step in range(12):
+        x_in = torch.from_numpy(G.normal(4000 + step, width)).to(dev)
+        speculative = step % 4 == 3
+        torch.cuda.synchronize()
+        mixer.Linear(0, [{"in": x_in, "conv_in": conv[cur], "conv_out": conv[1 - cur], "ssm": ssm,
+                          "ssm_out": spec if speculative else None, "y": y}])
+        ctx.synchronize()
+        cur = 1 - cur
+        assert rel_l2(y.cpu().numpy(), g["linear_y"][step]) <= DELTA_TOL, step
+        if speculative:
+            assert rel_l2(spec.cpu().numpy()[::G.SAMPLE], g[f"linear_spec_{step}"]) <= DELTA_TOL
+            if step % 8 == 3:
+                ssm.copy_(spec)
+    assert np.array_equal(bits(conv[cur].cpu().numpy()), bits(g["linear_conv"]))   # copies of inputs: exact
+    assert rel_l2(ssm.cpu().numpy(), g["linear_ssm"]) <= DELTA_TOL
+
+
+def test_deltanet_linear_batched_sequences(ctx, oracle):
+    """Several sequences in one launch equal the same sequences one by one."""
+    dev = torch.device("cuda:0")
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    mixer = CudaMixer(ctx, cfg, tensors)
+    width = cfg.conv_channels + cfg.value_dim + 2 * cfg.linear_value_heads
+    nseq = 19                                    # more than one launch's worth of descriptors
+    gen = torch.Generator(device=dev).manual_seed(9)
+    x_in = torch.randn(nseq, width, device=dev, generator=gen)
+    conv_in = torch.randn(nseq, mixer.conv_values(), device=dev, generator=gen)
+    ssm0 = torch.randn(nseq, mixer.ssm_values(), device=dev, generator=gen) * 0.1
+
+    def run(batched):
+        conv_out = torch.zeros_like(conv_in)
+        ssm = ssm0.clone()
+        y = torch.zeros(nseq, cfg.value_dim, device=dev)
+        seqs = [{"in": x_in[s], "conv_in": conv_in[s], "conv_out": conv_out[s], "ssm": ssm[s], "y": y[s]}
+                for s in range(nseq)]
+        torch.cuda.synchronize()
+        if batched:
+            mixer.Linear(0, seqs)
+        else:
+            for s in seqs:
+                mixer.Linear(0, [s])
+        ctx.synchronize()
+        return conv_out, ssm, y
+    a, b = run(True), run(False)
+    for got, want in zip(a, b):
+        assert torch.equal(got, want)
+    # And against the oracle for one of them.
+    from tests.test_oracle import _deltanet_cfg, _deltanet_weights
+    s = 7
+    conv = conv_in[s].cpu().numpy().copy()
+    ssm = ssm0[s].cpu().numpy().copy()
+    want_y, _ = oracle.deltanet_linear(_deltanet_cfg(cfg), _deltanet_weights(cfg, tensors, 0),
+                                       x_in[s].cpu().numpy(), conv, ssm)
+    assert rel_l2(a[2][s].cpu().numpy(), want_y) <= DELTA_TOL
+    assert rel_l2(a[1][s].cpu().numpy(), ssm) <= DELTA_TOL
+    assert np.array_equal(bits(a[0][s].cpu().numpy()), bits(conv))
