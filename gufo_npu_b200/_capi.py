@@ -51,6 +51,7 @@ SIGNATURES = {
     "gufo_cuda_ctx_destroy": (C.c_int, [C.c_void_p]),
     "gufo_cuda_ctx_set_stream": (C.c_int, [C.c_void_p, C.c_void_p]),
     "gufo_cuda_ctx_synchronize": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_ctx_set_option": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
     "gufo_cuda_last_error": (C.c_char_p, [C.c_void_p]),
     "gufo_cuda_launch_count": (C.c_int64, [C.c_void_p]),
     "gufo_cuda_malloc": (C.c_int, [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]),

@@ -104,6 +104,9 @@ class Context:
     def set_stream(self, stream: int) -> None:
         self._check(self.lib.gufo_cuda_ctx_set_stream(self.handle, C.c_void_p(stream)))
 
+    def set_option(self, name: str, value: int) -> None:
+        self._check(self.lib.gufo_cuda_ctx_set_option(self.handle, name.encode(), value))
+
     def synchronize(self) -> None:
         self._check(self.lib.gufo_cuda_ctx_synchronize(self.handle))
 

@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <unordered_map>
 
 #include "gufo_cuda.h"
@@ -44,10 +45,31 @@ void SetError(const std::string& text);
 int Fail(int status, const std::string& text);
 int CudaFail(cudaError_t e, const char* what);
 
+// One part of a product on a tensor-core GEMV kernel.
+struct FastGemvArgs {
+  const uint8_t* w;      // first row
+  int rows;
+  int cols;
+  int row_bytes;
+  const uint8_t* image;  // staged activations (mma_common.cuh)
+  float* y;              // [tokens][y_stride]
+  int y_stride;
+  int y_offset;          // column of y where this part starts
+  int tokens;
+};
+
 // Bytes of a row of `cols` values of `type`; 0 when the type is not run here or
 // cols is not a whole number of blocks.
 size_t RowBytes(int type, int64_t cols);
 
+}  // namespace gufo
+
+struct gufo_cuda_ctx;
+namespace gufo {
+// Enqueues one Q4_K part on the int8 tensor-core kernel against a staged image.
+int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
+// Whether the image of `tokens` rows of `cols` values fits in shared memory.
+bool Q4KFastFits(int cols, int tokens);
 }  // namespace gufo
 
 struct gufo_cuda_ctx {
@@ -64,7 +86,16 @@ struct gufo_cuda_ctx {
   size_t stage_x_bytes = 0;
   float* stage_y = nullptr;
   size_t stage_y_bytes = 0;
+  // Fixed-point image of the activations of the product in flight.
+  uint8_t* image = nullptr;
+  size_t image_bytes = 0;
   std::atomic<int64_t> launches{0};
+  // Test hook: route every product through the general kernel.
+  bool force_general = false;
+  // Timing hook: skip the staging kernel and multiply against the image of the
+  // previous product (wrong results unless x is unchanged).
+  bool reuse_image = false;
+  int gemv_variant = 0;
 
   const gufo::Matrix* FindMatrix(int64_t id) const {
     auto it = matrices.find(id);
@@ -83,7 +114,48 @@ struct gufo_cuda_ctx {
 
 namespace gufo {
 
+// Launches `kernel` so that it may begin while the previous kernel in the
+// stream is still draining (programmatic dependent launch). Such a kernel must
+// execute GridDependencyWait() before it reads anything an earlier kernel
+// wrote and before its first global write. `cluster_x` > 1 also groups the
+// grid's x dimension into thread-block clusters.
+template <typename... KernelArgs, typename... Args>
+cudaError_t LaunchOverlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                             size_t smem, cudaStream_t stream, int cluster_x,
+                             Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  config.attrs = attr;
+  config.numAttrs = n;
+  return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
 // ---- device helpers ------------------------------------------------------
+
+// Lets the next kernel of the stream start launching its blocks.
+__device__ __forceinline__ void GridLaunchDependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Waits until every earlier kernel of the stream has finished and its writes
+// are visible.
+__device__ __forceinline__ void GridDependencyWait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 // fp16 bits to fp32, exact for every input including subnormals (the
 // conversion quant::HalfToFloat spells out, src/core/quant.cpp:129-155).

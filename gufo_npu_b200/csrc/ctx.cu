@@ -130,6 +130,7 @@ int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx) {
   }
   cudaFree(ctx->stage_x);
   cudaFree(ctx->stage_y);
+  cudaFree(ctx->image);
   if (ctx->own_stream) {
     cudaStreamDestroy(ctx->stream);
   }
@@ -149,6 +150,26 @@ int gufo_cuda_ctx_set_stream(gufo_cuda_ctx* ctx, void* stream) {
   }
   ctx->stream = static_cast<cudaStream_t>(stream);
   return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value) {
+  if (ctx == nullptr || name == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "set_option: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (std::strcmp(name, "general_gemv") == 0) {
+    ctx->force_general = value != 0;
+    return GUFO_CUDA_OK;
+  }
+  if (std::strcmp(name, "gemv_variant") == 0) {
+    ctx->gemv_variant = value;
+    return GUFO_CUDA_OK;
+  }
+  if (std::strcmp(name, "reuse_image") == 0) {
+    ctx->reuse_image = value != 0;
+    return GUFO_CUDA_OK;
+  }
+  return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string("set_option: unknown option ") + name);
 }
 
 int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx) {

@@ -96,9 +96,28 @@ __device__ __forceinline__ float4 ColumnSum(float4 v, DeltaShared& sh, int jq,
 // The delta rule on this block's column tile. sh.q, sh.k, sh.v and sh.gate are
 // ready (a __syncthreads lies between their writes and this call). Leaves the
 // tile's kTileCols outputs in sh.y, visible after the trailing barrier.
-__device__ __forceinline__ void DeltaTile(const float* __restrict__ src,
-                                          float* __restrict__ dst, int dk,
-                                          int col0, DeltaShared& sh) {
+struct StateTile {
+  float4 s[kMaxRowsPerThread];
+};
+
+// Issues this thread's loads of the state tile; called first thing so that the
+// HBM latency runs under the prologue.
+__device__ __forceinline__ void LoadTile(StateTile& tile, const float* __restrict__ src,
+                                         int dk, int col0) {
+  const int jq = threadIdx.x & 7;
+  const int ig = threadIdx.x >> 3;
+  const int rows = dk / kRowGroups;
+  const size_t at = static_cast<size_t>(col0 + 4 * jq);
+#pragma unroll
+  for (int r = 0; r < kMaxRowsPerThread; ++r) {
+    if (r < rows) {
+      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kRowGroups + ig) * dk + at);
+    }
+  }
+}
+
+__device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ dst,
+                                          int dk, int col0, DeltaShared& sh) {
   const int tid = threadIdx.x;
   const int jq = tid & 7;
   const int ig = tid >> 3;
@@ -107,15 +126,8 @@ __device__ __forceinline__ void DeltaTile(const float* __restrict__ src,
   const int rows = dk / kRowGroups;
   const float decay = sh.gate[0];
   const float beta = sh.gate[1];
-
-  float4 s[kMaxRowsPerThread];
+  float4 (&s)[kMaxRowsPerThread] = tile.s;
   const size_t at = static_cast<size_t>(col0 + 4 * jq);
-#pragma unroll
-  for (int r = 0; r < kMaxRowsPerThread; ++r) {
-    if (r < rows) {
-      s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kRowGroups + ig) * dk + at);
-    }
-  }
   // Pass 1: u_j = sum_i S_ij * (k_i * decay).
   float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -172,6 +184,11 @@ DeltaRuleKernel(const __grid_constant__ DeltaRuleArgs args) {
   const int col0 = blockIdx.x * kTileCols;
   const int kh = head % args.key_heads;
   const int tid = threadIdx.x;
+  const size_t state_at = static_cast<size_t>(head) * dk * dk;
+  GridLaunchDependents();
+  GridDependencyWait();
+  StateTile tile;
+  LoadTile(tile, seq.state + state_at, dk, col0);
   if (tid < dk) {
     sh.q[tid] = seq.q[kh * dk + tid];
     sh.k[tid] = seq.k[kh * dk + tid];
@@ -184,9 +201,8 @@ DeltaRuleKernel(const __grid_constant__ DeltaRuleArgs args) {
     sh.gate[1] = seq.beta[head];
   }
   __syncthreads();
-  const size_t state_at = static_cast<size_t>(head) * dk * dk;
   float* dst = (seq.state_out != nullptr ? seq.state_out : seq.state) + state_at;
-  DeltaTile(seq.state + state_at, dst, dk, col0, sh);
+  DeltaTile(tile, dst, dk, col0, sh);
   if (tid < kTileCols) {
     seq.y[head * dk + col0 + tid] = sh.y[tid];
   }
@@ -236,6 +252,11 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const int kh = head % hk;
   const int tid = threadIdx.x;
   const float* x = seq.in;
+  const size_t state_at = static_cast<size_t>(head) * dk * dk;
+  GridLaunchDependents();
+  GridDependencyWait();
+  StateTile state_tile;
+  LoadTile(state_tile, seq.ssm + state_at, dk, col0);
 
   // Causal depthwise conv + SiLU of channel ch; also advances that channel's
   // window when this block is the one that owns it.
@@ -285,9 +306,8 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   }
   __syncthreads();
 
-  const size_t state_at = static_cast<size_t>(head) * dk * dk;
   float* dst = (seq.ssm_out != nullptr ? seq.ssm_out : seq.ssm) + state_at;
-  DeltaTile(seq.ssm + state_at, dst, dk, col0, sh);
+  DeltaTile(state_tile, dst, dk, col0, sh);
 
   // Gated RMSNorm over the head's dk outputs: RMS(o) * w * silu(z).
   float sq = 0.f;
@@ -363,9 +383,9 @@ int gufo_cuda_delta_rule_device(gufo_cuda_ctx* ctx,
     args.value_heads = value_heads;
     args.head_dim = head_dim;
     const dim3 grid(head_dim / gufo::kTileCols, value_heads, n);
-    gufo::DeltaRuleKernel<<<grid, gufo::kDeltaThreads, 0, ctx->stream>>>(args);
+    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaRuleKernel, grid, dim3(gufo::kDeltaThreads), 0,
+                                         ctx->stream, 1, args));
     ctx->launches.fetch_add(1);
-    GUFO_CUDA_TRY(cudaGetLastError());
   }
   return GUFO_CUDA_OK;
 }
@@ -484,18 +504,8 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
     args.dt_bias = l.dt_bias;
     args.ssm_norm = l.ssm_norm;
     const int tiles = l.head_dim / gufo::kTileCols;
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(tiles, l.value_heads, n);
-    config.blockDim = dim3(gufo::kDeltaThreads);
-    config.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = tiles;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    config.attrs = attr;
-    config.numAttrs = 1;
-    GUFO_CUDA_TRY(cudaLaunchKernelEx(&config, gufo::DeltaNetLinearKernel, args));
+    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaNetLinearKernel, dim3(tiles, l.value_heads, n),
+                                         dim3(gufo::kDeltaThreads), 0, ctx->stream, tiles, args));
     ctx->launches.fetch_add(1);
   }
   return GUFO_CUDA_OK;

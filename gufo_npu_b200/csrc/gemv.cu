@@ -29,7 +29,8 @@ struct GemvPart {
 struct GemvArgs {
   GemvPart parts[kMaxParts];
   int nparts;
-  int total_rows;   // sum of parts' rows = y's row stride
+  int total_rows;   // sum of these parts' rows
+  int y_stride;     // width of a y row
   int cols;
   const float* x;   // [tokens][cols]
   float* y;         // [tokens][total_rows]
@@ -163,7 +164,7 @@ GemvRows(const __grid_constant__ GemvArgs args) {
   for (int t = 0; t < M; ++t) {
     const float total = WarpSum(acc[t]);
     if (lane == 0) {
-      args.y[static_cast<size_t>(t) * args.total_rows + part.out_offset + local] = total;
+      args.y[static_cast<size_t>(t) * args.y_stride + part.out_offset + local] = total;
     }
   }
 }
@@ -177,22 +178,56 @@ void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
 
 }  // namespace
 
-// Enqueues y = [W_0 x | W_1 x | ...] for up to kMaxTokens tokens.
+int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
+                     int group, float extra, const uint8_t** image);
+
+// Enqueues y = [W_0 x | W_1 x | ...]: Q4_K parts on the tensor-core kernel
+// (x staged once, one launch per part), the rest together on the general
+// kernel; at most kMaxTokens tokens per pass.
 int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
-  GemvArgs args = base;
   for (int t0 = 0; t0 < tokens; t0 += kMaxTokens) {
     const int m = tokens - t0 < kMaxTokens ? tokens - t0 : kMaxTokens;
-    args.x = base.x + static_cast<size_t>(t0) * base.cols;
-    args.y = base.y + static_cast<size_t>(t0) * base.total_rows;
+    const float* x = base.x + static_cast<size_t>(t0) * base.cols;
+    float* y = base.y + static_cast<size_t>(t0) * base.y_stride;
+    GemvArgs rest = base;
+    rest.nparts = 0;
+    rest.total_rows = 0;
+    rest.x = x;
+    rest.y = y;
+    const bool fast = !ctx->force_general && Q4KFastFits(base.cols, m);
+    const uint8_t* image = nullptr;
+    for (int p = 0; p < base.nparts; ++p) {
+      const GemvPart& part = base.parts[p];
+      if (fast && part.type == GUFO_CUDA_Q4_K) {
+        if (image == nullptr) {
+          const int rc = StageActivations(ctx, x, m, base.cols, 32, 1.0f / 16.0f, &image);
+          if (rc != GUFO_CUDA_OK) {
+            return rc;
+          }
+        }
+        const FastGemvArgs args{part.data, part.rows, base.cols, part.row_bytes, image, y,
+                                base.y_stride, part.out_offset, m};
+        const int rc = LaunchGemvQ4KFast(ctx, args);
+        if (rc != GUFO_CUDA_OK) {
+          return rc;
+        }
+        continue;
+      }
+      rest.parts[rest.nparts++] = part;
+      rest.total_rows += part.rows;
+    }
+    if (rest.nparts == 0) {
+      continue;
+    }
     switch (m) {
-      case 1: LaunchRows<1>(args, ctx->stream); break;
-      case 2: LaunchRows<2>(args, ctx->stream); break;
-      case 3: LaunchRows<3>(args, ctx->stream); break;
-      case 4: LaunchRows<4>(args, ctx->stream); break;
-      case 5: LaunchRows<5>(args, ctx->stream); break;
-      case 6: LaunchRows<6>(args, ctx->stream); break;
-      case 7: LaunchRows<7>(args, ctx->stream); break;
-      default: LaunchRows<8>(args, ctx->stream); break;
+      case 1: LaunchRows<1>(rest, ctx->stream); break;
+      case 2: LaunchRows<2>(rest, ctx->stream); break;
+      case 3: LaunchRows<3>(rest, ctx->stream); break;
+      case 4: LaunchRows<4>(rest, ctx->stream); break;
+      case 5: LaunchRows<5>(rest, ctx->stream); break;
+      case 6: LaunchRows<6>(rest, ctx->stream); break;
+      case 7: LaunchRows<7>(rest, ctx->stream); break;
+      default: LaunchRows<8>(rest, ctx->stream); break;
     }
     ctx->launches.fetch_add(1);
     GUFO_CUDA_TRY(cudaGetLastError());
@@ -241,6 +276,7 @@ int BuildArgs(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
   }
   args->nparts = nparts;
   args->total_rows = static_cast<int>(total);
+  args->y_stride = static_cast<int>(total);
   args->cols = static_cast<int>(cols);
   return GUFO_CUDA_OK;
 }

@@ -1,0 +1,403 @@
+// Q4_K GEMV / small-M GEMM on the int8 tensor-core path (see mma_common.cuh for
+// the arithmetic). The product is the reference's fused Q4_K row dot
+// (gguf_dot::DotK4, src/models/qwen35/gguf_dot.hpp:115-188):
+//   y_r = sum_blocks [ d * sum_j sc_j (q_j . x_j)  -  dmin * sum_j m_j (sum x_j) ]
+// with the code dots (q_j . x_j) taken exactly by the MMA.
+//
+// Work split. A persistent grid (a few thread blocks per SM) takes the 16-row
+// tiles blockIdx.x, blockIdx.x + gridDim.x, ... A tile is cut into slabs of up
+// to eight 256-value blocks; a slab (16 rows x <= 1152 bytes) is copied from
+// global to shared memory by the whole thread block with 16-byte asynchronous
+// copies, each warp instruction covering 512 contiguous bytes of one row, three
+// slabs in flight per thread block. Warp w multiplies block w of the slab from
+// shared memory (rows padded by 32 bytes so the 64-bit fragment reads of the
+// eight rows of a quarter-warp fall in distinct banks). The warps' partial
+// sums for a tile meet in shared memory after the barrier of the next slab.
+// The staged activations (three byte planes per token) are copied into shared
+// memory once per thread block. The weights never depend on an earlier
+// kernel, so the first slabs are requested before the grid-dependency wait.
+//
+// MMA operand layout (m16n8k32, A row-major u8, B column-major s8). Lane
+// (g = lane / 4, t = lane % 4) holds rows g and g + 8. The 32 bytes of a nibble
+// pair p carry sub-block 2p in the low and 2p + 1 in the high nibbles; lane t
+// loads bytes 8t..8t+7, so its two A words per row are values 8t..8t+3 and
+// 8t+4..8t+7 of the sub-block and the matching B words are the same eight
+// bytes of column g's plane: one 64-bit shared load, no permutation. High
+// nibbles are fed as 16 q (mask 0xF0), the factor 1/16 is folded into the
+// column scale.
+#include "mma_common.cuh"
+
+namespace gufo {
+namespace {
+
+constexpr int kSlabBlocks = 8;                              // blocks per slab = warps
+constexpr int kSlabRowBytes = kSlabBlocks * kQ4KBytes + 32;   // padded row in shared memory
+constexpr int kSlabBytes = 16 * kSlabRowBytes;
+constexpr int kStages = 3;
+
+struct Q4KUnit {
+  uint4 head[2];   // rows g, g + 8: d|dmin, three scale words
+  uint2 code[8];   // index 2 * pair + (0: row g, 1: row g + 8)
+};
+
+// Reads this lane's fragments of block `block` of a slab in shared memory.
+__device__ __forceinline__ void LoadUnit(Q4KUnit& u, const uint8_t* slab, int block,
+                                         int g, int t) {
+  const uint8_t* b0 = slab + g * kSlabRowBytes + block * kQ4KBytes;
+  const uint8_t* b1 = b0 + 8 * kSlabRowBytes;
+  u.head[0] = *reinterpret_cast<const uint4*>(b0);
+  u.head[1] = *reinterpret_cast<const uint4*>(b1);
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    u.code[2 * p] = *reinterpret_cast<const uint2*>(b0 + 16 + 32 * p + 8 * t);
+    u.code[2 * p + 1] = *reinterpret_cast<const uint2*>(b1 + 16 + 32 * p + 8 * t);
+  }
+}
+
+// The eight 6-bit scales and mins of a block as bytes of two words each
+// (quant::ScaleMinK4, src/core/quant.cpp:158-167, four sub-blocks at a time).
+__device__ __forceinline__ void ScaleBytes(const uint4& h, uint32_t (&sc)[2],
+                                           uint32_t (&mn)[2]) {
+  sc[0] = h.y & 0x3F3F3F3Fu;
+  mn[0] = h.z & 0x3F3F3F3Fu;
+  sc[1] = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+  mn[1] = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+}
+
+// Scale byte of sub-block J (compile time) from the two scale words.
+template <int J>
+__device__ __forceinline__ int ScaleOf(const uint32_t (&sc)[2]) {
+  return ByteAt<(J & 3)>(sc[J >> 2]);
+}
+
+template <int TOKENS>
+struct Accum {
+  static constexpr int kNB = (TOKENS * kLimbs + 7) / 8;
+  float out[kNB][4];     // rows g, g + 8 x columns 2t, 2t + 1
+  float off[TOKENS];     // this lane's share of the dmin * m * sum(x) terms
+};
+
+// Nibble pair P of one unit: sub-blocks 2P (low nibbles) and 2P + 1 (high).
+template <int TOKENS, int P>
+__device__ __forceinline__ void MultiplyPair(const Q4KUnit& u, const uint32_t (&sc0)[2],
+                                             const uint32_t (&sc1)[2],
+                                             const uint8_t* __restrict__ at, int g,
+                                             int plane_stride,
+                                             int (&sum_lo)[Accum<TOKENS>::kNB][4],
+                                             int (&sum_hi)[Accum<TOKENS>::kNB][4]) {
+  constexpr int kNB = Accum<TOKENS>::kNB;
+  constexpr int kNCols = TOKENS * kLimbs;
+  const uint2 q0 = u.code[2 * P], q1 = u.code[2 * P + 1];
+  const uint32_t lo[4] = {q0.x & 0x0F0F0F0Fu, q1.x & 0x0F0F0F0Fu,
+                          q0.y & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu};
+  const uint32_t hi[4] = {q0.x & 0xF0F0F0F0u, q1.x & 0xF0F0F0F0u,
+                          q0.y & 0xF0F0F0F0u, q1.y & 0xF0F0F0F0u};
+  const int s_lo0 = ScaleOf<2 * P>(sc0), s_hi0 = ScaleOf<2 * P + 1>(sc0);
+  const int s_lo1 = ScaleOf<2 * P>(sc1), s_hi1 = ScaleOf<2 * P + 1>(sc1);
+#pragma unroll
+  for (int nb = 0; nb < kNB; ++nb) {
+    // Lanes whose column holds no token read a live plane all the same: their
+    // sums meet a zero column factor and are never stored.
+    const uint8_t* src = at + (nb * 8 + g < kNCols ? nb * 8 * plane_stride : 0) + 64 * P;
+    const uint2 xl = *reinterpret_cast<const uint2*>(src);
+    const uint2 xh = *reinterpret_cast<const uint2*>(src + 32);
+    int c[4];
+    MmaU8S8(c, lo, xl.x, xl.y);
+    sum_lo[nb][0] += s_lo0 * c[0];
+    sum_lo[nb][1] += s_lo0 * c[1];
+    sum_lo[nb][2] += s_lo1 * c[2];
+    sum_lo[nb][3] += s_lo1 * c[3];
+    MmaU8S8(c, hi, xh.x, xh.y);
+    sum_hi[nb][0] += s_hi0 * c[0];
+    sum_hi[nb][1] += s_hi0 * c[1];
+    sum_hi[nb][2] += s_hi1 * c[2];
+    sum_hi[nb][3] += s_hi1 * c[3];
+  }
+}
+
+// One unit: 16 rows x one 256-value block against every staged column.
+// `lane_plane` is this lane's column plane at byte 8t.
+template <int TOKENS>
+__device__ __forceinline__ void MultiplyUnit(const Q4KUnit& u, int b, int g, int t,
+                                             const uint8_t* __restrict__ lane_plane,
+                                             const ImageLayout& l,
+                                             const float* __restrict__ col_scale,
+                                             const float* __restrict__ sums,
+                                             Accum<TOKENS>& acc) {
+  constexpr int kNB = Accum<TOKENS>::kNB;
+  uint32_t sc[2][2], mn[2][2];
+  ScaleBytes(u.head[0], sc[0], mn[0]);
+  ScaleBytes(u.head[1], sc[1], mn[1]);
+  int sum_lo[kNB][4] = {}, sum_hi[kNB][4] = {};
+  const uint8_t* at = lane_plane + b * kSuperBlock;
+  MultiplyPair<TOKENS, 0>(u, sc[0], sc[1], at, g, l.plane_stride, sum_lo, sum_hi);
+  MultiplyPair<TOKENS, 1>(u, sc[0], sc[1], at, g, l.plane_stride, sum_lo, sum_hi);
+  MultiplyPair<TOKENS, 2>(u, sc[0], sc[1], at, g, l.plane_stride, sum_lo, sum_hi);
+  MultiplyPair<TOKENS, 3>(u, sc[0], sc[1], at, g, l.plane_stride, sum_lo, sum_hi);
+  const float d0 = HalfBitsToFloat(static_cast<uint16_t>(u.head[0].x & 0xFFFF));
+  const float d1 = HalfBitsToFloat(static_cast<uint16_t>(u.head[1].x & 0xFFFF));
+#pragma unroll
+  for (int nb = 0; nb < kNB; ++nb) {
+    const float2 cs = *reinterpret_cast<const float2*>(&col_scale[b * l.kcols + nb * 8 + 2 * t]);
+    // 16 * (even sub-blocks) + (odd sub-blocks, fed as 16 q): below 2^29.
+    acc.out[nb][0] = fmaf(static_cast<float>(sum_lo[nb][0] * 16 + sum_hi[nb][0]), d0 * cs.x, acc.out[nb][0]);
+    acc.out[nb][1] = fmaf(static_cast<float>(sum_lo[nb][1] * 16 + sum_hi[nb][1]), d0 * cs.y, acc.out[nb][1]);
+    acc.out[nb][2] = fmaf(static_cast<float>(sum_lo[nb][2] * 16 + sum_hi[nb][2]), d1 * cs.x, acc.out[nb][2]);
+    acc.out[nb][3] = fmaf(static_cast<float>(sum_lo[nb][3] * 16 + sum_hi[nb][3]), d1 * cs.y, acc.out[nb][3]);
+  }
+  // Offsets: lanes t = 0, 1 take sub-blocks 0..3 and 4..7 of row g, lanes
+  // t = 2, 3 the same of row g + 8.
+  const bool second = (t >> 1) != 0;
+  const bool upper = (t & 1) != 0;
+  const float dmin = HalfBitsToFloat(
+      static_cast<uint16_t>((second ? u.head[1].x : u.head[0].x) >> 16));
+  const uint32_t m4 = second ? (upper ? mn[1][1] : mn[1][0]) : (upper ? mn[0][1] : mn[0][0]);
+  const float m0 = SmallByteToFloat<0>(m4), m1 = SmallByteToFloat<1>(m4);
+  const float m2 = SmallByteToFloat<2>(m4), m3 = SmallByteToFloat<3>(m4);
+  const float* xs = sums + b * 8 + (upper ? 4 : 0);
+#pragma unroll
+  for (int k = 0; k < TOKENS; ++k) {
+    const float4 s = *reinterpret_cast<const float4*>(xs + k * (l.cols / 32));
+    acc.off[k] = fmaf(dmin, (m0 * s.x + m1 * s.y) + (m2 * s.z + m3 * s.w), acc.off[k]);
+  }
+}
+
+template <int TOKENS, int PER_SM>
+__global__ void __launch_bounds__(kFastThreads, PER_SM)
+GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  constexpr int kNB = Accum<TOKENS>::kNB;
+  constexpr int kNCols = TOKENS * kLimbs;
+  constexpr int kRowFloats = kNCols + TOKENS;   // per row in the exchange buffer
+  constexpr int kTileFloats = 16 * kRowFloats;
+  const ImageLayout l = MakeImageLayout(TOKENS, a.cols, 32);
+  const int blocks = a.cols / kSuperBlock;
+  const int slabs_per_tile = (blocks + kSlabBlocks - 1) / kSlabBlocks;
+  const float* col_scale = reinterpret_cast<const float*>(smem + l.scale_at);
+  const float* sums = reinterpret_cast<const float*>(smem + l.sums_at);
+  // After the image: the exchange buffer [2][warps][16 rows][kRowFloats], then
+  // the slab ring.
+  float* exchange = reinterpret_cast<float*>(smem + l.bytes);
+  uint8_t* ring = smem + l.bytes + 2 * kFastWarps * kTileFloats * 4;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  // Column g of the first MMA column group; lanes past the last token's planes
+  // wrap onto live ones (see MultiplyPair).
+  const uint8_t* lane_plane = smem + (g % kNCols) * l.plane_stride + 8 * t;
+  const int row_tiles = (a.rows + 15) >> 4;
+  const int stride = gridDim.x;
+  const int my_tiles = (row_tiles - static_cast<int>(blockIdx.x) + stride - 1) / stride;
+  const int my_slabs = my_tiles * slabs_per_tile;
+
+  // Requests slab q (tile q / slabs_per_tile): warp w copies rows 2w and 2w + 1,
+  // a lane the 16-byte chunks lane, lane + 32, lane + 64 of the row's segment.
+  const uint32_t ring_base = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+  int req_n = 0, req_s = 0;   // tile and slab of the next request
+  auto request = [&](int q) {
+    if (q < my_slabs) {
+      const int n = req_n;
+      const int s = req_s;
+      if (++req_s == slabs_per_tile) {
+        req_s = 0;
+        ++req_n;
+      }
+      const int nblk = min(kSlabBlocks, blocks - s * kSlabBlocks);
+      const int chunks = nblk * (kQ4KBytes / 16);
+      const uint32_t dst0 = ring_base + (q % kStages) * kSlabBytes;
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const int r = 2 * warp + rr;
+        // Rows past the end repeat the last row; their sums are never stored.
+        const int row = min((static_cast<int>(blockIdx.x) + n * stride) * 16 + r, a.rows - 1);
+        const uint8_t* src = a.w + static_cast<size_t>(row) * a.row_bytes + s * (kSlabBlocks * kQ4KBytes);
+        const uint32_t dst = dst0 + r * kSlabRowBytes;
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+          const int chunk = lane + 32 * c;
+          if (chunk < chunks) {
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + chunk * 16),
+                         "l"(src + chunk * 16) : "memory");
+          }
+        }
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+#pragma unroll
+  for (int q = 0; q < kStages - 1; ++q) {
+    request(q);
+  }
+  GridLaunchDependents();
+  // The weights above never depend on earlier kernels; the image and y do.
+  GridDependencyWait();
+  {
+    const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    for (int at = threadIdx.x * 16; at < l.bytes; at += kFastThreads * 16) {
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + at), "l"(a.image + at)
+                   : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+
+  Accum<TOKENS> acc;
+  auto clear = [&]() {
+#pragma unroll
+    for (int nb = 0; nb < kNB; ++nb) {
+      acc.out[nb][0] = acc.out[nb][1] = acc.out[nb][2] = acc.out[nb][3] = 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < TOKENS; ++k) {
+      acc.off[k] = 0.f;
+    }
+  };
+  // Sums the eight warps' partials of tile n (exchange buffer n & 1) into y.
+  auto gather = [&](int n) {
+    for (int o = threadIdx.x; o < 16 * TOKENS; o += kFastThreads) {
+      const int k = o % TOKENS;
+      const int r = o / TOKENS;
+      const int row = (static_cast<int>(blockIdx.x) + n * stride) * 16 + r;
+      if (row < a.rows) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kFastWarps; ++w) {
+          const float* part = exchange + ((n & 1) * kFastWarps + w) * kTileFloats + r * kRowFloats;
+          total += (part[k * kLimbs] + part[k * kLimbs + 1] + part[k * kLimbs + 2]) - part[kNCols + k];
+        }
+        a.y[static_cast<size_t>(k) * a.y_stride + a.y_offset + row] = total;
+      }
+    }
+  };
+  clear();
+  int n = 0, s = 0;   // tile and slab being multiplied
+  for (int q = 0; q < my_slabs; ++q) {
+    // Slab q (and, the first time, the image) has landed for this thread;
+    // the barrier makes every thread's copies visible and frees slab q - 1.
+    if (q == 0) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 2) : "memory");
+    }
+    __syncthreads();
+    request(q + kStages - 1);
+    if (s == 0 && n > 0) {
+      gather(n - 1);   // written before the barrier above
+    }
+    const int b = s * kSlabBlocks + warp;
+    if (b < blocks) {
+      Q4KUnit unit;
+      LoadUnit(unit, ring + (q % kStages) * kSlabBytes, warp, g, t);
+      MultiplyUnit<TOKENS>(unit, b, g, t, lane_plane, l, col_scale, sums, acc);
+    }
+    if (s == slabs_per_tile - 1) {
+      // Hand this tile's partial sums to the block.
+      float* tile = exchange + ((n & 1) * kFastWarps + warp) * kTileFloats;
+#pragma unroll
+      for (int nb = 0; nb < kNB; ++nb) {
+        const int col = nb * 8 + 2 * t;
+        if (col < kNCols) {
+          tile[g * kRowFloats + col] = acc.out[nb][0];
+          tile[(g + 8) * kRowFloats + col] = acc.out[nb][2];
+        }
+        if (col + 1 < kNCols) {
+          tile[g * kRowFloats + col + 1] = acc.out[nb][1];
+          tile[(g + 8) * kRowFloats + col + 1] = acc.out[nb][3];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < TOKENS; ++k) {
+        // Lanes t and t ^ 1 hold the two halves of one row's offsets.
+        const float both = acc.off[k] + __shfl_xor_sync(0xFFFFFFFFu, acc.off[k], 1);
+        if ((t & 1) == 0) {
+          tile[(g + 8 * (t >> 1)) * kRowFloats + kNCols + k] = both;
+        }
+      }
+      clear();
+      s = 0;
+      ++n;
+    } else {
+      ++s;
+    }
+  }
+  if (my_tiles > 0) {
+    __syncthreads();
+    gather(my_tiles - 1);
+  }
+}
+
+template <int TOKENS>
+size_t SharedBytes(int cols) {
+  const ImageLayout l = MakeImageLayout(TOKENS, cols, 32);
+  return static_cast<size_t>(l.bytes) +
+         static_cast<size_t>(2) * kFastWarps * 16 * (TOKENS * kLimbs + TOKENS) * 4 +
+         static_cast<size_t>(kStages) * kSlabBytes;
+}
+
+template <int TOKENS, int PER_SM>
+int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
+  const size_t smem = SharedBytes<TOKENS>(args.cols);
+  if (smem > static_cast<size_t>(kFastMaxShared)) {
+    return GUFO_CUDA_TOO_LARGE;
+  }
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemvQ4KMma<TOKENS, PER_SM>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kFastMaxShared));
+    configured[ctx->device & 15] = true;
+  }
+  const int row_tiles = (args.rows + 15) / 16;
+  const int slots = ctx->sm_count * PER_SM;
+  const int grid = row_tiles < slots ? row_tiles : slots;
+  GUFO_CUDA_TRY(LaunchOverlapped(GemvQ4KMma<TOKENS, PER_SM>, dim3(grid), dim3(kFastThreads), smem,
+                                 ctx->stream, 1, args));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+template <int TOKENS>
+int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
+  if (TOKENS == 1) {
+    switch (ctx->gemv_variant) {
+      case 1: return LaunchVariant<TOKENS == 1 ? 1 : TOKENS, 1>(ctx, args);
+      case 3: return LaunchVariant<TOKENS == 1 ? 1 : TOKENS, 3>(ctx, args);
+      default: break;
+    }
+  }
+  return LaunchVariant<TOKENS, 2>(ctx, args);
+}
+
+}  // namespace
+
+// Whether `tokens` rows of `cols` values fit the shared-memory image.
+bool Q4KFastFits(int cols, int tokens) {
+  switch (tokens) {
+    case 1: return SharedBytes<1>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 2: return SharedBytes<2>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 3: return SharedBytes<3>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 4: return SharedBytes<4>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 5: return SharedBytes<5>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 6: return SharedBytes<6>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 7: return SharedBytes<7>(cols) <= static_cast<size_t>(kFastMaxShared);
+    case 8: return SharedBytes<8>(cols) <= static_cast<size_t>(kFastMaxShared);
+    default: return false;
+  }
+}
+
+// Enqueues one Q4_K part against the staged image `args.image`.
+int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
+  switch (args.tokens) {
+    case 1: return Launch<1>(ctx, args);
+    case 2: return Launch<2>(ctx, args);
+    case 3: return Launch<3>(ctx, args);
+    case 4: return Launch<4>(ctx, args);
+    case 5: return Launch<5>(ctx, args);
+    case 6: return Launch<6>(ctx, args);
+    case 7: return Launch<7>(ctx, args);
+    case 8: return Launch<8>(ctx, args);
+    default: return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: 1 to 8 tokens per launch");
+  }
+}
+
+}  // namespace gufo

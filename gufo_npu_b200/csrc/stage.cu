@@ -1,0 +1,133 @@
+// Staging of fp32 activations into the fixed-point image the tensor-core GEMV
+// kernels multiply against (layout and rationale in mma_common.cuh).
+//
+// One warp converts one 256-value block of one token: every lane takes eight
+// adjacent values, the block's largest magnitude fixes the shift, and the three
+// signed byte planes, the per-group fp32 sums and the per-column scale factors
+// are written to the context's image buffer. The work is a few kilobytes; the
+// kernel exists so that this conversion happens once per product and not once
+// per thread block of the GEMV.
+#include "mma_common.cuh"
+
+namespace gufo {
+namespace {
+
+struct StageArgs {
+  const float* x;
+  uint8_t* image;
+  ImageLayout layout;
+  float extra;
+};
+
+__global__ void __launch_bounds__(kFastThreads)
+StageKernel(const __grid_constant__ StageArgs a) {
+  const ImageLayout& l = a.layout;
+  const int lane = threadIdx.x & 31;
+  const int blocks = l.cols / kSuperBlock;
+  const int item = blockIdx.x * kFastWarps + (threadIdx.x >> 5);
+  GridLaunchDependents();
+  GridDependencyWait();
+  float* scale = reinterpret_cast<float*>(a.image + l.scale_at);
+  if (blockIdx.x == 0) {
+    // Columns without a token keep a zero factor.
+    for (int i = threadIdx.x; i < blocks * l.kcols; i += kFastThreads) {
+      if (i % l.kcols >= l.tokens * kLimbs) {
+        scale[i] = 0.f;
+      }
+    }
+  }
+  if (item >= l.tokens * blocks) {
+    return;
+  }
+  const int tok = item / blocks;
+  const int b = item - tok * blocks;
+  const float* xp = a.x + static_cast<size_t>(tok) * l.cols + b * kSuperBlock + lane * 8;
+  const float4 v0 = *reinterpret_cast<const float4*>(xp);
+  const float4 v1 = *reinterpret_cast<const float4*>(xp + 4);
+  const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  // Largest magnitude by integer compare of the bit patterns, so that a NaN
+  // (above every finite pattern) is not lost.
+  uint32_t top = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    top = max(top, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    top = max(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
+  }
+  int e = static_cast<int>(top >> 23);  // biased exponent of the maximum
+  const bool finite = e != 255;
+  e = e < 22 ? 22 : e;
+  // |x| < 2^(e - 126), so x * 2^(148 - e) stays below 2^22 in magnitude.
+  const float up = __uint_as_float(static_cast<uint32_t>(275 - e) << 23);
+  const float down = finite ? __uint_as_float(static_cast<uint32_t>(e - 21) << 23)
+                            : __uint_as_float(0x7FC00000u);
+  // xi + 0x808080 has the balanced digits of xi, each offset by 128, in its
+  // three low bytes; flipping the offset bits leaves the signed bytes.
+  uint32_t z[8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int xi = finite ? __float2int_rn(v[i] * up) : 0;
+    z[i] = static_cast<uint32_t>(xi + 0x808080) ^ 0x808080u;
+    sum += v[i];
+  }
+#pragma unroll
+  for (int limb = 0; limb < kLimbs; ++limb) {
+    const uint32_t pick = 0x0040u + 0x11u * limb;  // byte `limb` of both operands
+    const uint32_t w0 = __byte_perm(__byte_perm(z[0], z[1], pick), __byte_perm(z[2], z[3], pick), 0x5410u);
+    const uint32_t w1 = __byte_perm(__byte_perm(z[4], z[5], pick), __byte_perm(z[6], z[7], pick), 0x5410u);
+    uint8_t* plane = a.image + static_cast<size_t>(tok * kLimbs + limb) * l.plane_stride;
+    *reinterpret_cast<uint2*>(plane + b * kSuperBlock + lane * 8) = make_uint2(w0, w1);
+  }
+  // Group sums of the fp32 values: the lanes of one group are adjacent.
+  const int lanes_per_group = l.group / 8;  // 4 (groups of 32) or 2 (of 16)
+  for (int o = 1; o < lanes_per_group; o <<= 1) {
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  }
+  if ((lane & (lanes_per_group - 1)) == 0) {
+    float* sums = reinterpret_cast<float*>(a.image + l.sums_at);
+    sums[static_cast<size_t>(tok) * (l.cols / l.group) + b * (kSuperBlock / l.group) +
+         lane / lanes_per_group] = sum;
+  }
+  if (lane < kLimbs) {
+    const float limb = lane == 0 ? 1.f : (lane == 1 ? 256.f : 65536.f);
+    scale[b * l.kcols + tok * kLimbs + lane] = down * limb * a.extra;
+  }
+}
+
+}  // namespace
+
+int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
+                     int group, float extra, const uint8_t** image) {
+  StageArgs args;
+  args.layout = MakeImageLayout(tokens, cols, group);
+  const size_t need = static_cast<size_t>(args.layout.bytes);
+  if (ctx->image_bytes < need) {
+    if (ctx->image != nullptr) {
+      GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+      GUFO_CUDA_TRY(cudaFree(ctx->image));
+      ctx->image = nullptr;
+      ctx->image_bytes = 0;
+    }
+    const size_t grown = need < (256u << 10) ? (256u << 10) : need;
+    GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&ctx->image), grown));
+    ctx->image_bytes = grown;
+  }
+  if (ctx->reuse_image) {
+    *image = ctx->image;
+    return GUFO_CUDA_OK;
+  }
+  args.x = x;
+  args.image = ctx->image;
+  args.extra = extra;
+  const int items = tokens * (cols / kSuperBlock);
+  const int grid = (items + kFastWarps - 1) / kFastWarps;
+  GUFO_CUDA_TRY(LaunchOverlapped(StageKernel, dim3(grid), dim3(kFastThreads), 0, ctx->stream, 1, args));
+  ctx->launches.fetch_add(1);
+  *image = ctx->image;
+  return GUFO_CUDA_OK;
+}
+
+}  // namespace gufo

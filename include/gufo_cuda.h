@@ -72,6 +72,11 @@ int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx);
 /* Text of the last failure of a call on `ctx` (or of ctx_create when ctx is
  * NULL) made by this thread; valid until that thread's next failing call. */
 const char* gufo_cuda_last_error(const gufo_cuda_ctx* ctx);
+/* Tuning and test switches, by name. "general_gemv" = 1 routes every product
+ * through the general (non tensor-core) kernel; 0 (default) picks per part.
+ * "reuse_image" = 1 is a timing aid: products skip the staging of x and
+ * multiply against the previously staged activations. */
+int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value);
 /* Number of kernels this context has launched so far. */
 int64_t gufo_cuda_launch_count(const gufo_cuda_ctx* ctx);
 

@@ -27,9 +27,12 @@ def bits(a):
     return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
 
 
-@pytest.fixture(scope="module")
-def ctx():
+@pytest.fixture(scope="module", params=["default", "general"])
+def ctx(request):
+    """Every test runs twice: with the kernels the dispatcher picks, and with every product
+    forced through the general kernel."""
     c = Context(0)
+    c.set_option("general_gemv", int(request.param == "general"))
     yield c
     c.close()
 
@@ -125,6 +128,32 @@ def test_gemv_shapes_random_blocks(ctx, oracle, name, rows, cols):
     exact = oracle.matmul([(raw, t, 0, n)], cols, x, exact=True)[0]
     assert np.all(np.abs(got[:n] - exact) < 2e-5 * magnitude)
     ctx.matrix_free(m)
+
+
+def test_activation_extremes(ctx, oracle):
+    """Activations with a wide dynamic range inside one 256-value block, zero blocks, tiny and
+    huge magnitudes: the fixed-point staging keeps fp32-level accuracy."""
+    rows, cols = 64, 1024
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal(cols).astype(np.float32)
+    x[0:256] = 0.0                                  # an all-zero block
+    x[256:512] *= 1e-30                             # tiny
+    x[512:768] *= 1e20                              # huge
+    x[768] = 3000.0                                 # one outlier among N(0, 1)
+    x[900:1024] *= np.float32(2.0) ** rng.integers(-20, 4, 124)
+    for name, t in TYPES.items():
+        raw = Q.random_blocks(t, rows, cols, seed=4).numpy()
+        m = ctx.matrix_upload(t, raw, rows, cols)
+        got = ctx.matmul([(m, 0, rows)], x, 1, rows)[0]
+        exact = oracle.matmul([(raw, t, 0, rows)], cols, x, exact=True)[0]
+        wabs = np.abs(oracle.dequantize(t, raw, rows * cols).reshape(rows, cols)).astype(np.float64)
+        magnitude = wabs @ np.abs(x).astype(np.float64)
+        assert np.all(np.abs(got - exact) < 2e-5 * magnitude)
+        # Non-finite activations give non-finite outputs, as on the CPU.
+        bad = x.copy()
+        bad[5] = np.inf
+        assert not np.isfinite(ctx.matmul([(m, 0, rows)], bad, 1, rows)).any()
+        ctx.matrix_free(m)
 
 
 @pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8, 9, 19])
