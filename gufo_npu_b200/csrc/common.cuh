@@ -20,12 +20,50 @@ constexpr int kSuperBlock = 256;   // values per K-quant super-block
 constexpr int kQ4KBytes = 144;     // d, dmin (fp16), 12 scale bytes, 128 nibble bytes
 constexpr int kQ6KBytes = 210;     // 128 ql, 64 qh, 16 int8 scales, d (fp16)
 
+// Q6_K rows are kept on the device in a planar arrangement of the same bytes:
+// GGUF blocks are 210 bytes, so inside a row they sit on 2-byte boundaries and
+// neither 16-byte copies nor 4-byte fragment loads could address them. Per row
+// the blocks are grouped in slabs of eight, and a slab of n blocks stores
+//   ql: n x 128 | qh: n x 64 | scales: n x 16 | d: n x 2        (n x 210 bytes)
+// each plane in block order. Rows start on 16-byte boundaries (the row stride
+// is rounded up to a multiple of 16; padding only arises when cols / 256 is
+// not a multiple of 8). quant::Dequantize's view of a block
+// (src/core/quant.cpp:98-125) maps one to one: see Q6KBlock below.
+constexpr int kQ6KSlabBlocks = 8;
+
+__host__ __device__ inline size_t Q6KDeviceRowBytes(int64_t cols) {
+  const size_t raw = static_cast<size_t>(cols / kSuperBlock) * kQ6KBytes;
+  return (raw + 15) / 16 * 16;
+}
+
+// Device addresses of the four parts of block `b` of a planar Q6_K row.
+struct Q6KBlock {
+  const uint8_t* ql;
+  const uint8_t* qh;
+  const int8_t* sc;
+  const uint8_t* d;
+};
+
+__host__ __device__ inline Q6KBlock Q6KBlockAt(const uint8_t* row, int blocks, int b) {
+  const int slab = b / kQ6KSlabBlocks;
+  const int j = b - slab * kQ6KSlabBlocks;
+  const int left = blocks - slab * kQ6KSlabBlocks;
+  const int n = left < kQ6KSlabBlocks ? left : kQ6KSlabBlocks;
+  const uint8_t* base = row + static_cast<size_t>(slab) * kQ6KSlabBlocks * kQ6KBytes;
+  Q6KBlock out;
+  out.ql = base + 128 * j;
+  out.qh = base + 128 * n + 64 * j;
+  out.sc = reinterpret_cast<const int8_t*>(base + 192 * n + 16 * j);
+  out.d = base + 208 * n + 2 * j;
+  return out;
+}
+
 struct Matrix {
   int type = 0;
-  const uint8_t* data = nullptr;  // device
+  const uint8_t* data = nullptr;  // device; Q6_K in the planar arrangement
   int64_t rows = 0;
   int64_t cols = 0;
-  size_t row_bytes = 0;
+  size_t row_bytes = 0;           // device row stride
   bool owned = false;
 };
 
@@ -61,6 +99,9 @@ struct FastGemvArgs {
 // Bytes of a row of `cols` values of `type`; 0 when the type is not run here or
 // cols is not a whole number of blocks.
 size_t RowBytes(int type, int64_t cols);
+// Device row stride of a matrix of `type` (differs from RowBytes for Q6_K rows
+// whose GGUF size is not a multiple of 16).
+size_t DeviceRowBytes(int type, int64_t cols);
 
 }  // namespace gufo
 
@@ -70,6 +111,9 @@ namespace gufo {
 int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 // Whether the image of `tokens` rows of `cols` values fits in shared memory.
 bool Q4KFastFits(int cols, int tokens);
+// The same for Q6_K parts (image with group sums of 16).
+int LaunchGemvQ6KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
+bool Q6KFastFits(int cols, int tokens);
 }  // namespace gufo
 
 struct gufo_cuda_ctx {

@@ -39,6 +39,70 @@ size_t RowBytes(int type, int64_t cols) {
   }
 }
 
+size_t DeviceRowBytes(int type, int64_t cols) {
+  return type == GUFO_CUDA_Q6_K ? Q6KDeviceRowBytes(cols) : RowBytes(type, cols);
+}
+
+namespace {
+
+// One thread per (row, block): moves the 210 bytes of a GGUF Q6_K block to
+// their planar places. Runs once per matrix at upload.
+__global__ void RepackQ6K(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                          int64_t rows, int blocks, size_t src_row, size_t dst_row) {
+  const int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (item >= rows * blocks) {
+    return;
+  }
+  const int64_t r = item / blocks;
+  const int b = static_cast<int>(item - r * blocks);
+  const uint8_t* in = src + r * src_row + static_cast<size_t>(b) * kQ6KBytes;
+  const Q6KBlock out = Q6KBlockAt(dst + r * dst_row, blocks, b);
+  uint8_t* ql = const_cast<uint8_t*>(out.ql);
+  uint8_t* qh = const_cast<uint8_t*>(out.qh);
+  uint8_t* sc = reinterpret_cast<uint8_t*>(const_cast<int8_t*>(out.sc));
+  uint8_t* d = const_cast<uint8_t*>(out.d);
+  // Blocks start on even addresses only: 2-byte moves.
+  const uint16_t* in16 = reinterpret_cast<const uint16_t*>(in);
+  for (int i = 0; i < 64; ++i) {
+    reinterpret_cast<uint16_t*>(ql)[i] = in16[i];
+  }
+  for (int i = 0; i < 32; ++i) {
+    reinterpret_cast<uint16_t*>(qh)[i] = in16[64 + i];
+  }
+  for (int i = 0; i < 8; ++i) {
+    reinterpret_cast<uint16_t*>(sc)[i] = in16[96 + i];
+  }
+  reinterpret_cast<uint16_t*>(d)[0] = in16[104];
+}
+
+}  // namespace
+
+// Copies GGUF Q6_K rows at `raw` (device) into a new planar buffer.
+int RepackQ6KRows(gufo_cuda_ctx* ctx, const uint8_t* raw, int64_t rows, int64_t cols,
+                  uint8_t** out) {
+  const size_t dst_row = Q6KDeviceRowBytes(cols);
+  const int blocks = static_cast<int>(cols / kSuperBlock);
+  void* dst = nullptr;
+  GUFO_CUDA_TRY(cudaMalloc(&dst, dst_row * static_cast<size_t>(rows) + 16));
+  cudaError_t e = cudaMemsetAsync(dst, 0, dst_row * static_cast<size_t>(rows) + 16, ctx->stream);
+  if (e == cudaSuccess) {
+    const int64_t items = rows * blocks;
+    const int grid = static_cast<int>((items + 255) / 256);
+    RepackQ6K<<<grid, 256, 0, ctx->stream>>>(raw, static_cast<uint8_t*>(dst), rows, blocks,
+                                              static_cast<size_t>(blocks) * kQ6KBytes, dst_row);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) {
+    e = cudaStreamSynchronize(ctx->stream);
+  }
+  if (e != cudaSuccess) {
+    cudaFree(dst);
+    return CudaFail(e, "repack Q6_K");
+  }
+  *out = static_cast<uint8_t*>(dst);
+  return GUFO_CUDA_OK;
+}
+
 }  // namespace gufo
 
 int gufo_cuda_ctx::Reserve(float** buffer, size_t* have, size_t want) {
@@ -241,7 +305,7 @@ static int AddMatrix(gufo_cuda_ctx* ctx, int type, const uint8_t* data,
   m.data = data;
   m.rows = rows;
   m.cols = cols;
-  m.row_bytes = gufo::RowBytes(type, cols);
+  m.row_bytes = gufo::DeviceRowBytes(type, cols);
   m.owned = owned;
   const int64_t id = ctx->next_id++;
   ctx->matrices.emplace(id, m);
@@ -294,6 +358,15 @@ int gufo_cuda_matrix_upload(gufo_cuda_ctx* ctx, int ggml_type,
     cudaFree(dev);
     return gufo::CudaFail(e, "matrix_upload copy");
   }
+  if (ggml_type == GUFO_CUDA_Q6_K) {
+    uint8_t* planar = nullptr;
+    rc = gufo::RepackQ6KRows(ctx, static_cast<const uint8_t*>(dev), rows, cols, &planar);
+    cudaFree(dev);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+    dev = planar;
+  }
   return AddMatrix(ctx, ggml_type, static_cast<const uint8_t*>(dev), rows, cols,
                    true, out);
 }
@@ -310,6 +383,16 @@ int gufo_cuda_matrix_from_device(gufo_cuda_ctx* ctx, int ggml_type,
                 "matrix_from_device: bytes must be 16-byte aligned");
   }
   std::lock_guard<std::mutex> lock(ctx->mu);
+  if (ggml_type == GUFO_CUDA_Q6_K) {
+    // Q6_K is rearranged into its planar device form: a copy, owned here.
+    GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+    uint8_t* planar = nullptr;
+    rc = gufo::RepackQ6KRows(ctx, static_cast<const uint8_t*>(device_bytes), rows, cols, &planar);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+    return AddMatrix(ctx, ggml_type, planar, rows, cols, true, out);
+  }
   return AddMatrix(ctx, ggml_type, static_cast<const uint8_t*>(device_bytes), rows,
                    cols, false, out);
 }

@@ -50,29 +50,30 @@ DequantQ4K(const uint8_t* __restrict__ src, float* __restrict__ dst,
   }
 }
 
-// One thread per (block, half, l): values l, l+32, l+64, l+96 of the half.
-// Blocks are 210 bytes, so only 2-byte alignment holds: byte loads.
+// One thread per (row, block, half, l): values l, l+32, l+64, l+96 of the
+// half, read from the planar device arrangement of the row.
 __global__ void __launch_bounds__(256)
 DequantQ6K(const uint8_t* __restrict__ src, float* __restrict__ dst,
-           int64_t blocks) {
-  const int64_t items = blocks * 64;
+           int64_t rows, int blocks, size_t row_bytes) {
+  const int64_t items = rows * blocks * 64;
   for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
        item < items; item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t b = item >> 6;
+    const int64_t rb = item >> 6;
+    const int64_t r = rb / blocks;
+    const int b = static_cast<int>(rb - r * blocks);
     const int half = static_cast<int>((item >> 5) & 1);
     const int l = static_cast<int>(item & 31);
-    const uint8_t* block = src + b * kQ6KBytes;
-    const uint8_t* ql = block + 64 * half;
-    const uint8_t* qh = block + 128 + 32 * half;
-    const int8_t* sc = reinterpret_cast<const int8_t*>(block + 192) + 8 * half + (l >> 4);
-    const float d = HalfBitsToFloat(
-        *reinterpret_cast<const uint16_t*>(block + 208));
+    const Q6KBlock block = Q6KBlockAt(src + r * row_bytes, blocks, b);
+    const uint8_t* ql = block.ql + 64 * half;
+    const uint8_t* qh = block.qh + 32 * half;
+    const int8_t* sc = block.sc + 8 * half + (l >> 4);
+    const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(block.d));
     const int a = ql[l], c = ql[l + 32], h = qh[l];
     const int q1 = ((a & 0xF) | ((h & 3) << 4)) - 32;
     const int q2 = ((c & 0xF) | (((h >> 2) & 3) << 4)) - 32;
     const int q3 = ((a >> 4) | (((h >> 4) & 3) << 4)) - 32;
     const int q4 = ((c >> 4) | (((h >> 6) & 3) << 4)) - 32;
-    float* out = dst + b * kSuperBlock + 128 * half + l;
+    float* out = dst + rb * kSuperBlock + 128 * half + l;
     out[0] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[0])), static_cast<float>(q1));
     out[32] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[2])), static_cast<float>(q2));
     out[64] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[4])), static_cast<float>(q3));
@@ -118,7 +119,8 @@ int gufo_cuda_dequantize_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix,
   if (m->type == GUFO_CUDA_Q4_K) {
     gufo::DequantQ4K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, blocks);
   } else {
-    gufo::DequantQ6K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, blocks);
+    gufo::DequantQ6K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, rows,
+                                                     static_cast<int>(m->cols / gufo::kSuperBlock), m->row_bytes);
   }
   ctx->launches.fetch_add(1);
   GUFO_CUDA_TRY(cudaGetLastError());

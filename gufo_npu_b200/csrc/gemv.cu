@@ -82,8 +82,8 @@ __device__ __forceinline__ void RowQ6K(const uint8_t* __restrict__ row, int cols
                                        float (&acc)[M]) {
   const int blocks = cols / kSuperBlock;
   for (int b = 0; b < blocks; ++b) {
-    const uint8_t* block = row + b * kQ6KBytes;
-    const float d = HalfBitsToFloat(__ldg(reinterpret_cast<const uint16_t*>(block + 208)));
+    const Q6KBlock block = Q6KBlockAt(row, blocks, b);
+    const float d = HalfBitsToFloat(__ldg(reinterpret_cast<const uint16_t*>(block.d)));
     float part[M];
 #pragma unroll
     for (int t = 0; t < M; ++t) {
@@ -91,9 +91,9 @@ __device__ __forceinline__ void RowQ6K(const uint8_t* __restrict__ row, int cols
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      const uint8_t* ql = block + 64 * half;
-      const uint8_t* qh = block + 128 + 32 * half;
-      const int8_t* sc = reinterpret_cast<const int8_t*>(block + 192) + 8 * half + (lane >> 4);
+      const uint8_t* ql = block.ql + 64 * half;
+      const uint8_t* qh = block.qh + 32 * half;
+      const int8_t* sc = block.sc + 8 * half + (lane >> 4);
       const int a = __ldg(ql + lane), c = __ldg(ql + lane + 32), h = __ldg(qh + lane);
       const float w0 = static_cast<float>(static_cast<int>(__ldg(sc))) *
                        static_cast<float>(((a & 0xF) | ((h & 3) << 4)) - 32);
@@ -181,9 +181,9 @@ void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
 int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
                      int group, float extra, const uint8_t** image);
 
-// Enqueues y = [W_0 x | W_1 x | ...]: Q4_K parts on the tensor-core kernel
-// (x staged once, one launch per part), the rest together on the general
-// kernel; at most kMaxTokens tokens per pass.
+// Enqueues y = [W_0 x | W_1 x | ...]: Q4_K and Q6_K parts on the tensor-core
+// kernels (x staged once per block format, one launch per part), the rest
+// together on the general kernel; at most kMaxTokens tokens per pass.
 int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
   for (int t0 = 0; t0 < tokens; t0 += kMaxTokens) {
     const int m = tokens - t0 < kMaxTokens ? tokens - t0 : kMaxTokens;
@@ -194,20 +194,27 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     rest.total_rows = 0;
     rest.x = x;
     rest.y = y;
-    const bool fast = !ctx->force_general && Q4KFastFits(base.cols, m);
+    const bool fast4 = !ctx->force_general && Q4KFastFits(base.cols, m);
+    const bool fast6 = !ctx->force_general && Q6KFastFits(base.cols, m);
     const uint8_t* image = nullptr;
+    int image_group = 0;   // group size the staged image carries sums for
     for (int p = 0; p < base.nparts; ++p) {
       const GemvPart& part = base.parts[p];
-      if (fast && part.type == GUFO_CUDA_Q4_K) {
-        if (image == nullptr) {
-          const int rc = StageActivations(ctx, x, m, base.cols, 32, 1.0f / 16.0f, &image);
+      const bool q4 = fast4 && part.type == GUFO_CUDA_Q4_K;
+      const bool q6 = fast6 && part.type == GUFO_CUDA_Q6_K;
+      if (q4 || q6) {
+        const int group = q4 ? 32 : 16;
+        if (image_group != group) {
+          // High nibbles of Q4_K reach the MMA as 16 q: fold 1/16 into the factors.
+          const int rc = StageActivations(ctx, x, m, base.cols, group, q4 ? 1.0f / 16.0f : 1.0f, &image);
           if (rc != GUFO_CUDA_OK) {
             return rc;
           }
+          image_group = group;
         }
         const FastGemvArgs args{part.data, part.rows, base.cols, part.row_bytes, image, y,
                                 base.y_stride, part.out_offset, m};
-        const int rc = LaunchGemvQ4KFast(ctx, args);
+        const int rc = q4 ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args);
         if (rc != GUFO_CUDA_OK) {
           return rc;
         }
