@@ -45,6 +45,29 @@ class DeltaNetParams(C.Structure):
                 ("dt_bias", _f32p), ("ssm_norm", _f32p)]
 
 
+class DecoderConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("layers", "hidden", "ffn", "vocab")] + [("rms_eps", C.c_float)] + \
+               [(n, C.c_int) for n in ("full_attention_interval", "heads", "kv_heads", "head_dim", "rope_dim")] + \
+               [("rope_theta", C.c_float)] + \
+               [(n, C.c_int) for n in ("conv_kernel", "linear_key_heads", "linear_value_heads", "linear_head_dim",
+                                       "max_positions", "use_graph")]
+
+
+LAYER_MATRICES = ("attn_qkv", "attn_gate", "ssm_alpha", "ssm_beta", "ssm_out", "attn_q", "attn_k", "attn_v",
+                  "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+LAYER_VECTORS = ("attn_norm", "post_attention_norm", "ssm_conv1d", "ssm_a", "ssm_dt_bias", "ssm_norm",
+                 "attn_q_norm", "attn_k_norm")
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in LAYER_MATRICES] + [(n, _f32p) for n in LAYER_VECTORS]
+
+
+class DecoderWeights(C.Structure):
+    _fields_ = [("token_embd", C.c_int64), ("output", C.c_int64), ("output_norm", _f32p),
+                ("layers", C.POINTER(LayerWeights))]
+
+
 # name -> (restype, argtypes); every symbol include/gufo_cuda.h declares.
 SIGNATURES = {
     "gufo_cuda_ctx_create": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p)]),
@@ -75,6 +98,14 @@ SIGNATURES = {
                                                   C.POINTER(C.c_int64)]),
     "gufo_cuda_deltanet_layer_free": (C.c_int, [C.c_void_p, C.c_int64]),
     "gufo_cuda_deltanet_linear_device": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(LinearSeq), C.c_int]),
+    "gufo_cuda_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderConfig), C.POINTER(DecoderWeights),
+                                           C.POINTER(C.c_void_p)]),
+    "gufo_cuda_decoder_destroy": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_decoder_reset": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_decoder_step": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "gufo_cuda_decoder_logits_device": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "gufo_cuda_decoder_position": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_decoder_linear_state": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

@@ -377,3 +377,99 @@ class CudaMixer:
         if layer not in self.layers:
             raise ValueError(f"deltanet: layer {layer} is not a DeltaNet layer")
         self.ctx.deltanet_linear_device(self.layers[layer], seqs)
+
+
+class CudaDecoder:
+    """qwen35::Decoder with every buffer on the device (dense models).
+
+    `Step(token)` mirrors Decoder::Step (src/models/qwen35/decoder.cpp:478-528): it runs the
+    token at the current position, advances the state and returns the vocab logits. The
+    matrices are the ones `projections` uploaded; the small vectors are copied.
+    """
+
+    # GGUF tensor name of each field of gufo_cuda_layer_weights.
+    _MATRIX_NAMES = {"attn_qkv": "attn_qkv.weight", "attn_gate": "attn_gate.weight",
+                     "ssm_alpha": "ssm_alpha.weight", "ssm_beta": "ssm_beta.weight", "ssm_out": "ssm_out.weight",
+                     "attn_q": "attn_q.weight", "attn_k": "attn_k.weight", "attn_v": "attn_v.weight",
+                     "attn_output": "attn_output.weight", "ffn_gate": "ffn_gate.weight", "ffn_up": "ffn_up.weight",
+                     "ffn_down": "ffn_down.weight"}
+    _VECTOR_NAMES = {"attn_norm": "attn_norm.weight", "post_attention_norm": "post_attention_norm.weight",
+                     "ssm_conv1d": "ssm_conv1d.weight", "ssm_a": "ssm_a", "ssm_dt_bias": "ssm_dt.bias",
+                     "ssm_norm": "ssm_norm.weight", "attn_q_norm": "attn_q_norm.weight",
+                     "attn_k_norm": "attn_k_norm.weight"}
+
+    def __init__(self, projections: CudaProjections, tensors: Dict[str, Tensor], max_positions: int = 4096,
+                 use_graph: bool = True):
+        c = projections.config
+        if c.is_moe:
+            raise RuntimeError("qwen35: the device-resident decoder runs dense models only")
+        self.ctx = projections.ctx
+        self.config = c
+        self.projections = projections
+        lib = self.ctx.lib
+        f32p = C.POINTER(C.c_float)
+        keep = []
+
+        def vec(name):
+            a = np.ascontiguousarray(tensors[name].data.cpu().numpy().view(np.float32))
+            keep.append(a)
+            return a.ctypes.data_as(f32p)
+        layers = (_capi.LayerWeights * c.layers)()
+        for il in range(c.layers):
+            p = f"blk.{il}."
+            for field, name in self._MATRIX_NAMES.items():
+                setattr(layers[il], field, projections._matrices.get(p + name, 0))
+            for field, name in self._VECTOR_NAMES.items():
+                if p + name in tensors:
+                    setattr(layers[il], field, vec(p + name))
+        weights = _capi.DecoderWeights(projections._matrices["token_embd.weight"],
+                                       0 if c.tied_embeddings else projections._matrices["output.weight"],
+                                       vec("output_norm.weight"), layers)
+        config = _capi.DecoderConfig(c.layers, c.hidden, c.ffn, c.vocab, c.rms_eps, c.full_attention_interval,
+                                     c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.rope_theta, c.conv_kernel,
+                                     c.linear_key_heads, c.linear_value_heads, c.linear_head_dim, max_positions,
+                                     int(use_graph))
+        handle = C.c_void_p()
+        _capi.check(lib, self.ctx.handle,
+                    lib.gufo_cuda_decoder_create(self.ctx.handle, C.byref(config), C.byref(weights), C.byref(handle)))
+        self.handle = handle
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.ctx.lib.gufo_cuda_decoder_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def Reset(self) -> None:
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_reset(self.handle))
+
+    def Step(self, token: int, logits: Optional[np.ndarray] = None) -> np.ndarray:
+        """Runs `token`; returns the logits (written into `logits` when given, e.g. pinned memory)."""
+        if logits is None:
+            logits = np.empty(self.config.vocab, dtype=np.float32)
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step(self.handle, token, C.c_void_p(_ptr(logits))))
+        return logits
+
+    def step_device(self, token: int) -> int:
+        """Runs `token` leaving the logits on the device; returns their device address."""
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step(self.handle, token, None))
+        out = C.c_void_p()
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_logits_device(self.handle, C.byref(out)))
+        return int(out.value)
+
+    @property
+    def position(self) -> int:
+        return int(self.ctx.lib.gufo_cuda_decoder_position(self.handle))
+
+    def linear_state(self, layer: int):
+        c = self.config
+        conv = np.empty((c.conv_kernel - 1) * c.conv_channels, dtype=np.float32)
+        ssm = np.empty(c.linear_value_heads * c.linear_head_dim ** 2, dtype=np.float32)
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_linear_state(self.handle, layer, C.c_void_p(conv.ctypes.data),
+                                                                    C.c_void_p(ssm.ctypes.data)))
+        return conv, ssm

@@ -79,6 +79,7 @@ struct DeltaNetLayer {
   float* ssm_norm = nullptr;
 };
 
+struct DeltaNetLayer;
 void SetError(const std::string& text);
 int Fail(int status, const std::string& text);
 int CudaFail(cudaError_t e, const char* what);
@@ -111,6 +112,9 @@ namespace gufo {
 int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 // Whether the image of `tokens` rows of `cols` values fits in shared memory.
 bool Q4KFastFits(int cols, int tokens);
+// One Mixer::Linear step per sequence; the caller holds ctx->mu.
+int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& layer,
+                          const gufo_cuda_linear_seq* seqs, int nseq);
 // The same for Q6_K parts (image with group sums of 16).
 int LaunchGemvQ6KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 bool Q6KFastFits(int cols, int tokens);

@@ -1,0 +1,814 @@
+// The decode step with every buffer resident on the device: the call sequence
+// of qwen35::Decoder::Step (src/models/qwen35/decoder.cpp:478-528 in the
+// reference) over this backend's GEMV and DeltaNet kernels, plus the small
+// kernels between them (embedding row, residual + RMSNorm, SwiGLU, gated
+// attention over the fp16 cache, src/models/qwen35/decoder.cpp:267-412).
+//
+// One token costs one 4-byte upload (the token id) and one download (the
+// logits). The position lives in device memory so that the whole step can be
+// replayed as a CUDA graph: two graphs, because the DeltaNet conv window
+// alternates between two buffers from step to step.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <vector>
+
+#include "gemv.cuh"
+
+namespace gufo {
+namespace {
+
+constexpr int kSmallThreads = 256;
+constexpr int kAttnSplits = 8;      // position slices per KV head
+constexpr int kMaxGroup = 8;        // query heads per KV head
+constexpr int kMaxPerLane = 8;      // head_dim / 32
+
+__device__ __forceinline__ float SigmoidF(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float SiluF(float x) { return x * SigmoidF(x); }
+
+__device__ __forceinline__ float BlockSum256(float v, float* scratch) {
+  v = WarpSum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+    scratch[threadIdx.x >> 5] = v;
+  }
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int w = 0; w < kSmallThreads / 32; ++w) {
+    total += scratch[w];
+  }
+  return total;
+}
+
+// h = dequantized row *token of the embedding matrix (quant::Dequantize of one
+// row, src/models/qwen35/decoder.cpp:486-489). One thread block.
+struct EmbedArgs {
+  const uint8_t* data;
+  int type;
+  int row_bytes;
+  int cols;
+  const int* token;
+  float* h;
+};
+
+__global__ void __launch_bounds__(kSmallThreads)
+EmbedKernel(const __grid_constant__ EmbedArgs a) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const uint8_t* row = a.data + static_cast<size_t>(*a.token) * a.row_bytes;
+  const int blocks = a.cols / kSuperBlock;
+  if (a.type == GUFO_CUDA_Q4_K) {
+    for (int item = threadIdx.x; item < blocks * 32; item += kSmallThreads) {
+      const int b = item >> 5, word = item & 31, p = word >> 3, c = word & 7;
+      const uint32_t* block = reinterpret_cast<const uint32_t*>(row + b * kQ4KBytes);
+      const uint32_t dd = block[0];
+      const float d = HalfBitsToFloat(static_cast<uint16_t>(dd & 0xFFFF));
+      const float dmin = HalfBitsToFloat(static_cast<uint16_t>(dd >> 16));
+      int sc_lo, m_lo, sc_hi, m_hi;
+      ScaleMinK4(2 * p, block[1], block[2], block[3], &sc_lo, &m_lo);
+      ScaleMinK4(2 * p + 1, block[1], block[2], block[3], &sc_hi, &m_hi);
+      const float d1 = __fmul_rn(d, static_cast<float>(sc_lo)), m1 = __fmul_rn(dmin, static_cast<float>(m_lo));
+      const float d2 = __fmul_rn(d, static_cast<float>(sc_hi)), m2 = __fmul_rn(dmin, static_cast<float>(m_hi));
+      const uint32_t q = block[4 + word];
+      float* out = a.h + b * kSuperBlock + 64 * p + 4 * c;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        out[i] = __fsub_rn(__fmul_rn(d1, static_cast<float>((q >> (8 * i)) & 0xF)), m1);
+        out[32 + i] = __fsub_rn(__fmul_rn(d2, static_cast<float>((q >> (8 * i + 4)) & 0xF)), m2);
+      }
+    }
+  } else if (a.type == GUFO_CUDA_Q6_K) {
+    for (int item = threadIdx.x; item < blocks * 64; item += kSmallThreads) {
+      const int b = item >> 6, half = (item >> 5) & 1, l = item & 31;
+      const Q6KBlock block = Q6KBlockAt(row, blocks, b);
+      const uint8_t* ql = block.ql + 64 * half;
+      const uint8_t* qh = block.qh + 32 * half;
+      const int8_t* sc = block.sc + 8 * half + (l >> 4);
+      const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(block.d));
+      const int x = ql[l], c = ql[l + 32], h = qh[l];
+      float* out = a.h + b * kSuperBlock + 128 * half + l;
+      out[0] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[0])), static_cast<float>(((x & 0xF) | ((h & 3) << 4)) - 32));
+      out[32] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[2])), static_cast<float>(((c & 0xF) | (((h >> 2) & 3) << 4)) - 32));
+      out[64] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[4])), static_cast<float>(((x >> 4) | (((h >> 4) & 3) << 4)) - 32));
+      out[96] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[6])), static_cast<float>(((c >> 4) | (((h >> 6) & 3) << 4)) - 32));
+    }
+  } else {
+    for (int i = threadIdx.x; i < a.cols; i += kSmallThreads) {
+      a.h[i] = reinterpret_cast<const float*>(row)[i];
+    }
+  }
+}
+
+// h += delta (when given), then normed = RMS(h) * w (vec::RmsNorm,
+// src/core/vec.hpp:57-63; the residual adds of decoder.cpp:504-506,519-521).
+// `advance`, when given, is incremented at the end: the sequence position.
+__global__ void __launch_bounds__(kSmallThreads)
+AddNormKernel(float* __restrict__ h, const float* __restrict__ delta,
+              const float* __restrict__ w, float eps, int n, float* __restrict__ normed,
+              int* advance) {
+  __shared__ float scratch[kSmallThreads / 32];
+  GridLaunchDependents();
+  GridDependencyWait();
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < n; i += kSmallThreads) {
+    float v = h[i];
+    if (delta != nullptr) {
+      v += delta[i];
+      h[i] = v;
+    }
+    sq = fmaf(v, v, sq);
+  }
+  const float total = BlockSum256(sq, scratch);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + eps);
+  for (int i = threadIdx.x; i < n; i += kSmallThreads) {
+    normed[i] = h[i] * inv * w[i];
+  }
+  if (advance != nullptr && threadIdx.x == 0) {
+    *advance += 1;
+  }
+}
+
+// act[i] = silu(gate[i]) * up[i] over [gate | up] (decoder.cpp:511-514).
+__global__ void __launch_bounds__(kSmallThreads)
+SwiGluKernel(const float* __restrict__ ffn, int f, float* __restrict__ act) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int i = blockIdx.x * kSmallThreads + threadIdx.x;
+  if (i < f) {
+    act[i] = SiluF(ffn[i]) * ffn[f + i];
+  }
+}
+
+struct AttnArgs {
+  int heads, kv_heads, head_dim, rope_dim, max_positions;
+  float rms_eps;
+  const int* position;
+  const float* in;          // [q and gate (2 heads hd, per head q | gate) | k | v]
+  const float* q_norm;
+  const float* k_norm;
+  const float* inv_freq;    // [rope_dim / 2]
+  __half* keys;             // [max_positions][kv_heads * hd]
+  __half* values;
+  float* queries;           // [heads][hd]
+  float* partials;          // [kv_heads][splits][group][hd + 2]
+  float* ctx;               // [heads][hd]
+};
+
+// q/k RMSNorm and RoPE; appends k and v to the cache in fp16
+// (decoder.cpp:280-323). Block h < heads: query head h; then one per KV head.
+__global__ void __launch_bounds__(kSmallThreads)
+AttnPrepKernel(const __grid_constant__ AttnArgs a) {
+  __shared__ float scratch[kSmallThreads / 32];
+  __shared__ float vec[kMaxPerLane * 32];
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int hd = a.head_dim;
+  const int half = a.rope_dim / 2;
+  const int pos = *a.position;
+  const int head = blockIdx.x;
+  const bool is_query = head < a.heads;
+  const int kh = head - a.heads;
+  const float* x = is_query ? a.in + static_cast<size_t>(head) * 2 * hd
+                            : a.in + static_cast<size_t>(a.heads) * 2 * hd + kh * hd;
+  const float* w = is_query ? a.q_norm : a.k_norm;
+  const int e = threadIdx.x;
+  const float v = e < hd ? x[e] : 0.f;
+  const float total = BlockSum256(v * v, scratch);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(hd) + a.rms_eps);
+  if (e < hd) {
+    vec[e] = v * inv * w[e];
+  }
+  __syncthreads();
+  float out = e < hd ? vec[e] : 0.f;
+  if (e < 2 * half) {
+    const int i = e < half ? e : e - half;
+    const double angle = static_cast<double>(pos) * static_cast<double>(a.inv_freq[i]);
+    const float cs = static_cast<float>(cos(angle));
+    const float sn = static_cast<float>(sin(angle));
+    const float lo = vec[i], hi = vec[i + half];
+    out = e < half ? lo * cs - hi * sn : lo * sn + hi * cs;
+  }
+  if (e < hd) {
+    if (is_query) {
+      a.queries[head * hd + e] = out;
+    } else {
+      const size_t at = (static_cast<size_t>(pos) * a.kv_heads + kh) * hd + e;
+      a.keys[at] = __float2half_rn(out);
+      const float val = a.in[static_cast<size_t>(a.heads) * 2 * hd + a.kv_heads * hd + kh * hd + e];
+      a.values[at] = __float2half_rn(val);
+    }
+  }
+}
+
+// One slice of the cached positions for one KV head and the query heads that
+// share it: partial softmax (weighted values, max, sum) per query head
+// (the split-K jobs of decoder.cpp:326-381). grid = (splits, kv_heads).
+__global__ void __launch_bounds__(kSmallThreads)
+AttnSliceKernel(const __grid_constant__ AttnArgs a) {
+  __shared__ float q_sh[kMaxGroup][kMaxPerLane * 32];
+  __shared__ float merge_m[kSmallThreads / 32][kMaxGroup];
+  __shared__ float merge_l[kSmallThreads / 32][kMaxGroup];
+  __shared__ float merge_acc[kSmallThreads / 32][kMaxPerLane * 32];
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int hd = a.head_dim;
+  const int per = hd / 32;
+  const int group = a.heads / a.kv_heads;
+  const int kh = blockIdx.y;
+  const int length = *a.position + 1;
+  const int slice = (length + kAttnSplits - 1) / kAttnSplits;
+  const int begin = blockIdx.x * slice;
+  const int end = min(length, begin + slice);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float scale = 1.0f / sqrtf(static_cast<float>(hd));
+  for (int i = threadIdx.x; i < group * hd; i += kSmallThreads) {
+    q_sh[i / hd][i % hd] = a.queries[(kh * group) * hd + i];
+  }
+  __syncthreads();
+  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][kMaxPerLane];
+#pragma unroll
+  for (int g = 0; g < kMaxGroup; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      acc[g][i] = 0.f;
+    }
+  }
+  const int kv = a.kv_heads * hd;
+  for (int j = begin + warp; j < end; j += kSmallThreads / 32) {
+    const __half* key = a.keys + static_cast<size_t>(j) * kv + kh * hd + lane * per;
+    const __half* val = a.values + static_cast<size_t>(j) * kv + kh * hd + lane * per;
+    float kf[kMaxPerLane], vf[kMaxPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      kf[i] = i < per ? __half2float(key[i]) : 0.f;
+      vf[i] = i < per ? __half2float(val[i]) : 0.f;
+    }
+#pragma unroll
+    for (int g = 0; g < kMaxGroup; ++g) {
+      if (g < group) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) {
+          if (i < per) {
+            dot = fmaf(q_sh[g][lane * per + i], kf[i], dot);
+          }
+        }
+        const float s = WarpSum(dot) * scale;
+        const float m_new = fmaxf(m[g], s);
+        const float keep = expf(m[g] - m_new);   // 0 on the first position
+        const float p = expf(s - m_new);
+        l[g] = l[g] * keep + p;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) {
+          acc[g][i] = acc[g][i] * keep + p * vf[i];
+        }
+        m[g] = m_new;
+      }
+    }
+  }
+  // Merge the warps, one query head at a time.
+  for (int g = 0; g < group; ++g) {
+    float mg = -INFINITY, lg = 0.f, ag[kMaxPerLane];
+#pragma unroll
+    for (int gg = 0; gg < kMaxGroup; ++gg) {
+      if (gg == g) {
+        mg = m[gg];
+        lg = l[gg];
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) {
+          ag[i] = acc[gg][i];
+        }
+      }
+    }
+    __syncthreads();
+    if (lane == 0) {
+      merge_m[warp][0] = mg;
+    }
+    __syncthreads();
+    float top = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kSmallThreads / 32; ++w) {
+      top = fmaxf(top, merge_m[w][0]);
+    }
+    const float wgt = mg == -INFINITY ? 0.f : expf(mg - top);
+    if (lane == 0) {
+      merge_l[warp][0] = lg * wgt;
+    }
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+      if (i < per) {
+        merge_acc[warp][lane * per + i] = ag[i] * wgt;
+      }
+    }
+    __syncthreads();
+    float* out = a.partials + ((static_cast<size_t>(kh) * kAttnSplits + blockIdx.x) * group + g) * (hd + 2);
+    for (int e = threadIdx.x; e < hd; e += kSmallThreads) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSmallThreads / 32; ++w) {
+        total += merge_acc[w][e];
+      }
+      out[e] = total;
+    }
+    if (threadIdx.x == 0) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kSmallThreads / 32; ++w) {
+        total += merge_l[w][0];
+      }
+      out[hd] = top;
+      out[hd + 1] = total;
+    }
+  }
+}
+
+// Merges the slices per query head and applies the output gate
+// (decoder.cpp:383-411). grid = heads.
+__global__ void __launch_bounds__(kSmallThreads)
+AttnMergeKernel(const __grid_constant__ AttnArgs a) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int hd = a.head_dim;
+  const int group = a.heads / a.kv_heads;
+  const int qh = blockIdx.x;
+  const int kh = qh / group, g = qh % group;
+  auto slice = [&](int s) {
+    return a.partials + ((static_cast<size_t>(kh) * kAttnSplits + s) * group + g) * (hd + 2);
+  };
+  float top = -INFINITY;
+  for (int s = 0; s < kAttnSplits; ++s) {
+    top = fmaxf(top, slice(s)[hd]);
+  }
+  float total = 0.f;
+  float wgt[kAttnSplits];
+  for (int s = 0; s < kAttnSplits; ++s) {
+    const float ms = slice(s)[hd];
+    wgt[s] = ms == -INFINITY ? 0.f : expf(ms - top);
+    total += wgt[s] * slice(s)[hd + 1];
+  }
+  const float inv_total = 1.0f / total;
+  const float* gate = a.in + static_cast<size_t>(qh) * 2 * hd + hd;
+  for (int e = threadIdx.x; e < hd; e += kSmallThreads) {
+    float out = 0.f;
+    for (int s = 0; s < kAttnSplits; ++s) {
+      out += wgt[s] * slice(s)[e];
+    }
+    a.ctx[qh * hd + e] = out * (inv_total * SigmoidF(gate[e]));
+  }
+}
+
+template <typename T>
+int Upload(gufo_cuda_ctx* ctx, const T* host, size_t n, T** dev) {
+  GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(dev), n * sizeof(T)));
+  GUFO_CUDA_TRY(cudaMemcpyAsync(*dev, host, n * sizeof(T), cudaMemcpyHostToDevice, ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace gufo
+
+struct gufo_cuda_decoder {
+  gufo_cuda_ctx* ctx = nullptr;
+  gufo_cuda_decoder_config c{};
+  struct Layer {
+    bool attention = false;
+    gufo::GemvArgs in, out, ffn_in, ffn_down;
+    gufo::DeltaNetLayer linear;        // small weights (device), DeltaNet layers
+    float* attn_norm = nullptr;
+    float* post_norm = nullptr;
+    float* q_norm = nullptr;
+    float* k_norm = nullptr;
+    float* conv[2] = {nullptr, nullptr};
+    float* ssm = nullptr;
+    __half* keys = nullptr;
+    __half* values = nullptr;
+  };
+  std::vector<Layer> layers;
+  gufo::GemvArgs lm_head;
+  gufo::Matrix embed;
+  float* output_norm = nullptr;
+  float* inv_freq = nullptr;
+  // Activations.
+  float *h = nullptr, *normed = nullptr, *in = nullptr, *mixed = nullptr, *out = nullptr;
+  float *ffn = nullptr, *act = nullptr, *logits = nullptr, *queries = nullptr, *partials = nullptr;
+  int* position_dev = nullptr;
+  int* token_dev = nullptr;
+  int* token_pinned = nullptr;
+  int position = 0;
+  int steps = 0;
+  int64_t kernels_per_step = 0;
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  std::vector<void*> owned;   // every device allocation, for destroy
+
+  int in_width(const Layer& l) const { return l.in.total_rows; }
+};
+
+namespace gufo {
+namespace {
+
+int Alloc(gufo_cuda_decoder* d, size_t bytes, void** out) {
+  GUFO_CUDA_TRY(cudaMalloc(out, bytes));
+  d->owned.push_back(*out);
+  return GUFO_CUDA_OK;
+}
+
+int UploadVec(gufo_cuda_decoder* d, const float* host, size_t n, float** dev, const char* name) {
+  if (host == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string("decoder_create: missing vector ") + name);
+  }
+  int rc = Alloc(d, n * 4, reinterpret_cast<void**>(dev));
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  GUFO_CUDA_TRY(cudaMemcpyAsync(*dev, host, n * 4, cudaMemcpyHostToDevice, d->ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+// Stacks whole matrices into one product and checks their shape, as
+// GgufProjections' CheckShape does (gguf_projections.cpp:27-46).
+int Stack(gufo_cuda_ctx* ctx, const gufo_cuda_matrix* handles, const int64_t* want_rows, int n,
+          int64_t want_cols, const char* what, GemvArgs* args) {
+  gufo_cuda_rows parts[kMaxParts];
+  for (int i = 0; i < n; ++i) {
+    const Matrix* m = ctx->FindMatrix(handles[i]);
+    if (m == nullptr) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string("decoder_create: no matrix for ") + what);
+    }
+    if (m->rows != want_rows[i] || m->cols != want_cols) {
+      return Fail(GUFO_CUDA_SHAPE, std::string("decoder_create: ") + what + " has shape [" +
+                                       std::to_string(m->cols) + ", " + std::to_string(m->rows) +
+                                       "], expected [" + std::to_string(want_cols) + ", " +
+                                       std::to_string(want_rows[i]) + "]");
+    }
+    parts[i] = {handles[i], 0, m->rows};
+  }
+  return BuildGemvArgs(ctx, parts, n, args);
+}
+
+int Product(gufo_cuda_ctx* ctx, GemvArgs args, const float* x, float* y) {
+  args.x = x;
+  args.y = y;
+  return LaunchGemv(ctx, args, 1);
+}
+
+#define GUFO_STEP_TRY(expr)           \
+  do {                                \
+    const int gufo_rc_ = (expr);      \
+    if (gufo_rc_ != GUFO_CUDA_OK) {   \
+      return gufo_rc_;                \
+    }                                 \
+  } while (0)
+
+// Enqueues one step's kernels; `parity` picks the conv window that is current.
+int EnqueueStep(gufo_cuda_decoder* d, int parity) {
+  gufo_cuda_ctx* ctx = d->ctx;
+  const gufo_cuda_decoder_config& c = d->c;
+  cudaStream_t st = ctx->stream;
+  const dim3 one(1), block(kSmallThreads);
+  EmbedArgs embed{d->embed.data, d->embed.type, static_cast<int>(d->embed.row_bytes), c.hidden,
+                  d->token_dev, d->h};
+  GUFO_CUDA_TRY(LaunchOverlapped(EmbedKernel, one, block, 0, st, 1, embed));
+  ctx->launches.fetch_add(1);
+  const float* pending = nullptr;   // projection output not yet added to h
+  for (int il = 0; il < c.layers; ++il) {
+    auto& l = d->layers[il];
+    GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, pending, (const float*)l.attn_norm,
+                                   c.rms_eps, c.hidden, d->normed, (int*)nullptr));
+    ctx->launches.fetch_add(1);
+    GUFO_STEP_TRY(Product(ctx, l.in, d->normed, d->in));
+    if (l.attention) {
+      AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps,
+                 d->position_dev, d->in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values,
+                 d->queries, d->partials, d->mixed};
+      GUFO_CUDA_TRY(LaunchOverlapped(AttnPrepKernel, dim3(c.heads + c.kv_heads), block, 0, st, 1, a));
+      GUFO_CUDA_TRY(LaunchOverlapped(AttnSliceKernel, dim3(kAttnSplits, c.kv_heads), block, 0, st, 1, a));
+      GUFO_CUDA_TRY(LaunchOverlapped(AttnMergeKernel, dim3(c.heads), block, 0, st, 1, a));
+      ctx->launches.fetch_add(3);
+    } else {
+      gufo_cuda_linear_seq seq{d->in, l.conv[parity], l.conv[parity ^ 1], l.ssm, nullptr, d->mixed};
+      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1));
+    }
+    GUFO_STEP_TRY(Product(ctx, l.out, d->mixed, d->out));
+    GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, (const float*)d->out,
+                                   (const float*)l.post_norm, c.rms_eps, c.hidden, d->normed, (int*)nullptr));
+    ctx->launches.fetch_add(1);
+    GUFO_STEP_TRY(Product(ctx, l.ffn_in, d->normed, d->ffn));
+    GUFO_CUDA_TRY(LaunchOverlapped(SwiGluKernel, dim3((c.ffn + kSmallThreads - 1) / kSmallThreads), block, 0, st,
+                                   1, (const float*)d->ffn, c.ffn, d->act));
+    ctx->launches.fetch_add(1);
+    GUFO_STEP_TRY(Product(ctx, l.ffn_down, d->act, d->out));
+    pending = d->out;
+  }
+  GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, pending, (const float*)d->output_norm,
+                                 c.rms_eps, c.hidden, d->normed, d->position_dev));
+  ctx->launches.fetch_add(1);
+  GUFO_STEP_TRY(Product(ctx, d->lm_head, d->normed, d->logits));
+  return GUFO_CUDA_OK;
+}
+
+}  // namespace
+}  // namespace gufo
+
+using gufo::Fail;
+
+extern "C" {
+
+int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config* config,
+                             const gufo_cuda_decoder_weights* weights, gufo_cuda_decoder** out) {
+  if (ctx == nullptr || config == nullptr || weights == nullptr || out == nullptr ||
+      weights->layers == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_create: null pointer");
+  }
+  *out = nullptr;
+  const gufo_cuda_decoder_config& c = *config;
+  if (c.layers <= 0 || c.hidden <= 0 || c.ffn <= 0 || c.vocab <= 0 || c.full_attention_interval <= 0 ||
+      c.kv_heads <= 0 || c.heads % c.kv_heads != 0 || c.heads / c.kv_heads > gufo::kMaxGroup ||
+      c.head_dim % 32 != 0 || c.head_dim > 32 * gufo::kMaxPerLane || c.rope_dim > c.head_dim ||
+      c.rope_dim % 2 != 0 || c.max_positions <= 0 || c.hidden % 256 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "decoder_create: unsupported or inconsistent shape");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  auto* d = new gufo_cuda_decoder();
+  d->ctx = ctx;
+  d->c = c;
+  auto fail = [&](int rc) {
+    gufo_cuda_decoder_destroy(d);
+    return rc;
+  };
+  const int64_t key_dim = static_cast<int64_t>(c.linear_key_heads) * c.linear_head_dim;
+  const int64_t value_dim = static_cast<int64_t>(c.linear_value_heads) * c.linear_head_dim;
+  const int64_t channels = 2 * key_dim + value_dim;
+  const int64_t attn_dim = static_cast<int64_t>(c.heads) * c.head_dim;
+  const int64_t kv_dim = static_cast<int64_t>(c.kv_heads) * c.head_dim;
+  int rc;
+  const gufo::Matrix* embed = ctx->FindMatrix(weights->token_embd);
+  if (embed == nullptr || embed->cols != c.hidden || embed->rows != c.vocab) {
+    return fail(Fail(GUFO_CUDA_SHAPE, "decoder_create: token_embd must be [hidden, vocab]"));
+  }
+  d->embed = *embed;
+  {
+    const gufo_cuda_matrix head = weights->output != 0 ? weights->output : weights->token_embd;
+    const int64_t rows = c.vocab;
+    if ((rc = gufo::Stack(ctx, &head, &rows, 1, c.hidden, "the LM head", &d->lm_head)) != GUFO_CUDA_OK) {
+      return fail(rc);
+    }
+  }
+  if ((rc = gufo::UploadVec(d, weights->output_norm, c.hidden, &d->output_norm, "output_norm")) != GUFO_CUDA_OK) {
+    return fail(rc);
+  }
+  size_t in_max = 0;
+  d->layers.resize(c.layers);
+  for (int il = 0; il < c.layers; ++il) {
+    const gufo_cuda_layer_weights& w = weights->layers[il];
+    auto& l = d->layers[il];
+    l.attention = (il + 1) % c.full_attention_interval == 0;
+    if ((rc = gufo::UploadVec(d, w.attn_norm, c.hidden, &l.attn_norm, "attn_norm")) != GUFO_CUDA_OK ||
+        (rc = gufo::UploadVec(d, w.post_attention_norm, c.hidden, &l.post_norm, "post_attention_norm")) !=
+            GUFO_CUDA_OK) {
+      return fail(rc);
+    }
+    if (l.attention) {
+      const gufo_cuda_matrix in[3] = {w.attn_q, w.attn_k, w.attn_v};
+      const int64_t rows[3] = {2 * attn_dim, kv_dim, kv_dim};
+      if ((rc = gufo::Stack(ctx, in, rows, 3, c.hidden, "attn_q/k/v", &l.in)) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+      const int64_t out_rows = c.hidden;
+      if ((rc = gufo::Stack(ctx, &w.attn_output, &out_rows, 1, attn_dim, "attn_output", &l.out)) != GUFO_CUDA_OK ||
+          (rc = gufo::UploadVec(d, w.attn_q_norm, c.head_dim, &l.q_norm, "attn_q_norm")) != GUFO_CUDA_OK ||
+          (rc = gufo::UploadVec(d, w.attn_k_norm, c.head_dim, &l.k_norm, "attn_k_norm")) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+      const size_t cache = static_cast<size_t>(c.max_positions) * kv_dim * sizeof(__half);
+      if ((rc = gufo::Alloc(d, cache, reinterpret_cast<void**>(&l.keys))) != GUFO_CUDA_OK ||
+          (rc = gufo::Alloc(d, cache, reinterpret_cast<void**>(&l.values))) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+    } else {
+      if (c.linear_head_dim % 32 != 0 || c.linear_head_dim > 128 || c.linear_key_heads <= 0 ||
+          c.linear_value_heads % c.linear_key_heads != 0 || c.conv_kernel < 2 || c.conv_kernel > 8) {
+        return fail(Fail(GUFO_CUDA_SHAPE, "decoder_create: unsupported DeltaNet shape"));
+      }
+      const gufo_cuda_matrix in[4] = {w.attn_qkv, w.attn_gate, w.ssm_alpha, w.ssm_beta};
+      const int64_t rows[4] = {channels, value_dim, c.linear_value_heads, c.linear_value_heads};
+      if ((rc = gufo::Stack(ctx, in, rows, 4, c.hidden, "attn_qkv/gate/ssm_alpha/ssm_beta", &l.in)) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+      const int64_t out_rows = c.hidden;
+      if ((rc = gufo::Stack(ctx, &w.ssm_out, &out_rows, 1, value_dim, "ssm_out", &l.out)) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+      l.linear.key_heads = c.linear_key_heads;
+      l.linear.value_heads = c.linear_value_heads;
+      l.linear.head_dim = c.linear_head_dim;
+      l.linear.conv_kernel = c.conv_kernel;
+      l.linear.rms_eps = c.rms_eps;
+      if ((rc = gufo::UploadVec(d, w.ssm_conv1d, channels * c.conv_kernel, &l.linear.conv, "ssm_conv1d")) != GUFO_CUDA_OK ||
+          (rc = gufo::UploadVec(d, w.ssm_a, c.linear_value_heads, &l.linear.ssm_a, "ssm_a")) != GUFO_CUDA_OK ||
+          (rc = gufo::UploadVec(d, w.ssm_dt_bias, c.linear_value_heads, &l.linear.dt_bias, "ssm_dt.bias")) != GUFO_CUDA_OK ||
+          (rc = gufo::UploadVec(d, w.ssm_norm, c.linear_head_dim, &l.linear.ssm_norm, "ssm_norm")) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
+      const size_t ssm_bytes = static_cast<size_t>(value_dim) * c.linear_head_dim * 4;
+      if ((rc = gufo::Alloc(d, conv_bytes, reinterpret_cast<void**>(&l.conv[0]))) != GUFO_CUDA_OK ||
+          (rc = gufo::Alloc(d, conv_bytes, reinterpret_cast<void**>(&l.conv[1]))) != GUFO_CUDA_OK ||
+          (rc = gufo::Alloc(d, ssm_bytes, reinterpret_cast<void**>(&l.ssm))) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+    }
+    const gufo_cuda_matrix gate_up[2] = {w.ffn_gate, w.ffn_up};
+    const int64_t ffn_rows[2] = {c.ffn, c.ffn};
+    const int64_t down_rows = c.hidden;
+    if ((rc = gufo::Stack(ctx, gate_up, ffn_rows, 2, c.hidden, "ffn_gate/up", &l.ffn_in)) != GUFO_CUDA_OK ||
+        (rc = gufo::Stack(ctx, &w.ffn_down, &down_rows, 1, c.ffn, "ffn_down", &l.ffn_down)) != GUFO_CUDA_OK) {
+      return fail(rc);
+    }
+    in_max = std::max(in_max, static_cast<size_t>(l.in.total_rows));
+  }
+  std::vector<float> inv_freq(c.rope_dim / 2 > 0 ? c.rope_dim / 2 : 1);
+  for (int i = 0; i < c.rope_dim / 2; ++i) {
+    // The reference's table (decoder.cpp:85-90).
+    inv_freq[i] = static_cast<float>(
+        1.0 / std::pow(static_cast<double>(c.rope_theta), 2.0 * i / static_cast<double>(c.rope_dim)));
+  }
+  if ((rc = gufo::UploadVec(d, inv_freq.data(), inv_freq.size(), &d->inv_freq, "rope")) != GUFO_CUDA_OK) {
+    return fail(rc);
+  }
+  const size_t mixed = static_cast<size_t>(std::max<int64_t>(value_dim, attn_dim));
+  const int group = c.heads / c.kv_heads;
+  struct Buf {
+    float** p;
+    size_t n;
+  } bufs[] = {{&d->h, static_cast<size_t>(c.hidden)}, {&d->normed, static_cast<size_t>(c.hidden)},
+              {&d->in, in_max}, {&d->mixed, mixed}, {&d->out, static_cast<size_t>(c.hidden)},
+              {&d->ffn, static_cast<size_t>(2) * c.ffn}, {&d->act, static_cast<size_t>(c.ffn)},
+              {&d->logits, static_cast<size_t>(c.vocab)}, {&d->queries, static_cast<size_t>(attn_dim)},
+              {&d->partials, static_cast<size_t>(c.kv_heads) * gufo::kAttnSplits * group * (c.head_dim + 2)}};
+  for (auto& b : bufs) {
+    if ((rc = gufo::Alloc(d, b.n * 4, reinterpret_cast<void**>(b.p))) != GUFO_CUDA_OK) {
+      return fail(rc);
+    }
+  }
+  if ((rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->position_dev))) != GUFO_CUDA_OK ||
+      (rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->token_dev))) != GUFO_CUDA_OK) {
+    return fail(rc);
+  }
+  cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&d->token_pinned), 4);
+  if (e != cudaSuccess) {
+    return fail(gufo::CudaFail(e, "cudaMallocHost"));
+  }
+  *out = d;
+  // Zero states (the lock is already held: reset's body inline).
+  for (auto& l : d->layers) {
+    if (!l.attention) {
+      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
+      cudaMemsetAsync(l.conv[0], 0, conv_bytes, ctx->stream);
+      cudaMemsetAsync(l.conv[1], 0, conv_bytes, ctx->stream);
+      cudaMemsetAsync(l.ssm, 0, static_cast<size_t>(value_dim) * c.linear_head_dim * 4, ctx->stream);
+    }
+  }
+  cudaMemsetAsync(d->position_dev, 0, 4, ctx->stream);
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_destroy(gufo_cuda_decoder* d) {
+  if (d == nullptr) {
+    return GUFO_CUDA_OK;
+  }
+  cudaSetDevice(d->ctx->device);
+  cudaStreamSynchronize(d->ctx->stream);
+  for (auto& g : d->graph) {
+    if (g != nullptr) {
+      cudaGraphExecDestroy(g);
+    }
+  }
+  for (void* p : d->owned) {
+    cudaFree(p);
+  }
+  if (d->token_pinned != nullptr) {
+    cudaFreeHost(d->token_pinned);
+  }
+  delete d;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_reset(gufo_cuda_decoder* d) {
+  if (d == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_reset: null decoder");
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  const gufo_cuda_decoder_config& c = d->c;
+  const size_t channels = static_cast<size_t>(2 * c.linear_key_heads + c.linear_value_heads) * c.linear_head_dim;
+  for (auto& l : d->layers) {
+    if (!l.attention) {
+      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
+      GUFO_CUDA_TRY(cudaMemsetAsync(l.conv[0], 0, conv_bytes, ctx->stream));
+      GUFO_CUDA_TRY(cudaMemsetAsync(l.conv[1], 0, conv_bytes, ctx->stream));
+      GUFO_CUDA_TRY(cudaMemsetAsync(l.ssm, 0, static_cast<size_t>(c.linear_value_heads) * c.linear_head_dim *
+                                                  c.linear_head_dim * 4, ctx->stream));
+    }
+  }
+  GUFO_CUDA_TRY(cudaMemsetAsync(d->position_dev, 0, 4, ctx->stream));
+  d->position = 0;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) {
+  if (d == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: null decoder");
+  }
+  if (token < 0 || token >= d->c.vocab) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "qwen35: token id out of range");
+  }
+  if (d->position >= d->c.max_positions) {
+    return Fail(GUFO_CUDA_TOO_LARGE, "decoder_step: the attention cache is full");
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  *d->token_pinned = token;
+  GUFO_CUDA_TRY(cudaMemcpyAsync(d->token_dev, d->token_pinned, 4, cudaMemcpyHostToDevice, ctx->stream));
+  const int parity = d->position & 1;
+  // The first steps run eagerly (they size the staging buffer and set kernel
+  // attributes); later ones replay a captured graph per parity.
+  if (d->c.use_graph && d->steps >= 2) {
+    if (d->graph[parity] == nullptr) {
+      cudaGraph_t graph = nullptr;
+      GUFO_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+      const int64_t before = ctx->launches.load();
+      const int rc = gufo::EnqueueStep(d, parity);
+      d->kernels_per_step = ctx->launches.load() - before;
+      ctx->launches.store(before);   // counted at every replay instead
+      const cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+      if (rc != GUFO_CUDA_OK || e != cudaSuccess) {
+        if (graph != nullptr) {
+          cudaGraphDestroy(graph);
+        }
+        return rc != GUFO_CUDA_OK ? rc : gufo::CudaFail(e, "cudaStreamEndCapture");
+      }
+      const cudaError_t ei = cudaGraphInstantiate(&d->graph[parity], graph, 0);
+      cudaGraphDestroy(graph);
+      if (ei != cudaSuccess) {
+        d->graph[parity] = nullptr;
+        return gufo::CudaFail(ei, "cudaGraphInstantiate");
+      }
+    }
+    GUFO_CUDA_TRY(cudaGraphLaunch(d->graph[parity], ctx->stream));
+    ctx->launches.fetch_add(d->kernels_per_step);
+  } else {
+    const int rc = gufo::EnqueueStep(d, parity);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+  }
+  ++d->position;
+  ++d->steps;
+  if (host_logits != nullptr) {
+    GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(d->c.vocab) * 4,
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  }
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_logits_device(gufo_cuda_decoder* d, const float** device_logits) {
+  if (d == nullptr || device_logits == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_logits_device: null pointer");
+  }
+  *device_logits = d->logits;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_position(const gufo_cuda_decoder* d) { return d == nullptr ? -1 : d->position; }
+
+int gufo_cuda_decoder_linear_state(gufo_cuda_decoder* d, int layer, float* host_conv, float* host_ssm) {
+  if (d == nullptr || layer < 0 || layer >= static_cast<int>(d->layers.size()) || d->layers[layer].attention) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_linear_state: not a DeltaNet layer");
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const gufo_cuda_decoder_config& c = d->c;
+  const auto& l = d->layers[layer];
+  const size_t channels = static_cast<size_t>(2 * c.linear_key_heads + c.linear_value_heads) * c.linear_head_dim;
+  if (host_conv != nullptr) {
+    GUFO_CUDA_TRY(cudaMemcpyAsync(host_conv, l.conv[d->position & 1], (c.conv_kernel - 1) * channels * 4,
+                                  cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  if (host_ssm != nullptr) {
+    GUFO_CUDA_TRY(cudaMemcpyAsync(host_ssm, l.ssm, static_cast<size_t>(c.linear_value_heads) * c.linear_head_dim *
+                                                       c.linear_head_dim * 4, cudaMemcpyDeviceToHost, ctx->stream));
+  }
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return GUFO_CUDA_OK;
+}
+
+}  // extern "C"

@@ -486,8 +486,16 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
   if (it == ctx->deltanet_layers.end()) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_linear: unknown layer handle");
   }
-  const gufo::DeltaNetLayer& l = it->second;
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  return gufo::EnqueueDeltaNetLinear(ctx, it->second, seqs, nseq);
+}
+
+}  // extern "C"
+
+namespace gufo {
+
+int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
+                          const gufo_cuda_linear_seq* seqs, int nseq) {
   for (int s0 = 0; s0 < nseq; s0 += gufo::kMaxSeqs) {
     const int n = nseq - s0 < gufo::kMaxSeqs ? nseq - s0 : gufo::kMaxSeqs;
     gufo::LinearArgs args{};
@@ -511,4 +519,4 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
   return GUFO_CUDA_OK;
 }
 
-}  // extern "C"
+}  // namespace gufo

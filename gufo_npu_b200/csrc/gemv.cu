@@ -11,30 +11,9 @@
 //   Q6_K:  d * sum_g sc_g * ((q - 32) . x)_g
 // fp32 accumulation throughout; lanes are combined with warp shuffles.
 // HBM-bound: algorithmic bytes are the GGUF row bytes plus x and y.
-#include "common.cuh"
+#include "gemv.cuh"
 
 namespace gufo {
-
-constexpr int kMaxParts = 8;
-constexpr int kMaxTokens = 8;
-
-struct GemvPart {
-  const uint8_t* data;  // first row of the range
-  int rows;
-  int out_offset;       // column of y where this part starts
-  int type;
-  int row_bytes;
-};
-
-struct GemvArgs {
-  GemvPart parts[kMaxParts];
-  int nparts;
-  int total_rows;   // sum of these parts' rows
-  int y_stride;     // width of a y row
-  int cols;
-  const float* x;   // [tokens][cols]
-  float* y;         // [tokens][total_rows]
-};
 
 namespace {
 
@@ -178,9 +157,6 @@ void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
 
 }  // namespace
 
-int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
-                     int group, float extra, const uint8_t** image);
-
 // Enqueues y = [W_0 x | W_1 x | ...]: Q4_K and Q6_K parts on the tensor-core
 // kernels (x staged once per block format, one launch per part), the rest
 // together on the general kernel; at most kMaxTokens tokens per pass.
@@ -246,11 +222,11 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
 
 using gufo::Fail;
 
-namespace {
+namespace gufo {
 
 // Validates `parts` and fills the launch arguments; ctx->mu is held.
-int BuildArgs(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
-              gufo::GemvArgs* args) {
+int BuildGemvArgs(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
+                  GemvArgs* args) {
   if (nparts < 1 || nparts > gufo::kMaxParts) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul: 1 to 8 parts per product");
   }
@@ -288,7 +264,7 @@ int BuildArgs(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
   return GUFO_CUDA_OK;
 }
 
-}  // namespace
+}  // namespace gufo
 
 extern "C" {
 
@@ -306,7 +282,7 @@ int gufo_cuda_matmul_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
   }
   std::lock_guard<std::mutex> lock(ctx->mu);
   gufo::GemvArgs args{};
-  int rc = BuildArgs(ctx, parts, nparts, &args);
+  int rc = gufo::BuildGemvArgs(ctx, parts, nparts, &args);
   if (rc != GUFO_CUDA_OK || tokens == 0) {
     return rc;
   }
@@ -326,7 +302,7 @@ int gufo_cuda_matmul(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts
   }
   std::lock_guard<std::mutex> lock(ctx->mu);
   gufo::GemvArgs args{};
-  int rc = BuildArgs(ctx, parts, nparts, &args);
+  int rc = gufo::BuildGemvArgs(ctx, parts, nparts, &args);
   if (rc != GUFO_CUDA_OK || tokens == 0) {
     return rc;
   }

@@ -218,6 +218,88 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
                                      const gufo_cuda_linear_seq* seqs,
                                      int nseq);
 
+/* ---- device-resident decode step ---------------------------------------- */
+
+/* Shape of a dense Qwen3.5-family model: the fields of qwen35::Config
+ * (src/models/qwen35/config.hpp:13-62) the decode step reads, plus the capacity
+ * of the attention cache. */
+typedef struct gufo_cuda_decoder_config {
+  int layers;
+  int hidden;
+  int ffn;
+  int vocab;
+  float rms_eps;
+  int full_attention_interval;
+  int heads;
+  int kv_heads;
+  int head_dim;
+  int rope_dim;
+  float rope_theta;
+  int conv_kernel;
+  int linear_key_heads;
+  int linear_value_heads;
+  int linear_head_dim;
+  int max_positions; /* attention cache rows per layer */
+  int use_graph;     /* replay the step as a CUDA graph after the first steps */
+} gufo_cuda_decoder_config;
+
+/* One layer's weights: matrix handles of this context (0 where the layer kind
+ * has none) and host fp32 vectors, copied. Names are the GGUF tensor names the
+ * reference loads (src/models/qwen35/gguf_projections.cpp:100-175,
+ * decoder.cpp:67-98,441-455). */
+typedef struct gufo_cuda_layer_weights {
+  gufo_cuda_matrix attn_qkv, attn_gate, ssm_alpha, ssm_beta, ssm_out; /* DeltaNet */
+  gufo_cuda_matrix attn_q, attn_k, attn_v, attn_output;               /* attention */
+  gufo_cuda_matrix ffn_gate, ffn_up, ffn_down;
+  const float* attn_norm;           /* [hidden] */
+  const float* post_attention_norm; /* [hidden] */
+  const float* ssm_conv1d;          /* [channels][conv_kernel] */
+  const float* ssm_a;               /* [value heads] */
+  const float* ssm_dt_bias;         /* [value heads] */
+  const float* ssm_norm;            /* [head dim] */
+  const float* attn_q_norm;         /* [head_dim] */
+  const float* attn_k_norm;         /* [head_dim] */
+} gufo_cuda_layer_weights;
+
+typedef struct gufo_cuda_decoder_weights {
+  gufo_cuda_matrix token_embd;
+  gufo_cuda_matrix output;      /* 0 when the LM head is token_embd */
+  const float* output_norm;     /* [hidden] */
+  const gufo_cuda_layer_weights* layers; /* [config.layers] */
+} gufo_cuda_decoder_weights;
+
+typedef struct gufo_cuda_decoder gufo_cuda_decoder;
+
+/* qwen35::Decoder (src/models/qwen35/decoder.hpp:105-132) with every buffer on
+ * the device: the residual stream, the DeltaNet states and conv windows, the
+ * fp16 attention cache and the logits stay in HBM between steps, as the
+ * reference's NPU decoders keep the residual stream on their device
+ * (src/models/qwen35_2b/npu_decoder.hpp:18-21). Dense models only. The
+ * matrices must outlive the decoder. Holds one sequence (DecodeState). */
+int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx,
+                             const gufo_cuda_decoder_config* config,
+                             const gufo_cuda_decoder_weights* weights,
+                             gufo_cuda_decoder** out);
+int gufo_cuda_decoder_destroy(gufo_cuda_decoder* decoder);
+/* A fresh sequence: Mixer::NewState (src/models/qwen35/decoder.cpp:144-159). */
+int gufo_cuda_decoder_reset(gufo_cuda_decoder* decoder);
+/* Decoder::Step (src/models/qwen35/decoder.cpp:478-528): runs `token` at the
+ * current position, advances the state, and copies the vocab logits to
+ * host_logits (may be NULL to leave them on the device). Returns
+ * GUFO_CUDA_BAD_ARGUMENT for a token outside [0, vocab) and GUFO_CUDA_TOO_LARGE
+ * when the attention cache is full. */
+int gufo_cuda_decoder_step(gufo_cuda_decoder* decoder, int token,
+                           float* host_logits);
+/* Device address of the last step's logits (vocab fp32). */
+int gufo_cuda_decoder_logits_device(gufo_cuda_decoder* decoder,
+                                    const float** device_logits);
+int gufo_cuda_decoder_position(const gufo_cuda_decoder* decoder);
+/* Copies DeltaNet layer `layer`'s conv window [conv_kernel - 1][channels] and
+ * state [value heads][dk][dk] to the host (either may be NULL): the checkpoint
+ * read of src/models/qwen35/state_capture.hpp:8-14. */
+int gufo_cuda_decoder_linear_state(gufo_cuda_decoder* decoder, int layer,
+                                   float* host_conv, float* host_ssm);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,7 +7,7 @@ import torch
 
 from gufo_npu_b200 import quantize as Q
 from gufo_npu_b200 import synth
-from gufo_npu_b200.backend import Context, CudaMixer, CudaProjections, Stage, stage_inputs
+from gufo_npu_b200.backend import Context, CudaDecoder, CudaMixer, CudaProjections, Stage, stage_inputs
 from tests.golden import make_golden as G
 
 pytestmark = pytest.mark.gpu
@@ -389,3 +389,52 @@ def test_deltanet_linear_batched_sequences(ctx, oracle):
     assert rel_l2(a[2][s].cpu().numpy(), want_y) <= DELTA_TOL
     assert rel_l2(a[1][s].cpu().numpy(), ssm) <= DELTA_TOL
     assert np.array_equal(bits(a[0][s].cpu().numpy()), bits(conv))
+
+
+# ---- the decode step ------------------------------------------------------------
+
+STEP_TOL = 2e-3      # logits relative L2: the reference's own bound between its decoder and its
+                     # oracle (tests/models/qwen35_2b/decoder_test.cpp:30-31)
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_decoder_step_matches_reference_logits(ctx, golden, use_graph):
+    """CudaDecoder.Step against the committed logits of the reference's Decoder::Step on the
+    same synthetic dense model (3 DeltaNet layers + 1 attention layer), 8 tokens."""
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    proj = CudaProjections(ctx, cfg, tensors)
+    dec = CudaDecoder(proj, tensors, max_positions=64, use_graph=use_graph)
+    g = golden("decoder")
+    tokens = [int(t) for t in g["decoder_dense_tokens"]]
+    worst = 0.0
+    for i, tok in enumerate(tokens):
+        logits = dec.Step(tok)
+        want = g["decoder_dense_logits"][i]
+        err = rel_l2(logits, want)
+        worst = max(worst, err)
+        assert err <= STEP_TOL, (i, err)
+        assert int(np.argmax(logits)) == int(np.argmax(want))
+    assert worst < 1e-4
+    assert dec.position == len(tokens)
+    # A second sequence after Reset reproduces the first.
+    dec.Reset()
+    again = dec.Step(tokens[0])
+    assert rel_l2(again, g["decoder_dense_logits"][0]) <= STEP_TOL
+    from gufo_npu_b200._capi import GufoCudaError
+    with pytest.raises(GufoCudaError):
+        dec.Step(cfg.vocab)
+    dec.close()
+
+
+def test_decoder_cache_capacity(ctx):
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    dec = CudaDecoder(CudaProjections(ctx, cfg, tensors), tensors, max_positions=3, use_graph=False)
+    for tok in (1, 2, 3):
+        dec.Step(tok)
+    from gufo_npu_b200._capi import GufoCudaError
+    with pytest.raises(GufoCudaError) as e:
+        dec.Step(4)
+    assert e.value.status == 7
+    dec.close()
