@@ -45,6 +45,13 @@ class DeltaNetParams(C.Structure):
                 ("dt_bias", _f32p), ("ssm_norm", _f32p)]
 
 
+class AttentionArgs(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("heads", "kv_heads", "head_dim", "rope_dim", "max_positions")] + \
+               [("rms_eps", C.c_float)] + \
+               [(n, C.c_void_p) for n in ("position", "in_", "q_norm", "k_norm", "inv_freq", "keys", "values",
+                                          "queries", "partials", "ctx_out")]
+
+
 class DecoderConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("layers", "hidden", "ffn", "vocab")] + [("rms_eps", C.c_float)] + \
                [(n, C.c_int) for n in ("full_attention_interval", "heads", "kv_heads", "head_dim", "rope_dim")] + \
@@ -98,6 +105,11 @@ SIGNATURES = {
                                                   C.POINTER(C.c_int64)]),
     "gufo_cuda_deltanet_layer_free": (C.c_int, [C.c_void_p, C.c_int64]),
     "gufo_cuda_deltanet_linear_device": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(LinearSeq), C.c_int]),
+    "gufo_cuda_embed_device": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "gufo_cuda_add_rms_norm_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
+                                                C.c_void_p, C.c_void_p]),
+    "gufo_cuda_swiglu_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "gufo_cuda_attention_device": (C.c_int, [C.c_void_p, C.POINTER(AttentionArgs)]),
     "gufo_cuda_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderConfig), C.POINTER(DecoderWeights),
                                            C.POINTER(C.c_void_p)]),
     "gufo_cuda_decoder_destroy": (C.c_int, [C.c_void_p]),

@@ -368,8 +368,81 @@ int Upload(gufo_cuda_ctx* ctx, const T* host, size_t n, T** dev) {
   return GUFO_CUDA_OK;
 }
 
+int EnqueueAttention(gufo_cuda_ctx* ctx, const AttnArgs& a) {
+  const dim3 block(kSmallThreads);
+  GUFO_CUDA_TRY(LaunchOverlapped(AttnPrepKernel, dim3(a.heads + a.kv_heads), block, 0, ctx->stream, 1, a));
+  GUFO_CUDA_TRY(LaunchOverlapped(AttnSliceKernel, dim3(kAttnSplits, a.kv_heads), block, 0, ctx->stream, 1, a));
+  GUFO_CUDA_TRY(LaunchOverlapped(AttnMergeKernel, dim3(a.heads), block, 0, ctx->stream, 1, a));
+  ctx->launches.fetch_add(3);
+  return GUFO_CUDA_OK;
+}
+
 }  // namespace
 }  // namespace gufo
+
+extern "C" {
+
+int gufo_cuda_embed_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix, const int* device_token, float* h) {
+  if (ctx == nullptr || device_token == nullptr || h == nullptr) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "embed: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  const gufo::Matrix* m = ctx->FindMatrix(matrix);
+  if (m == nullptr) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "embed: unknown matrix handle");
+  }
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::EmbedArgs a{m->data, m->type, static_cast<int>(m->row_bytes), static_cast<int>(m->cols), device_token, h};
+  GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::EmbedKernel, dim3(1), dim3(gufo::kSmallThreads), 0, ctx->stream, 1, a));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_add_rms_norm_device(gufo_cuda_ctx* ctx, float* h, const float* delta, const float* weight,
+                                  float eps, int n, float* normed, int* advance) {
+  if (ctx == nullptr || h == nullptr || weight == nullptr || normed == nullptr || n <= 0) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "add_rms_norm: bad argument");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::AddNormKernel, dim3(1), dim3(gufo::kSmallThreads), 0, ctx->stream, 1,
+                                       h, delta, weight, eps, n, normed, advance));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_swiglu_device(gufo_cuda_ctx* ctx, const float* ffn, int f, float* act) {
+  if (ctx == nullptr || ffn == nullptr || act == nullptr || f <= 0) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "swiglu: bad argument");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::SwiGluKernel, dim3((f + gufo::kSmallThreads - 1) / gufo::kSmallThreads),
+                                       dim3(gufo::kSmallThreads), 0, ctx->stream, 1, ffn, f, act));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_attention_device(gufo_cuda_ctx* ctx, const gufo_cuda_attention_args* p) {
+  if (ctx == nullptr || p == nullptr || p->position == nullptr || p->in == nullptr || p->q_norm == nullptr ||
+      p->k_norm == nullptr || p->inv_freq == nullptr || p->keys == nullptr || p->values == nullptr ||
+      p->queries == nullptr || p->partials == nullptr || p->ctx_out == nullptr) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "attention: null pointer");
+  }
+  if (p->kv_heads <= 0 || p->heads % p->kv_heads != 0 || p->heads / p->kv_heads > gufo::kMaxGroup ||
+      p->head_dim % 32 != 0 || p->head_dim > 32 * gufo::kMaxPerLane || p->rope_dim > p->head_dim ||
+      p->rope_dim % 2 != 0) {
+    return gufo::Fail(GUFO_CUDA_SHAPE, "attention: unsupported head shape");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::AttnArgs a{p->heads, p->kv_heads, p->head_dim, p->rope_dim, p->max_positions, p->rms_eps, p->position,
+                   p->in, p->q_norm, p->k_norm, p->inv_freq, static_cast<__half*>(p->keys),
+                   static_cast<__half*>(p->values), p->queries, p->partials, p->ctx_out};
+  return gufo::EnqueueAttention(ctx, a);
+}
+
+}  // extern "C"
 
 struct gufo_cuda_decoder {
   gufo_cuda_ctx* ctx = nullptr;
@@ -484,10 +557,7 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
       AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps,
                  d->position_dev, d->in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values,
                  d->queries, d->partials, d->mixed};
-      GUFO_CUDA_TRY(LaunchOverlapped(AttnPrepKernel, dim3(c.heads + c.kv_heads), block, 0, st, 1, a));
-      GUFO_CUDA_TRY(LaunchOverlapped(AttnSliceKernel, dim3(kAttnSplits, c.kv_heads), block, 0, st, 1, a));
-      GUFO_CUDA_TRY(LaunchOverlapped(AttnMergeKernel, dim3(c.heads), block, 0, st, 1, a));
-      ctx->launches.fetch_add(3);
+      GUFO_STEP_TRY(EnqueueAttention(ctx, a));
     } else {
       gufo_cuda_linear_seq seq{d->in, l.conv[parity], l.conv[parity ^ 1], l.ssm, nullptr, d->mixed};
       GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1));

@@ -1,0 +1,268 @@
+"""Row-split tensor parallelism of the decode step over the GPUs of one box.
+
+Every output row of a projection is an independent dot product
+(src/models/qwen35/gguf_projections.cpp:241-243 in the reference), so a stage's stacked rows
+are cut into `world` equal runs; rank r computes run r with this backend's GEMV kernels and an
+NCCL all-gather over NVLink rebuilds the full vector on every rank. The mixers, norms and
+activations between the products run replicated (they need the full vectors and are a few
+percent of a step's bytes). The reference itself has no distributed execution; this module is
+new work on top of its operator interface.
+
+One process per GPU (torch.distributed, backend "nccl"); the step is captured once per conv
+parity into a CUDA graph, collectives included.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import _capi
+from . import quantize as Q
+from .synth import ModelConfig, Tensor
+
+
+def shard_rows(parts: Sequence[Tuple[str, int]], rank: int, world: int) -> List[Tuple[str, int, int]]:
+    """Cuts the stacked rows of `parts` [(name, rows)] into `world` equal runs and returns run
+    `rank` as [(name, first, count)]. The total must divide by `world`."""
+    total = sum(rows for _, rows in parts)
+    if total % world:
+        raise ValueError(f"{total} stacked rows do not divide over {world} ranks")
+    per = total // world
+    lo, hi = rank * per, (rank + 1) * per
+    out, at = [], 0
+    for name, rows in parts:
+        first, last = max(lo, at), min(hi, at + rows)
+        if first < last:
+            out.append((name, first - at, last - first))
+        at += rows
+    return out
+
+
+def stage_tensors(cfg: ModelConfig, il: int) -> Dict[str, List[str]]:
+    """GGUF tensor names stacked per stage of layer `il`, in the reference's order
+    (src/models/qwen35/gguf_projections.cpp:139-171)."""
+    p = f"blk.{il}."
+    if cfg.is_full_attention(il):
+        first = [p + "attn_q.weight", p + "attn_k.weight", p + "attn_v.weight"]
+        out = [p + "attn_output.weight"]
+    else:
+        first = [p + "attn_qkv.weight", p + "attn_gate.weight", p + "ssm_alpha.weight", p + "ssm_beta.weight"]
+        out = [p + "ssm_out.weight"]
+    return {"in": first, "out": out, "ffn_in": [p + "ffn_gate.weight", p + "ffn_up.weight"],
+            "ffn_down": [p + "ffn_down.weight"]}
+
+
+class TpDecoder:
+    """One rank of the row-split decode step (dense models)."""
+
+    def __init__(self, ctx, cfg: ModelConfig, tensors: Dict[str, Tensor], rank: int, world: int,
+                 max_positions: int = 4096):
+        self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
+        self.lib = ctx.lib
+        dev = torch.device("cuda", ctx.device)
+        self.dev = dev
+        self._keep = []
+        c = cfg
+
+        def f32(name):
+            t = tensors[name].data.to(dev).view(torch.float32).contiguous()
+            self._keep.append(t)
+            return t
+
+        def product(names):
+            """(parts array, nparts, local rows, total rows) of this rank's run of a stage."""
+            runs = shard_rows([(n, tensors[n].rows) for n in names], rank, world)
+            arr = (_capi.Rows * len(runs))()
+            for i, (name, first, count) in enumerate(runs):
+                t = tensors[name]
+                rb = Q.row_bytes(t.ggml_type, t.cols)
+                view = t.data.to(dev)[first * rb:(first + count) * rb]
+                self._keep.append(view)
+                arr[i] = _capi.Rows(ctx.matrix_from_device(t.ggml_type, view.data_ptr(), count, t.cols), 0, count)
+            local = sum(count for _, _, count in runs)
+            return arr, len(runs), local, local * world
+
+        self.layers = []
+        for il in range(c.layers):
+            names = stage_tensors(c, il)
+            layer = {k: product(v) for k, v in names.items()}
+            p = f"blk.{il}."
+            layer["attn_norm"] = f32(p + "attn_norm.weight")
+            layer["post_norm"] = f32(p + "post_attention_norm.weight")
+            if c.is_full_attention(il):
+                layer["q_norm"] = f32(p + "attn_q_norm.weight")
+                layer["k_norm"] = f32(p + "attn_k_norm.weight")
+                kv = c.kv_heads * c.head_dim
+                layer["keys"] = torch.zeros(max_positions, kv, dtype=torch.float16, device=dev)
+                layer["values"] = torch.zeros(max_positions, kv, dtype=torch.float16, device=dev)
+            else:
+                layer["linear"] = ctx.deltanet_layer_create(
+                    c.linear_key_heads, c.linear_value_heads, c.linear_head_dim, c.conv_kernel, c.rms_eps,
+                    *(tensors[p + n].data.cpu().numpy().view(np.float32) for n in
+                      ("ssm_conv1d.weight", "ssm_a", "ssm_dt.bias", "ssm_norm.weight")))
+                layer["conv"] = [torch.zeros((c.conv_kernel - 1) * c.conv_channels, device=dev) for _ in range(2)]
+                layer["ssm"] = torch.zeros(c.linear_value_heads * c.linear_head_dim ** 2, device=dev)
+            self.layers.append(layer)
+        head = "token_embd.weight" if c.tied_embeddings else "output.weight"
+        self.lm_head = product([head])
+        embed = tensors["token_embd.weight"]
+        self._embed_data = embed.data.to(dev)
+        self.embed = ctx.matrix_from_device(embed.ggml_type, self._embed_data.data_ptr(), embed.rows, embed.cols)
+        self.output_norm = f32("output_norm.weight")
+        self.inv_freq = torch.tensor([1.0 / (float(c.rope_theta) ** (2.0 * i / c.rope_dim))
+                                      for i in range(c.rope_dim // 2)], dtype=torch.float64).float().to(dev)
+        self.max_positions = max_positions
+        width = max(l["in"][3] for l in self.layers)
+        z = lambda n: torch.zeros(n, device=dev)
+        self.h, self.normed, self.out = z(c.hidden), z(c.hidden), z(c.hidden)
+        self.full_in, self.mixed = z(width), z(max(c.value_dim, c.heads * c.head_dim))
+        self.ffn, self.act, self.logits = z(2 * c.ffn), z(c.ffn), z(c.vocab)
+        self.local = z(max(max(max(l[k][2] for k in ("in", "out", "ffn_in", "ffn_down")) for l in self.layers),
+                           self.lm_head[2]))
+        self.queries = z(c.heads * c.head_dim)
+        self.partials = z(c.kv_heads * 8 * (c.heads // c.kv_heads) * (c.head_dim + 2))
+        self.position_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.token_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.position = 0
+        self.graphs = {}
+        self.kernels_per_step = 0
+        self.replayed_kernels = 0      # this backend's kernels launched through graph replays
+        self.gathers_per_step = 4 * c.layers + 1
+
+    def _check(self, status):
+        _capi.check(self.lib, self.ctx.handle, status)
+
+    def _product(self, prod, x, y_full):
+        """Local rows of a stage into self.local, then all-gather into y_full."""
+        arr, n, local, total = prod
+        self.ctx.matmul_device(arr, n, x, 1, self.local)
+        if self.world == 1:
+            y_full[:total].copy_(self.local[:local])
+        else:
+            dist.all_gather_into_tensor(y_full[:total], self.local[:local])
+
+    def _add_norm(self, delta, weight, advance=False):
+        c = self.cfg
+        self._check(self.lib.gufo_cuda_add_rms_norm_device(
+            self.ctx.handle, self.h.data_ptr(), delta.data_ptr() if delta is not None else None,
+            weight.data_ptr(), c.rms_eps, c.hidden, self.normed.data_ptr(),
+            self.position_dev.data_ptr() if advance else None))
+
+    def enqueue(self, parity: int) -> None:
+        c = self.cfg
+        lib, h = self.lib, self.ctx.handle
+        self._check(lib.gufo_cuda_embed_device(h, self.embed, self.token_dev.data_ptr(), self.h.data_ptr()))
+        pending = None
+        for il, l in enumerate(self.layers):
+            self._add_norm(pending, l["attn_norm"])
+            self._product(l["in"], self.normed, self.full_in)
+            if c.is_full_attention(il):
+                args = _capi.AttentionArgs(c.heads, c.kv_heads, c.head_dim, c.rope_dim, self.max_positions, c.rms_eps,
+                                           self.position_dev.data_ptr(), self.full_in.data_ptr(),
+                                           l["q_norm"].data_ptr(), l["k_norm"].data_ptr(), self.inv_freq.data_ptr(),
+                                           l["keys"].data_ptr(), l["values"].data_ptr(), self.queries.data_ptr(),
+                                           self.partials.data_ptr(), self.mixed.data_ptr())
+                self._check(lib.gufo_cuda_attention_device(h, C.byref(args)))
+            else:
+                self.ctx.deltanet_linear_device(l["linear"], [{
+                    "in": self.full_in, "conv_in": l["conv"][parity], "conv_out": l["conv"][parity ^ 1],
+                    "ssm": l["ssm"], "y": self.mixed}])
+            self._product(l["out"], self.mixed, self.out)
+            self._add_norm(self.out, l["post_norm"])
+            self._product(l["ffn_in"], self.normed, self.ffn)
+            self._check(lib.gufo_cuda_swiglu_device(h, self.ffn.data_ptr(), c.ffn, self.act.data_ptr()))
+            self._product(l["ffn_down"], self.act, self.out)
+            pending = self.out
+        self._add_norm(pending, self.output_norm, advance=True)
+        self._product(self.lm_head, self.normed, self.logits)
+
+    def step(self, token: int, stream, use_graph: bool = True) -> torch.Tensor:
+        """Runs `token` at the current position on every rank; returns the full logits (device)."""
+        if self.position >= self.max_positions:
+            raise RuntimeError("the attention cache is full")
+        self.token_dev.fill_(token)
+        parity = self.position & 1
+        if not use_graph or self.position < 2:
+            self.enqueue(parity)
+        else:
+            if parity not in self.graphs:
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize()
+                before = self.ctx.launch_count()
+                with torch.cuda.graph(g, stream=stream):
+                    self.enqueue(parity)
+                self.kernels_per_step = self.ctx.launch_count() - before
+                self.graphs[parity] = g
+            self.graphs[parity].replay()
+            self.replayed_kernels += self.kernels_per_step
+        self.position += 1
+        return self.logits
+
+
+def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> None:
+    """bench.py's N > 1 arm: launched by torchrun, one rank per GPU."""
+    from . import synth
+    from .backend import Context
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    tensors = synth.build_model(cfg, seed=1, device=f"cuda:{local}")
+    ctx = Context(local, stream.cuda_stream)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64)
+    del tensors
+    rng = np.random.default_rng(7)
+    tokens = iter(rng.integers(0, cfg.vocab, size=2 * (steps + warmup) + 8).tolist())
+    host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
+    for _ in range(warmup):
+        dec.step(next(tokens), stream)
+    torch.cuda.synchronize()
+
+    def timed(fn):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=f"cuda:{local}")
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    launches0 = ctx.launch_count() + dec.replayed_kernels
+    ms_resident = timed(lambda: dec.step(next(tokens), stream))
+    launches = ctx.launch_count() + dec.replayed_kernels - launches0
+
+    def e2e_step():
+        logits = dec.step(next(tokens), stream)
+        host.copy_(logits, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    ms_e2e = timed(e2e_step)
+    if rank == 0:
+        print(json.dumps({
+            "metric": metric, "value": 1e3 / ms_resident, "unit": unit, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
+            "data": "synthetic",
+            "config": {"workload": workload, "seed": 1, "parallelism": f"tp{world}: projections row-split, "
+                       f"{dec.gathers_per_step} NCCL all-gathers per step, mixers replicated",
+                       "l2": "weights exceed L2; no flush needed"},
+            "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
+                    "ms_per_step": ms_e2e},
+            "gpu_launches": int(launches),
+            "roofline": None, "cpu_baseline": None,
+        }))
+    dist.barrier()
+    dist.destroy_process_group()

@@ -218,6 +218,49 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
                                      const gufo_cuda_linear_seq* seqs,
                                      int nseq);
 
+/* ---- the small steps between the products ------------------------------- */
+
+/* The CPU work Decoder::Step does between its Projections calls, as device
+ * operations on the context's stream, so that a host-side decode loop (for
+ * example one that all-gathers row-split products between them) never leaves
+ * the device. All pointers are device pointers. */
+
+/* h = row *device_token of `matrix`, dequantized (the embedding lookup,
+ * src/models/qwen35/decoder.cpp:486-489). */
+int gufo_cuda_embed_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix,
+                           const int* device_token, float* h);
+/* h += delta (delta may be NULL), then normed = RMS(h) * weight (vec::RmsNorm,
+ * src/core/vec.hpp:57-63, with the residual add of decoder.cpp:504-506).
+ * `advance` (may be NULL) is an int counter incremented afterwards. */
+int gufo_cuda_add_rms_norm_device(gufo_cuda_ctx* ctx, float* h,
+                                  const float* delta, const float* weight,
+                                  float eps, int n, float* normed, int* advance);
+/* act[i] = silu(ffn[i]) * ffn[f + i] (decoder.cpp:511-514). */
+int gufo_cuda_swiglu_device(gufo_cuda_ctx* ctx, const float* ffn, int f,
+                            float* act);
+
+/* Mixer::Attention for one token (src/models/qwen35/decoder.cpp:267-412): q/k
+ * RMSNorm and RoPE, the fp16 cache append at *position, softmax over positions
+ * 0..*position in slices, the output gate. `in` is the kAttentionIn row
+ * [q and gate | k | v]; `ctx_out` gets heads * head_dim values. */
+typedef struct gufo_cuda_attention_args {
+  int heads, kv_heads, head_dim, rope_dim, max_positions;
+  float rms_eps;
+  const int* position;   /* device int: rows already in the cache */
+  const float* in;
+  const float* q_norm;   /* [head_dim] */
+  const float* k_norm;   /* [head_dim] */
+  const float* inv_freq; /* [rope_dim / 2]: 1 / theta^(2i / rope_dim) */
+  void* keys;            /* fp16 [max_positions][kv_heads * head_dim] */
+  void* values;
+  float* queries;        /* scratch [heads][head_dim] */
+  float* partials;       /* scratch [kv_heads][8][heads / kv_heads][head_dim + 2] */
+  float* ctx_out;
+} gufo_cuda_attention_args;
+
+int gufo_cuda_attention_device(gufo_cuda_ctx* ctx,
+                               const gufo_cuda_attention_args* args);
+
 /* ---- device-resident decode step ---------------------------------------- */
 
 /* Shape of a dense Qwen3.5-family model: the fields of qwen35::Config

@@ -1,0 +1,59 @@
+// Step-level drop-in check: TEST INFRASTRUCTURE ONLY.
+//
+// Runs the reference's own Decoder::Step twice over one GGUF file, once with its
+// GgufProjections (fp32) and once with the CUDA adapter
+// (integration/src_cuda/cuda_projections.cpp over libgufo_cuda.so) plugged in
+// behind the same Projections interface, and compares the logits of every
+// step. Built by oracle/Makefile from the reference's sources where they lie;
+// the mixers, norms and sampling stay the reference's CPU code in both runs.
+//
+//   adapter_parity <model.gguf> <tokens>     exit 0 when every step agrees
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+
+#include "core/gguf.hpp"
+#include "cuda/cuda_projections.hpp"
+#include "models/qwen35/decoder.hpp"
+#include "models/qwen35/gguf_projections.hpp"
+
+int main(int argc, char** argv) {
+  if (argc != 3) {
+    std::fprintf(stderr, "usage: adapter_parity <model.gguf> <tokens>\n");
+    return 2;
+  }
+  namespace qwen35 = gufo_npu::qwen35;
+  const auto file = gufo_npu::gguf::File::Open(argv[1]);
+  const int steps = std::atoi(argv[2]);
+  qwen35::GgufProjections cpu(*file, qwen35::GgufProjections::Precision::kFloat);
+  gufo_npu::cuda::CudaProjections gpu(*file, 0);
+  qwen35::Decoder a(*file, cpu);
+  qwen35::Decoder b(*file, gpu);
+  auto sa = a.NewState();
+  auto sb = b.NewState();
+  const int vocab = a.config().vocab;
+  double worst = 0;
+  for (int s = 0; s < steps; ++s) {
+    const int token = (s * 7919 + 13) % vocab;
+    const std::vector<float> want = a.Step(token, sa);
+    const std::vector<float>& got = b.Step(token, sb);
+    double num = 0, den = 0;
+    int arg_want = 0, arg_got = 0;
+    for (int i = 0; i < vocab; ++i) {
+      num += (double(got[i]) - want[i]) * (double(got[i]) - want[i]);
+      den += double(want[i]) * want[i];
+      if (want[i] > want[arg_want]) arg_want = i;
+      if (got[i] > got[arg_got]) arg_got = i;
+    }
+    const double err = std::sqrt(num / den);
+    worst = err > worst ? err : worst;
+    std::printf("step %d: logits rel-L2 %.3e argmax %d/%d\n", s, err, arg_got, arg_want);
+    if (err > 2e-3 || arg_want != arg_got) {
+      std::printf("FAIL\n");
+      return 1;
+    }
+  }
+  std::printf("PASS: %d steps, worst rel-L2 %.3e\n", steps, worst);
+  return 0;
+}

@@ -438,3 +438,43 @@ def test_decoder_cache_capacity(ctx):
         dec.Step(4)
     assert e.value.status == 7
     dec.close()
+
+
+def test_row_split_decoder_single_rank_matches_reference_logits(golden):
+    """The tensor-parallel decode loop (host-side steps over the C ABI's small operations) with
+    one rank: same logits as the reference's Decoder::Step, eager and graph-replayed."""
+    from gufo_npu_b200.tp import TpDecoder
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        c = Context(0, stream.cuda_stream)
+        cfg = synth.ModelConfig(**G.DENSE)
+        tensors = synth.build_model(cfg, G.DENSE_SEED)
+        dec = TpDecoder(c, cfg, tensors, rank=0, world=1, max_positions=32)
+        g = golden("decoder")
+        for i, tok in enumerate(int(t) for t in g["decoder_dense_tokens"]):
+            logits = dec.step(tok, stream).cpu().numpy()
+            assert rel_l2(logits, g["decoder_dense_logits"][i]) <= STEP_TOL, i
+        assert dec.graphs and dec.kernels_per_step > 0
+    torch.cuda.synchronize()
+    c.close()
+
+
+@pytest.mark.parametrize("tag,kwargs,seed", [("dense", G.DENSE, G.DENSE_SEED), ("moe", G.MOE, G.MOE_SEED)])
+def test_reference_decoder_with_cuda_adapter(tmp_path, tag, kwargs, seed):
+    """Drop-in at step level: the reference's own Decoder::Step (its mixers, norms, routing)
+    with the C++ adapter over this library plugged in behind qwen35::Projections, against the
+    same decoder over its GgufProjections. Dense and MoE (ApplyExpert through Route) models.
+    Runs the binary oracle/Makefile builds where the reference tree is mounted."""
+    import os
+    import subprocess
+    binary = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref",
+                          "adapter_parity")
+    if not os.path.exists(binary):
+        pytest.skip("oracle/_ref/adapter_parity was not built (no reference tree here)")
+    cfg = synth.ModelConfig(**kwargs)
+    image = synth.to_gguf(cfg, synth.build_model(cfg, seed))
+    path = tmp_path / f"{tag}.gguf"
+    image.tofile(path)
+    run = subprocess.run([binary, str(path), "6"], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "PASS" in run.stdout
