@@ -99,6 +99,8 @@ SIGNATURES = {
     "gufo_cuda_matmul": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "gufo_cuda_matmul_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int,
                                           C.c_void_p]),
+    "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                                     C.c_int, C.c_void_p]),
     "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,
                                               C.c_int]),
     "gufo_cuda_deltanet_layer_create": (C.c_int, [C.c_void_p, C.POINTER(DeltaNetParams),

@@ -146,6 +146,29 @@ int gufo_cuda_matmul_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
                             int nparts, const float* device_x, int tokens,
                             float* device_y);
 
+/* The Q4_K product for callers that must not allocate device memory while
+ * they run: code inside a region where cudaMalloc is off limits (a stream that
+ * is being captured, a latency-critical loop) or a host that has handed the
+ * whole device to its own arena and plans every byte up front. It has no
+ * counterpart in the reference. The weights are plain GGUF Q4_K bytes the
+ * caller already holds on the device (`rows` rows of `cols` values, 16-byte
+ * aligned); x is `tokens` (1..8) rows of `cols` fp32, y `tokens` rows of `rows`
+ * fp32, both on the device. The fixed-point copy of x that the tensor-core
+ * kernel multiplies against goes into a 64 KiB buffer built into the library
+ * (every GPU that loads the library holds those 64 KiB until the process ends)
+ * instead of the context's growable buffer, and the call performs no
+ * cudaMalloc, cudaFree or other allocating call. Shapes whose staged
+ * activations exceed the 64 KiB (3 * tokens * (cols + 32) + tokens * cols / 8 +
+ * cols / 8 bytes, roughly) return GUFO_CUDA_TOO_LARGE.
+ * The first call on a device looks up the buffer's address; make that call
+ * before any stream capture begins. All calls share the one buffer: calls that
+ * can overlap on the GPU (different streams or contexts) race on it. Nothing
+ * in it needs clearing between calls; each call rewrites what it reads. */
+int gufo_cuda_matmul_q4k_static_device(gufo_cuda_ctx* ctx,
+                                       const void* device_weights, int64_t rows,
+                                       int64_t cols, const float* device_x,
+                                       int tokens, float* device_y);
+
 /* ---- Gated DeltaNet decode step ---------------------------------------- */
 
 /* One sequence's inputs to the delta rule with the gates already evaluated
