@@ -339,13 +339,55 @@ def run_ours(args):
     print(json.dumps(line))
 
 
+def run_probe(which: str) -> None:
+    """A handful of launches of one kernel family on a small case (a few hundred MB on the
+    device, inputs larger than L2): the program `ncu` captures for the summaries in profiles/."""
+    from gufo_npu_b200 import _capi
+    from gufo_npu_b200.backend import Context
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    ctx = Context(0, stream.cuda_stream)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    if which in ("q4k", "q6k"):
+        t = Q.GGML_Q4_K if which == "q4k" else Q.GGML_Q6_K
+        rows, cols, copies = (6144, 2048, 24) if which == "q4k" else (131072, 2048, 1)
+        raw = Q.quantize(t, torch.randn(rows, cols, device=dev, generator=gen) * 0.02)
+        keep = [raw.clone() for _ in range(copies)]
+        mats = [Context._parts([(ctx.matrix_from_device(t, r.data_ptr(), rows, cols), 0, rows)]) for r in keep]
+        x = torch.randn(1, cols, device=dev, generator=gen)
+        y = torch.empty(1, rows, device=dev)
+        for i in range(8):
+            ctx.matmul_device(mats[i % copies], 1, x, 1, y)
+    else:
+        hv, dk, nseq, sets = 16, 128, 8, 12
+        st = torch.randn(sets, nseq, hv, dk, dk, device=dev, generator=gen) * 0.1
+        q = torch.nn.functional.normalize(torch.randn(nseq, hv, dk, device=dev, generator=gen), dim=-1)
+        k = torch.nn.functional.normalize(torch.randn(nseq, hv, dk, device=dev, generator=gen), dim=-1)
+        v = torch.randn(nseq, hv, dk, device=dev, generator=gen)
+        decay, beta = torch.rand(nseq, hv, device=dev, generator=gen), torch.rand(nseq, hv, device=dev, generator=gen)
+        y = torch.empty(nseq, hv, dk, device=dev)
+        for c in range(8):
+            arr = (_capi.DeltaSeq * nseq)()
+            for s in range(nseq):
+                arr[s] = _capi.DeltaSeq(st[c, s].data_ptr(), 0, q[s].data_ptr(), k[s].data_ptr(), v[s].data_ptr(),
+                                        decay[s].data_ptr(), beta[s].data_ptr(), y[s].data_ptr())
+            ctx._check(ctx.lib.gufo_cuda_delta_rule_device(ctx.handle, arr, nseq, hv, hv, dk))
+    torch.cuda.synchronize()
+    print(json.dumps({"probe": which, "launches": ctx.launch_count()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--probe", default=None, choices=["q4k", "q6k", "deltanet"],
+                    help="run a few launches of one kernel on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
+    if args.probe:
+        return run_probe(args.probe)
     if args.impl == "reference":
         return run_reference(args)
     if not torch.cuda.is_available():
