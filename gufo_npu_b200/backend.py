@@ -462,6 +462,17 @@ class CudaDecoder:
         self.ctx._check(self.ctx.lib.gufo_cuda_decoder_logits_device(self.handle, C.byref(out)))
         return int(out.value)
 
+    TIMELINE_KINDS = ("embed", "in", "deltanet", "attention", "out", "ffn_in", "ffn_down", "lm_head")
+
+    def timeline(self, enable: bool) -> Dict[str, float]:
+        """Per-stage device milliseconds per step collected since the last switch; then turns
+        collection on or off (collection runs the step eagerly, without graph replay)."""
+        ms = (C.c_double * len(self.TIMELINE_KINDS))()
+        steps = C.c_int()
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_timeline(self.handle, int(enable), ms, C.byref(steps)))
+        n = max(steps.value, 1)
+        return {k: ms[i] / n for i, k in enumerate(self.TIMELINE_KINDS)}
+
     @property
     def position(self) -> int:
         return int(self.ctx.lib.gufo_cuda_decoder_position(self.handle))

@@ -84,18 +84,63 @@ void SetError(const std::string& text);
 int Fail(int status, const std::string& text);
 int CudaFail(cudaError_t e, const char* what);
 
-// One part of a product on a tensor-core GEMV kernel.
-struct FastGemvArgs {
-  const uint8_t* w;      // first row
+// How a tensor-core GEMV obtains its input vector. The fused forms mirror the
+// prologues of the reference's NPU GEMV (npu::Prologue kPlain / kAct /
+// kResNorm, src/npu/gemv.hpp:58-63): they remove a kernel boundary, not a
+// weight read.
+enum FastPrologue {
+  kPrologueImage = 0,    // a fixed-point image staged earlier (any token count)
+  kProloguePlain = 1,    // x fp32 [cols], staged by every thread block
+  kPrologueResNorm = 2,  // x = RMS(h_in + delta) * norm_w; block 0 also writes h_out and normed_out
+  kPrologueSwiGlu = 3,   // x[i] = silu(x_in[i]) * x_in[cols + i]
+};
+
+constexpr int kFastMaxParts = 4;
+
+struct FastPart {
+  const uint8_t* w;   // first row
   int rows;
+  int y_offset;       // column of y where this part starts
+};
+
+// One launch of a tensor-core GEMV kernel: parts of one block format sharing
+// one input.
+struct FastGemvArgs {
+  FastPart parts[kFastMaxParts];
+  int nparts;
   int cols;
   int row_bytes;
-  const uint8_t* image;  // staged activations (mma_common.cuh)
   float* y;              // [tokens][y_stride]
   int y_stride;
-  int y_offset;          // column of y where this part starts
-  int tokens;
+  int tokens;            // fused prologues: 1
+  int prologue;
+  const uint8_t* image;  // kPrologueImage
+  const float* x;        // kProloguePlain: [cols]; kPrologueSwiGlu: [2 * cols]
+  const float* h_in;     // kPrologueResNorm: the residual stream [cols] ...
+  const float* delta;    //   ... plus this (may be null)
+  const float* norm_w;
+  float eps;
+  float* h_out;          //   h_in + delta, written by block 0 (must not alias h_in)
+  float* normed_out;     //   the normed vector, written by block 0 (may be null)
+  int* advance;          //   incremented once by block 0 (may be null)
 };
+
+// A single-part launch against a staged image.
+inline FastGemvArgs ImageGemvArgs(const uint8_t* w, int rows, int cols, int row_bytes,
+                                  const uint8_t* image, float* y, int y_stride, int y_offset,
+                                  int tokens) {
+  FastGemvArgs a{};
+  a.parts[0] = {w, rows, y_offset};
+  a.nparts = 1;
+  a.cols = cols;
+  a.row_bytes = row_bytes;
+  a.y = y;
+  a.y_stride = y_stride;
+  a.tokens = tokens;
+  a.prologue = kPrologueImage;
+  a.image = image;
+  return a;
+}
 
 // Bytes of a row of `cols` values of `type`; 0 when the type is not run here or
 // cols is not a whole number of blocks.
@@ -113,8 +158,10 @@ int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 // Whether the image of `tokens` rows of `cols` values fits in shared memory.
 bool Q4KFastFits(int cols, int tokens);
 // One Mixer::Linear step per sequence; the caller holds ctx->mu.
+// `early_state`: the states were not written by the kernels just before this
+// one in the stream, so their loads may run ahead of the dependency wait.
 int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& layer,
-                          const gufo_cuda_linear_seq* seqs, int nseq);
+                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state);
 // The same for Q6_K parts (image with group sums of 16).
 int LaunchGemvQ6KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 bool Q6KFastFits(int cols, int tokens);
@@ -144,6 +191,9 @@ struct gufo_cuda_ctx {
   // previous product (wrong results unless x is unchanged).
   bool reuse_image = false;
   int gemv_variant = 0;
+  // The caller's promise that DeltaNet states passed to this context were not
+  // written by the two kernels enqueued just before the call.
+  bool early_state = false;
 
   const gufo::Matrix* FindMatrix(int64_t id) const {
     auto it = matrices.find(id);

@@ -229,6 +229,10 @@ int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value) {
     ctx->gemv_variant = value;
     return GUFO_CUDA_OK;
   }
+  if (std::strcmp(name, "deltanet_early_state") == 0) {
+    ctx->early_state = value != 0;
+    return GUFO_CUDA_OK;
+  }
   if (std::strcmp(name, "reuse_image") == 0) {
     ctx->reuse_image = value != 0;
     return GUFO_CUDA_OK;

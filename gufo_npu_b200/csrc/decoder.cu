@@ -101,11 +101,11 @@ EmbedKernel(const __grid_constant__ EmbedArgs a) {
   }
 }
 
-// h += delta (when given), then normed = RMS(h) * w (vec::RmsNorm,
+// h = h_in + delta (delta when given; h may be h_in), then normed = RMS(h) * w (vec::RmsNorm,
 // src/core/vec.hpp:57-63; the residual adds of decoder.cpp:504-506,519-521).
 // `advance`, when given, is incremented at the end: the sequence position.
 __global__ void __launch_bounds__(kSmallThreads)
-AddNormKernel(float* __restrict__ h, const float* __restrict__ delta,
+AddNormKernel(const float* h_in, float* h, const float* __restrict__ delta,
               const float* __restrict__ w, float eps, int n, float* __restrict__ normed,
               int* advance) {
   __shared__ float scratch[kSmallThreads / 32];
@@ -113,9 +113,11 @@ AddNormKernel(float* __restrict__ h, const float* __restrict__ delta,
   GridDependencyWait();
   float sq = 0.f;
   for (int i = threadIdx.x; i < n; i += kSmallThreads) {
-    float v = h[i];
+    float v = h_in[i];
     if (delta != nullptr) {
       v += delta[i];
+    }
+    if (delta != nullptr || h != h_in) {
       h[i] = v;
     }
     sq = fmaf(v, v, sq);
@@ -406,7 +408,7 @@ int gufo_cuda_add_rms_norm_device(gufo_cuda_ctx* ctx, float* h, const float* del
   std::lock_guard<std::mutex> lock(ctx->mu);
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
   GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::AddNormKernel, dim3(1), dim3(gufo::kSmallThreads), 0, ctx->stream, 1,
-                                       h, delta, weight, eps, n, normed, advance));
+                                       static_cast<const float*>(h), h, delta, weight, eps, n, normed, advance));
   ctx->launches.fetch_add(1);
   return GUFO_CUDA_OK;
 }
@@ -466,7 +468,8 @@ struct gufo_cuda_decoder {
   float* output_norm = nullptr;
   float* inv_freq = nullptr;
   // Activations.
-  float *h = nullptr, *normed = nullptr, *in = nullptr, *mixed = nullptr, *out = nullptr;
+  float* h[2] = {nullptr, nullptr};   // the residual stream alternates between two buffers
+  float *normed = nullptr, *in = nullptr, *mixed = nullptr, *out = nullptr;
   float *ffn = nullptr, *act = nullptr, *logits = nullptr, *queries = nullptr, *partials = nullptr;
   int* position_dev = nullptr;
   int* token_dev = nullptr;
@@ -474,6 +477,13 @@ struct gufo_cuda_decoder {
   int position = 0;
   int steps = 0;
   int64_t kernels_per_step = 0;
+  // Per-stage device time (the reference keeps the same kind of split,
+  // NpuDecoder::Timeline, src/models/qwen35_2b/npu_decoder.hpp:121-154).
+  bool timeline = false;
+  std::vector<cudaEvent_t> marks;
+  std::vector<int> mark_kind;
+  double stage_ms[GUFO_CUDA_TIMELINE_KINDS] = {};
+  int timeline_steps = 0;
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   std::vector<void*> owned;   // every device allocation, for destroy
 
@@ -522,12 +532,6 @@ int Stack(gufo_cuda_ctx* ctx, const gufo_cuda_matrix* handles, const int64_t* wa
   return BuildGemvArgs(ctx, parts, n, args);
 }
 
-int Product(gufo_cuda_ctx* ctx, GemvArgs args, const float* x, float* y) {
-  args.x = x;
-  args.y = y;
-  return LaunchGemv(ctx, args, 1);
-}
-
 #define GUFO_STEP_TRY(expr)           \
   do {                                \
     const int gufo_rc_ = (expr);      \
@@ -536,47 +540,180 @@ int Product(gufo_cuda_ctx* ctx, GemvArgs args, const float* x, float* y) {
     }                                 \
   } while (0)
 
+// Where a product's input comes from (FastPrologue, common.cuh).
+struct Input {
+  int prologue;
+  const float* x = nullptr;        // plain: the vector; SwiGLU: [gate | up]
+  const float* h_in = nullptr;     // residual + norm
+  const float* delta = nullptr;
+  const float* norm_w = nullptr;
+  float* h_out = nullptr;
+  int* advance = nullptr;
+};
+
+// One stage's product with its input fused into the GEMV kernels where every
+// part allows it; otherwise the input is materialised by the small kernels
+// first. `scratch` holds the materialised / normed vector.
+int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y) {
+  gufo_cuda_ctx* ctx = d->ctx;
+  const gufo_cuda_decoder_config& c = d->c;
+  const dim3 block(kSmallThreads);
+  bool fused = !ctx->force_general && stage.nparts <= kFastMaxParts;
+  int fast_parts = 0;
+  for (int p = 0; p < stage.nparts; ++p) {
+    const int type = stage.parts[p].type;
+    if (type == GUFO_CUDA_Q4_K) {
+      fused = fused && Q4KFastFits(stage.cols, 1);
+      ++fast_parts;
+    } else if (type == GUFO_CUDA_Q6_K) {
+      fused = fused && Q6KFastFits(stage.cols, 1);
+      ++fast_parts;
+    } else if (in.prologue == kPrologueSwiGlu) {
+      fused = false;   // other rows would need the activated vector in memory
+    }
+  }
+  if (!fused || fast_parts == 0) {
+    const float* x = in.x;
+    if (in.prologue == kPrologueResNorm) {
+      GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, dim3(1), block, 0, ctx->stream, 1, in.h_in, in.h_out, in.delta,
+                                     in.norm_w, c.rms_eps, stage.cols, scratch, in.advance));
+      ctx->launches.fetch_add(1);
+      x = scratch;
+    } else if (in.prologue == kPrologueSwiGlu) {
+      GUFO_CUDA_TRY(LaunchOverlapped(SwiGluKernel, dim3((stage.cols + kSmallThreads - 1) / kSmallThreads), block, 0,
+                                     ctx->stream, 1, in.x, stage.cols, scratch));
+      ctx->launches.fetch_add(1);
+      x = scratch;
+    }
+    GemvArgs args = stage;
+    args.x = x;
+    args.y = y;
+    return LaunchGemv(ctx, args, 1);
+  }
+  bool first = true;
+  for (int type : {GUFO_CUDA_Q4_K, GUFO_CUDA_Q6_K}) {
+    FastGemvArgs args{};
+    args.cols = stage.cols;
+    args.y = y;
+    args.y_stride = stage.y_stride;
+    args.tokens = 1;
+    args.prologue = in.prologue;
+    args.x = in.x;
+    args.h_in = in.h_in;
+    args.delta = in.delta;
+    args.norm_w = in.norm_w;
+    args.eps = c.rms_eps;
+    args.h_out = in.h_out;
+    args.normed_out = in.prologue == kPrologueResNorm ? scratch : nullptr;
+    for (int p = 0; p < stage.nparts; ++p) {
+      const GemvPart& part = stage.parts[p];
+      if (part.type != type) {
+        continue;
+      }
+      args.row_bytes = part.row_bytes;
+      args.parts[args.nparts++] = {part.data, part.rows, part.out_offset};
+    }
+    if (args.nparts == 0) {
+      continue;
+    }
+    args.advance = first ? in.advance : nullptr;
+    first = false;
+    GUFO_STEP_TRY(type == GUFO_CUDA_Q4_K ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args));
+  }
+  // Rows of other formats (the F32 alpha / beta rows) read the vector block 0 wrote.
+  GemvArgs rest = stage;
+  rest.nparts = 0;
+  rest.total_rows = 0;
+  for (int p = 0; p < stage.nparts; ++p) {
+    if (stage.parts[p].type != GUFO_CUDA_Q4_K && stage.parts[p].type != GUFO_CUDA_Q6_K) {
+      rest.parts[rest.nparts++] = stage.parts[p];
+      rest.total_rows += stage.parts[p].rows;
+    }
+  }
+  if (rest.nparts > 0) {
+    rest.x = in.prologue == kPrologueResNorm ? scratch : in.x;
+    rest.y = y;
+    GUFO_STEP_TRY(LaunchGemv(ctx, rest, 1));
+  }
+  return GUFO_CUDA_OK;
+}
+
 // Enqueues one step's kernels; `parity` picks the conv window that is current.
+// Records an event that closes a stage of kind `kind` (timeline mode only).
+void Mark(gufo_cuda_decoder* d, int kind) {
+  if (!d->timeline) {
+    return;
+  }
+  const size_t used = d->mark_kind.size();
+  if (used >= d->marks.size()) {
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    d->marks.push_back(e);
+  }
+  cudaEventRecord(d->marks[used], d->ctx->stream);
+  d->mark_kind.push_back(kind);
+}
+
 int EnqueueStep(gufo_cuda_decoder* d, int parity) {
   gufo_cuda_ctx* ctx = d->ctx;
   const gufo_cuda_decoder_config& c = d->c;
   cudaStream_t st = ctx->stream;
   const dim3 one(1), block(kSmallThreads);
+  int cur = 0;   // which residual buffer is current
   EmbedArgs embed{d->embed.data, d->embed.type, static_cast<int>(d->embed.row_bytes), c.hidden,
-                  d->token_dev, d->h};
+                  d->token_dev, d->h[0]};
   GUFO_CUDA_TRY(LaunchOverlapped(EmbedKernel, one, block, 0, st, 1, embed));
   ctx->launches.fetch_add(1);
-  const float* pending = nullptr;   // projection output not yet added to h
+  Mark(d, -1);
+  Mark(d, GUFO_CUDA_TIMELINE_EMBED);
+  const float* pending = nullptr;   // projection output not yet added to the residual
   for (int il = 0; il < c.layers; ++il) {
     auto& l = d->layers[il];
-    GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, pending, (const float*)l.attn_norm,
-                                   c.rms_eps, c.hidden, d->normed, (int*)nullptr));
-    ctx->launches.fetch_add(1);
-    GUFO_STEP_TRY(Product(ctx, l.in, d->normed, d->in));
+    Input norm1{kPrologueResNorm};
+    norm1.h_in = d->h[cur];
+    norm1.delta = pending;
+    norm1.norm_w = l.attn_norm;
+    norm1.h_out = d->h[cur ^ 1];
+    GUFO_STEP_TRY(FusedProduct(d, l.in, norm1, d->normed, d->in));
+    Mark(d, GUFO_CUDA_TIMELINE_IN);
+    cur ^= 1;
     if (l.attention) {
       AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps,
                  d->position_dev, d->in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values,
                  d->queries, d->partials, d->mixed};
       GUFO_STEP_TRY(EnqueueAttention(ctx, a));
+      Mark(d, GUFO_CUDA_TIMELINE_ATTENTION);
     } else {
       gufo_cuda_linear_seq seq{d->in, l.conv[parity], l.conv[parity ^ 1], l.ssm, nullptr, d->mixed};
-      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1));
+      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1, true));
+      Mark(d, GUFO_CUDA_TIMELINE_DELTANET);
     }
-    GUFO_STEP_TRY(Product(ctx, l.out, d->mixed, d->out));
-    GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, (const float*)d->out,
-                                   (const float*)l.post_norm, c.rms_eps, c.hidden, d->normed, (int*)nullptr));
-    ctx->launches.fetch_add(1);
-    GUFO_STEP_TRY(Product(ctx, l.ffn_in, d->normed, d->ffn));
-    GUFO_CUDA_TRY(LaunchOverlapped(SwiGluKernel, dim3((c.ffn + kSmallThreads - 1) / kSmallThreads), block, 0, st,
-                                   1, (const float*)d->ffn, c.ffn, d->act));
-    ctx->launches.fetch_add(1);
-    GUFO_STEP_TRY(Product(ctx, l.ffn_down, d->act, d->out));
+    Input plain{kProloguePlain};
+    plain.x = d->mixed;
+    GUFO_STEP_TRY(FusedProduct(d, l.out, plain, d->act, d->out));
+    Mark(d, GUFO_CUDA_TIMELINE_OUT);
+    Input norm2{kPrologueResNorm};
+    norm2.h_in = d->h[cur];
+    norm2.delta = d->out;
+    norm2.norm_w = l.post_norm;
+    norm2.h_out = d->h[cur ^ 1];
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_in, norm2, d->normed, d->ffn));
+    Mark(d, GUFO_CUDA_TIMELINE_FFN_IN);
+    cur ^= 1;
+    Input swiglu{kPrologueSwiGlu};
+    swiglu.x = d->ffn;
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, swiglu, d->act, d->out));
+    Mark(d, GUFO_CUDA_TIMELINE_FFN_DOWN);
     pending = d->out;
   }
-  GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, d->h, pending, (const float*)d->output_norm,
-                                 c.rms_eps, c.hidden, d->normed, d->position_dev));
-  ctx->launches.fetch_add(1);
-  GUFO_STEP_TRY(Product(ctx, d->lm_head, d->normed, d->logits));
+  Input last{kPrologueResNorm};
+  last.h_in = d->h[cur];
+  last.delta = pending;
+  last.norm_w = d->output_norm;
+  last.h_out = d->h[cur ^ 1];
+  last.advance = d->position_dev;
+  GUFO_STEP_TRY(FusedProduct(d, d->lm_head, last, d->normed, d->logits));
+  Mark(d, GUFO_CUDA_TIMELINE_LM_HEAD);
   return GUFO_CUDA_OK;
 }
 
@@ -715,7 +852,8 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
   struct Buf {
     float** p;
     size_t n;
-  } bufs[] = {{&d->h, static_cast<size_t>(c.hidden)}, {&d->normed, static_cast<size_t>(c.hidden)},
+  } bufs[] = {{&d->h[0], static_cast<size_t>(c.hidden)}, {&d->h[1], static_cast<size_t>(c.hidden)},
+              {&d->normed, static_cast<size_t>(c.hidden)},
               {&d->in, in_max}, {&d->mixed, mixed}, {&d->out, static_cast<size_t>(c.hidden)},
               {&d->ffn, static_cast<size_t>(2) * c.ffn}, {&d->act, static_cast<size_t>(c.ffn)},
               {&d->logits, static_cast<size_t>(c.vocab)}, {&d->queries, static_cast<size_t>(attn_dim)},
@@ -761,6 +899,9 @@ int gufo_cuda_decoder_destroy(gufo_cuda_decoder* d) {
   }
   for (void* p : d->owned) {
     cudaFree(p);
+  }
+  for (cudaEvent_t e : d->marks) {
+    cudaEventDestroy(e);
   }
   if (d->token_pinned != nullptr) {
     cudaFreeHost(d->token_pinned);
@@ -810,7 +951,7 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) 
   const int parity = d->position & 1;
   // The first steps run eagerly (they size the staging buffer and set kernel
   // attributes); later ones replay a captured graph per parity.
-  if (d->c.use_graph && d->steps >= 2) {
+  if (d->c.use_graph && d->steps >= 2 && !d->timeline) {
     if (d->graph[parity] == nullptr) {
       cudaGraph_t graph = nullptr;
       GUFO_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
@@ -842,6 +983,19 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) 
   }
   ++d->position;
   ++d->steps;
+  if (d->timeline) {
+    // Fold this step's marks into the per-stage totals.
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    for (size_t i = 1; i < d->mark_kind.size(); ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, d->marks[i - 1], d->marks[i]);
+      if (d->mark_kind[i] >= 0) {
+        d->stage_ms[d->mark_kind[i]] += ms;
+      }
+    }
+    d->mark_kind.clear();
+    ++d->timeline_steps;
+  }
   if (host_logits != nullptr) {
     GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(d->c.vocab) * 4,
                                   cudaMemcpyDeviceToHost, ctx->stream));
@@ -855,6 +1009,29 @@ int gufo_cuda_decoder_logits_device(gufo_cuda_decoder* d, const float** device_l
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_logits_device: null pointer");
   }
   *device_logits = d->logits;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_timeline(gufo_cuda_decoder* d, int enable, double* stage_ms, int* steps) {
+  if (d == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_timeline: null decoder");
+  }
+  std::lock_guard<std::mutex> lock(d->ctx->mu);
+  if (stage_ms != nullptr) {
+    for (int k = 0; k < GUFO_CUDA_TIMELINE_KINDS; ++k) {
+      stage_ms[k] = d->stage_ms[k];
+    }
+  }
+  if (steps != nullptr) {
+    *steps = d->timeline_steps;
+  }
+  if ((enable != 0) != d->timeline) {
+    d->timeline = enable != 0;
+    for (double& v : d->stage_ms) {
+      v = 0;
+    }
+    d->timeline_steps = 0;
+  }
   return GUFO_CUDA_OK;
 }
 

@@ -6,36 +6,34 @@
 // kept on chip across the retrieval pass (u = (decay S)^T k), the rank-1 update
 // (S' = decay S + k delta^T) and the readout (y = S'^T q), and written once:
 // algorithmic traffic is 2 * dk * dk * 4 bytes per head, the HBM roofline of
-// this kernel. Columns of S evolve independently, so a head is split into
-// column tiles of kTileCols values, one thread block each; the blocks of one
-// head form a thread-block cluster so that the gated RMSNorm over the head's dk
-// outputs is reduced through distributed shared memory without a second pass.
+// this kernel. Columns of S evolve independently
+// (src/models/qwen35/prefill_mixer.cpp:662-667), so one thread block takes one
+// (sequence, value head) and each of its warps one tile of 32 columns.
 //
-// Thread layout (128 threads): jq = tid % 8 owns four adjacent columns (one
-// float4), ig = tid / 8 owns rows ig, ig + 16, ..., so a warp's load of one
-// register covers four 128-byte row segments. A thread keeps its dk/16 float4
-// of S in registers between the passes; only the column sums cross threads
-// (warp shuffles, then shared memory across the four warps).
+// Warp layout: lane = 8 * ig + jq; jq owns four adjacent columns (one float4),
+// ig owns rows ig, ig + 4, ..., so one load instruction of a warp covers four
+// 128-byte row segments. A lane keeps its dk / 4 float4 of S (128 registers at
+// dk = 128) from the loads to the stores: all of a tile's state is requested
+// from HBM at once, the column sums of the two passes need only two shuffle
+// steps, and the block meets just once, for the gated RMSNorm over the head's
+// dk outputs.
 #include "common.cuh"
-
-#include <cooperative_groups.h>
-
-namespace cg = cooperative_groups;
 
 namespace gufo {
 
 constexpr int kTileCols = 32;
-constexpr int kDeltaThreads = 128;
 constexpr int kMaxHeadDim = 128;
-constexpr int kRowGroups = kDeltaThreads / 8;          // 16
-constexpr int kMaxRowsPerThread = kMaxHeadDim / kRowGroups;  // 8
-constexpr int kMaxSeqs = 16;                           // descriptors per launch
+constexpr int kDeltaThreads = kMaxHeadDim;            // one thread per column
+constexpr int kRowGroups = 4;                         // lanes / 8
+constexpr int kMaxRowsPerLane = kMaxHeadDim / kRowGroups;  // 32
+constexpr int kMaxSeqs = 16;                          // descriptors per launch
 
 struct DeltaRuleArgs {
   gufo_cuda_delta_seq seq[kMaxSeqs];
   int key_heads;
   int value_heads;
   int head_dim;
+  int early_state;   // as in LinearArgs below
 };
 
 struct LinearArgs {
@@ -49,6 +47,9 @@ struct LinearArgs {
   const float* ssm_a;
   const float* dt_bias;
   const float* ssm_norm;
+  // When the caller knows that no kernel shortly before this one in the stream
+  // wrote the states, their loads may start ahead of the dependency wait.
+  int early_state;
 };
 
 namespace {
@@ -56,82 +57,58 @@ namespace {
 struct DeltaShared {
   float q[kMaxHeadDim];
   float k[kMaxHeadDim];
-  float v[kTileCols];
-  float part[kDeltaThreads / 32][kTileCols];  // per-warp column sums
-  float y[kTileCols];
+  float v[kMaxHeadDim];
+  float y[kMaxHeadDim];
   float gate[2];                              // decay, beta
-  float norm_part;                            // this tile's sum of y^2
   float scratch[kDeltaThreads / 32];
 };
 
-// Sums a float4 of column partials over the block's 16 row groups; every
-// thread receives the total of its four columns.
-__device__ __forceinline__ float4 ColumnSum(float4 v, DeltaShared& sh, int jq,
-                                            int warp, int lane) {
-  v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, 8);
-  v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, 8);
-  v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, 8);
-  v.w += __shfl_xor_sync(0xFFFFFFFFu, v.w, 8);
-  v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, 16);
-  v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, 16);
-  v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, 16);
-  v.w += __shfl_xor_sync(0xFFFFFFFFu, v.w, 16);
-  __syncthreads();  // the previous use of sh.part is over
-  if (lane < 8) {
-    *reinterpret_cast<float4*>(&sh.part[warp][4 * jq]) = v;
-  }
-  __syncthreads();
-  float4 total = *reinterpret_cast<const float4*>(&sh.part[0][4 * jq]);
-#pragma unroll
-  for (int w = 1; w < kDeltaThreads / 32; ++w) {
-    const float4 o = *reinterpret_cast<const float4*>(&sh.part[w][4 * jq]);
-    total.x += o.x;
-    total.y += o.y;
-    total.z += o.z;
-    total.w += o.w;
-  }
-  return total;
-}
-
-// The delta rule on this block's column tile. sh.q, sh.k, sh.v and sh.gate are
-// ready (a __syncthreads lies between their writes and this call). Leaves the
-// tile's kTileCols outputs in sh.y, visible after the trailing barrier.
 struct StateTile {
-  float4 s[kMaxRowsPerThread];
+  float4 s[kMaxRowsPerLane];
 };
 
-// Issues this thread's loads of the state tile; called first thing so that the
-// HBM latency runs under the prologue.
-__device__ __forceinline__ void LoadTile(StateTile& tile, const float* __restrict__ src,
-                                         int dk, int col0) {
-  const int jq = threadIdx.x & 7;
-  const int ig = threadIdx.x >> 3;
+// Issues this lane's loads of its warp's column tile.
+__device__ __forceinline__ void LoadTile(StateTile& tile, const float* __restrict__ src, int dk,
+                                         int tile_index) {
+  const int lane = threadIdx.x & 31;
+  const int col = tile_index * kTileCols + 4 * (lane & 7);
+  const int ig = lane >> 3;
   const int rows = dk / kRowGroups;
-  const size_t at = static_cast<size_t>(col0 + 4 * jq);
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerThread; ++r) {
+  for (int r = 0; r < kMaxRowsPerLane; ++r) {
     if (r < rows) {
-      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kRowGroups + ig) * dk + at);
+      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kRowGroups + ig) * dk + col);
     }
   }
 }
 
-__device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ dst,
-                                          int dk, int col0, DeltaShared& sh) {
-  const int tid = threadIdx.x;
-  const int jq = tid & 7;
-  const int ig = tid >> 3;
-  const int warp = tid >> 5;
-  const int lane = tid & 31;
+// Sum over the warp's four row groups; every lane gets its columns' totals.
+__device__ __forceinline__ float4 ColumnSum(float4 v) {
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, o);
+    v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, o);
+    v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, o);
+    v.w += __shfl_xor_sync(0xFFFFFFFFu, v.w, o);
+  }
+  return v;
+}
+
+// The delta rule on this warp's column tile. sh.q, sh.k, sh.v and sh.gate are
+// ready. Writes S' to dst and the tile's outputs to sh.y (no barrier).
+__device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ dst, int dk,
+                                          int tile_index, DeltaShared& sh) {
+  const int lane = threadIdx.x & 31;
+  const int col = tile_index * kTileCols + 4 * (lane & 7);
+  const int ig = lane >> 3;
   const int rows = dk / kRowGroups;
   const float decay = sh.gate[0];
   const float beta = sh.gate[1];
-  float4 (&s)[kMaxRowsPerThread] = tile.s;
-  const size_t at = static_cast<size_t>(col0 + 4 * jq);
+  float4 (&s)[kMaxRowsPerLane] = tile.s;
   // Pass 1: u_j = sum_i S_ij * (k_i * decay).
   float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerThread; ++r) {
+  for (int r = 0; r < kMaxRowsPerLane; ++r) {
     if (r < rows) {
       const float ki = sh.k[r * kRowGroups + ig] * decay;
       u.x = fmaf(s[r].x, ki, u.x);
@@ -140,8 +117,8 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
       u.w = fmaf(s[r].w, ki, u.w);
     }
   }
-  u = ColumnSum(u, sh, jq, warp, lane);
-  const float4 v = *reinterpret_cast<const float4*>(&sh.v[4 * jq]);
+  u = ColumnSum(u);
+  const float4 v = *reinterpret_cast<const float4*>(&sh.v[col]);
   float4 delta;
   delta.x = beta * (v.x - u.x);
   delta.y = beta * (v.y - u.y);
@@ -150,7 +127,7 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
   // Pass 2: S'_ij = S_ij * decay + k_i * delta_j; y_j = sum_i S'_ij * q_i.
   float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerThread; ++r) {
+  for (int r = 0; r < kMaxRowsPerLane; ++r) {
     if (r < rows) {
       const int i = r * kRowGroups + ig;
       const float ki = sh.k[i];
@@ -160,52 +137,55 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
       n.y = fmaf(s[r].y, decay, ki * delta.y);
       n.z = fmaf(s[r].z, decay, ki * delta.z);
       n.w = fmaf(s[r].w, decay, ki * delta.w);
-      *reinterpret_cast<float4*>(dst + static_cast<size_t>(i) * dk + at) = n;
+      *reinterpret_cast<float4*>(dst + static_cast<size_t>(i) * dk + col) = n;
       y.x = fmaf(n.x, qi, y.x);
       y.y = fmaf(n.y, qi, y.y);
       y.z = fmaf(n.z, qi, y.z);
       y.w = fmaf(n.w, qi, y.w);
     }
   }
-  y = ColumnSum(y, sh, jq, warp, lane);
-  if (tid < 8) {
-    *reinterpret_cast<float4*>(&sh.y[4 * jq]) = y;
+  y = ColumnSum(y);
+  if (ig == 0) {
+    *reinterpret_cast<float4*>(&sh.y[col]) = y;
   }
-  __syncthreads();
 }
 
-// grid = (dk / kTileCols, value_heads, sequences); gates given.
-__global__ void __launch_bounds__(kDeltaThreads)
+// Gates given: one warp per thread block, grid = (dk / 32, value_heads,
+// sequences). The tiles of a head need nothing from one another here, and
+// several small blocks per SM let one tile's stores overlap another's loads.
+__global__ void __launch_bounds__(32)
 DeltaRuleKernel(const __grid_constant__ DeltaRuleArgs args) {
   __shared__ __align__(16) DeltaShared sh;
   const gufo_cuda_delta_seq& seq = args.seq[blockIdx.z];
   const int head = blockIdx.y;
+  const int tile = blockIdx.x;
   const int dk = args.head_dim;
-  const int col0 = blockIdx.x * kTileCols;
   const int kh = head % args.key_heads;
-  const int tid = threadIdx.x;
+  const int lane = threadIdx.x;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
+  StateTile state;
   GridLaunchDependents();
+  if (args.early_state) {
+    LoadTile(state, seq.state + state_at, dk, tile);
+  }
   GridDependencyWait();
-  StateTile tile;
-  LoadTile(tile, seq.state + state_at, dk, col0);
-  if (tid < dk) {
-    sh.q[tid] = seq.q[kh * dk + tid];
-    sh.k[tid] = seq.k[kh * dk + tid];
+  if (!args.early_state) {
+    LoadTile(state, seq.state + state_at, dk, tile);
   }
-  if (tid < kTileCols) {
-    sh.v[tid] = seq.v[head * dk + col0 + tid];
+  for (int i = lane; i < dk; i += 32) {
+    sh.q[i] = seq.q[kh * dk + i];
+    sh.k[i] = seq.k[kh * dk + i];
   }
-  if (tid == 0) {
+  sh.v[tile * kTileCols + lane] = seq.v[head * dk + tile * kTileCols + lane];
+  if (lane == 0) {
     sh.gate[0] = seq.decay[head];
     sh.gate[1] = seq.beta[head];
   }
-  __syncthreads();
+  __syncwarp();
   float* dst = (seq.state_out != nullptr ? seq.state_out : seq.state) + state_at;
-  DeltaTile(tile, dst, dk, col0, sh);
-  if (tid < kTileCols) {
-    seq.y[head * dk + col0 + tid] = sh.y[tid];
-  }
+  DeltaTile(state, dst, dk, tile, sh);
+  __syncwarp();
+  seq.y[head * dk + tile * kTileCols + lane] = sh.y[tile * kTileCols + lane];
 }
 
 __device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -215,7 +195,7 @@ __device__ __forceinline__ float Softplus(float x) {
 }
 
 // Block-wide sum of one value per thread; result to every thread.
-__device__ __forceinline__ float BlockSum(float v, DeltaShared& sh) {
+__device__ __forceinline__ float BlockSum(float v, DeltaShared& sh, int warps) {
   v = WarpSum(v);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) {
@@ -223,113 +203,113 @@ __device__ __forceinline__ float BlockSum(float v, DeltaShared& sh) {
   }
   __syncthreads();
   float total = 0.f;
-#pragma unroll
-  for (int w = 0; w < kDeltaThreads / 32; ++w) {
+  for (int w = 0; w < warps; ++w) {
     total += sh.scratch[w];
   }
   return total;
 }
 
-// Mixer::Linear for one (sequence, value head, column tile); the blocks of a
-// head are one cluster (cluster dims = (dk / kTileCols, 1, 1)).
+// Mixer::Linear for one (sequence, value head). grid = (value_heads,
+// sequences), dk threads: thread t owns channel / column t of the head.
 __global__ void __launch_bounds__(kDeltaThreads)
 DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   __shared__ __align__(16) DeltaShared sh;
-  cg::cluster_group cluster = cg::this_cluster();
-  const gufo_cuda_linear_seq& seq = args.seq[blockIdx.z];
-  const int head = blockIdx.y;
-  const int tile = blockIdx.x;
-  const int tiles = gridDim.x;
+  const gufo_cuda_linear_seq& seq = args.seq[blockIdx.y];
+  const int head = blockIdx.x;
   const int hk = args.key_heads;
   const int hv = args.value_heads;
   const int dk = args.head_dim;
+  const int warps = dk / 32;
   const int key_dim = hk * dk;
   const int value_dim = hv * dk;
   const int channels = 2 * key_dim + value_dim;
   const int kernel = args.conv_kernel;
   const int window = kernel - 1;
-  const int col0 = tile * kTileCols;
   const int kh = head % hk;
   const int tid = threadIdx.x;
   const float* x = seq.in;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
-  GridLaunchDependents();
-  GridDependencyWait();
   StateTile state_tile;
-  LoadTile(state_tile, seq.ssm + state_at, dk, col0);
+  GridLaunchDependents();
+  if (args.early_state) {
+    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+  }
+  GridDependencyWait();
+  if (!args.early_state) {
+    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+  }
+  // What the epilogue needs, requested now so that it has arrived by then.
+  const float z = x[channels + head * dk + tid];
+  const float norm_w = args.ssm_norm[tid];
 
   // Causal depthwise conv + SiLU of channel ch; also advances that channel's
-  // window when this block is the one that owns it.
-  auto conv = [&](int ch, bool owner) -> float {
+  // window when this block is the one that owns it. All loads of the three
+  // channels are issued before the first store, so they overlap.
+  constexpr int kMaxWindow = 7;
+  struct Taps {
+    float cur;
+    float old[kMaxWindow];
+    float w[kMaxWindow + 1];
+  };
+  auto fetch = [&](int ch, Taps& taps) {
     const float* kw = args.conv + static_cast<size_t>(ch) * kernel;
-    const float cur = x[ch];
-    float acc = kw[window] * cur;
-    for (int t = 0; t < window; ++t) {
-      const float old = seq.conv_in[static_cast<size_t>(t) * channels + ch];
-      acc = fmaf(kw[t], old, acc);
-      if (owner && t > 0) {
-        seq.conv_out[static_cast<size_t>(t - 1) * channels + ch] = old;
+    taps.cur = x[ch];
+#pragma unroll
+    for (int t = 0; t < kMaxWindow; ++t) {
+      if (t < window) {
+        taps.old[t] = seq.conv_in[static_cast<size_t>(t) * channels + ch];
+        taps.w[t] = kw[t];
+      }
+    }
+    taps.w[kMaxWindow] = kw[window];
+  };
+  auto conv = [&](int ch, const Taps& taps, bool owner) -> float {
+    float acc = taps.w[kMaxWindow] * taps.cur;
+#pragma unroll
+    for (int t = 0; t < kMaxWindow; ++t) {
+      if (t < window) {
+        acc = fmaf(taps.w[t], taps.old[t], acc);
+        if (owner && t > 0) {
+          seq.conv_out[static_cast<size_t>(t - 1) * channels + ch] = taps.old[t];
+        }
       }
     }
     if (owner) {
-      seq.conv_out[static_cast<size_t>(window - 1) * channels + ch] = cur;
+      seq.conv_out[static_cast<size_t>(window - 1) * channels + ch] = taps.cur;
     }
     return Silu(acc);
   };
-  // q and k of the key head (every tile needs all dk of each); the window of
-  // those channels is advanced by the first value head that reads the key
-  // head, each tile taking its own kTileCols channels.
-  float qv = 0.f, kv = 0.f;
-  if (tid < dk) {
-    const bool owner = head < hk && tid >= col0 && tid < col0 + kTileCols;
-    qv = conv(kh * dk + tid, owner);
-    kv = conv(key_dim + kh * dk + tid, owner);
-  }
-  if (tid < kTileCols) {
-    sh.v[tid] = conv(2 * key_dim + head * dk + col0 + tid, true);
-  }
-  // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
-  const float qq = BlockSum(qv * qv, sh);
-  const float kk = BlockSum(kv * kv, sh);
-  if (tid < dk) {
-    const float q_inv = 1.0f / sqrtf(qq + 1e-6f);
-    const float k_inv = 1.0f / sqrtf(kk + 1e-6f);
-    sh.q[tid] = qv * (q_inv * (1.0f / sqrtf(static_cast<float>(dk))));
-    sh.k[tid] = kv * k_inv;
-  }
+  // The window of the key head's q and k channels is advanced by the first
+  // value head that reads the key head; every head advances its own v.
+  Taps tq, tk, tv;
+  fetch(kh * dk + tid, tq);
+  fetch(key_dim + kh * dk + tid, tk);
+  fetch(2 * key_dim + head * dk + tid, tv);
+  const float* gates = x + channels + value_dim;  // alpha | beta follow z
+  const float alpha = gates[head], beta = gates[hv + head];
+  const float ssm_a = args.ssm_a[head], dt_bias = args.dt_bias[head];
+  const float qv = conv(kh * dk + tid, tq, head < hk);
+  const float kv = conv(key_dim + kh * dk + tid, tk, head < hk);
+  sh.v[tid] = conv(2 * key_dim + head * dk + tid, tv, true);
   if (tid == 0) {
-    const float* z_end = x + channels + value_dim;  // alpha | beta follow z
-    const float alpha = z_end[head];
-    const float beta = z_end[hv + head];
-    sh.gate[0] = expf(args.ssm_a[head] * Softplus(alpha + args.dt_bias[head]));
+    sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
     sh.gate[1] = Sigmoid(beta);
   }
+  // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
+  const float qq = BlockSum(qv * qv, sh, warps);
+  const float kk = BlockSum(kv * kv, sh, warps);
+  sh.q[tid] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
+  sh.k[tid] = kv * (1.0f / sqrtf(kk + 1e-6f));
   __syncthreads();
 
   float* dst = (seq.ssm_out != nullptr ? seq.ssm_out : seq.ssm) + state_at;
-  DeltaTile(state_tile, dst, dk, col0, sh);
-
+  DeltaTile(state_tile, dst, dk, tid >> 5, sh);
+  __syncwarp();
   // Gated RMSNorm over the head's dk outputs: RMS(o) * w * silu(z).
-  float sq = 0.f;
-  if (tid < kTileCols) {
-    sq = sh.y[tid] * sh.y[tid];
-  }
-  sq = BlockSum(sq, sh);
-  if (tid == 0) {
-    sh.norm_part = sq;
-  }
-  cluster.sync();
-  float total = 0.f;
-  for (int r = 0; r < tiles; ++r) {
-    total += *cluster.map_shared_rank(&sh.norm_part, r);
-  }
+  const float o = sh.y[tid];
+  const float total = BlockSum(o * o, sh, warps);
   const float inv = 1.0f / sqrtf(total / static_cast<float>(dk) + args.rms_eps);
-  if (tid < kTileCols) {
-    const int j = col0 + tid;
-    const float z = x[channels + head * dk + j];
-    seq.y[head * dk + j] = sh.y[tid] * inv * args.ssm_norm[j] * Silu(z);
-  }
-  cluster.sync();  // peers may still be reading this block's shared memory
+  seq.y[head * dk + tid] = o * inv * norm_w * Silu(z);
 }
 
 int CheckHeads(int key_heads, int value_heads, int head_dim) {
@@ -382,8 +362,9 @@ int gufo_cuda_delta_rule_device(gufo_cuda_ctx* ctx,
     args.key_heads = key_heads;
     args.value_heads = value_heads;
     args.head_dim = head_dim;
+    args.early_state = ctx->early_state ? 1 : 0;
     const dim3 grid(head_dim / gufo::kTileCols, value_heads, n);
-    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaRuleKernel, grid, dim3(gufo::kDeltaThreads), 0,
+    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaRuleKernel, grid, dim3(32), 0,
                                          ctx->stream, 1, args));
     ctx->launches.fetch_add(1);
   }
@@ -487,7 +468,7 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_linear: unknown layer handle");
   }
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
-  return gufo::EnqueueDeltaNetLinear(ctx, it->second, seqs, nseq);
+  return gufo::EnqueueDeltaNetLinear(ctx, it->second, seqs, nseq, ctx->early_state);
 }
 
 }  // extern "C"
@@ -495,7 +476,7 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
 namespace gufo {
 
 int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
-                          const gufo_cuda_linear_seq* seqs, int nseq) {
+                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state) {
   for (int s0 = 0; s0 < nseq; s0 += gufo::kMaxSeqs) {
     const int n = nseq - s0 < gufo::kMaxSeqs ? nseq - s0 : gufo::kMaxSeqs;
     gufo::LinearArgs args{};
@@ -511,9 +492,9 @@ int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
     args.ssm_a = l.ssm_a;
     args.dt_bias = l.dt_bias;
     args.ssm_norm = l.ssm_norm;
-    const int tiles = l.head_dim / gufo::kTileCols;
-    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaNetLinearKernel, dim3(tiles, l.value_heads, n),
-                                         dim3(gufo::kDeltaThreads), 0, ctx->stream, tiles, args));
+    args.early_state = early_state ? 1 : 0;
+    GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaNetLinearKernel, dim3(l.value_heads, n),
+                                         dim3(l.head_dim), 0, ctx->stream, 1, args));
     ctx->launches.fetch_add(1);
   }
   return GUFO_CUDA_OK;

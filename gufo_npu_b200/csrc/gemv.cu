@@ -172,28 +172,55 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     rest.y = y;
     const bool fast4 = !ctx->force_general && Q4KFastFits(base.cols, m);
     const bool fast6 = !ctx->force_general && Q6KFastFits(base.cols, m);
-    const uint8_t* image = nullptr;
-    int image_group = 0;   // group size the staged image carries sums for
-    for (int p = 0; p < base.nparts; ++p) {
-      const GemvPart& part = base.parts[p];
-      const bool q4 = fast4 && part.type == GUFO_CUDA_Q4_K;
-      const bool q6 = fast6 && part.type == GUFO_CUDA_Q6_K;
-      if (q4 || q6) {
-        const int group = q4 ? 32 : 16;
-        if (image_group != group) {
+    // Parts of one block format share one staged image and one launch.
+    for (int type : {GUFO_CUDA_Q4_K, GUFO_CUDA_Q6_K}) {
+      if (!(type == GUFO_CUDA_Q4_K ? fast4 : fast6)) {
+        continue;
+      }
+      FastGemvArgs args{};
+      args.cols = base.cols;
+      args.y = y;
+      args.y_stride = base.y_stride;
+      args.tokens = m;
+      args.prologue = kPrologueImage;
+      auto flush = [&]() -> int {
+        if (args.nparts == 0) {
+          return GUFO_CUDA_OK;
+        }
+        const int rc = type == GUFO_CUDA_Q4_K ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args);
+        args.nparts = 0;
+        return rc;
+      };
+      for (int p = 0; p < base.nparts; ++p) {
+        const GemvPart& part = base.parts[p];
+        if (part.type != type) {
+          continue;
+        }
+        if (args.image == nullptr) {
           // High nibbles of Q4_K reach the MMA as 16 q: fold 1/16 into the factors.
-          const int rc = StageActivations(ctx, x, m, base.cols, group, q4 ? 1.0f / 16.0f : 1.0f, &image);
+          const int rc = StageActivations(ctx, x, m, base.cols, type == GUFO_CUDA_Q4_K ? 32 : 16,
+                                          type == GUFO_CUDA_Q4_K ? 1.0f / 16.0f : 1.0f, &args.image);
           if (rc != GUFO_CUDA_OK) {
             return rc;
           }
-          image_group = group;
         }
-        const FastGemvArgs args{part.data, part.rows, base.cols, part.row_bytes, image, y,
-                                base.y_stride, part.out_offset, m};
-        const int rc = q4 ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args);
-        if (rc != GUFO_CUDA_OK) {
-          return rc;
+        args.row_bytes = part.row_bytes;
+        args.parts[args.nparts++] = {part.data, part.rows, part.out_offset};
+        if (args.nparts == kFastMaxParts) {
+          const int rc = flush();
+          if (rc != GUFO_CUDA_OK) {
+            return rc;
+          }
         }
+      }
+      const int rc = flush();
+      if (rc != GUFO_CUDA_OK) {
+        return rc;
+      }
+    }
+    for (int p = 0; p < base.nparts; ++p) {
+      const GemvPart& part = base.parts[p];
+      if ((fast4 && part.type == GUFO_CUDA_Q4_K) || (fast6 && part.type == GUFO_CUDA_Q6_K)) {
         continue;
       }
       rest.parts[rest.nparts++] = part;

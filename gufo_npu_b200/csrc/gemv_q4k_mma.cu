@@ -187,7 +187,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   // Column g of the first MMA column group; lanes past the last token's planes
   // wrap onto live ones (see MultiplyPair).
   const uint8_t* lane_plane = smem + (g % kNCols) * l.plane_stride + 8 * t;
-  const int row_tiles = (a.rows + 15) >> 4;
+  const int row_tiles = TotalTiles(a);
   const int stride = gridDim.x;
   const int my_tiles = (row_tiles - static_cast<int>(blockIdx.x) + stride - 1) / stride;
   const int my_slabs = my_tiles * slabs_per_tile;
@@ -207,12 +207,14 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
       const int nblk = min(kSlabBlocks, blocks - s * kSlabBlocks);
       const int chunks = nblk * (kQ4KBytes / 16);
       const uint32_t dst0 = ring_base + (q % kStages) * kSlabBytes;
+      int part, local;
+      LocateTile(a, static_cast<int>(blockIdx.x) + n * stride, &part, &local);
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         const int r = 2 * warp + rr;
         // Rows past the end repeat the last row; their sums are never stored.
-        const int row = min((static_cast<int>(blockIdx.x) + n * stride) * 16 + r, a.rows - 1);
-        const uint8_t* src = a.w + static_cast<size_t>(row) * a.row_bytes + s * (kSlabBlocks * kQ4KBytes);
+        const int row = min(local * 16 + r, a.parts[part].rows - 1);
+        const uint8_t* src = a.parts[part].w + static_cast<size_t>(row) * a.row_bytes + s * (kSlabBlocks * kQ4KBytes);
         const uint32_t dst = dst0 + r * kSlabRowBytes;
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
@@ -233,13 +235,19 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   GridLaunchDependents();
   // The weights above never depend on earlier kernels; the image and y do.
   GridDependencyWait();
-  {
+  if (a.prologue == kPrologueImage) {
     const uint32_t base = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
     for (int at = threadIdx.x * 16; at < l.bytes; at += kFastThreads * 16) {
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(base + at), "l"(a.image + at)
                    : "memory");
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
+  } else {
+    // The fp32 scratch borrows the ring's last stage (first requested after
+    // the barrier below) when it fits, else its own space behind the ring.
+    float* xs = reinterpret_cast<float*>(a.cols * 4 <= kSlabBytes ? ring + (kStages - 1) * kSlabBytes
+                                                                    : ring + kStages * kSlabBytes);
+    FillImage(a, l, smem, xs, 1.0f / 16.0f);
   }
 
   Accum<TOKENS> acc;
@@ -255,18 +263,20 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   };
   // Sums the eight warps' partials of tile n (exchange buffer n & 1) into y.
   auto gather = [&](int n) {
+    int part, local;
+    LocateTile(a, static_cast<int>(blockIdx.x) + n * stride, &part, &local);
     for (int o = threadIdx.x; o < 16 * TOKENS; o += kFastThreads) {
       const int k = o % TOKENS;
       const int r = o / TOKENS;
-      const int row = (static_cast<int>(blockIdx.x) + n * stride) * 16 + r;
-      if (row < a.rows) {
+      const int row = local * 16 + r;
+      if (row < a.parts[part].rows) {
         float total = 0.f;
 #pragma unroll
         for (int w = 0; w < kFastWarps; ++w) {
           const float* part = exchange + ((n & 1) * kFastWarps + w) * kTileFloats + r * kRowFloats;
           total += (part[k * kLimbs] + part[k * kLimbs + 1] + part[k * kLimbs + 2]) - part[kNCols + k];
         }
-        a.y[static_cast<size_t>(k) * a.y_stride + a.y_offset + row] = total;
+        a.y[static_cast<size_t>(k) * a.y_stride + a.parts[part].y_offset + row] = total;
       }
     }
   };
@@ -332,7 +342,8 @@ size_t SharedBytes(int cols) {
   const ImageLayout l = MakeImageLayout(TOKENS, cols, 32);
   return static_cast<size_t>(l.bytes) +
          static_cast<size_t>(2) * kFastWarps * 16 * (TOKENS * kLimbs + TOKENS) * 4 +
-         static_cast<size_t>(kStages) * kSlabBytes;
+         static_cast<size_t>(kStages) * kSlabBytes +
+         (static_cast<size_t>(cols) * 4 > static_cast<size_t>(kSlabBytes) ? static_cast<size_t>(cols) * 4 : 0);
 }
 
 template <int TOKENS, int PER_SM>
@@ -347,7 +358,13 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, kFastMaxShared));
     configured[ctx->device & 15] = true;
   }
-  const int row_tiles = (args.rows + 15) / 16;
+  int row_tiles = 0;
+  for (int p = 0; p < args.nparts; ++p) {
+    row_tiles += (args.parts[p].rows + 15) / 16;
+  }
+  if (args.prologue != kPrologueImage && args.tokens != 1) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: fused prologues take one token");
+  }
   const int slots = ctx->sm_count * PER_SM;
   const int grid = row_tiles < slots ? row_tiles : slots;
   GUFO_CUDA_TRY(LaunchOverlapped(GemvQ4KMma<TOKENS, PER_SM>, dim3(grid), dim3(kFastThreads), smem,

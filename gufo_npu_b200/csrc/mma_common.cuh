@@ -109,6 +109,169 @@ __device__ __forceinline__ void CopyImageToShared(uint8_t* dst, const uint8_t* s
   __syncthreads();
 }
 
+// Converts one 256-value block of one token into the image at `image` (shared
+// or global memory): the calling warp's lane holds values 8 * lane .. + 7 of the
+// block in v. Writes the three byte planes, the group sums and the column
+// factors of block `b`.
+__device__ __forceinline__ void StageBlock(const float (&v)[8], int lane, int tok, int b,
+                                           const ImageLayout& l, uint8_t* image, float extra) {
+  // Largest magnitude by integer compare of the bit patterns, so that a NaN
+  // (above every finite pattern) is not lost.
+  uint32_t top = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    top = max(top, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    top = max(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
+  }
+  int e = static_cast<int>(top >> 23);  // biased exponent of the maximum
+  const bool finite = e != 255;
+  e = e < 22 ? 22 : e;
+  // |x| < 2^(e - 126), so x * 2^(148 - e) stays below 2^22 in magnitude.
+  const float up = __uint_as_float(static_cast<uint32_t>(275 - e) << 23);
+  const float down = finite ? __uint_as_float(static_cast<uint32_t>(e - 21) << 23)
+                            : __uint_as_float(0x7FC00000u);
+  // xi + 0x808080 has the balanced digits of xi, each offset by 128, in its
+  // three low bytes; flipping the offset bits leaves the signed bytes.
+  uint32_t z[8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int xi = finite ? __float2int_rn(v[i] * up) : 0;
+    z[i] = static_cast<uint32_t>(xi + 0x808080) ^ 0x808080u;
+    sum += v[i];
+  }
+#pragma unroll
+  for (int limb = 0; limb < kLimbs; ++limb) {
+    const uint32_t pick = 0x0040u + 0x11u * limb;  // byte `limb` of both operands
+    const uint32_t w0 = __byte_perm(__byte_perm(z[0], z[1], pick), __byte_perm(z[2], z[3], pick), 0x5410u);
+    const uint32_t w1 = __byte_perm(__byte_perm(z[4], z[5], pick), __byte_perm(z[6], z[7], pick), 0x5410u);
+    uint8_t* plane = image + static_cast<size_t>(tok * kLimbs + limb) * l.plane_stride;
+    *reinterpret_cast<uint2*>(plane + b * kSuperBlock + lane * 8) = make_uint2(w0, w1);
+  }
+  // Group sums of the fp32 values: the lanes of one group are adjacent.
+  const int lanes_per_group = l.group / 8;  // 4 (groups of 32) or 2 (of 16)
+  for (int o = 1; o < lanes_per_group; o <<= 1) {
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+  }
+  if ((lane & (lanes_per_group - 1)) == 0) {
+    float* sums = reinterpret_cast<float*>(image + l.sums_at);
+    sums[static_cast<size_t>(tok) * (l.cols / l.group) + b * (kSuperBlock / l.group) +
+         lane / lanes_per_group] = sum;
+  }
+  if (lane < kLimbs) {
+    const float limb = lane == 0 ? 1.f : (lane == 1 ? 256.f : 65536.f);
+    float* scale = reinterpret_cast<float*>(image + l.scale_at);
+    scale[b * l.kcols + tok * kLimbs + lane] = down * limb * extra;
+  }
+}
+
+__device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + expf(-x))); }
+
+// Builds the one-token image in shared memory at `image` from the launch's
+// fused input (prologue != kPrologueImage). `xs` is a shared fp32 scratch of
+// `cols` values. Ends with a __syncthreads. kFastThreads threads.
+__device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
+                                          uint8_t* image, float* xs, float extra) {
+  __shared__ float reduce[kFastWarps];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n = a.cols;
+  const bool first = blockIdx.x == 0;
+  if (a.prologue == kPrologueResNorm) {
+    // vec::RmsNorm (src/core/vec.hpp:57-63) of the residual stream after its
+    // pending add (src/models/qwen35/decoder.cpp:493,504-508).
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < n; i += kFastThreads) {
+      float v = a.h_in[i];
+      if (a.delta != nullptr) {
+        v += a.delta[i];
+      }
+      xs[i] = v;
+      sq = fmaf(v, v, sq);
+    }
+    sq = WarpSum(sq);
+    if (lane == 0) {
+      reduce[warp] = sq;
+    }
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < kFastWarps; ++w) {
+      total += reduce[w];
+    }
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + a.eps);
+    for (int i = threadIdx.x; i < n; i += kFastThreads) {
+      const float v = xs[i];
+      const float out = v * inv * a.norm_w[i];
+      xs[i] = out;
+      if (first) {
+        a.h_out[i] = v;
+        if (a.normed_out != nullptr) {
+          a.normed_out[i] = out;
+        }
+      }
+    }
+    if (first && threadIdx.x == 0 && a.advance != nullptr) {
+      *a.advance += 1;
+    }
+  } else if (a.prologue == kPrologueSwiGlu) {
+    for (int i = threadIdx.x; i < n; i += kFastThreads) {
+      xs[i] = SiluFast(a.x[i]) * a.x[n + i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += kFastThreads) {
+      xs[i] = a.x[i];
+    }
+  }
+  // Columns without a token keep a zero factor.
+  float* scale = reinterpret_cast<float*>(image + l.scale_at);
+  const int blocks = n / kSuperBlock;
+  for (int i = threadIdx.x; i < blocks * l.kcols; i += kFastThreads) {
+    if (i % l.kcols >= kLimbs) {
+      scale[i] = 0.f;
+    }
+  }
+  __syncthreads();
+  for (int b = warp; b < blocks; b += kFastWarps) {
+    const float4 v0 = *reinterpret_cast<const float4*>(xs + b * kSuperBlock + lane * 8);
+    const float4 v1 = *reinterpret_cast<const float4*>(xs + b * kSuperBlock + lane * 8 + 4);
+    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    StageBlock(v, lane, 0, b, l, image, extra);
+  }
+  __syncthreads();
+}
+
+// Tiles of 16 rows are numbered across the parts of a launch, each part
+// rounded up to whole tiles.
+__device__ __forceinline__ int TotalTiles(const FastGemvArgs& a) {
+  int tiles = 0;
+#pragma unroll
+  for (int p = 0; p < kFastMaxParts; ++p) {
+    if (p < a.nparts) {
+      tiles += (a.parts[p].rows + 15) >> 4;
+    }
+  }
+  return tiles;
+}
+
+// Part and tile-within-part of global tile `tile`.
+__device__ __forceinline__ void LocateTile(const FastGemvArgs& a, int tile, int* part, int* local) {
+  int p = 0;
+#pragma unroll
+  for (int i = 0; i < kFastMaxParts - 1; ++i) {
+    const int tiles = (a.parts[i].rows + 15) >> 4;
+    if (p == i && i + 1 < a.nparts && tile >= tiles) {
+      tile -= tiles;
+      p = i + 1;
+    }
+  }
+  *part = p;
+  *local = tile;
+}
+
 // Byte `i` (compile-time) of a word, zero extended.
 template <int I>
 __device__ __forceinline__ int ByteAt(uint32_t w) {

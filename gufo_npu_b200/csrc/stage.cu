@@ -45,56 +45,7 @@ StageKernel(const __grid_constant__ StageArgs a) {
   const float4 v0 = *reinterpret_cast<const float4*>(xp);
   const float4 v1 = *reinterpret_cast<const float4*>(xp + 4);
   const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-  // Largest magnitude by integer compare of the bit patterns, so that a NaN
-  // (above every finite pattern) is not lost.
-  uint32_t top = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    top = max(top, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    top = max(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
-  }
-  int e = static_cast<int>(top >> 23);  // biased exponent of the maximum
-  const bool finite = e != 255;
-  e = e < 22 ? 22 : e;
-  // |x| < 2^(e - 126), so x * 2^(148 - e) stays below 2^22 in magnitude.
-  const float up = __uint_as_float(static_cast<uint32_t>(275 - e) << 23);
-  const float down = finite ? __uint_as_float(static_cast<uint32_t>(e - 21) << 23)
-                            : __uint_as_float(0x7FC00000u);
-  // xi + 0x808080 has the balanced digits of xi, each offset by 128, in its
-  // three low bytes; flipping the offset bits leaves the signed bytes.
-  uint32_t z[8];
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int xi = finite ? __float2int_rn(v[i] * up) : 0;
-    z[i] = static_cast<uint32_t>(xi + 0x808080) ^ 0x808080u;
-    sum += v[i];
-  }
-#pragma unroll
-  for (int limb = 0; limb < kLimbs; ++limb) {
-    const uint32_t pick = 0x0040u + 0x11u * limb;  // byte `limb` of both operands
-    const uint32_t w0 = __byte_perm(__byte_perm(z[0], z[1], pick), __byte_perm(z[2], z[3], pick), 0x5410u);
-    const uint32_t w1 = __byte_perm(__byte_perm(z[4], z[5], pick), __byte_perm(z[6], z[7], pick), 0x5410u);
-    uint8_t* plane = a.image + static_cast<size_t>(tok * kLimbs + limb) * l.plane_stride;
-    *reinterpret_cast<uint2*>(plane + b * kSuperBlock + lane * 8) = make_uint2(w0, w1);
-  }
-  // Group sums of the fp32 values: the lanes of one group are adjacent.
-  const int lanes_per_group = l.group / 8;  // 4 (groups of 32) or 2 (of 16)
-  for (int o = 1; o < lanes_per_group; o <<= 1) {
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
-  }
-  if ((lane & (lanes_per_group - 1)) == 0) {
-    float* sums = reinterpret_cast<float*>(a.image + l.sums_at);
-    sums[static_cast<size_t>(tok) * (l.cols / l.group) + b * (kSuperBlock / l.group) +
-         lane / lanes_per_group] = sum;
-  }
-  if (lane < kLimbs) {
-    const float limb = lane == 0 ? 1.f : (lane == 1 ? 256.f : 65536.f);
-    scale[b * l.kcols + tok * kLimbs + lane] = down * limb * a.extra;
-  }
+  StageBlock(v, lane, tok, b, l, a.image, a.extra);
 }
 
 }  // namespace
@@ -200,8 +151,8 @@ extern "C" int gufo_cuda_matmul_q4k_static_device(gufo_cuda_ctx* ctx, const void
   GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::StageKernel, dim3((items + gufo::kFastWarps - 1) / gufo::kFastWarps),
                                        dim3(gufo::kFastThreads), 0, ctx->stream, 1, stage));
   ctx->launches.fetch_add(1);
-  const gufo::FastGemvArgs args{static_cast<const uint8_t*>(device_weights), static_cast<int>(rows),
-                                static_cast<int>(cols), static_cast<int>(gufo::RowBytes(GUFO_CUDA_Q4_K, cols)),
-                                image, device_y, static_cast<int>(rows), 0, tokens};
+  const gufo::FastGemvArgs args = gufo::ImageGemvArgs(
+      static_cast<const uint8_t*>(device_weights), static_cast<int>(rows), static_cast<int>(cols),
+      static_cast<int>(gufo::RowBytes(GUFO_CUDA_Q4_K, cols)), image, device_y, static_cast<int>(rows), 0, tokens);
   return gufo::LaunchGemvQ4KFast(ctx, args);
 }

@@ -74,6 +74,10 @@ int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx);
 const char* gufo_cuda_last_error(const gufo_cuda_ctx* ctx);
 /* Tuning and test switches, by name. "general_gemv" = 1 routes every product
  * through the general (non tensor-core) kernel; 0 (default) picks per part.
+ * "deltanet_early_state" = 1 is the caller's promise that the DeltaNet states it
+ * passes were not written by the two kernels enqueued just before the call
+ * (true when each state is touched once per decode step): the kernels then
+ * request the state ahead of their dependency on the previous kernel.
  * "reuse_image" = 1 is a timing aid: products skip the staging of x and
  * multiply against the previously staged activations. */
 int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value);
@@ -360,6 +364,25 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* decoder, int token,
 int gufo_cuda_decoder_logits_device(gufo_cuda_decoder* decoder,
                                     const float** device_logits);
 int gufo_cuda_decoder_position(const gufo_cuda_decoder* decoder);
+/* Device time per stage of the step, by CUDA events between the stages: the
+ * split the reference's NpuDecoder::Timeline keeps
+ * (src/models/qwen35_2b/npu_decoder.hpp:121-154). While enabled, steps are
+ * launched eagerly (no graph replay). The call returns the totals in
+ * milliseconds and the number of steps accumulated so far (either pointer may
+ * be NULL), then switches collection on or off; switching clears the totals. */
+enum {
+  GUFO_CUDA_TIMELINE_EMBED = 0,
+  GUFO_CUDA_TIMELINE_IN = 1,        /* norm + kLinearIn / kAttentionIn */
+  GUFO_CUDA_TIMELINE_DELTANET = 2,
+  GUFO_CUDA_TIMELINE_ATTENTION = 3,
+  GUFO_CUDA_TIMELINE_OUT = 4,       /* kMixerOut */
+  GUFO_CUDA_TIMELINE_FFN_IN = 5,    /* residual + norm + kFfnIn */
+  GUFO_CUDA_TIMELINE_FFN_DOWN = 6,  /* SwiGLU + kFfnDown */
+  GUFO_CUDA_TIMELINE_LM_HEAD = 7,   /* residual + norm + kLmHead */
+  GUFO_CUDA_TIMELINE_KINDS = 8
+};
+int gufo_cuda_decoder_timeline(gufo_cuda_decoder* decoder, int enable,
+                               double* stage_ms, int* steps);
 /* Copies DeltaNet layer `layer`'s conv window [conv_kernel - 1][channels] and
  * state [value heads][dk][dk] to the host (either may be NULL): the checkpoint
  * read of src/models/qwen35/state_capture.hpp:8-14. */
