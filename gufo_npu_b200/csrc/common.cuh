@@ -123,6 +123,10 @@ struct FastGemvArgs {
   float* h_out;          //   h_in + delta, written by block 0 (must not alias h_in)
   float* normed_out;     //   the normed vector, written by block 0 (may be null)
   int* advance;          //   incremented once by block 0 (may be null)
+  // Thread blocks per 16-row tile (a cluster): block r of a cluster takes the
+  // slabs r, r + ksplit, ... and the partial sums meet in block 0's shared
+  // memory. Set by the launcher for matrices with few rows.
+  int ksplit;
 };
 
 // A single-part launch against a staged image.
@@ -241,6 +245,81 @@ cudaError_t LaunchOverlapped(void (*kernel)(KernelArgs...), dim3 grid, dim3 bloc
   config.attrs = attr;
   config.numAttrs = n;
   return cudaLaunchKernelEx(&config, kernel, std::forward<Args>(args)...);
+}
+
+// How many blocks of `kernel` (in clusters of `cluster_x`) the device holds at
+// once with `smem` bytes of dynamic shared memory each. Asked of the runtime
+// once per (device, smem, cluster) and remembered; 0 when the query fails.
+template <typename Kernel>
+int ResidentBlocks(Kernel kernel, int device, int threads, size_t smem, int cluster_x) {
+  struct Entry {
+    int device;
+    size_t smem;
+    int cluster;
+    int blocks;
+  };
+  static Entry cache[32];
+  static int cached = 0;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  for (int i = 0; i < cached; ++i) {
+    if (cache[i].device == device && cache[i].smem == smem && cache[i].cluster == cluster_x) {
+      return cache[i].blocks;
+    }
+  }
+  int blocks = 0;
+  if (cluster_x > 1) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(cluster_x * 64);
+    config.blockDim = dim3(threads);
+    config.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = cluster_x;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    config.attrs = &attr;
+    config.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    blocks = clusters * cluster_x;
+  } else {
+    int per_sm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, smem) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) {
+      cudaGetLastError();
+      per_sm = 0;
+    }
+    blocks = per_sm * sms;
+  }
+  if (cached < 32) {
+    cache[cached++] = Entry{device, smem, cluster_x, blocks};
+  }
+  return blocks;
+}
+
+// Picks how many blocks share a tile's slabs (1, 2, 3 or 4: the largest that
+// still lets every tile run at once) and the grid for it.
+template <typename Kernel>
+void PlanFastGrid(Kernel kernel, int device, int threads, size_t smem, int row_tiles, int slabs,
+                  int* ksplit, int* grid) {
+  for (int ks = slabs < 4 ? slabs : 4; ks >= 2; --ks) {
+    const int resident = ResidentBlocks(kernel, device, threads, smem, ks);
+    if (row_tiles * ks <= resident) {
+      *ksplit = ks;
+      *grid = row_tiles * ks;
+      return;
+    }
+  }
+  int resident = ResidentBlocks(kernel, device, threads, smem, 1);
+  if (resident <= 0) {
+    resident = 1;
+  }
+  *ksplit = 1;
+  *grid = row_tiles < resident ? row_tiles : resident;
 }
 
 // ---- device helpers ------------------------------------------------------

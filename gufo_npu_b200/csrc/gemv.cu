@@ -182,7 +182,12 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
       args.y = y;
       args.y_stride = base.y_stride;
       args.tokens = m;
-      args.prologue = kPrologueImage;
+      // One token: every thread block stages x itself, which saves the staging
+      // kernel (it reads x with 16-byte loads); more tokens share one staged image.
+      const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+      args.prologue = m == 1 && aligned && !ctx->reuse_image ? kProloguePlain : kPrologueImage;
+      args.x = x;
+      bool staged = false;
       auto flush = [&]() -> int {
         if (args.nparts == 0) {
           return GUFO_CUDA_OK;
@@ -196,7 +201,8 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
         if (part.type != type) {
           continue;
         }
-        if (args.image == nullptr) {
+        if (args.prologue == kPrologueImage && !staged) {
+          staged = true;
           // High nibbles of Q4_K reach the MMA as 16 q: fold 1/16 into the factors.
           const int rc = StageActivations(ctx, x, m, base.cols, type == GUFO_CUDA_Q4_K ? 32 : 16,
                                           type == GUFO_CUDA_Q4_K ? 1.0f / 16.0f : 1.0f, &args.image);

@@ -20,6 +20,8 @@
 // multiplied twice, against B fragments in which the other group's lanes read
 // a plane of zeros; every product then holds one group's 16 dots and takes
 // that group's int8 scale.
+#include <cooperative_groups.h>
+
 #include "mma_common.cuh"
 
 namespace gufo {
@@ -195,6 +197,8 @@ template <int TOKENS, int PER_SM>
 __global__ void __launch_bounds__(kFastThreads, PER_SM)
 GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
   extern __shared__ __align__(16) uint8_t smem[];
+  // Where the blocks of a cluster leave their sums for block 0: [2][8][16][TOKENS].
+  __shared__ float peers[2 * 8 * 16 * TOKENS];
   constexpr int kNB = Accum<TOKENS>::kNB;
   constexpr int kNCols = TOKENS * kLimbs;
   constexpr int kRowFloats = kNCols + TOKENS;   // per row in the exchange buffer
@@ -222,19 +226,24 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
   const uint8_t* lane_first = t < 2 ? plane : none;
   const uint8_t* lane_second = t < 2 ? none : plane;
   const int row_tiles = TotalTiles(a);
-  const int stride = gridDim.x;
-  const int my_tiles = (row_tiles - static_cast<int>(blockIdx.x) + stride - 1) / stride;
-  const int my_slabs = my_tiles * slabs_per_tile;
+  // With ksplit > 1 a cluster of ksplit blocks shares each tile.
+  const int ks = a.ksplit > 1 ? a.ksplit : 1;
+  const int rank = static_cast<int>(blockIdx.x) % ks;
+  const int slot = static_cast<int>(blockIdx.x) / ks;
+  const int stride = static_cast<int>(gridDim.x) / ks;
+  const int my_tiles = (row_tiles - slot + stride - 1) / stride;
+  const int slabs_mine = (slabs_per_tile - rank + ks - 1) / ks;
+  const int my_slabs = my_tiles * slabs_mine;
 
   // Requests the next slab: warp w copies rows 2w and 2w + 1, a lane the
   // 16-byte chunks lane, lane + 32, ... of the row's run.
   const uint32_t ring_base = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
-  int req_n = 0, req_s = 0;
+  int req_n = 0, req_s = 0;   // tile and own-slab index of the next request
   auto request = [&](int q) {
     if (q < my_slabs) {
       const int n = req_n;
-      const int s = req_s;
-      if (++req_s == slabs_per_tile) {
+      const int s = rank + req_s * ks;
+      if (++req_s == slabs_mine) {
         req_s = 0;
         ++req_n;
       }
@@ -242,7 +251,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
       const int chunks = (min(kSlabDataBytes, a.row_bytes - s * kSlabDataBytes) + 15) / 16;
       const uint32_t dst0 = ring_base + (q % kStages) * kSlabBytes;
       int part, local;
-      LocateTile(a, static_cast<int>(blockIdx.x) + n * stride, &part, &local);
+      LocateTile(a, slot + n * stride, &part, &local);
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         const int r = 2 * warp + rr;
@@ -280,11 +289,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    // The fp32 scratch borrows the ring's last stage (first requested after
-    // the barrier below) when it fits, else its own space behind the ring.
-    float* xs = reinterpret_cast<float*>(a.cols * 4 <= kSlabBytes ? ring + (kStages - 1) * kSlabBytes
-                                                                    : ring + kStages * kSlabBytes);
-    FillImage(a, l, smem, xs, 1.0f);
+    FillImage(a, l, smem, 1.0f);
   }
 
   Accum<TOKENS> acc;
@@ -298,27 +303,47 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
       acc.off[k] = 0.f;
     }
   };
-  // Sums the eight warps' partials of tile n (exchange buffer n & 1) into y.
+  // Sums the eight warps' partials of tile n (exchange buffer n & 1); with a
+  // cluster, block 0 then adds the blocks' sums. One output per thread.
+  cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
   auto gather = [&](int n) {
     int part, local;
-    LocateTile(a, static_cast<int>(blockIdx.x) + n * stride, &part, &local);
-    for (int o = threadIdx.x; o < 16 * TOKENS; o += kFastThreads) {
-      const int k = o % TOKENS;
-      const int r = o / TOKENS;
-      const int row = local * 16 + r;
-      if (row < a.parts[part].rows) {
-        float total = 0.f;
+    LocateTile(a, slot + n * stride, &part, &local);
+    const int o = threadIdx.x;
+    const int k = o % TOKENS;
+    const int r = (o / TOKENS) & 15;
+    const int row = local * 16 + r;
+    const bool live = o < 16 * TOKENS && row < a.parts[part].rows;
+    float total = 0.f;
+    if (o < 16 * TOKENS) {
 #pragma unroll
-        for (int w = 0; w < kFastWarps; ++w) {
-          const float* part = exchange + ((n & 1) * kFastWarps + w) * kTileFloats + r * kRowFloats;
-          total += (part[k * kLimbs] + part[k * kLimbs + 1] + part[k * kLimbs + 2]) - part[kNCols + k];
-        }
-        a.y[static_cast<size_t>(k) * a.y_stride + a.parts[part].y_offset + row] = total;
+      for (int w = 0; w < kFastWarps; ++w) {
+        const float* from = exchange + ((n & 1) * kFastWarps + w) * kTileFloats + r * kRowFloats;
+        total += (from[k * kLimbs] + from[k * kLimbs + 1] + from[k * kLimbs + 2]) - from[kNCols + k];
       }
+    }
+    if (ks > 1) {
+      float* slot_in_leader = cluster.map_shared_rank(peers, 0) + ((n & 1) * 8 + rank) * 16 * TOKENS;
+      if (o < 16 * TOKENS) {
+        slot_in_leader[o] = total;
+      }
+      cluster.sync();
+      if (rank != 0) {
+        return;
+      }
+      total = 0.f;
+      if (o < 16 * TOKENS) {
+        for (int p = 0; p < ks; ++p) {
+          total += peers[((n & 1) * 8 + p) * 16 * TOKENS + o];
+        }
+      }
+    }
+    if (live) {
+      a.y[static_cast<size_t>(k) * a.y_stride + a.parts[part].y_offset + row] = total;
     }
   };
   clear();
-  int n = 0, s = 0;   // tile and slab being multiplied
+  int n = 0, s = 0;   // tile and own-slab index being multiplied
   for (int q = 0; q < my_slabs; ++q) {
     // Slab q (and, the first time, the image) has landed for this thread;
     // the barrier makes every thread's copies visible and frees slab q - 1.
@@ -332,13 +357,14 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     if (s == 0 && n > 0) {
       gather(n - 1);   // written before the barrier above
     }
-    const int b = s * kSlabBlocks + warp;
+    const int slab = rank + s * ks;
+    const int b = slab * kSlabBlocks + warp;
     if (b < blocks) {
       Q6KUnit unit;
-      LoadUnit(unit, ring + (q % kStages) * kSlabBytes, warp, min(kSlabBlocks, blocks - s * kSlabBlocks), g, t);
+      LoadUnit(unit, ring + (q % kStages) * kSlabBytes, warp, min(kSlabBlocks, blocks - slab * kSlabBlocks), g, t);
       MultiplyUnit<TOKENS>(unit, b, g, t, lane_first, lane_second, l, col_scale, sums, acc);
     }
-    if (s == slabs_per_tile - 1) {
+    if (s == slabs_mine - 1) {
       // Hand this tile's partial sums to the block.
       float* tile = exchange + ((n & 1) * kFastWarps + warp) * kTileFloats;
 #pragma unroll
@@ -379,8 +405,7 @@ size_t SharedBytes(int cols) {
   const ImageLayout l = MakeImageLayout(TOKENS, cols, 16);
   return static_cast<size_t>(l.bytes) + l.plane_stride +
          static_cast<size_t>(2) * kFastWarps * 16 * (TOKENS * kLimbs + TOKENS) * 4 +
-         static_cast<size_t>(kStages) * kSlabBytes +
-         (static_cast<size_t>(cols) * 4 > static_cast<size_t>(kSlabBytes) ? static_cast<size_t>(cols) * 4 : 0);
+         static_cast<size_t>(kStages) * kSlabBytes;
 }
 
 template <int TOKENS>
@@ -403,10 +428,13 @@ int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   if (args.prologue != kPrologueImage && args.tokens != 1) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: fused prologues take one token");
   }
-  const int slots = ctx->sm_count * kPerSm;
-  const int grid = row_tiles < slots ? row_tiles : slots;
+  // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
+  FastGemvArgs launch = args;
+  const int slabs = (args.cols / kSuperBlock + kSlabBlocks - 1) / kSlabBlocks;
+  int grid = 1;
+  PlanFastGrid(GemvQ6KMma<TOKENS, kPerSm>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit, &grid);
   GUFO_CUDA_TRY(LaunchOverlapped(GemvQ6KMma<TOKENS, kPerSm>, dim3(grid), dim3(kFastThreads), smem,
-                                 ctx->stream, 1, args));
+                                 ctx->stream, launch.ksplit, launch));
   ctx->launches.fetch_add(1);
   return GUFO_CUDA_OK;
 }

@@ -171,26 +171,62 @@ __device__ __forceinline__ void StageBlock(const float (&v)[8], int lane, int to
 __device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + expf(-x))); }
 
 // Builds the one-token image in shared memory at `image` from the launch's
-// fused input (prologue != kPrologueImage). `xs` is a shared fp32 scratch of
-// `cols` values. Ends with a __syncthreads. kFastThreads threads.
+// fused input (prologue != kPrologueImage). Warp w converts blocks w, w + 8,
+// ...; a lane holds eight adjacent values, so nothing is staged in between.
+// Ends with a __syncthreads. kFastThreads threads.
 __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
-                                          uint8_t* image, float* xs, float extra) {
+                                          uint8_t* image, float extra) {
   __shared__ float reduce[kFastWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n = a.cols;
+  const int blocks = n / kSuperBlock;
   const bool first = blockIdx.x == 0;
+  auto load8 = [&](const float* p, float (&v)[8]) {
+    const float4 v0 = *reinterpret_cast<const float4*>(p);
+    const float4 v1 = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = v0.x, v[1] = v0.y, v[2] = v0.z, v[3] = v0.w;
+    v[4] = v1.x, v[5] = v1.y, v[6] = v1.z, v[7] = v1.w;
+  };
+  auto store8 = [&](float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  };
+  // Columns without a token keep a zero factor.
+  float* scale = reinterpret_cast<float*>(image + l.scale_at);
+  for (int i = threadIdx.x; i < blocks * l.kcols; i += kFastThreads) {
+    if (i % l.kcols >= kLimbs) {
+      scale[i] = 0.f;
+    }
+  }
   if (a.prologue == kPrologueResNorm) {
     // vec::RmsNorm (src/core/vec.hpp:57-63) of the residual stream after its
-    // pending add (src/models/qwen35/decoder.cpp:493,504-508).
-    float sq = 0.f;
-    for (int i = threadIdx.x; i < n; i += kFastThreads) {
-      float v = a.h_in[i];
+    // pending add (src/models/qwen35/decoder.cpp:493,504-508). The first pass
+    // sums the squares; the second reads the same values again (they sit in
+    // L2, and the warp's first block is still in registers).
+    auto residual = [&](int at, float (&v)[8]) {
+      load8(a.h_in + at, v);
       if (a.delta != nullptr) {
-        v += a.delta[i];
+        float d[8];
+        load8(a.delta + at, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[i] += d[i];
+        }
       }
-      xs[i] = v;
-      sq = fmaf(v, v, sq);
+    };
+    float keep[8] = {};
+    float sq = 0.f;
+    for (int b = warp; b < blocks; b += kFastWarps) {
+      float v[8];
+      residual(b * kSuperBlock + lane * 8, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sq = fmaf(v[i], v[i], sq);
+        if (b == warp) {
+          keep[i] = v[i];
+        }
+      }
     }
     sq = WarpSum(sq);
     if (lane == 0) {
@@ -203,43 +239,48 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
       total += reduce[w];
     }
     const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + a.eps);
-    for (int i = threadIdx.x; i < n; i += kFastThreads) {
-      const float v = xs[i];
-      const float out = v * inv * a.norm_w[i];
-      xs[i] = out;
+    for (int b = warp; b < blocks; b += kFastWarps) {
+      const int at = b * kSuperBlock + lane * 8;
+      float v[8], w[8], out[8];
+      if (b == warp) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[i] = keep[i];
+        }
+      } else {
+        residual(at, v);
+      }
+      load8(a.norm_w + at, w);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        out[i] = v[i] * inv * w[i];
+      }
       if (first) {
-        a.h_out[i] = v;
+        store8(a.h_out + at, v);
         if (a.normed_out != nullptr) {
-          a.normed_out[i] = out;
+          store8(a.normed_out + at, out);
         }
       }
+      StageBlock(out, lane, 0, b, l, image, extra);
     }
     if (first && threadIdx.x == 0 && a.advance != nullptr) {
       *a.advance += 1;
     }
-  } else if (a.prologue == kPrologueSwiGlu) {
-    for (int i = threadIdx.x; i < n; i += kFastThreads) {
-      xs[i] = SiluFast(a.x[i]) * a.x[n + i];
-    }
   } else {
-    for (int i = threadIdx.x; i < n; i += kFastThreads) {
-      xs[i] = a.x[i];
+    for (int b = warp; b < blocks; b += kFastWarps) {
+      const int at = b * kSuperBlock + lane * 8;
+      float v[8];
+      load8(a.x + at, v);
+      if (a.prologue == kPrologueSwiGlu) {
+        float up[8];
+        load8(a.x + n + at, up);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          v[i] = SiluFast(v[i]) * up[i];
+        }
+      }
+      StageBlock(v, lane, 0, b, l, image, extra);
     }
-  }
-  // Columns without a token keep a zero factor.
-  float* scale = reinterpret_cast<float*>(image + l.scale_at);
-  const int blocks = n / kSuperBlock;
-  for (int i = threadIdx.x; i < blocks * l.kcols; i += kFastThreads) {
-    if (i % l.kcols >= kLimbs) {
-      scale[i] = 0.f;
-    }
-  }
-  __syncthreads();
-  for (int b = warp; b < blocks; b += kFastWarps) {
-    const float4 v0 = *reinterpret_cast<const float4*>(xs + b * kSuperBlock + lane * 8);
-    const float4 v1 = *reinterpret_cast<const float4*>(xs + b * kSuperBlock + lane * 8 + 4);
-    const float v[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-    StageBlock(v, lane, 0, b, l, image, extra);
   }
   __syncthreads();
 }
