@@ -57,17 +57,23 @@ class DecoderConfig(C.Structure):
                [(n, C.c_int) for n in ("full_attention_interval", "heads", "kv_heads", "head_dim", "rope_dim")] + \
                [("rope_theta", C.c_float)] + \
                [(n, C.c_int) for n in ("conv_kernel", "linear_key_heads", "linear_value_heads", "linear_head_dim",
-                                       "max_positions", "use_graph")]
+                                       "max_positions", "use_graph", "experts", "experts_used", "expert_ffn")]
 
 
 LAYER_MATRICES = ("attn_qkv", "attn_gate", "ssm_alpha", "ssm_beta", "ssm_out", "attn_q", "attn_k", "attn_v",
-                  "attn_output", "ffn_gate", "ffn_up", "ffn_down")
+                  "attn_output", "ffn_gate", "ffn_up", "ffn_down", "ffn_gate_inp", "ffn_gate_inp_shexp",
+                  "ffn_gate_exps", "ffn_up_exps", "ffn_down_exps")
 LAYER_VECTORS = ("attn_norm", "post_attention_norm", "ssm_conv1d", "ssm_a", "ssm_dt_bias", "ssm_norm",
                  "attn_q_norm", "attn_k_norm")
 
 
 class LayerWeights(C.Structure):
     _fields_ = [(n, C.c_int64) for n in LAYER_MATRICES] + [(n, _f32p) for n in LAYER_VECTORS]
+
+
+class ExpertBank(C.Structure):
+    _fields_ = [("gate_exps", C.c_int64), ("up_exps", C.c_int64), ("down_exps", C.c_int64),
+                ("experts", C.c_int), ("expert_ffn", C.c_int), ("hidden", C.c_int)]
 
 
 class DecoderWeights(C.Structure):
@@ -112,6 +118,12 @@ SIGNATURES = {
                                                 C.c_void_p, C.c_void_p]),
     "gufo_cuda_swiglu_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
     "gufo_cuda_attention_device": (C.c_int, [C.c_void_p, C.POINTER(AttentionArgs)]),
+    "gufo_cuda_route_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                         C.c_void_p, C.c_void_p]),
+    "gufo_cuda_expert_ffn_device": (C.c_int, [C.c_void_p, C.POINTER(ExpertBank), C.c_void_p, C.c_int, C.c_void_p,
+                                              C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "gufo_cuda_moe_combine_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                               C.c_int, C.c_int, C.c_void_p]),
     "gufo_cuda_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderConfig), C.POINTER(DecoderWeights),
                                            C.POINTER(C.c_void_p)]),
     "gufo_cuda_decoder_destroy": (C.c_int, [C.c_void_p]),

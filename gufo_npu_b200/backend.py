@@ -184,6 +184,24 @@ class Context:
         self._check(self.lib.gufo_cuda_matmul_device(self.handle, parts_arr, nparts, C.c_void_p(_ptr(x)), tokens,
                                                      C.c_void_p(_ptr(y))))
 
+    # -- routed experts -------------------------------------------------------
+    def route_device(self, router, stride: int, tokens: int, experts: int, k: int, chosen, weights,
+                     shared_scale=None) -> None:
+        self._check(self.lib.gufo_cuda_route_device(self.handle, C.c_void_p(_ptr(router)), stride, tokens, experts, k,
+                                                    C.c_void_p(_ptr(chosen)), C.c_void_p(_ptr(weights)),
+                                                    C.c_void_p(_ptr(shared_scale))))
+
+    def expert_ffn_device(self, bank: "_capi.ExpertBank", ids, pairs: int, x, x_stride: int, ffn, act, y) -> None:
+        self._check(self.lib.gufo_cuda_expert_ffn_device(self.handle, C.byref(bank), C.c_void_p(_ptr(ids)), pairs,
+                                                         C.c_void_p(_ptr(x)), x_stride, C.c_void_p(_ptr(ffn)),
+                                                         C.c_void_p(_ptr(act)), C.c_void_p(_ptr(y))))
+
+    def moe_combine_device(self, shared, scale, weights, expert_out, tokens: int, k: int, hidden: int, out) -> None:
+        self._check(self.lib.gufo_cuda_moe_combine_device(self.handle, C.c_void_p(_ptr(shared)),
+                                                          C.c_void_p(_ptr(scale)), C.c_void_p(_ptr(weights)),
+                                                          C.c_void_p(_ptr(expert_out)), tokens, k, hidden,
+                                                          C.c_void_p(_ptr(out))))
+
     # -- DeltaNet -----------------------------------------------------------
     def delta_rule_device(self, seqs: List[dict], key_heads: int, value_heads: int, head_dim: int) -> None:
         arr = (_capi.DeltaSeq * max(len(seqs), 1))()
@@ -347,6 +365,83 @@ class CudaProjections:
         self.ctx.matmul_device(Context._parts(parts), len(parts), x, tokens, y)
 
 
+class CudaMoe:
+    """Decoder::MoeFfn (src/models/qwen35/decoder.cpp:535-557) for a few tokens with every
+    step on the device: router product, Route, the chosen experts' FFN as grouped products,
+    the weighted sum onto the scaled shared expert's output.
+
+    `expert_range` = (first, count) keeps only those experts on this device (expert
+    parallelism): pairs routed elsewhere are skipped and their rows of `expert_out` stay zero,
+    so that a sum over the ranks restores every row before `combine`.
+    """
+
+    def __init__(self, projections: "CudaProjections", max_tokens: int = 4, expert_range=None):
+        import torch
+        c = projections.config
+        if not c.is_moe:
+            raise RuntimeError("qwen35: not a MoE model")
+        self.projections = projections
+        self.ctx = projections.ctx
+        self.config = c
+        self.max_tokens = max_tokens
+        self.expert_range = expert_range
+        dev = torch.device("cuda", self.ctx.device)
+        k = c.experts_used
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.router = torch.empty(max_tokens, c.experts + 1, **f32)
+        self.chosen = torch.empty(max_tokens, k, dtype=torch.int32, device=dev)
+        self.local = torch.empty(max_tokens, k, dtype=torch.int32, device=dev)
+        self.weights = torch.empty(max_tokens, k, **f32)
+        self.scale = torch.empty(max_tokens, **f32)
+        self.ffn = torch.empty(max_tokens * k, 2 * c.expert_ffn, **f32)
+        self.act = torch.empty(max_tokens * k, c.expert_ffn, **f32)
+        self.expert_out = torch.zeros(max_tokens, k, c.hidden, **f32)
+        self.banks = []
+        for l in projections.layers:
+            self.banks.append(_capi.ExpertBank(l["gate_exps"], l["up_exps"], l["down_exps"], c.experts,
+                                               c.expert_ffn, c.hidden))
+
+    def route(self, layer: int, normed, tokens: int) -> None:
+        """Router product and top-k of `tokens` normed rows (device tensor)."""
+        c = self.config
+        self.projections.apply_device(Stage.kRouter, layer, normed, tokens, self.router)
+        self.ctx.route_device(self.router, c.experts + 1, tokens, c.experts, c.experts_used, self.chosen,
+                              self.weights, self.scale)
+
+    def experts(self, layer: int, normed, tokens: int) -> None:
+        """The chosen experts' FFN of every (token, slot) pair held here, into expert_out."""
+        c = self.config
+        k = c.experts_used
+        ids = self.chosen
+        if self.expert_range is not None:
+            first, count = self.expert_range
+            held = (self.chosen >= first) & (self.chosen < first + count)
+            self.local.copy_(torch_where(held, self.chosen, -1))
+            self.expert_out.zero_()
+            ids = self.local
+        for t in range(tokens):
+            self.ctx.expert_ffn_device(self.banks[layer], ids[t], k, normed[t], 0, self.ffn[t * k:], self.act[t * k:],
+                                       self.expert_out[t])
+
+    def combine(self, shared, tokens: int, out) -> None:
+        c = self.config
+        self.ctx.moe_combine_device(shared, self.scale, self.weights, self.expert_out, tokens, c.experts_used,
+                                    c.hidden, out)
+
+    def MoeFfn(self, layer: int, normed, shared, tokens: int, out) -> None:
+        """out[t] = shared[t] * scale + sum of the routed experts' outputs (device tensors)."""
+        if tokens > self.max_tokens:
+            raise ValueError("CudaMoe: more tokens than max_tokens")
+        self.route(layer, normed, tokens)
+        self.experts(layer, normed, tokens)
+        self.combine(shared, tokens, out)
+
+
+def torch_where(cond, a, b):
+    import torch
+    return torch.where(cond, a, torch.full_like(a, b))
+
+
 class CudaMixer:
     """Gated DeltaNet decode step with the state resident on the device (Mixer::Linear)."""
 
@@ -380,7 +475,7 @@ class CudaMixer:
 
 
 class CudaDecoder:
-    """qwen35::Decoder with every buffer on the device (dense models).
+    """qwen35::Decoder with every buffer on the device (dense and MoE models).
 
     `Step(token)` mirrors Decoder::Step (src/models/qwen35/decoder.cpp:478-528): it runs the
     token at the current position, advances the state and returns the vocab logits. The
@@ -393,6 +488,11 @@ class CudaDecoder:
                      "attn_q": "attn_q.weight", "attn_k": "attn_k.weight", "attn_v": "attn_v.weight",
                      "attn_output": "attn_output.weight", "ffn_gate": "ffn_gate.weight", "ffn_up": "ffn_up.weight",
                      "ffn_down": "ffn_down.weight"}
+    # MoE layers: the shared expert stands where the dense FFN does.
+    _MOE_MATRIX_NAMES = {"ffn_gate": "ffn_gate_shexp.weight", "ffn_up": "ffn_up_shexp.weight",
+                         "ffn_down": "ffn_down_shexp.weight", "ffn_gate_inp": "ffn_gate_inp.weight",
+                         "ffn_gate_inp_shexp": "ffn_gate_inp_shexp.weight", "ffn_gate_exps": "ffn_gate_exps.weight",
+                         "ffn_up_exps": "ffn_up_exps.weight", "ffn_down_exps": "ffn_down_exps.weight"}
     _VECTOR_NAMES = {"attn_norm": "attn_norm.weight", "post_attention_norm": "post_attention_norm.weight",
                      "ssm_conv1d": "ssm_conv1d.weight", "ssm_a": "ssm_a", "ssm_dt_bias": "ssm_dt.bias",
                      "ssm_norm": "ssm_norm.weight", "attn_q_norm": "attn_q_norm.weight",
@@ -401,8 +501,6 @@ class CudaDecoder:
     def __init__(self, projections: CudaProjections, tensors: Dict[str, Tensor], max_positions: int = 4096,
                  use_graph: bool = True):
         c = projections.config
-        if c.is_moe:
-            raise RuntimeError("qwen35: the device-resident decoder runs dense models only")
         self.ctx = projections.ctx
         self.config = c
         self.projections = projections
@@ -417,7 +515,8 @@ class CudaDecoder:
         layers = (_capi.LayerWeights * c.layers)()
         for il in range(c.layers):
             p = f"blk.{il}."
-            for field, name in self._MATRIX_NAMES.items():
+            names = dict(self._MATRIX_NAMES, **self._MOE_MATRIX_NAMES) if c.is_moe else self._MATRIX_NAMES
+            for field, name in names.items():
                 setattr(layers[il], field, projections._matrices.get(p + name, 0))
             for field, name in self._VECTOR_NAMES.items():
                 if p + name in tensors:
@@ -425,10 +524,10 @@ class CudaDecoder:
         weights = _capi.DecoderWeights(projections._matrices["token_embd.weight"],
                                        0 if c.tied_embeddings else projections._matrices["output.weight"],
                                        vec("output_norm.weight"), layers)
-        config = _capi.DecoderConfig(c.layers, c.hidden, c.ffn, c.vocab, c.rms_eps, c.full_attention_interval,
+        config = _capi.DecoderConfig(c.layers, c.hidden, c.ffn_width, c.vocab, c.rms_eps, c.full_attention_interval,
                                      c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.rope_theta, c.conv_kernel,
                                      c.linear_key_heads, c.linear_value_heads, c.linear_head_dim, max_positions,
-                                     int(use_graph))
+                                     int(use_graph), c.experts, c.experts_used, c.expert_ffn)
         handle = C.c_void_p()
         _capi.check(lib, self.ctx.handle,
                     lib.gufo_cuda_decoder_create(self.ctx.handle, C.byref(config), C.byref(weights), C.byref(handle)))

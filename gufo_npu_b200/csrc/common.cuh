@@ -127,6 +127,14 @@ struct FastGemvArgs {
   // slabs r, r + ksplit, ... and the partial sums meet in block 0's shared
   // memory. Set by the launcher for matrices with few rows.
   int ksplit;
+  // Grouped launches (the routed experts of a MoE layer): the parts are stacks
+  // of `rows`-row matrices, group g multiplies matrix group_ids[g] of every
+  // part (a negative id skips the group) with its own input and output. The
+  // ids live on the device, so a router kernel can feed the launch directly.
+  const int* group_ids;   // null: one ungrouped product
+  int groups;
+  int x_group_stride;     // floats between the groups' inputs (0: shared)
+  int y_group_stride;     // floats between the groups' outputs
 };
 
 // A single-part launch against a staged image.

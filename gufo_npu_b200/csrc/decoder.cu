@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "gemv.cuh"
+#include "moe.cuh"
 
 namespace gufo {
 namespace {
@@ -452,6 +453,8 @@ struct gufo_cuda_decoder {
   struct Layer {
     bool attention = false;
     gufo::GemvArgs in, out, ffn_in, ffn_down;
+    gufo::GemvArgs router;             // MoE: router rows and the shared expert's gate
+    gufo::ExpertBank bank;             // MoE: the stacked expert tensors
     gufo::DeltaNetLayer linear;        // small weights (device), DeltaNet layers
     float* attn_norm = nullptr;
     float* post_norm = nullptr;
@@ -471,6 +474,10 @@ struct gufo_cuda_decoder {
   float* h[2] = {nullptr, nullptr};   // the residual stream alternates between two buffers
   float *normed = nullptr, *in = nullptr, *mixed = nullptr, *out = nullptr;
   float *ffn = nullptr, *act = nullptr, *logits = nullptr, *queries = nullptr, *partials = nullptr;
+  // MoE scratch: router outputs, the routing, the experts' intermediate rows.
+  float *router = nullptr, *route_weights = nullptr, *shared_scale = nullptr;
+  float *expert_ffn = nullptr, *expert_act = nullptr, *expert_out = nullptr;
+  int* chosen = nullptr;
   int* position_dev = nullptr;
   int* token_dev = nullptr;
   int* token_pinned = nullptr;
@@ -703,6 +710,20 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
     Input swiglu{kPrologueSwiGlu};
     swiglu.x = d->ffn;
     GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, swiglu, d->act, d->out));
+    if (c.experts > 0) {
+      // Decoder::MoeFfn (decoder.cpp:535-557): d->out holds the shared
+      // expert's output, d->normed the layer's normed input.
+      GemvArgs router = l.router;
+      router.x = d->normed;
+      router.y = d->router;
+      GUFO_STEP_TRY(LaunchGemv(ctx, router, 1));
+      GUFO_STEP_TRY(EnqueueRoute(ctx, d->router, c.experts + 1, 1, c.experts, c.experts_used, d->chosen,
+                                 d->route_weights, d->shared_scale));
+      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, c.experts_used, d->normed, 0, d->expert_ffn,
+                                     d->expert_act, d->expert_out));
+      GUFO_STEP_TRY(EnqueueMoeCombine(ctx, d->out, d->shared_scale, d->route_weights, d->expert_out, 1,
+                                      c.experts_used, c.hidden, d->out));
+    }
     Mark(d, GUFO_CUDA_TIMELINE_FFN_DOWN);
     pending = d->out;
   }
@@ -735,7 +756,9 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
   if (c.layers <= 0 || c.hidden <= 0 || c.ffn <= 0 || c.vocab <= 0 || c.full_attention_interval <= 0 ||
       c.kv_heads <= 0 || c.heads % c.kv_heads != 0 || c.heads / c.kv_heads > gufo::kMaxGroup ||
       c.head_dim % 32 != 0 || c.head_dim > 32 * gufo::kMaxPerLane || c.rope_dim > c.head_dim ||
-      c.rope_dim % 2 != 0 || c.max_positions <= 0 || c.hidden % 256 != 0) {
+      c.rope_dim % 2 != 0 || c.max_positions <= 0 || c.hidden % 256 != 0 || c.experts < 0 ||
+      (c.experts > 0 && (c.experts_used <= 0 || c.experts_used > c.experts || c.expert_ffn <= 0 ||
+                         c.expert_ffn % 256 != 0))) {
     return Fail(GUFO_CUDA_SHAPE, "decoder_create: unsupported or inconsistent shape");
   }
   std::lock_guard<std::mutex> lock(ctx->mu);
@@ -836,6 +859,17 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
         (rc = gufo::Stack(ctx, &w.ffn_down, &down_rows, 1, c.ffn, "ffn_down", &l.ffn_down)) != GUFO_CUDA_OK) {
       return fail(rc);
     }
+    if (c.experts > 0) {
+      const gufo_cuda_matrix router[2] = {w.ffn_gate_inp, w.ffn_gate_inp_shexp};
+      const int64_t router_rows[2] = {c.experts, 1};
+      const gufo_cuda_expert_bank bank{w.ffn_gate_exps, w.ffn_up_exps, w.ffn_down_exps, c.experts, c.expert_ffn,
+                                       c.hidden};
+      if ((rc = gufo::Stack(ctx, router, router_rows, 2, c.hidden, "ffn_gate_inp/ffn_gate_inp_shexp", &l.router)) !=
+              GUFO_CUDA_OK ||
+          (rc = gufo::BuildExpertBank(ctx, bank, &l.bank)) != GUFO_CUDA_OK) {
+        return fail(rc);
+      }
+    }
     in_max = std::max(in_max, static_cast<size_t>(l.in.total_rows));
   }
   std::vector<float> inv_freq(c.rope_dim / 2 > 0 ? c.rope_dim / 2 : 1);
@@ -857,13 +891,22 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
               {&d->in, in_max}, {&d->mixed, mixed}, {&d->out, static_cast<size_t>(c.hidden)},
               {&d->ffn, static_cast<size_t>(2) * c.ffn}, {&d->act, static_cast<size_t>(c.ffn)},
               {&d->logits, static_cast<size_t>(c.vocab)}, {&d->queries, static_cast<size_t>(attn_dim)},
-              {&d->partials, static_cast<size_t>(c.kv_heads) * gufo::kAttnSplits * group * (c.head_dim + 2)}};
+              {&d->partials, static_cast<size_t>(c.kv_heads) * gufo::kAttnSplits * group * (c.head_dim + 2)},
+              // MoE scratch (a few floats for a dense model).
+              {&d->router, static_cast<size_t>(c.experts) + 1},
+              {&d->route_weights, static_cast<size_t>(c.experts_used) + 1},
+              {&d->shared_scale, 1},
+              {&d->expert_ffn, static_cast<size_t>(c.experts_used) * 2 * c.expert_ffn + 1},
+              {&d->expert_act, static_cast<size_t>(c.experts_used) * c.expert_ffn + 1},
+              {&d->expert_out, static_cast<size_t>(c.experts_used) * c.hidden + 1}};
   for (auto& b : bufs) {
     if ((rc = gufo::Alloc(d, b.n * 4, reinterpret_cast<void**>(b.p))) != GUFO_CUDA_OK) {
       return fail(rc);
     }
   }
-  if ((rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->position_dev))) != GUFO_CUDA_OK ||
+  if ((rc = gufo::Alloc(d, 4 * (static_cast<size_t>(c.experts_used) + 1), reinterpret_cast<void**>(&d->chosen))) !=
+          GUFO_CUDA_OK ||
+      (rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->position_dev))) != GUFO_CUDA_OK ||
       (rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->token_dev))) != GUFO_CUDA_OK) {
     return fail(rc);
   }

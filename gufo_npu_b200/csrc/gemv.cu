@@ -127,23 +127,34 @@ GemvRows(const __grid_constant__ GemvArgs args) {
   }
   const GemvPart& part = args.parts[p];
   const uint8_t* data = part.data + static_cast<size_t>(local) * part.row_bytes;
+  const float* x = args.x;
+  float* y = args.y;
+  if (args.group_ids != nullptr) {
+    const int id = args.group_ids[blockIdx.y];
+    if (id < 0) {
+      return;
+    }
+    data += static_cast<size_t>(id) * part.rows * part.row_bytes;
+    x += static_cast<size_t>(blockIdx.y) * args.x_group_stride;
+    y += static_cast<size_t>(blockIdx.y) * args.y_group_stride;
+  }
   float acc[M];
 #pragma unroll
   for (int t = 0; t < M; ++t) {
     acc[t] = 0.f;
   }
   if (part.type == GUFO_CUDA_Q4_K) {
-    RowQ4K<M>(data, args.cols, args.x, lane, acc);
+    RowQ4K<M>(data, args.cols, x, lane, acc);
   } else if (part.type == GUFO_CUDA_Q6_K) {
-    RowQ6K<M>(data, args.cols, args.x, lane, acc);
+    RowQ6K<M>(data, args.cols, x, lane, acc);
   } else {
-    RowF32<M>(data, args.cols, args.x, lane, acc);
+    RowF32<M>(data, args.cols, x, lane, acc);
   }
 #pragma unroll
   for (int t = 0; t < M; ++t) {
     const float total = WarpSum(acc[t]);
     if (lane == 0) {
-      args.y[static_cast<size_t>(t) * args.y_stride + part.out_offset + local] = total;
+      y[static_cast<size_t>(t) * args.y_stride + part.out_offset + local] = total;
     }
   }
 }
@@ -151,7 +162,7 @@ GemvRows(const __grid_constant__ GemvArgs args) {
 template <int M>
 void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
   const int warps = 8;
-  const int grid = (args.total_rows + warps - 1) / warps;
+  const dim3 grid((args.total_rows + warps - 1) / warps, args.group_ids != nullptr ? args.groups : 1);
   GemvRows<M><<<grid, warps * 32, 0, stream>>>(args);
 }
 
@@ -245,6 +256,86 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
       case 7: LaunchRows<7>(rest, ctx->stream); break;
       default: LaunchRows<8>(rest, ctx->stream); break;
     }
+    ctx->launches.fetch_add(1);
+    GUFO_CUDA_TRY(cudaGetLastError());
+  }
+  return GUFO_CUDA_OK;
+}
+
+namespace {
+
+// act[g][i] = silu(x[g][i]) * x[g][n + i] for the groups that run.
+__global__ void __launch_bounds__(256)
+SwiGluGroups(const float* __restrict__ x, int n, int x_stride, const int* __restrict__ ids,
+             float* __restrict__ act) {
+  const int g = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ids[g] < 0 || i >= n) {
+    return;
+  }
+  const float* in = x + static_cast<size_t>(g) * x_stride;
+  const float v = in[i];
+  act[static_cast<size_t>(g) * n + i] = v * (1.0f / (1.0f + expf(-v))) * in[n + i];
+}
+
+}  // namespace
+
+int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, float* scratch) {
+  if (base.group_ids == nullptr || base.groups <= 0 ||
+      (prologue != kProloguePlain && prologue != kPrologueSwiGlu)) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "grouped product: ids, groups and a plain or SwiGLU input");
+  }
+  const bool aligned = (reinterpret_cast<uintptr_t>(base.x) & 15) == 0 && base.x_group_stride % 4 == 0;
+  const bool fast4 = !ctx->force_general && aligned && Q4KFastFits(base.cols, 1);
+  GemvArgs rest = base;
+  rest.nparts = 0;
+  rest.total_rows = 0;
+  FastGemvArgs args{};
+  args.cols = base.cols;
+  args.y = base.y;
+  args.y_stride = base.y_stride;
+  args.tokens = 1;
+  args.prologue = prologue;
+  args.x = base.x;
+  args.group_ids = base.group_ids;
+  args.groups = base.groups;
+  args.x_group_stride = base.x_group_stride;
+  args.y_group_stride = base.y_group_stride;
+  for (int p = 0; p < base.nparts; ++p) {
+    const GemvPart& part = base.parts[p];
+    if (fast4 && part.type == GUFO_CUDA_Q4_K) {
+      args.row_bytes = part.row_bytes;
+      args.parts[args.nparts++] = {part.data, part.rows, part.out_offset};
+      if (args.nparts == kFastMaxParts) {
+        const int rc = LaunchGemvQ4KFast(ctx, args);
+        if (rc != GUFO_CUDA_OK) {
+          return rc;
+        }
+        args.nparts = 0;
+      }
+    } else {
+      rest.parts[rest.nparts++] = part;
+      rest.total_rows += part.rows;
+    }
+  }
+  if (args.nparts > 0) {
+    const int rc = LaunchGemvQ4KFast(ctx, args);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+  }
+  if (rest.nparts > 0) {
+    if (prologue == kPrologueSwiGlu) {
+      if (scratch == nullptr) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "grouped product: no scratch for the activated input");
+      }
+      SwiGluGroups<<<dim3((base.cols + 255) / 256, base.groups), 256, 0, ctx->stream>>>(
+          base.x, base.cols, base.x_group_stride, base.group_ids, scratch);
+      ctx->launches.fetch_add(1);
+      rest.x = scratch;
+      rest.x_group_stride = base.cols;
+    }
+    LaunchRows<1>(rest, ctx->stream);
     ctx->launches.fetch_add(1);
     GUFO_CUDA_TRY(cudaGetLastError());
   }

@@ -25,7 +25,19 @@ struct GemvArgs {
   int cols;
   const float* x;   // [tokens][cols]
   float* y;         // [tokens][total_rows]
+  // Grouped products (see FastGemvArgs): null for an ordinary product.
+  const int* group_ids = nullptr;
+  int groups = 0;
+  int x_group_stride = 0;
+  int y_group_stride = 0;
 };
+
+// Enqueues, for every group g with group_ids[g] >= 0 (device memory), the
+// one-token product of matrix group_ids[g] of each stacked part with the group's
+// input; `prologue` is kProloguePlain (x fp32) or kPrologueSwiGlu (x = [gate |
+// up] per group; `scratch` then holds groups * cols activated values for parts
+// the tensor-core kernel does not run). Fill the group fields of `args`.
+int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& args, int prologue, float* scratch);
 
 // Enqueues y = [W_0 x | W_1 x | ...] for `tokens` rows; x and y on the device.
 // The caller holds ctx->mu.

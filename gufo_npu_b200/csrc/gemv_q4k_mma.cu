@@ -191,7 +191,9 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   // Column g of the first MMA column group; lanes past the last token's planes
   // wrap onto live ones (see MultiplyPair).
   const uint8_t* lane_plane = smem + (g % kNCols) * l.plane_stride + 8 * t;
-  const int row_tiles = TotalTiles(a);
+  const int tiles_per_group = TotalTiles(a);
+  const bool grouped = a.group_ids != nullptr;
+  const int row_tiles = grouped ? tiles_per_group * a.groups : tiles_per_group;
   // With ksplit > 1 a cluster of ksplit blocks shares each tile.
   const int ks = a.ksplit > 1 ? a.ksplit : 1;
   const int rank = static_cast<int>(blockIdx.x) % ks;
@@ -200,6 +202,22 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   const int my_tiles = (row_tiles - slot + stride - 1) / stride;
   const int slabs_mine = (slabs_per_tile - rank + ks - 1) / ks;
   const int my_slabs = my_tiles * slabs_mine;
+  // A grouped launch has one block per tile; the block's group picks the
+  // matrix of each part, the input and the output.
+  int group = 0;
+  size_t matrix = 0;
+  if (grouped) {
+    GridDependencyWait();   // the ids come from an earlier kernel
+    group = slot / tiles_per_group;
+    const int id = a.group_ids[group];
+    if (id < 0) {
+      return;
+    }
+    matrix = static_cast<size_t>(id);
+  }
+  auto locate = [&](int n, int* part, int* local) {
+    LocateTile(a, grouped ? slot - group * tiles_per_group : slot + n * stride, part, local);
+  };
 
   // Requests slab q (tile q / slabs_per_tile): warp w copies rows 2w and 2w + 1,
   // a lane the 16-byte chunks lane, lane + 32, lane + 64 of the row's segment.
@@ -217,13 +235,15 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
       const int chunks = nblk * (kQ4KBytes / 16);
       const uint32_t dst0 = ring_base + (q % kStages) * kSlabBytes;
       int part, local;
-      LocateTile(a, slot + n * stride, &part, &local);
+      locate(n, &part, &local);
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         const int r = 2 * warp + rr;
         // Rows past the end repeat the last row; their sums are never stored.
         const int row = min(local * 16 + r, a.parts[part].rows - 1);
-        const uint8_t* src = a.parts[part].w + static_cast<size_t>(row) * a.row_bytes + s * (kSlabBlocks * kQ4KBytes);
+        const uint8_t* src = a.parts[part].w +
+                             (matrix * a.parts[part].rows + static_cast<size_t>(row)) * a.row_bytes +
+                             s * (kSlabBlocks * kQ4KBytes);
         const uint32_t dst = dst0 + r * kSlabRowBytes;
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
@@ -252,7 +272,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 1.0f / 16.0f);
+    FillImage(a, l, smem, 1.0f / 16.0f, a.x + static_cast<size_t>(group) * a.x_group_stride);
   }
 
   Accum<TOKENS> acc;
@@ -271,7 +291,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
   cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
   auto gather = [&](int n) {
     int part, local;
-    LocateTile(a, slot + n * stride, &part, &local);
+    locate(n, &part, &local);
     const int o = threadIdx.x;
     const int k = o % TOKENS;
     const int r = (o / TOKENS) & 15;
@@ -302,7 +322,8 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
       }
     }
     if (live) {
-      a.y[static_cast<size_t>(k) * a.y_stride + a.parts[part].y_offset + row] = total;
+      a.y[static_cast<size_t>(group) * a.y_group_stride + static_cast<size_t>(k) * a.y_stride +
+          a.parts[part].y_offset + row] = total;
     }
   };
   clear();
@@ -394,7 +415,15 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   FastGemvArgs launch = args;
   const int slabs = (args.cols / kSuperBlock + kSlabBlocks - 1) / kSlabBlocks;
   int grid = 1;
-  PlanFastGrid(GemvQ4KMma<TOKENS, PER_SM>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit, &grid);
+  if (args.group_ids != nullptr) {
+    if (args.groups <= 0 || args.tokens != 1 || args.prologue == kPrologueImage) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: a grouped launch takes one token and a fused input");
+    }
+    launch.ksplit = 1;
+    grid = row_tiles * args.groups;   // one block per tile
+  } else {
+    PlanFastGrid(GemvQ4KMma<TOKENS, PER_SM>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit, &grid);
+  }
   GUFO_CUDA_TRY(LaunchOverlapped(GemvQ4KMma<TOKENS, PER_SM>, dim3(grid), dim3(kFastThreads), smem,
                                  ctx->stream, launch.ksplit, launch));
   ctx->launches.fetch_add(1);

@@ -289,7 +289,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 1.0f);
+    FillImage(a, l, smem, 1.0f, a.x);
   }
 
   Accum<TOKENS> acc;
@@ -427,6 +427,9 @@ int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   }
   if (args.prologue != kPrologueImage && args.tokens != 1) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: fused prologues take one token");
+  }
+  if (args.group_ids != nullptr) {
+    return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "fast gemv: grouped launches run Q4_K only");
   }
   // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
   FastGemvArgs launch = args;

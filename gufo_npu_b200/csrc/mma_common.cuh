@@ -173,9 +173,10 @@ __device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + 
 // Builds the one-token image in shared memory at `image` from the launch's
 // fused input (prologue != kPrologueImage). Warp w converts blocks w, w + 8,
 // ...; a lane holds eight adjacent values, so nothing is staged in between.
-// Ends with a __syncthreads. kFastThreads threads.
+// `x` is the plain / SwiGLU input (a.x, or a group's part of it). Ends with a
+// __syncthreads. kFastThreads threads.
 __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
-                                          uint8_t* image, float extra) {
+                                          uint8_t* image, float extra, const float* x) {
   __shared__ float reduce[kFastWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -270,10 +271,10 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     for (int b = warp; b < blocks; b += kFastWarps) {
       const int at = b * kSuperBlock + lane * 8;
       float v[8];
-      load8(a.x + at, v);
+      load8(x + at, v);
       if (a.prologue == kPrologueSwiGlu) {
         float up[8];
-        load8(a.x + n + at, up);
+        load8(x + n + at, up);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           v[i] = SiluFast(v[i]) * up[i];

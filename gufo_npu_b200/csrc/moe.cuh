@@ -1,0 +1,33 @@
+// Launch interface of the routed-expert FFN, shared by the C-ABI entry points
+// and the device-resident decoder.
+#pragma once
+
+#include "gemv.cuh"
+
+namespace gufo {
+
+// The stacked expert tensors of one layer as grouped products: `in` = gate and
+// up rows of one expert ([2 * expert_ffn] outputs), `down` = its down rows.
+struct ExpertBank {
+  int experts = 0;
+  int expert_ffn = 0;
+  int hidden = 0;
+  GemvArgs in;
+  GemvArgs down;
+};
+
+// Checks the handles and shapes of `bank`; ctx->mu is held.
+int BuildExpertBank(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank& bank, ExpertBank* out);
+
+// Top-k routing of `tokens` rows of router outputs (row width `stride`).
+int EnqueueRoute(gufo_cuda_ctx* ctx, const float* logits, int stride, int tokens, int experts, int k,
+                 int* chosen, float* weights, float* shared_scale);
+
+// y[p] = down_e(silu(gate_e x_p) * up_e x_p) for the pairs with ids[p] = e >= 0.
+int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, int pairs, const float* x,
+                     int x_stride, float* ffn, float* act, float* y);
+
+int EnqueueMoeCombine(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,
+                      const float* expert_out, int tokens, int k, int hidden, float* out);
+
+}  // namespace gufo

@@ -288,9 +288,57 @@ typedef struct gufo_cuda_attention_args {
 int gufo_cuda_attention_device(gufo_cuda_ctx* ctx,
                                const gufo_cuda_attention_args* args);
 
+/* ---- routed experts (MoE models) ---------------------------------------- */
+
+/* Route and SharedExpertScale (src/models/qwen35/moe.cpp:16-47) for `tokens`
+ * rows of router outputs on the device, `stride` floats apart: softmax in
+ * double over the first `experts` values of a row, the `k` most probable
+ * experts in descending order (ties: lower id), their weights renormalised
+ * with the sum floored at 6.103515625e-5. chosen and weights are
+ * [tokens][k] on the device. shared_scale (may be NULL) gets, per token, the
+ * sigmoid of the row's value at index `experts` (the shared expert's gate,
+ * Stage::kRouter's last output). */
+int gufo_cuda_route_device(gufo_cuda_ctx* ctx, const float* router, int stride,
+                           int tokens, int experts, int k, int* chosen,
+                           float* weights, float* shared_scale);
+
+/* The stacked expert tensors of one layer, each [cols, rows, experts] in GGUF
+ * terms and uploaded as one matrix of rows * experts rows
+ * (src/models/qwen35/gguf_projections.cpp:132-139,229-233). */
+typedef struct gufo_cuda_expert_bank {
+  gufo_cuda_matrix gate_exps;  /* [hidden, expert_ffn, experts] */
+  gufo_cuda_matrix up_exps;    /* [hidden, expert_ffn, experts] */
+  gufo_cuda_matrix down_exps;  /* [expert_ffn, hidden, experts] */
+  int experts;
+  int expert_ffn;
+  int hidden;
+} gufo_cuda_expert_bank;
+
+/* The loop body of Decoder::MoeFfn (src/models/qwen35/decoder.cpp:545-551,
+ * i.e. ApplyExpert(kExpertIn), SwiGLU, ApplyExpert(kExpertDown)) for `pairs`
+ * (input row, expert) pairs in two grouped launches: y[p] = down_e(silu(gate_e
+ * x_p) * up_e x_p) with e = ids[p], read from DEVICE memory at run time, so
+ * the ids may come straight from gufo_cuda_route_device. ids[p] < 0 skips the
+ * pair and leaves y[p] untouched (expert-parallel ranks pass -1 for experts
+ * they do not hold). x_p = x + p * x_stride; x_stride 0 shares one input.
+ * Scratch: ffn [pairs][2 * expert_ffn], act [pairs][expert_ffn]. */
+int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx,
+                                const gufo_cuda_expert_bank* bank,
+                                const int* ids, int pairs, const float* x,
+                                int64_t x_stride, float* ffn, float* act,
+                                float* y);
+
+/* out[t] = shared[t] * scale[t] + sum over slots, in slot order, of
+ * weights[t][slot] * expert_out[t][slot] (decoder.cpp:541-556). out may be
+ * shared. */
+int gufo_cuda_moe_combine_device(gufo_cuda_ctx* ctx, const float* shared,
+                                 const float* scale, const float* weights,
+                                 const float* expert_out, int tokens, int k,
+                                 int hidden, float* out);
+
 /* ---- device-resident decode step ---------------------------------------- */
 
-/* Shape of a dense Qwen3.5-family model: the fields of qwen35::Config
+/* Shape of a Qwen3.5-family model: the fields of qwen35::Config
  * (src/models/qwen35/config.hpp:13-62) the decode step reads, plus the capacity
  * of the attention cache. */
 typedef struct gufo_cuda_decoder_config {
@@ -311,6 +359,11 @@ typedef struct gufo_cuda_decoder_config {
   int linear_head_dim;
   int max_positions; /* attention cache rows per layer */
   int use_graph;     /* replay the step as a CUDA graph after the first steps */
+  /* MoE models (qwen35moe): 0 experts for a dense model. `ffn` is then the
+   * shared expert's width (Config::FfnWidth, config.hpp). */
+  int experts;
+  int experts_used;
+  int expert_ffn;
 } gufo_cuda_decoder_config;
 
 /* One layer's weights: matrix handles of this context (0 where the layer kind
@@ -320,7 +373,11 @@ typedef struct gufo_cuda_decoder_config {
 typedef struct gufo_cuda_layer_weights {
   gufo_cuda_matrix attn_qkv, attn_gate, ssm_alpha, ssm_beta, ssm_out; /* DeltaNet */
   gufo_cuda_matrix attn_q, attn_k, attn_v, attn_output;               /* attention */
-  gufo_cuda_matrix ffn_gate, ffn_up, ffn_down;
+  gufo_cuda_matrix ffn_gate, ffn_up, ffn_down; /* dense FFN, or the shared expert */
+  /* MoE layers: the router [hidden, experts] and the shared expert's gate
+   * [hidden, 1] (both F32), and the stacked expert tensors. */
+  gufo_cuda_matrix ffn_gate_inp, ffn_gate_inp_shexp;
+  gufo_cuda_matrix ffn_gate_exps, ffn_up_exps, ffn_down_exps;
   const float* attn_norm;           /* [hidden] */
   const float* post_attention_norm; /* [hidden] */
   const float* ssm_conv1d;          /* [channels][conv_kernel] */
@@ -344,8 +401,10 @@ typedef struct gufo_cuda_decoder gufo_cuda_decoder;
  * the device: the residual stream, the DeltaNet states and conv windows, the
  * fp16 attention cache and the logits stay in HBM between steps, as the
  * reference's NPU decoders keep the residual stream on their device
- * (src/models/qwen35_2b/npu_decoder.hpp:18-21). Dense models only. The
- * matrices must outlive the decoder. Holds one sequence (DecodeState). */
+ * (src/models/qwen35_2b/npu_decoder.hpp:18-21). Dense and MoE models; in a
+ * MoE layer the router, the top-k and the routed experts run on the device
+ * too (Decoder::MoeFfn, decoder.cpp:535-557). The matrices must outlive the
+ * decoder. Holds one sequence (DecodeState). */
 int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx,
                              const gufo_cuda_decoder_config* config,
                              const gufo_cuda_decoder_weights* weights,
