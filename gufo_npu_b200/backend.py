@@ -86,6 +86,15 @@ class Context:
         _capi.check(self.lib, None, status)
         self.handle = handle
         self.device = device
+        self.stream = stream or None
+
+    def require_torch_stream(self) -> None:
+        """Raises unless this context enqueues on torch's current stream: callers that mix torch
+        ops with this library's kernels on the same buffers need one stream for both."""
+        import torch
+        if self.stream is None or self.stream != torch.cuda.current_stream(self.device).cuda_stream:
+            raise RuntimeError("gufo_cuda: create the Context on torch's current (non-default) stream, e.g. "
+                               "s = torch.cuda.Stream(); Context(0, s.cuda_stream); with torch.cuda.stream(s): ...")
 
     def close(self) -> None:
         if getattr(self, "handle", None):
@@ -103,6 +112,7 @@ class Context:
 
     def set_stream(self, stream: int) -> None:
         self._check(self.lib.gufo_cuda_ctx_set_stream(self.handle, C.c_void_p(stream)))
+        self.stream = stream or None
 
     def set_option(self, name: str, value: int) -> None:
         self._check(self.lib.gufo_cuda_ctx_set_option(self.handle, name.encode(), value))
@@ -414,6 +424,7 @@ class CudaMoe:
         k = c.experts_used
         ids = self.chosen
         if self.expert_range is not None:
+            self.ctx.require_torch_stream()
             first, count = self.expert_range
             held = (self.chosen >= first) & (self.chosen < first + count)
             self.local.copy_(torch_where(held, self.chosen, -1))

@@ -265,4 +265,11 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "roofline": None, "cpu_baseline": None,
         }))
     dist.barrier()
-    dist.destroy_process_group()
+    torch.cuda.synchronize()
+    # Captured graphs hold NCCL kernels: release them before the communicator goes away, and
+    # leave without the collective teardown (it blocked here while graphs were alive).
+    dec.graphs.clear()
+    import sys
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)

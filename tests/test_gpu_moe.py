@@ -125,8 +125,7 @@ def test_grouped_expert_ffn_matches_per_expert_products(ctx, proj_type):
 
 def test_moe_ffn_matches_oracle_route_and_per_expert_sum(ctx, oracle):
     """CudaMoe.MoeFfn for 3 tokens against Decoder::MoeFfn's recipe on the host: oracle Route on the
-    same router outputs, experts in slot order, fp32 sum onto the scaled shared output. Then the
-    expert-parallel form: two halves of the experts, rows summed, equal to the whole."""
+    same router outputs, experts in slot order, fp32 sum onto the scaled shared output."""
     cfg, _, proj = _moe_model(ctx)
     dev = torch.device("cuda:0")
     tokens, k = 3, cfg.experts_used
@@ -149,17 +148,34 @@ def test_moe_ffn_matches_oracle_route_and_per_expert_sum(ctx, oracle):
             act = (gate / (1.0 + np.exp(-gate.astype(np.float64)))).astype(np.float32) * up
             want = want + weights[slot] * proj.ApplyExpert(Stage.kExpertDown, 0, int(chosen[slot]), act, 1)[0]
         assert rel_l2(got[t], want) <= 1e-5, t
-    # Expert parallelism on one device: each half computes its own pairs, the rows add up.
-    half = cfg.experts // 2
-    parts = []
-    for first in (0, half):
-        part = CudaMoe(proj, max_tokens=4, expert_range=(first, half))
-        part.route(0, nd, tokens)
-        part.experts(0, nd, tokens)
-        parts.append(part)
-    total = parts[0].expert_out + parts[1].expert_out
-    ctx.synchronize()
-    assert torch.equal(total[:tokens], moe.expert_out[:tokens])
+
+
+def test_expert_parallel_halves_add_up_to_the_whole():
+    """Expert parallelism on one device: two CudaMoe, each holding half of the experts, compute
+    their own pairs; the rows add up (only zeros are added) to the single-device rows, bit for
+    bit. torch ops sit between the kernels here, so the context shares torch's stream."""
+    stream = torch.cuda.Stream()
+    ctx = Context(0, stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        cfg, _, proj = _moe_model(ctx)
+        dev = torch.device("cuda:0")
+        tokens = 3
+        nd = torch.from_numpy(G.normal(92, tokens, cfg.hidden)).to(dev)
+        whole = CudaMoe(proj, max_tokens=4)
+        whole.route(0, nd, tokens)
+        whole.experts(0, nd, tokens)
+        half = cfg.experts // 2
+        parts = []
+        for first in (0, half):
+            part = CudaMoe(proj, max_tokens=4, expert_range=(first, half))
+            part.route(0, nd, tokens)
+            part.experts(0, nd, tokens)
+            parts.append(part)
+        total = parts[0].expert_out + parts[1].expert_out
+        stream.synchronize()
+        assert torch.equal(total[:tokens], whole.expert_out[:tokens])
+        assert float(whole.expert_out[:tokens].abs().sum()) > 0
+    ctx.close()
 
 
 @pytest.mark.parametrize("use_graph", [False, True])

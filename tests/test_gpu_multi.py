@@ -1,0 +1,128 @@
+"""Multi-rank GPU parity over NCCL: the row-split decode step against the reference's logits,
+and the expert-parallel exchanges against one device holding every expert. One process per
+GPU. The two-rank cases skip on a box with one GPU; the one-rank cases run the same code
+(collectives included) everywhere."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from gufo_npu_b200 import synth
+from tests.golden import make_golden as G
+
+pytestmark = pytest.mark.gpu
+
+STEP_TOL = 2e-3
+
+
+def rel_l2(got, want):
+    got = np.asarray(got, dtype=np.float64).ravel()
+    want = np.asarray(want, dtype=np.float64).ravel()
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
+def _worker(rank, world, port, out):
+    """Always reports: (rank, failures) or (rank, [traceback]). A rank that is stuck dumps its
+    stack to stderr and exits instead of holding the box."""
+    import faulthandler
+    faulthandler.dump_traceback_later(200, exit=True)
+    try:
+        _checks(rank, world, port, out)
+    except Exception:   # noqa: BLE001 - the parent prints it
+        import traceback
+        out.put((rank, [traceback.format_exc()]))
+    # Leave without tearing the process group down: rank 0 hosts the rendezvous store, and a
+    # rank that outlives it would wait on the dead store inside the teardown.
+    out.close()
+    out.join_thread()
+    os._exit(0)
+
+
+def _checks(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from gufo_npu_b200.backend import Context, CudaMoe, CudaProjections
+    from gufo_npu_b200.ep import EpMoe
+    from gufo_npu_b200.tp import TpDecoder
+    dev = torch.device("cuda", rank)
+    stream = torch.cuda.Stream()
+    failures = []
+    with torch.cuda.stream(stream):
+        ctx = Context(rank, stream.cuda_stream)
+        # Row-split decode step against the committed logits of the reference's Decoder::Step.
+        cfg = synth.ModelConfig(**G.DENSE)
+        tensors = synth.build_model(cfg, G.DENSE_SEED)
+        dec = TpDecoder(ctx, cfg, tensors, rank=rank, world=world, max_positions=32)
+        g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decoder.npz"))
+        for i, tok in enumerate(int(t) for t in g["decoder_dense_tokens"]):
+            logits = dec.step(tok, stream).cpu().numpy()
+            err = rel_l2(logits, g["decoder_dense_logits"][i])
+            if err > STEP_TOL:
+                failures.append(("tp logits", i, err))
+        # Expert parallelism against one device with every expert.
+        mcfg = synth.ModelConfig(**G.MOE)
+        mtensors = synth.build_model(mcfg, G.MOE_SEED)
+        proj = CudaProjections(ctx, mcfg, mtensors)
+        whole = CudaMoe(proj, max_tokens=4)
+        ep = EpMoe(ctx, mcfg, mtensors, proj, rank, world, max_tokens=4)
+        tokens = 3
+        shared = torch.from_numpy(G.normal(93, tokens, mcfg.hidden)).to(dev)
+        # Replicated tokens: the same rows on every rank.
+        same = torch.from_numpy(G.normal(92, tokens, mcfg.hidden)).to(dev)
+        want = torch.empty(tokens, mcfg.hidden, device=dev)
+        got = torch.empty_like(want)
+        whole.MoeFfn(0, same, shared, tokens, want)
+        ep.moe_ffn_replicated(0, same, shared, tokens, got)
+        stream.synchronize()
+        if not torch.equal(got, want):
+            failures.append(("ep replicated", float((got - want).abs().max())))
+        # Token-sharded: every rank brings its own rows.
+        own = torch.from_numpy(G.normal(192 + rank, tokens, mcfg.hidden)).to(dev)
+        whole.MoeFfn(1, own, shared, tokens, want)
+        ep.moe_ffn_sharded(1, own, shared, tokens, got)
+        stream.synchronize()
+        if not torch.equal(got, want):
+            failures.append(("ep sharded", float((got - want).abs().max())))
+        if float(want.abs().sum()) == 0:
+            failures.append(("ep", "all-zero outputs"))
+    dist.barrier()
+    torch.cuda.synchronize()
+    out.put((rank, failures))
+
+
+def _run(world):
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = 33500 + os.getpid() % 2000 + world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in range(world):
+            results.append(out.get(timeout=240))
+    except Exception:   # noqa: BLE001 - queue.Empty: a rank died or hung
+        pass
+    for p in procs:
+        p.join(timeout=20)
+        if p.is_alive():
+            p.terminate()
+            p.join(timeout=20)
+    assert len(results) == world, f"{world - len(results)} rank(s) did not report: {results}"
+    for rank, failures in results:
+        assert not failures, (rank, "\n".join(str(f) for f in failures))
+
+
+def test_one_rank_nccl_paths():
+    _run(1)
+
+
+def test_two_ranks_row_split_and_expert_parallel():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    _run(2)
