@@ -196,6 +196,12 @@ struct gufo_cuda_ctx {
   // Fixed-point image of the activations of the product in flight.
   uint8_t* image = nullptr;
   size_t image_bytes = 0;
+  // Scratch of the tcgen05 GEMM: an error word, the fp16 activation tile
+  // images, the partial sums of split products.
+  uint8_t* tc_scratch = nullptr;
+  size_t tc_scratch_bytes = 0;
+  // Products of 16 or more token rows run on the tcgen05 GEMM (option "tc_gemm").
+  bool tc_gemm = true;
   std::atomic<int64_t> launches{0};
   // Test hook: route every product through the general kernel.
   bool force_general = false;

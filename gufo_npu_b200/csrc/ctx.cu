@@ -1,5 +1,6 @@
 // Context, device memory and weight handles of the C ABI (include/gufo_cuda.h).
 #include "common.cuh"
+#include "gemm_tc.cuh"
 
 #include <cstring>
 #include <new>
@@ -195,6 +196,7 @@ int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx) {
   cudaFree(ctx->stage_x);
   cudaFree(ctx->stage_y);
   cudaFree(ctx->image);
+  cudaFree(ctx->tc_scratch);
   if (ctx->own_stream) {
     cudaStreamDestroy(ctx->stream);
   }
@@ -233,6 +235,10 @@ int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value) {
     ctx->early_state = value != 0;
     return GUFO_CUDA_OK;
   }
+  if (std::strcmp(name, "tc_gemm") == 0) {
+    ctx->tc_gemm = value != 0;
+    return GUFO_CUDA_OK;
+  }
   if (std::strcmp(name, "reuse_image") == 0) {
     ctx->reuse_image = value != 0;
     return GUFO_CUDA_OK;
@@ -244,7 +250,20 @@ int gufo_cuda_ctx_synchronize(gufo_cuda_ctx* ctx) {
   if (ctx == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "synchronize: ctx is null");
   }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
   GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  // A bounded wait of the tcgen05 GEMM that ran out leaves its code behind.
+  int code = 0;
+  const int rc = gufo::TcGemmError(ctx, &code);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (code != 0) {
+    cudaMemsetAsync(ctx->tc_scratch, 0, sizeof(int), ctx->stream);
+    return Fail(GUFO_CUDA_TIMEOUT, "tcgen05 gemm: a wait on a shared-memory barrier ran out (code " +
+                                       std::to_string(code) + "); the outputs of that product are invalid");
+  }
   return GUFO_CUDA_OK;
 }
 

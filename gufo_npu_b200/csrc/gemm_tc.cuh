@@ -1,0 +1,24 @@
+// Launch interface of the tcgen05 small-M GEMM (16 to 128 token rows per
+// weight read).
+#pragma once
+
+#include "gemv.cuh"
+#include "mma_common.cuh"
+
+namespace gufo {
+
+constexpr int kTcMinTokens = 16;    // below this the GEMV kernels re-read the weights per 8 tokens
+constexpr int kTcMaxTokens = 128;   // token rows per pass (the MMA's N)
+
+// Whether a product of `tokens` rows against parts of `type` runs on this path.
+bool TcGemmRuns(const gufo_cuda_ctx* ctx, int type, int cols, int tokens);
+
+// Enqueues y = [W_0 x | W_1 x | ...] for `tokens` >= kTcMinTokens rows; every
+// part of `base` must satisfy TcGemmRuns. x is 16-byte aligned.
+int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens);
+
+// Reads (after synchronizing the stream) the code a bounded wait of the GEMM
+// kernel left when it ran out; 0 when none did.
+int TcGemmError(gufo_cuda_ctx* ctx, int* code);
+
+}  // namespace gufo

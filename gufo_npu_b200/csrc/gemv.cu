@@ -12,6 +12,7 @@
 // fp32 accumulation throughout; lanes are combined with warp shuffles.
 // HBM-bound: algorithmic bytes are the GGUF row bytes plus x and y.
 #include "gemv.cuh"
+#include "gemm_tc.cuh"
 
 namespace gufo {
 
@@ -172,6 +173,25 @@ void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
 // kernels (x staged once per block format, one launch per part), the rest
 // together on the general kernel; at most kMaxTokens tokens per pass.
 int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
+  if (tokens >= kTcMinTokens && (reinterpret_cast<uintptr_t>(base.x) & 15) == 0) {
+    // Many token rows: the parts the tcgen05 GEMM runs read their weights once
+    // for all rows; the other parts take the 8-token passes below.
+    GemvArgs tc = base, other = base;
+    tc.nparts = other.nparts = 0;
+    tc.total_rows = other.total_rows = 0;
+    for (int p = 0; p < base.nparts; ++p) {
+      GemvArgs& to = TcGemmRuns(ctx, base.parts[p].type, base.cols, tokens) ? tc : other;
+      to.parts[to.nparts++] = base.parts[p];
+      to.total_rows += base.parts[p].rows;
+    }
+    if (tc.nparts > 0) {
+      const int rc = LaunchGemmTc(ctx, tc, tokens);
+      if (rc != GUFO_CUDA_OK || other.nparts == 0) {
+        return rc;
+      }
+      return LaunchGemv(ctx, other, tokens);
+    }
+  }
   for (int t0 = 0; t0 < tokens; t0 += kMaxTokens) {
     const int m = tokens - t0 < kMaxTokens ? tokens - t0 : kMaxTokens;
     const float* x = base.x + static_cast<size_t>(t0) * base.cols;
