@@ -363,6 +363,10 @@ def run_probe(which: str) -> None:
         y = torch.empty(1, rows, device=dev)
         for i in range(8):
             ctx.matmul_device(mats[i % copies], 1, x, 1, y)
+    elif which == "gemm":
+        return probe_gemm(ctx, stream, dev, gen)
+    elif which == "moe":
+        return probe_moe(ctx, stream, dev, gen)
     else:
         hv, dk, nseq, sets = 16, 128, 8, 12
         st = torch.randn(sets, nseq, hv, dk, dk, device=dev, generator=gen) * 0.1
@@ -381,9 +385,112 @@ def run_probe(which: str) -> None:
     print(json.dumps({"probe": which, "launches": ctx.launch_count()}))
 
 
+def graph_us(stream, enqueue, rounds: int = 5) -> float:
+    """Device microseconds of one replay of the work `enqueue()` puts on `stream`, captured
+    into a CUDA graph (so that host launch time does not pace the kernels), median of rounds."""
+    enqueue()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        enqueue()
+    g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(rounds):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return float(np.median(times))
+
+
+def probe_gemm(ctx, stream, dev, gen) -> None:
+    """The verify batch's FFN input product at 4B-class shapes: gate and up 9728 x 2560 Q4_K
+    stacked, M = 32 / 64 / 128 packed token rows, rotating over 6 weight copies (168 MB, larger
+    than L2). Prints device time per product with its HBM and tensor-core rates."""
+    from gufo_npu_b200.backend import Context
+    rows, cols, copies = 9728, 2560, 6
+    peak, _ = measured_peaks()
+    sets = []
+    keep = []
+    for _ in range(copies):
+        parts = []
+        for _ in range(2):
+            raw = Q.quantize(Q.GGML_Q4_K, torch.randn(rows, cols, device=dev, generator=gen) * 0.02)
+            keep.append(raw)
+            parts.append((ctx.matrix_from_device(Q.GGML_Q4_K, raw.data_ptr(), rows, cols), 0, rows))
+        sets.append(Context._parts(parts))
+    weight_bytes = 2 * rows * Q.row_bytes(Q.GGML_Q4_K, cols)
+    out = {"probe": "gemm", "shape": f"2 x {rows} x {cols} Q4_K", "results": []}
+    for m in (32, 64, 128):
+        x = torch.randn(m, cols, device=dev, generator=gen)
+        y = torch.empty(m, 2 * rows, device=dev)
+
+        def enqueue():
+            for c in range(copies):
+                ctx.matmul_device(sets[c], 2, x, m, y)
+        us = graph_us(stream, enqueue) / copies
+        algorithmic = weight_bytes + 4 * m * cols + 4 * m * 2 * rows
+        out["results"].append({"tokens": m, "us": us, "GB/s": algorithmic / us / 1e3,
+                               "hbm_frac": algorithmic / us / 1e3 / peak,
+                               "TFLOP/s": 2.0 * m * 2 * rows * cols / us / 1e6})
+    ctx.synchronize()
+    out["launches"] = ctx.launch_count()
+    print(json.dumps(out))
+
+
+def probe_moe(ctx, stream, dev, gen) -> None:
+    """One MoE token-layer at 35B-A3B-class shapes: hidden 2048, 256 experts of width 512 (Q4_K,
+    453 MB per bank, two banks alternated), top-8 routing of N(0,1) router logits on the device,
+    grouped expert products, weighted sum; 1 to 4 tokens."""
+    from gufo_npu_b200 import _capi
+    hidden, ef, experts, k, banks = 2048, 512, 256, 8, 2
+    peak, _ = measured_peaks()
+    keep, handles = [], []
+    for _ in range(banks):
+        ids = []
+        for rows, cols in ((ef, hidden), (ef, hidden), (hidden, ef)):
+            raw = Q.quantize(Q.GGML_Q4_K, torch.randn(experts * rows, cols, device=dev, generator=gen) * 0.02)
+            keep.append(raw)
+            ids.append(ctx.matrix_from_device(Q.GGML_Q4_K, raw.data_ptr(), experts * rows, cols))
+        handles.append(_capi.ExpertBank(*ids, experts, ef, hidden))
+    per_expert = 2 * ef * Q.row_bytes(Q.GGML_Q4_K, hidden) + hidden * Q.row_bytes(Q.GGML_Q4_K, ef)
+    out = {"probe": "moe", "shape": f"{experts} experts x (2 x {ef} x {hidden} + {hidden} x {ef}) Q4_K, top-{k}",
+           "results": []}
+    rounds = 6
+    for tokens in (1, 2, 4):
+        logits = torch.randn(rounds, tokens, experts + 1, device=dev, generator=gen)
+        x = torch.randn(tokens, hidden, device=dev, generator=gen)
+        shared = torch.randn(tokens, hidden, device=dev, generator=gen)
+        chosen = torch.empty(tokens, k, dtype=torch.int32, device=dev)
+        weights = torch.empty(tokens, k, device=dev)
+        scale = torch.empty(tokens, device=dev)
+        ffn = torch.empty(tokens * k, 2 * ef, device=dev)
+        act = torch.empty(tokens * k, ef, device=dev)
+        rows_out = torch.empty(tokens, k, hidden, device=dev)
+        y = torch.empty(tokens, hidden, device=dev)
+
+        def enqueue():
+            for r in range(rounds):
+                ctx.route_device(logits[r], experts + 1, tokens, experts, k, chosen, weights, scale)
+                for t in range(tokens):
+                    ctx.expert_ffn_device(handles[r % banks], chosen[t], k, x[t], 0, ffn[t * k:], act[t * k:],
+                                          rows_out[t])
+                ctx.moe_combine_device(shared, scale, weights, rows_out, tokens, k, hidden, y)
+        us = graph_us(stream, enqueue) / rounds
+        algorithmic = tokens * k * per_expert
+        out["results"].append({"tokens": tokens, "us": us, "GB/s": algorithmic / us / 1e3,
+                               "hbm_frac": algorithmic / us / 1e3 / peak})
+    ctx.synchronize()
+    out["launches"] = ctx.launch_count()
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["q4k", "q6k", "deltanet"],
+    ap.add_argument("--probe", default=None, choices=["q4k", "q6k", "deltanet", "gemm", "moe"],
                     help="run a few launches of one kernel on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

@@ -4,29 +4,42 @@
 // 128 token rows share one weight read - the ragged verify batch, where every
 // sequence brings a few draft tokens and the packed rows form one matrix.
 //
-// One thread block multiplies 128 weight rows by all the tokens:
-//   D[128 rows][N tokens] (fp32, tensor memory) += A[128][64] * B[N][64]^T
-// per 64 columns, with A the weights as fp16 and B the activations as fp16.
-//   - loader warp: bulk copies (cp.async.bulk, completion on an mbarrier) bring
-//     the rows' Q4_K blocks (144 B each) and the activation tiles into shared
-//     memory; the activations were converted once per product into tile images
-//     that already carry the shared-memory swizzle, so a tile is one copy;
-//   - four dequant warps, one thread per weight row: w = d*sc*q - dmin*m in fp32
+// One thread block multiplies 256 weight rows by all the tokens over a range
+// of K:
+//   D[128 token rows][256 weight rows] (fp32, tensor memory) += X[128][64] * W[256][64]^T
+// per 64 columns. The tokens sit on the MMA's M (the tensor core spends M cycles
+// per instruction whatever N is, measured here: 128 x 32 x 16 took as long as
+// 128 x 128 x 16), the weight rows fill its N = 256.
+//   - two loader warps copy one Q4_K block (144 B) of each of the 256 rows per
+//     stage with 16-byte cp.async whose completion arrives on an mbarrier
+//     (tiled TMA boxes this narrow, 144 B wide, ran no faster);
+//   - one loader thread brings the activation tiles with one bulk copy
+//     (cp.async.bulk) each: the activations were converted once per product into
+//     fp16 tile images that already carry the shared-memory swizzle;
+//   - sixteen dequant warps, two threads per weight row: w = d*sc*q - dmin*m in fp32
 //     (DequantQ4_K, src/core/quant.cpp:33-59), rounded once to fp16 and stored
 //     in the 128-byte-swizzled K-major layout the MMA reads;
-//   - one thread issues tcgen05.mma (kind::f16, M = 128, N = tokens rounded to
-//     16, K = 16, four per tile) and tcgen05.commit hands the tile buffers back;
-//   - the dequant warps then read the accumulator with tcgen05.ld and store
-//     y[token][row], 32 consecutive rows per warp store.
+//   - one thread issues tcgen05.mma (kind::f16, M = 128, N = 256, K = 16, four
+//     per tile) and tcgen05.commit hands the tile buffers back;
+//   - four epilogue warps read the accumulator with tcgen05.ld (lane = token,
+//     column = weight row) and store y[token][row] while the other warps are
+//     already on the next unit of work: thread blocks are persistent, walk their
+//     (row tile, K range) units round-robin, and tensor memory holds two
+//     accumulators.
 // Each activation row is scaled by a power of two into fp16 range first and the
 // outputs scaled back, so range never costs precision. Rounding w and x to
 // fp16 (11 significant bits) bounds the relative L2 error of y near 2e-4.
 //
-// Roofline: weights stream once from HBM (0.5625 B per weight); 2 * 128 * N * 64
-// flops per tile. Below N ~ 64 the bound is HBM (and the dequant arithmetic,
-// about 4 instructions per weight); above it the tensor pipe.
-// Matrices with few rows split K over several thread blocks; their partial
-// sums are added in a fixed order by a second kernel.
+// Roofline: weights stream once from HBM (0.5625 B per weight); a tile costs
+// 4 MMAs of 128 cycles for 256 x 64 weights, 32 weights per cycle per SM, and
+// about 4 instructions per weight of dequant arithmetic. What binds today is
+// shared-memory bandwidth: every weight is written as fp16 (2 B) and read by
+// the MMA (2 B), its Q4_K bytes pass through shared memory (1.1 B), and the
+// activation tile of 16 KiB is written and read once per 16384 weights (2 B):
+// about 7 B per weight against 128 B per cycle, 16 to 18 weights per cycle per
+// SM, which is what the kernel measures. Matrices with few row tiles split K
+// over thread blocks when the modelled time says so; the partial sums are
+// added in a fixed order by a second kernel.
 //
 // Every wait on an mbarrier is bounded: a wait that runs out records an error
 // code, raises a block-wide abort flag that ends all other waits, and the
@@ -39,44 +52,62 @@ namespace gufo {
 
 namespace {
 
-constexpr int kTileRows = 128;
-constexpr int kTileK = 64;                 // values per A / B tile (one swizzle row of fp16)
-constexpr int kTileBytes = kTileRows * kTileK * 2;   // 16 KiB
-constexpr int kAbStages = 4;
-constexpr int kRawStages = 3;
-constexpr int kRawBytes = kTileRows * kQ4KBytes;     // one Q4_K block of every row
-constexpr int kDequantThreads = 128;
-constexpr int kTcThreads = kDequantThreads + 64;     // + loader warp + MMA warp
-constexpr int kTmemColumns = 128;
+constexpr int kTileRows = 256;             // weight rows per thread block (the MMA's N)
+constexpr int kTokenRows = 128;            // token rows per tile image (the MMA's M)
+constexpr int kTileK = 64;                 // values per tile (one swizzle row of fp16)
+constexpr int kWTileBytes = kTileRows * kTileK * 2;    // 32 KiB
+constexpr int kXTileBytes = kTokenRows * kTileK * 2;   // 16 KiB
+constexpr int kWStages = 3;
+constexpr int kXStages = 3;
+constexpr int kRawStages = 2;
+constexpr int kRawBytes = kTileRows * kQ4KBytes;       // one Q4_K block of every row
+constexpr int kDequantThreads = 2 * kTileRows;         // two threads per weight row
+constexpr int kEpilogueWarp = kDequantThreads / 32;    // four epilogue warps, one per lane quarter
+constexpr int kEpilogueWarps = 4;
+constexpr int kLoaderWarp = kEpilogueWarp + kEpilogueWarps;   // and the next: weight loaders
+constexpr int kMmaWarp = kLoaderWarp + 2;
+constexpr int kTileLoaderWarp = kMmaWarp + 1;
+constexpr int kTcThreads = (kTileLoaderWarp + 1) * 32;
+constexpr int kTmemColumns = 512;                      // two accumulators of 256 columns
 constexpr long long kWaitCycles = 1ll << 31;   // about a second of SM clocks
 
 // Dynamic shared memory, from a 1024-byte aligned base.
 struct Smem {
-  static constexpr int kA = 0;
-  static constexpr int kB = kA + kAbStages * kTileBytes;
-  static constexpr int kRaw = kB + kAbStages * kTileBytes;
+  static constexpr int kW = 0;
+  static constexpr int kX = kW + kWStages * kWTileBytes;
+  static constexpr int kRaw = kX + kXStages * kXTileBytes;
   static constexpr int kBars = kRaw + kRawStages * kRawBytes;
-  // raw_full[3], raw_empty[3], ab_full[4], ab_empty[4], acc_full
-  static constexpr int kBarCount = 2 * kRawStages + 2 * kAbStages + 1;
+  // raw_full[2], raw_empty[2], w_full[3], w_empty[3], x_full[3], x_empty[3], acc_full[2], acc_empty[2]
+  static constexpr int kBarCount = 2 * kRawStages + 2 * kWStages + 2 * kXStages + 4;
   static constexpr int kTmemSlot = kBars + kBarCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kBytes = kAbort + 4 + 1024;   // + room to align the base
 };
+static_assert(Smem::kX % 1024 == 0 && Smem::kRaw % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+static_assert(Smem::kBytes <= 227 * 1024, "beyond the shared memory of a thread block");
 
-struct TcGemmArgs {
+constexpr int kTcMaxParts = 4;
+
+struct TcPart {
   const uint8_t* w;        // first row
   int rows;
   int row_bytes;
-  int blocks;              // Q4_K blocks per row
-  int blocks_per_unit;     // K range of one thread block
-  int ksplit;
-  const uint8_t* xh;       // activation tile images [blocks * 4][npad][64] fp16, swizzled
-  const float* unscale;    // [npad]: factor that undoes the row's power-of-two scale
-  int npad;                // tokens rounded up to a multiple of 16
-  int tokens;
+  int tiles;               // 256-row tiles of this part
   float* out;              // ksplit == 1: y + offset; else partial sums [ksplit][tokens][rows]
   int out_stride;          // floats between token rows of out
   size_t split_stride;     // floats between the K ranges' partial sums
+};
+
+struct TcGemmArgs {
+  TcPart parts[kTcMaxParts];
+  int nparts;
+  int blocks;              // Q4_K blocks per row
+  int blocks_per_unit;     // K range of one unit of work
+  int ksplit;
+  int total_units;         // tiles * ksplit, dealt round-robin to the thread blocks
+  const uint8_t* xh;       // activation tile images [blocks * 4][128][64] fp16, swizzled
+  const float* unscale;    // [128]: factor that undoes the row's power-of-two scale
+  int tokens;
   int* error;              // device int: 0, or the code of the first wait that ran out
 };
 
@@ -172,20 +203,70 @@ __device__ __forceinline__ void TmemLoad16(uint32_t taddr, float (&v)[16]) {
   }
 }
 
-// Eight weights of one sub-block from the low nibbles of two words, as four
-// fp16 pairs: w = scale * q - offset.
-__device__ __forceinline__ uint4 EightWeights(uint32_t w0, uint32_t w1, float scale, float offset) {
-  const float q0 = SmallByteToFloat<0>(w0), q1 = SmallByteToFloat<1>(w0);
-  const float q2 = SmallByteToFloat<2>(w0), q3 = SmallByteToFloat<3>(w0);
-  const float q4 = SmallByteToFloat<0>(w1), q5 = SmallByteToFloat<1>(w1);
-  const float q6 = SmallByteToFloat<2>(w1), q7 = SmallByteToFloat<3>(w1);
-  const __half2 h0 = __floats2half2_rn(fmaf(q0, scale, -offset), fmaf(q1, scale, -offset));
-  const __half2 h1 = __floats2half2_rn(fmaf(q2, scale, -offset), fmaf(q3, scale, -offset));
-  const __half2 h2 = __floats2half2_rn(fmaf(q4, scale, -offset), fmaf(q5, scale, -offset));
-  const __half2 h3 = __floats2half2_rn(fmaf(q6, scale, -offset), fmaf(q7, scale, -offset));
-  return make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
-                    *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+// Nibble I (bits 4I .. 4I + 3, I <= 4) of `w` as a float: the nibble is masked
+// in place under the exponent whose mantissa bit 4I is worth 1, which reads as
+// 2^(23 - 4I) + code; subtracting the power of two leaves the code exactly.
+// One logic instruction and one add instead of a byte permute (half rate here).
+template <int I>
+__device__ __forceinline__ float Nibble(uint32_t w) {
+  static_assert(I >= 0 && I <= 4, "the nibble must sit below the exponent");
+  constexpr uint32_t kExponent = static_cast<uint32_t>(127 + 23 - 4 * I) << 23;
+  return __uint_as_float((w & (0xFu << (4 * I))) | kExponent) - __uint_as_float(kExponent);
 }
+
+// The sixteen weights in two words of a sub-block pair's nibble bytes: the low
+// nibbles of the eight bytes (sub-block 2t) and the high nibbles (sub-block
+// 2t + 1), each as four fp16 pairs in byte order: w = scale * code - offset in
+// fp32, rounded once.
+__device__ __forceinline__ void SixteenWeights(uint32_t w0, uint32_t w1, float a_lo, float b_lo, float a_hi,
+                                               float b_hi, uint4* low, uint4* high) {
+  // Nibbles 5 to 7 of a word are nibbles 2 to 4 of the word shifted down by 12.
+  const uint32_t s0 = w0 >> 12, s1 = w1 >> 12;
+  auto pack = [](float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  };
+  low->x = pack(fmaf(Nibble<0>(w0), a_lo, -b_lo), fmaf(Nibble<2>(w0), a_lo, -b_lo));
+  low->y = pack(fmaf(Nibble<4>(w0), a_lo, -b_lo), fmaf(Nibble<3>(s0), a_lo, -b_lo));
+  low->z = pack(fmaf(Nibble<0>(w1), a_lo, -b_lo), fmaf(Nibble<2>(w1), a_lo, -b_lo));
+  low->w = pack(fmaf(Nibble<4>(w1), a_lo, -b_lo), fmaf(Nibble<3>(s1), a_lo, -b_lo));
+  high->x = pack(fmaf(Nibble<1>(w0), a_hi, -b_hi), fmaf(Nibble<3>(w0), a_hi, -b_hi));
+  high->y = pack(fmaf(Nibble<2>(s0), a_hi, -b_hi), fmaf(Nibble<4>(s0), a_hi, -b_hi));
+  high->z = pack(fmaf(Nibble<1>(w1), a_hi, -b_hi), fmaf(Nibble<3>(w1), a_hi, -b_hi));
+  high->w = pack(fmaf(Nibble<2>(s1), a_hi, -b_hi), fmaf(Nibble<4>(s1), a_hi, -b_hi));
+}
+
+// Where unit `u` of a launch works: its part, weight rows and K range.
+struct Unit {
+  int part;
+  int row0;
+  int split;
+  int first_block;
+  int blocks;
+};
+
+__device__ __forceinline__ Unit LocateUnit(const TcGemmArgs& a, int u) {
+  Unit unit;
+  int tile = u / a.ksplit;
+  unit.split = u - tile * a.ksplit;
+  unit.part = 0;
+#pragma unroll
+  for (int p = 0; p < kTcMaxParts - 1; ++p) {
+    if (unit.part == p && p + 1 < a.nparts && tile >= a.parts[p].tiles) {
+      tile -= a.parts[p].tiles;
+      unit.part = p + 1;
+    }
+  }
+  unit.row0 = tile * kTileRows;
+  unit.first_block = unit.split * a.blocks_per_unit;
+  unit.blocks = min(a.blocks_per_unit, a.blocks - unit.first_block);   // >= 1 by construction
+  return unit;
+}
+
+// Row of the MMA's M that token t occupies: tokens are dealt round-robin to the
+// four 32-lane quarters of tensor memory, so that all four epilogue warps (each
+// can read one quarter) share the work of a small batch.
+__host__ __device__ __forceinline__ int TokenRow(int t) { return (t & 3) * 32 + (t >> 2); }
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
@@ -196,31 +277,36 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
   const uint32_t bars = base + Smem::kBars;
   auto raw_full = [&](int s) { return bars + 8u * s; };
   auto raw_empty = [&](int s) { return bars + 8u * (kRawStages + s); };
-  auto ab_full = [&](int s) { return bars + 8u * (2 * kRawStages + s); };
-  auto ab_empty = [&](int s) { return bars + 8u * (2 * kRawStages + kAbStages + s); };
-  const uint32_t acc_full = bars + 8u * (2 * kRawStages + 2 * kAbStages);
+  auto w_full = [&](int s) { return bars + 8u * (2 * kRawStages + s); };
+  auto w_empty = [&](int s) { return bars + 8u * (2 * kRawStages + kWStages + s); };
+  auto x_full = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kWStages + s); };
+  auto x_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kWStages + kXStages + s); };
+  auto acc_full = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kWStages + 2 * kXStages + s); };
+  auto acc_empty = [&](int s) { return bars + 8u * (2 * kRawStages + 2 * kWStages + 2 * kXStages + 2 + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Smem::kTmemSlot);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + Smem::kAbort);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tile = static_cast<int>(blockIdx.x) / a.ksplit;
-  const int split = static_cast<int>(blockIdx.x) % a.ksplit;
-  const int first_block = split * a.blocks_per_unit;
-  const int unit_blocks = min(a.blocks_per_unit, a.blocks - first_block);   // >= 1 by construction
-  const int row0 = tile * kTileRows;
-  const uint32_t b_tile_bytes = static_cast<uint32_t>(a.npad) * (kTileK * 2);
+  const int units = a.total_units;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
-      MbarInit(raw_full(s), 1);
-      MbarInit(raw_empty(s), kDequantThreads);
+      MbarInit(raw_full(s), 64);
+      MbarInit(raw_empty(s), kDequantThreads / 32);
     }
-    for (int s = 0; s < kAbStages; ++s) {
-      MbarInit(ab_full(s), kDequantThreads + 1);
-      MbarInit(ab_empty(s), 1);
+    for (int s = 0; s < kWStages; ++s) {
+      MbarInit(w_full(s), kTileRows / 32);
+      MbarInit(w_empty(s), 1);
     }
-    MbarInit(acc_full, 1);
+    for (int s = 0; s < kXStages; ++s) {
+      MbarInit(x_full(s), 1);
+      MbarInit(x_empty(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      MbarInit(acc_full(s), 1);
+      MbarInit(acc_empty(s), kEpilogueWarps);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -234,141 +320,210 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
-  // The weights never depend on earlier kernels; the activation tiles do.
+  // The weights never depend on earlier kernels; the activation tiles and the
+  // outputs do.
   GridLaunchDependents();
 
-  if (warp == 4) {
-    // ---- loader ----------------------------------------------------------
-    // Weight blocks are requested kRawStages blocks ahead of the activation
-    // tiles, whose buffers only free up as the MMAs retire.
-    int raw_next = 0;
-    auto request_blocks = [&](int upto) {
-      for (; raw_next < upto && raw_next < unit_blocks; ++raw_next) {
-        const int s = raw_next % kRawStages;
-        const uint32_t phase = (raw_next / kRawStages) & 1u;
+  // Every role walks the same units, blockIdx.x, blockIdx.x + gridDim.x, ...;
+  // the stage counters run on across units, so the pipeline never drains
+  // between them.
+  if (warp == kLoaderWarp || warp == kLoaderWarp + 1) {
+    // ---- weight loaders: 2304 16-byte chunks per block (9 per row), split
+    // between the two warps; consecutive lanes take consecutive chunks, so one
+    // instruction touches the 144-byte runs of three or four rows ---------------
+    const int which = warp - kLoaderWarp;
+    constexpr int kChunksPerRow = kQ4KBytes / 16;
+    constexpr int kChunks = kTileRows * kChunksPerRow;
+    int i = 0;   // blocks requested so far
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const Unit unit = LocateUnit(a, u);
+      const TcPart& part = a.parts[unit.part];
+      for (int b = 0; b < unit.blocks; ++b, ++i) {
+        const int s = i % kRawStages;
+        const uint32_t phase = (i / kRawStages) & 1u;
         BoundedWait(raw_empty(s), phase ^ 1u, abort_flag, a.error, 1);
+        const uint32_t to = base + Smem::kRaw + s * kRawBytes;
+        const size_t column = static_cast<size_t>(unit.first_block + b) * kQ4KBytes;
+#pragma unroll 6
+        for (int c = which * 32 + lane; c < kChunks; c += 64) {
+          const int r = c / kChunksPerRow;
+          const int chunk = c - r * kChunksPerRow;
+          // Rows past the end repeat the last row; their sums are never stored.
+          const int row = min(unit.row0 + r, part.rows - 1);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to + c * 16),
+                       "l"(part.w + static_cast<size_t>(row) * part.row_bytes + column + chunk * 16) : "memory");
+        }
+        // Arrives on the stage's barrier once this thread's copies have landed.
+        asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(s)) : "memory");
+      }
+    }
+  } else if (warp == kTileLoaderWarp) {
+    // ---- activation tile loader ------------------------------------------------
+    GridDependencyWait();
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const Unit unit = LocateUnit(a, u);
+      for (int i = 0; i < unit.blocks * 4; ++i) {
+        BoundedWait(x_empty(stage), phase ^ 1u, abort_flag, a.error, 2);
         if (lane == 0) {
-          MbarArriveExpectTx(raw_full(s), kRawBytes);
+          MbarArriveExpectTx(x_full(stage), kXTileBytes);
+          BulkCopy(base + Smem::kX + stage * kXTileBytes,
+                   a.xh + (static_cast<size_t>(unit.first_block) * 4 + i) * kXTileBytes, kXTileBytes, x_full(stage));
+        }
+        if (++stage == kXStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ---- MMA issue ---------------------------------------------------------
+    // kind::f16, fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
+    const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(kTileRows >> 3) << 17) |
+                           (static_cast<uint32_t>(kTokenRows >> 4) << 24);
+    int ws = 0, xs = 0;
+    uint32_t w_phase = 0, x_phase = 0;
+    int n = 0;   // units done
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++n) {
+      const Unit unit = LocateUnit(a, u);
+      const int buffer = n & 1;
+      // The epilogue of the unit before last has read this accumulator.
+      BoundedWait(acc_empty(buffer), ((n >> 1) & 1u) ^ 1u, abort_flag, a.error, 8);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t accumulator = tmem + static_cast<uint32_t>(buffer * kTileRows);
+      for (int i = 0; i < unit.blocks * 4; ++i) {
+        BoundedWait(w_full(ws), w_phase, abort_flag, a.error, 3);
+        BoundedWait(x_full(xs), x_phase, abort_flag, a.error, 7);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (lane == 0) {
+          const uint64_t desc_x = TileDescriptor(base + Smem::kX + xs * kXTileBytes);
+          const uint64_t desc_w = TileDescriptor(base + Smem::kW + ws * kWTileBytes);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            // 16 values = 32 bytes further along K inside the swizzled rows.
+            MmaF16(accumulator, desc_x + 2u * k, desc_w + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          // Each commit arrives once everything issued so far has retired.
+          MmaCommit(w_empty(ws));
+          MmaCommit(x_empty(xs));
+          if (i == unit.blocks * 4 - 1) {
+            MmaCommit(acc_full(buffer));
+          }
         }
         __syncwarp();
-        const int block = first_block + raw_next;
-#pragma unroll
-        for (int rr = 0; rr < kTileRows / 32; ++rr) {
-          const int r = rr * 32 + lane;
-          // Rows past the end repeat the last row; their sums are never stored.
-          const int row = min(row0 + r, a.rows - 1);
-          BulkCopy(base + Smem::kRaw + s * kRawBytes + r * kQ4KBytes,
-                   a.w + static_cast<size_t>(row) * a.row_bytes + static_cast<size_t>(block) * kQ4KBytes,
-                   kQ4KBytes, raw_full(s));
+        if (++ws == kWStages) {
+          ws = 0;
+          w_phase ^= 1u;
         }
-      }
-    };
-    request_blocks(kRawStages - 1);
-    GridDependencyWait();
-    int ab_stage = 0;
-    uint32_t ab_phase = 0;
-    for (int i = 0; i < unit_blocks; ++i) {
-      request_blocks(i + kRawStages);
-      const int block = first_block + i;
-      for (int t = 0; t < 4; ++t) {
-        BoundedWait(ab_empty(ab_stage), ab_phase ^ 1u, abort_flag, a.error, 2);
-        if (lane == 0) {
-          MbarArriveExpectTx(ab_full(ab_stage), b_tile_bytes);
-          BulkCopy(base + Smem::kB + ab_stage * kTileBytes,
-                   a.xh + (static_cast<size_t>(block) * 4 + t) * b_tile_bytes, b_tile_bytes, ab_full(ab_stage));
-        }
-        if (++ab_stage == kAbStages) {
-          ab_stage = 0;
-          ab_phase ^= 1u;
+        if (++xs == kXStages) {
+          xs = 0;
+          x_phase ^= 1u;
         }
       }
     }
-  } else if (warp == 5) {
-    // ---- MMA issue ---------------------------------------------------------
-    // kind::f16, fp32 accumulate, fp16 A and B, both K-major, N = npad, M = 128.
-    const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(a.npad >> 3) << 17) | (8u << 24);
-    int ab_stage = 0;
-    uint32_t ab_phase = 0;
-    for (int i = 0; i < unit_blocks * 4; ++i) {
-      BoundedWait(ab_full(ab_stage), ab_phase, abort_flag, a.error, 3);
+  } else if (warp >= kEpilogueWarp && warp < kEpilogueWarp + kEpilogueWarps) {
+    // ---- epilogue: lane of tensor memory = token row, column = weight row;
+    // warp q reads quarter q, i.e. tokens q, q + 4, q + 8, ... -------------------
+    const int quarter = warp - kEpilogueWarp;
+    const int token = lane * 4 + quarter;
+    int n = 0;
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++n) {
+      const Unit unit = LocateUnit(a, u);
+      const TcPart& part = a.parts[unit.part];
+      const int buffer = n & 1;
+      const bool ready = BoundedWait(acc_full(buffer), (n >> 1) & 1u, abort_flag, a.error, 6);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (lane == 0) {
-        const uint64_t desc_a = TileDescriptor(base + Smem::kA + ab_stage * kTileBytes);
-        const uint64_t desc_b = TileDescriptor(base + Smem::kB + ab_stage * kTileBytes);
+      const bool live = ready && token < a.tokens;
+      const float unscale = live ? a.unscale[token] : 0.f;
+      float* out = part.out + static_cast<size_t>(unit.split) * part.split_stride +
+                   static_cast<size_t>(token) * part.out_stride + unit.row0;
+      // 16-byte stores where the output rows allow them.
+      const bool vector_stores = (reinterpret_cast<uintptr_t>(part.out) & 15) == 0 && part.out_stride % 4 == 0 &&
+                                 part.split_stride % 4 == 0;
+      // A quarter without tokens is skipped (uniform over the warp, as
+      // tcgen05.ld requires).
+      if (quarter < a.tokens) {
+        for (int col0 = 0; col0 < kTileRows; col0 += 16) {
+          float v[16];
+          TmemLoad16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * kTileRows + col0, v);
+          if (live) {
+            if (vector_stores && unit.row0 + col0 + 16 <= part.rows) {
 #pragma unroll
-        for (int k = 0; k < kTileK / 16; ++k) {
-          // 16 values = 32 bytes further along K inside the swizzled rows.
-          MmaF16(tmem, desc_a + 2u * k, desc_b + 2u * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        MmaCommit(ab_empty(ab_stage));
-        if (i == unit_blocks * 4 - 1) {
-          MmaCommit(acc_full);
-        }
-      }
-      __syncwarp();
-      if (++ab_stage == kAbStages) {
-        ab_stage = 0;
-        ab_phase ^= 1u;
-      }
-    }
-  } else {
-    // ---- dequant: thread r owns weight row r of the tile ---------------------
-    const int r = threadIdx.x;
-    int ab_stage = 0;
-    uint32_t ab_phase = 0;
-    for (int i = 0; i < unit_blocks; ++i) {
-      const int s = i % kRawStages;
-      const uint32_t phase = (i / kRawStages) & 1u;
-      BoundedWait(raw_full(s), phase, abort_flag, a.error, 4);
-      const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * kQ4KBytes;
-      const uint4 head = *reinterpret_cast<const uint4*>(block);
-      const float d = HalfBitsToFloat(static_cast<uint16_t>(head.x & 0xFFFF));
-      const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head.x >> 16));
+              for (int j = 0; j < 16; j += 4) {
+                *reinterpret_cast<float4*>(out + col0 + j) =
+                    make_float4(v[j] * unscale, v[j + 1] * unscale, v[j + 2] * unscale, v[j + 3] * unscale);
+              }
+            } else {
 #pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        int sc_lo, m_lo, sc_hi, m_hi;
-        ScaleMinK4(2 * t, head.y, head.z, head.w, &sc_lo, &m_lo);
-        ScaleMinK4(2 * t + 1, head.y, head.z, head.w, &sc_hi, &m_hi);
-        const float a_lo = d * static_cast<float>(sc_lo), b_lo = dmin * static_cast<float>(m_lo);
-        const float a_hi = d * static_cast<float>(sc_hi), b_hi = dmin * static_cast<float>(m_hi);
-        const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t);
-        const uint4 q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
-        const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-        BoundedWait(ab_empty(ab_stage), ab_phase ^ 1u, abort_flag, a.error, 5);
-        uint8_t* tile_row = smem + Smem::kA + ab_stage * kTileBytes + r * 128;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
-          const uint32_t w0 = words[2 * c], w1 = words[2 * c + 1];
-          const uint4 low = EightWeights(w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, a_lo, b_lo);
-          const uint4 high = EightWeights((w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, a_hi, b_hi);
-          *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) = low;
-          *reinterpret_cast<uint4*>(tile_row + (((4 + c) ^ (r & 7)) << 4)) = high;
-        }
-        // Make the generic-proxy stores visible to the tensor core's reads.
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        MbarArrive(ab_full(ab_stage));
-        if (++ab_stage == kAbStages) {
-          ab_stage = 0;
-          ab_phase ^= 1u;
-        }
-      }
-      MbarArrive(raw_empty(s));
-    }
-    // ---- epilogue: lane = weight row, column = token ---------------------------
-    const bool ready = BoundedWait(acc_full, 0, abort_flag, a.error, 6);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int row = row0 + r;
-    float* out = a.out + static_cast<size_t>(split) * a.split_stride + row;
-    for (int col0 = 0; col0 < a.npad; col0 += 16) {
-      float v[16];
-      TmemLoad16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + col0, v);
-      if (ready && row < a.rows) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (col0 + j < a.tokens) {
-            out[static_cast<size_t>(col0 + j) * a.out_stride] = v[j] * a.unscale[col0 + j];
+              for (int j = 0; j < 16; ++j) {
+                if (unit.row0 + col0 + j < part.rows) {
+                  out[col0 + j] = v[j] * unscale;
+                }
+              }
+            }
           }
+        }
+      }
+      // This accumulator may be overwritten now.
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        MbarArrive(acc_empty(buffer));
+      }
+    }
+  } else if (warp < kDequantThreads / 32) {
+    // ---- dequant: threads r and r + 256 own weight row r of the tile; the
+    // first takes sub-block pairs 0 and 1 of every block, the second 2 and 3.
+    // Tile g = 4 * block + pair of the thread block's stream lands in buffer g % 3.
+    const int r = threadIdx.x & (kTileRows - 1);
+    const int half = threadIdx.x / kTileRows;
+    int i = 0;   // blocks done so far
+    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+      const Unit unit = LocateUnit(a, u);
+      for (int b = 0; b < unit.blocks; ++b, ++i) {
+        const int s = i % kRawStages;
+        const uint32_t phase = (i / kRawStages) & 1u;
+        BoundedWait(raw_full(s), phase, abort_flag, a.error, 4);
+        const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * kQ4KBytes;
+        const uint4 head = *reinterpret_cast<const uint4*>(block);
+        const float d = HalfBitsToFloat(static_cast<uint16_t>(head.x & 0xFFFF));
+        const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head.x >> 16));
+#pragma unroll
+        for (int tt = 0; tt < 2; ++tt) {
+          const int t = 2 * half + tt;
+          const int g = 4 * i + t;
+          const int ws = g % kWStages;
+          const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
+          int sc_lo, m_lo, sc_hi, m_hi;
+          ScaleMinK4(2 * t, head.y, head.z, head.w, &sc_lo, &m_lo);
+          ScaleMinK4(2 * t + 1, head.y, head.z, head.w, &sc_hi, &m_hi);
+          const float a_lo = d * static_cast<float>(sc_lo), a_hi = d * static_cast<float>(sc_hi);
+          const float b_lo = dmin * static_cast<float>(m_lo), b_hi = dmin * static_cast<float>(m_hi);
+          const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t);
+          const uint4 q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
+          const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+          BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
+          uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
+            uint4 low, high;
+            SixteenWeights(words[2 * c], words[2 * c + 1], a_lo, b_lo, a_hi, b_hi, &low, &high);
+            *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) = low;
+            *reinterpret_cast<uint4*>(tile_row + (((4 + c) ^ (r & 7)) << 4)) = high;
+          }
+          // Make the generic-proxy stores visible to the tensor core's reads; one
+          // lane then arrives for the warp.
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) {
+            MbarArrive(w_full(ws));
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          MbarArrive(raw_empty(s));
         }
       }
     }
@@ -388,7 +543,8 @@ StageHalfKernel(const float* __restrict__ x, int tokens, int cols, int npad, uin
                 float* __restrict__ unscale) {
   __shared__ uint32_t warp_top[8];
   GridDependencyWait();
-  const int n = blockIdx.x;
+  const int n = blockIdx.x;                  // token
+  const int image_row = TokenRow(n);        // its row of the MMA's M
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   float up = 1.0f;
@@ -437,7 +593,8 @@ StageHalfKernel(const float* __restrict__ x, int tokens, int cols, int npad, uin
     }
     const int tile = k / kTileK;
     const int c = (k % kTileK) / 8;
-    *reinterpret_cast<uint4*>(xh + tile * tile_bytes + static_cast<size_t>(n) * 128 + ((c ^ (n & 7)) << 4)) = packed;
+    *reinterpret_cast<uint4*>(xh + tile * tile_bytes + static_cast<size_t>(image_row) * 128 +
+                              ((c ^ (image_row & 7)) << 4)) = packed;
   }
 }
 
@@ -474,6 +631,7 @@ int ReserveTc(gufo_cuda_ctx* ctx, size_t bytes) {
   return GUFO_CUDA_OK;
 }
 
+
 }  // namespace
 
 bool TcGemmRuns(const gufo_cuda_ctx* ctx, int type, int cols, int tokens) {
@@ -491,31 +649,51 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     GUFO_CUDA_TRY(cudaFuncSetAttribute(GemmQ4KTc, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
     configured[ctx->device & 15] = true;
   }
+  for (int p = 0; p < base.nparts; ++p) {
+    if ((reinterpret_cast<uintptr_t>(base.parts[p].data) & 15) != 0 || base.parts[p].row_bytes % 16 != 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "tcgen05 gemm: weight rows must be 16-byte aligned");
+    }
+  }
+  // K ranges per 256-row tile; up to kTcMaxParts parts share a launch and its split.
+  // The split with the least modelled time: rounds of units over the persistent
+  // thread blocks, each a K range plus a little for the accumulator hand-over;
+  // a split pays for its partial sums; ties go to the smaller split.
+  auto splits_for = [&](int tiles, int m) {
+    // In units of one block's time on one SM (about 1.5 us): what the partial
+    // sums of one more K range cost in HBM traffic, written once and read once.
+    const double range_cost = 2.0 * m * (static_cast<double>(tiles) * kTileRows) * 4.0 / 6.0e6 / 1.5;
+    int best = 1;
+    double best_cost = 1e30;
+    for (int ksplit = 1; ksplit <= blocks; ++ksplit) {
+      const int per = (blocks + ksplit - 1) / ksplit;
+      const int ranges = (blocks + per - 1) / per;   // no empty K range
+      if (ranges != ksplit) {
+        continue;
+      }
+      const int rounds = (tiles * ksplit + ctx->sm_count - 1) / ctx->sm_count;
+      const double cost = rounds * (per + 0.3) + (ksplit > 1 ? 2.0 + ksplit * range_cost : 0.0);
+      if (cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = ksplit;
+      }
+    }
+    return best;
+  };
   for (int t0 = 0; t0 < tokens; t0 += kTcMaxTokens) {
     const int m = tokens - t0 < kTcMaxTokens ? tokens - t0 : kTcMaxTokens;
-    const int npad = (m + 15) / 16 * 16;
-    const size_t image_bytes = static_cast<size_t>(blocks) * 4 * npad * (kTileK * 2);
-    int max_rows = 0;
-    for (int p = 0; p < base.nparts; ++p) {
-      max_rows = base.parts[p].rows > max_rows ? base.parts[p].rows : max_rows;
-    }
-    // Enough thread blocks to cover the SMs once: split K when the rows alone do not.
-    auto splits_for = [&](int rows) {
-      const int tiles = (rows + kTileRows - 1) / kTileRows;
-      int ksplit = 1;
-      if (tiles * 5 < ctx->sm_count * 3) {
-        ksplit = ctx->sm_count / tiles;
-        ksplit = ksplit > blocks ? blocks : ksplit;
-        ksplit = ksplit < 1 ? 1 : ksplit;
-      }
-      const int per = (blocks + ksplit - 1) / ksplit;
-      return (blocks + per - 1) / per;   // no empty K range
-    };
+    const size_t image_bytes = static_cast<size_t>(blocks) * 4 * kXTileBytes;
+    // Worst case for the partial sums: every part split into blocks / 2 ranges.
     size_t partial_floats = 0;
-    for (int p = 0; p < base.nparts; ++p) {
-      const int ksplit = splits_for(base.parts[p].rows);
+    for (int p0 = 0; p0 < base.nparts; p0 += kTcMaxParts) {
+      int tiles = 0;
+      size_t rows = 0;
+      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+        tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
+        rows += base.parts[p].rows;
+      }
+      const int ksplit = splits_for(tiles, m);
       if (ksplit > 1) {
-        const size_t need = static_cast<size_t>(ksplit) * m * base.parts[p].rows;
+        const size_t need = static_cast<size_t>(ksplit) * m * rows;
         partial_floats = need > partial_floats ? need : partial_floats;
       }
     }
@@ -530,42 +708,54 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     float* unscale = reinterpret_cast<float*>(ctx->tc_scratch + unscale_at);
     float* partial = reinterpret_cast<float*>(ctx->tc_scratch + partial_at);
     const float* x = base.x + static_cast<size_t>(t0) * cols;
-    GUFO_CUDA_TRY(LaunchOverlapped(StageHalfKernel, dim3(npad), dim3(256), 0, ctx->stream, 1, x, m, cols, npad, xh,
-                                   unscale));
+    GUFO_CUDA_TRY(LaunchOverlapped(StageHalfKernel, dim3(kTokenRows), dim3(256), 0, ctx->stream, 1, x, m, cols,
+                                   kTokenRows, xh, unscale));
     ctx->launches.fetch_add(1);
-    for (int p = 0; p < base.nparts; ++p) {
-      const GemvPart& part = base.parts[p];
+    for (int p0 = 0; p0 < base.nparts; p0 += kTcMaxParts) {
       TcGemmArgs args{};
-      args.w = part.data;
-      args.rows = part.rows;
-      args.row_bytes = part.row_bytes;
       args.blocks = blocks;
-      args.ksplit = splits_for(part.rows);
-      args.blocks_per_unit = (blocks + args.ksplit - 1) / args.ksplit;
       args.xh = xh;
       args.unscale = unscale;
-      args.npad = npad;
       args.tokens = m;
       args.error = reinterpret_cast<int*>(ctx->tc_scratch);
-      float* y = base.y + static_cast<size_t>(t0) * base.y_stride + part.out_offset;
-      if (args.ksplit == 1) {
-        args.out = y;
-        args.out_stride = base.y_stride;
-        args.split_stride = 0;
-      } else {
-        args.out = partial;
-        args.out_stride = part.rows;
-        args.split_stride = static_cast<size_t>(m) * part.rows;
+      int tiles = 0;
+      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+        tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
       }
-      const int tiles = (part.rows + kTileRows - 1) / kTileRows;
-      GUFO_CUDA_TRY(LaunchOverlapped(GemmQ4KTc, dim3(tiles * args.ksplit), dim3(kTcThreads), Smem::kBytes,
-                                     ctx->stream, 1, args));
+      args.ksplit = splits_for(tiles, m);
+      args.blocks_per_unit = (blocks + args.ksplit - 1) / args.ksplit;
+      float* next_partial = partial;
+      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+        const GemvPart& part = base.parts[p];
+        TcPart& to = args.parts[args.nparts++];
+        to.w = part.data;
+        to.rows = part.rows;
+        to.row_bytes = part.row_bytes;
+        to.tiles = (part.rows + kTileRows - 1) / kTileRows;
+        if (args.ksplit == 1) {
+          to.out = base.y + static_cast<size_t>(t0) * base.y_stride + part.out_offset;
+          to.out_stride = base.y_stride;
+          to.split_stride = 0;
+        } else {
+          to.out = next_partial;
+          to.out_stride = part.rows;
+          to.split_stride = static_cast<size_t>(m) * part.rows;
+          next_partial += static_cast<size_t>(args.ksplit) * m * part.rows;
+        }
+      }
+      args.total_units = tiles * args.ksplit;
+      const int grid = args.total_units < ctx->sm_count ? args.total_units : ctx->sm_count;
+      GUFO_CUDA_TRY(LaunchOverlapped(GemmQ4KTc, dim3(grid), dim3(kTcThreads), Smem::kBytes, ctx->stream, 1, args));
       ctx->launches.fetch_add(1);
       if (args.ksplit > 1) {
-        GUFO_CUDA_TRY(LaunchOverlapped(SumSplitsKernel, dim3((part.rows + 255) / 256, m), dim3(256), 0, ctx->stream, 1,
-                                       static_cast<const float*>(partial), args.ksplit, args.split_stride, part.rows,
-                                       m, y, base.y_stride));
-        ctx->launches.fetch_add(1);
+        for (int i = 0; i < args.nparts; ++i) {
+          const GemvPart& part = base.parts[p0 + i];
+          float* y = base.y + static_cast<size_t>(t0) * base.y_stride + part.out_offset;
+          GUFO_CUDA_TRY(LaunchOverlapped(SumSplitsKernel, dim3((part.rows + 255) / 256, m), dim3(256), 0, ctx->stream,
+                                         1, static_cast<const float*>(args.parts[i].out), args.ksplit,
+                                         args.parts[i].split_stride, part.rows, m, y, base.y_stride));
+          ctx->launches.fetch_add(1);
+        }
       }
     }
   }
@@ -583,3 +773,5 @@ int TcGemmError(gufo_cuda_ctx* ctx, int* code) {
 }
 
 }  // namespace gufo
+
+

@@ -159,17 +159,20 @@ def test_activation_extremes(ctx, oracle):
 @pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8, 9, 19])
 def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
     """Results do not depend on how many tokens come together
-    (src/models/qwen35/gguf_projections.cpp:241-243)."""
+    (src/models/qwen35/gguf_projections.cpp:241-243): to fp32 summation order below 16 tokens, and
+    to the fp16 rounding of the tcgen05 path (Q4_K, 16 tokens and more) above, both far inside
+    the 1e-3 bound."""
     rows, cols = 96, 768
     x = G.normal(50 + tokens, tokens, cols)
+    exact_tol, same_tol = (1e-5, 1e-6) if tokens < 16 else (4e-4, 4e-4)
     for name, t in TYPES.items():
         raw = Q.quantize(t, torch.from_numpy(G.normal(60, rows, cols) * 0.02)).numpy()
         m = ctx.matrix_upload(t, raw, rows, cols)
         got = ctx.matmul([(m, 0, rows)], x, tokens, rows)
         want = oracle.matmul([(raw, t, 0, rows)], cols, x)
-        assert rel_l2(got, want) <= 1e-5
+        assert rel_l2(got, want) <= exact_tol
         single = np.stack([ctx.matmul([(m, 0, rows)], x[i], 1, rows)[0] for i in range(tokens)])
-        assert rel_l2(got, single) <= 1e-6
+        assert rel_l2(got, single) <= same_tol
         ctx.matrix_free(m)
 
 
