@@ -475,9 +475,8 @@ def probe_moe(ctx, stream, dev, gen) -> None:
         def enqueue():
             for r in range(rounds):
                 ctx.route_device(logits[r], experts + 1, tokens, experts, k, chosen, weights, scale)
-                for t in range(tokens):
-                    ctx.expert_ffn_device(handles[r % banks], chosen[t], k, x[t], 0, ffn[t * k:], act[t * k:],
-                                          rows_out[t])
+                ctx.expert_ffn_device(handles[r % banks], chosen, tokens * k, x, hidden, ffn, act, rows_out,
+                                      pairs_per_input=k)
                 ctx.moe_combine_device(shared, scale, weights, rows_out, tokens, k, hidden, y)
         us = graph_us(stream, enqueue) / rounds
         algorithmic = tokens * k * per_expert

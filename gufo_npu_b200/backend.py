@@ -201,9 +201,12 @@ class Context:
                                                     C.c_void_p(_ptr(chosen)), C.c_void_p(_ptr(weights)),
                                                     C.c_void_p(_ptr(shared_scale))))
 
-    def expert_ffn_device(self, bank: "_capi.ExpertBank", ids, pairs: int, x, x_stride: int, ffn, act, y) -> None:
+    def expert_ffn_device(self, bank: "_capi.ExpertBank", ids, pairs: int, x, x_stride: int, ffn, act, y,
+                          pairs_per_input: int = 1) -> None:
+        """Pair p multiplies input row p // pairs_per_input (rows x_stride floats apart)."""
         self._check(self.lib.gufo_cuda_expert_ffn_device(self.handle, C.byref(bank), C.c_void_p(_ptr(ids)), pairs,
-                                                         C.c_void_p(_ptr(x)), x_stride, C.c_void_p(_ptr(ffn)),
+                                                         C.c_void_p(_ptr(x)), x_stride, pairs_per_input,
+                                                         C.c_void_p(_ptr(ffn)),
                                                          C.c_void_p(_ptr(act)), C.c_void_p(_ptr(y))))
 
     def moe_combine_device(self, shared, scale, weights, expert_out, tokens: int, k: int, hidden: int, out) -> None:
@@ -430,9 +433,9 @@ class CudaMoe:
             self.local.copy_(torch_where(held, self.chosen, -1))
             self.expert_out.zero_()
             ids = self.local
-        for t in range(tokens):
-            self.ctx.expert_ffn_device(self.banks[layer], ids[t], k, normed[t], 0, self.ffn[t * k:], self.act[t * k:],
-                                       self.expert_out[t])
+        # One pair of grouped launches for the whole batch: pair (t, slot) reads token t's row.
+        self.ctx.expert_ffn_device(self.banks[layer], ids, tokens * k, normed, c.hidden, self.ffn, self.act,
+                                   self.expert_out, pairs_per_input=k)
 
     def combine(self, shared, tokens: int, out) -> None:
         c = self.config

@@ -133,7 +133,8 @@ struct FastGemvArgs {
   // ids live on the device, so a router kernel can feed the launch directly.
   const int* group_ids;   // null: one ungrouped product
   int groups;
-  int x_group_stride;     // floats between the groups' inputs (0: shared)
+  int x_group_stride;     // floats between the inputs (0: shared)
+  int x_group_div;        // groups per input: group g reads input g / x_group_div (0 counts as 1)
   int y_group_stride;     // floats between the groups' outputs
 };
 

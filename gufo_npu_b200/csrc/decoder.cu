@@ -719,7 +719,7 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
       GUFO_STEP_TRY(LaunchGemv(ctx, router, 1));
       GUFO_STEP_TRY(EnqueueRoute(ctx, d->router, c.experts + 1, 1, c.experts, c.experts_used, d->chosen,
                                  d->route_weights, d->shared_scale));
-      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, c.experts_used, d->normed, 0, d->expert_ffn,
+      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, c.experts_used, d->normed, 0, 1, d->expert_ffn,
                                      d->expert_act, d->expert_out));
       GUFO_STEP_TRY(EnqueueMoeCombine(ctx, d->out, d->shared_scale, d->route_weights, d->expert_out, 1,
                                       c.experts_used, c.hidden, d->out));

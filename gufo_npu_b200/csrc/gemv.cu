@@ -136,7 +136,7 @@ GemvRows(const __grid_constant__ GemvArgs args) {
       return;
     }
     data += static_cast<size_t>(id) * part.rows * part.row_bytes;
-    x += static_cast<size_t>(blockIdx.y) * args.x_group_stride;
+    x += static_cast<size_t>(blockIdx.y / (args.x_group_div > 1 ? args.x_group_div : 1)) * args.x_group_stride;
     y += static_cast<size_t>(blockIdx.y) * args.y_group_stride;
   }
   float acc[M];
@@ -286,14 +286,14 @@ namespace {
 
 // act[g][i] = silu(x[g][i]) * x[g][n + i] for the groups that run.
 __global__ void __launch_bounds__(256)
-SwiGluGroups(const float* __restrict__ x, int n, int x_stride, const int* __restrict__ ids,
+SwiGluGroups(const float* __restrict__ x, int n, int x_stride, int x_div, const int* __restrict__ ids,
              float* __restrict__ act) {
   const int g = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (ids[g] < 0 || i >= n) {
     return;
   }
-  const float* in = x + static_cast<size_t>(g) * x_stride;
+  const float* in = x + static_cast<size_t>(g / x_div) * x_stride;
   const float v = in[i];
   act[static_cast<size_t>(g) * n + i] = v * (1.0f / (1.0f + expf(-v))) * in[n + i];
 }
@@ -320,6 +320,7 @@ int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, fl
   args.group_ids = base.group_ids;
   args.groups = base.groups;
   args.x_group_stride = base.x_group_stride;
+  args.x_group_div = base.x_group_div;
   args.y_group_stride = base.y_group_stride;
   for (int p = 0; p < base.nparts; ++p) {
     const GemvPart& part = base.parts[p];
@@ -350,10 +351,11 @@ int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, fl
         return Fail(GUFO_CUDA_BAD_ARGUMENT, "grouped product: no scratch for the activated input");
       }
       SwiGluGroups<<<dim3((base.cols + 255) / 256, base.groups), 256, 0, ctx->stream>>>(
-          base.x, base.cols, base.x_group_stride, base.group_ids, scratch);
+          base.x, base.cols, base.x_group_stride, base.x_group_div > 1 ? base.x_group_div : 1, base.group_ids, scratch);
       ctx->launches.fetch_add(1);
       rest.x = scratch;
       rest.x_group_stride = base.cols;
+      rest.x_group_div = 1;
     }
     LaunchRows<1>(rest, ctx->stream);
     ctx->launches.fetch_add(1);

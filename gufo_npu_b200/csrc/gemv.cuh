@@ -29,6 +29,7 @@ struct GemvArgs {
   const int* group_ids = nullptr;
   int groups = 0;
   int x_group_stride = 0;
+  int x_group_div = 1;
   int y_group_stride = 0;
 };
 

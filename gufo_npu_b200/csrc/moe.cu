@@ -17,71 +17,67 @@ namespace gufo {
 
 namespace {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 32;
+constexpr int kRouteMaxExperts = 1024;
 // The smallest positive normal fp16: the floor of the top-k probability mass
 // (moe.cpp:12).
 constexpr double kWeightSumFloor = 6.103515625e-5;
 
-// One block per token. Probabilities are exp(logit - max) in double; the sums
-// run in index / slot order on one thread, as the reference's loops do, so the
-// weights differ from the host's only where the device's exp differs.
+// One warp per token; lane l holds experts l, l + 32, ... (PER_LANE of them) in
+// registers. Probabilities are exp(logit - max) in double as in the reference;
+// their sum is a shuffle tree instead of the reference's index-order loop,
+// which can move a weight by the last bit of its fp32 value. The arg-max rounds
+// order (probability, id) exactly as the reference does (moe.cpp:28-32).
+template <int PER_LANE>
 __global__ void __launch_bounds__(kRouteThreads)
 RouteKernel(const float* __restrict__ logits, int stride, int experts, int k,
             int* __restrict__ chosen, float* __restrict__ weights, float* __restrict__ shared_scale) {
-  extern __shared__ double prob[];   // [experts], then the k chosen probabilities
-  __shared__ float warp_max[kRouteThreads / 32];
-  __shared__ double warp_best[kRouteThreads / 32];
-  __shared__ int warp_at[kRouteThreads / 32];
-  __shared__ double total_shared;
+  extern __shared__ double picked[];   // [k]: the chosen probabilities in slot order
   GridDependencyWait();
   const int token = blockIdx.x;
   const float* row = logits + static_cast<size_t>(token) * stride;
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  double* picked = prob + experts;
-
+  const int lane = threadIdx.x;
+  double prob[PER_LANE];
   float top = -FLT_MAX;
-  for (int e = threadIdx.x; e < experts; e += kRouteThreads) {
-    top = fmaxf(top, row[e]);
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    if (e < experts) {
+      top = fmaxf(top, row[e]);
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
   }
-  if (lane == 0) {
-    warp_max[warp] = top;
-  }
-  __syncthreads();
-  top = warp_max[0];
-#pragma unroll
-  for (int w = 1; w < kRouteThreads / 32; ++w) {
-    top = fmaxf(top, warp_max[w]);
-  }
   const double max_logit = static_cast<double>(top);
-  for (int e = threadIdx.x; e < experts; e += kRouteThreads) {
-    prob[e] = exp(static_cast<double>(row[e]) - max_logit);
+  double total = 0;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    // Entries past the end never win a round.
+    prob[j] = e < experts ? exp(static_cast<double>(row[e]) - max_logit) : -1.0;
+    total += e < experts ? prob[j] : 0.0;
   }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    double total = 0;
-    for (int e = 0; e < experts; ++e) {
-      total += prob[e];
-    }
-    total_shared = total;
-    if (shared_scale != nullptr) {
-      shared_scale[token] = static_cast<float>(1.0 / (1.0 + exp(-static_cast<double>(row[experts]))));
-    }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    total += __shfl_xor_sync(0xFFFFFFFFu, total, o);
   }
-  // k rounds of arg-max: larger probability first, lower id on ties
-  // (moe.cpp:28-32). A taken entry drops to -1.
+  if (lane == 0 && shared_scale != nullptr) {
+    shared_scale[token] = static_cast<float>(1.0 / (1.0 + exp(-static_cast<double>(row[experts]))));
+  }
+  // k rounds: every lane offers its best remaining entry, the warp keeps the
+  // larger probability and the lower id on ties; the winner drops to -1.
+  double mass = 0;
   for (int slot = 0; slot < k; ++slot) {
     double best = -2.0;
     int at = 0x7FFFFFFF;
-    for (int e = threadIdx.x; e < experts; e += kRouteThreads) {
-      const double p = prob[e];
-      if (p > best || (p == best && e < at)) {
-        best = p;
-        at = e;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      // Ascending j is ascending id, so a strict compare keeps the lower id.
+      if (prob[j] > best) {
+        best = prob[j];
+        at = lane + 32 * j;
       }
     }
 #pragma unroll
@@ -93,36 +89,25 @@ RouteKernel(const float* __restrict__ logits, int stride, int experts, int k,
         at = other_at;
       }
     }
-    if (lane == 0) {
-      warp_best[warp] = best;
-      warp_at[warp] = at;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      best = warp_best[0];
-      at = warp_at[0];
-      for (int w = 1; w < kRouteThreads / 32; ++w) {
-        if (warp_best[w] > best || (warp_best[w] == best && warp_at[w] < at)) {
-          best = warp_best[w];
-          at = warp_at[w];
+    if ((at & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j) {
+        if (j == (at >> 5)) {
+          prob[j] = -1.0;
         }
       }
+    }
+    if (lane == 0) {
       picked[slot] = best;
       chosen[static_cast<size_t>(token) * k + slot] = at;
-      prob[at] = -1.0;
     }
-    __syncthreads();
+    // The slot-order sum of the chosen probabilities (moe.cpp:33-36).
+    mass += best / total;
   }
-  if (threadIdx.x == 0) {
-    const double total = total_shared;
-    double mass = 0;
-    for (int slot = 0; slot < k; ++slot) {
-      mass += picked[slot] / total;
-    }
-    mass = mass > kWeightSumFloor ? mass : kWeightSumFloor;
-    for (int slot = 0; slot < k; ++slot) {
-      weights[static_cast<size_t>(token) * k + slot] = static_cast<float>(picked[slot] / total / mass);
-    }
+  __syncwarp();
+  mass = mass > kWeightSumFloor ? mass : kWeightSumFloor;
+  for (int slot = lane; slot < k; slot += 32) {
+    weights[static_cast<size_t>(token) * k + slot] = static_cast<float>(picked[slot] / total / mass);
   }
 }
 
@@ -151,12 +136,17 @@ CombineKernel(const float* shared, const float* __restrict__ scale,
 
 int EnqueueRoute(gufo_cuda_ctx* ctx, const float* logits, int stride, int tokens, int experts, int k,
                  int* chosen, float* weights, float* shared_scale) {
-  if (tokens <= 0 || experts <= 0 || k <= 0 || k > experts || experts > 4096 || stride < experts) {
-    return Fail(GUFO_CUDA_BAD_ARGUMENT, "route: 1 <= k <= experts <= 4096, stride >= experts");
+  if (tokens <= 0 || experts <= 0 || k <= 0 || k > experts || experts > kRouteMaxExperts || stride < experts) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "route: 1 <= k <= experts <= 1024, stride >= experts");
   }
-  const size_t smem = static_cast<size_t>(experts + k) * sizeof(double);
-  GUFO_CUDA_TRY(LaunchOverlapped(RouteKernel, dim3(tokens), dim3(kRouteThreads), smem, ctx->stream, 1, logits,
-                                 stride, experts, k, chosen, weights, shared_scale));
+  const size_t smem = static_cast<size_t>(k) * sizeof(double);
+  if (experts <= 256) {
+    GUFO_CUDA_TRY(LaunchOverlapped(RouteKernel<8>, dim3(tokens), dim3(kRouteThreads), smem, ctx->stream, 1, logits,
+                                   stride, experts, k, chosen, weights, shared_scale));
+  } else {
+    GUFO_CUDA_TRY(LaunchOverlapped(RouteKernel<32>, dim3(tokens), dim3(kRouteThreads), smem, ctx->stream, 1, logits,
+                                   stride, experts, k, chosen, weights, shared_scale));
+  }
   ctx->launches.fetch_add(1);
   return GUFO_CUDA_OK;
 }
@@ -209,7 +199,7 @@ int BuildExpertBank(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank& bank, Exper
 }
 
 int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, int pairs, const float* x,
-                     int x_stride, float* ffn, float* act, float* y) {
+                     int x_stride, int pairs_per_input, float* ffn, float* act, float* y) {
   if (pairs <= 0 || ids == nullptr || x == nullptr || ffn == nullptr || y == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "expert ffn: null pointer or no pairs");
   }
@@ -219,6 +209,7 @@ int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids,
   in.group_ids = ids;
   in.groups = pairs;
   in.x_group_stride = x_stride;
+  in.x_group_div = pairs_per_input > 1 ? pairs_per_input : 1;
   in.y_group_stride = 2 * bank.expert_ffn;
   int rc = LaunchGemvGrouped(ctx, in, kProloguePlain, nullptr);
   if (rc != GUFO_CUDA_OK) {
@@ -265,7 +256,8 @@ int gufo_cuda_route_device(gufo_cuda_ctx* ctx, const float* router, int stride, 
 }
 
 int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank* bank, const int* ids, int pairs,
-                                const float* x, int64_t x_stride, float* ffn, float* act, float* y) {
+                                const float* x, int64_t x_stride, int pairs_per_input, float* ffn, float* act,
+                                float* y) {
   if (ctx == nullptr || bank == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "expert ffn: null pointer");
   }
@@ -282,7 +274,10 @@ int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank*
   if (act == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "expert ffn: null scratch");
   }
-  return gufo::EnqueueExpertFfn(ctx, built, ids, pairs, x, static_cast<int>(x_stride), ffn, act, y);
+  if (pairs_per_input < 1) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "expert ffn: pairs_per_input is at least 1");
+  }
+  return gufo::EnqueueExpertFfn(ctx, built, ids, pairs, x, static_cast<int>(x_stride), pairs_per_input, ffn, act, y);
 }
 
 int gufo_cuda_moe_combine_device(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,

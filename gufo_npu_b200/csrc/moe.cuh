@@ -25,7 +25,7 @@ int EnqueueRoute(gufo_cuda_ctx* ctx, const float* logits, int stride, int tokens
 
 // y[p] = down_e(silu(gate_e x_p) * up_e x_p) for the pairs with ids[p] = e >= 0.
 int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, int pairs, const float* x,
-                     int x_stride, float* ffn, float* act, float* y);
+                     int x_stride, int pairs_per_input, float* ffn, float* act, float* y);
 
 int EnqueueMoeCombine(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,
                       const float* expert_out, int tokens, int k, int hidden, float* out);

@@ -146,8 +146,10 @@ class EpMoe:
         self.ctx.require_torch_stream()
         self.route(layer, normed, tokens)
         ids = local_ids(self.chosen[:tokens], self.first, self.count)
-        rows = normed[:tokens].repeat_interleave(k, dim=0)
-        y = self._run_pairs(layer, rows, ids.reshape(-1))
+        pairs = tokens * k
+        y = torch.zeros(pairs, c.hidden, dtype=torch.float32, device=self.dev)
+        self.ctx.expert_ffn_device(self.banks[layer], ids.reshape(-1).contiguous(), pairs, normed, c.hidden, self.ffn,
+                                   self.act, y, pairs_per_input=k)
         if self.world > 1:
             dist.all_reduce(y, group=self.group)
         self.expert_out[:tokens] = y.reshape(tokens, k, c.hidden)

@@ -294,8 +294,8 @@ int gufo_cuda_attention_device(gufo_cuda_ctx* ctx,
  * rows of router outputs on the device, `stride` floats apart: softmax in
  * double over the first `experts` values of a row, the `k` most probable
  * experts in descending order (ties: lower id), their weights renormalised
- * with the sum floored at 6.103515625e-5. chosen and weights are
- * [tokens][k] on the device. shared_scale (may be NULL) gets, per token, the
+ * with the sum floored at 6.103515625e-5 (experts <= 1024). chosen and weights
+ * are [tokens][k] on the device. shared_scale (may be NULL) gets, per token, the
  * sigmoid of the row's value at index `experts` (the shared expert's gate,
  * Stage::kRouter's last output). */
 int gufo_cuda_route_device(gufo_cuda_ctx* ctx, const float* router, int stride,
@@ -320,13 +320,15 @@ typedef struct gufo_cuda_expert_bank {
  * x_p) * up_e x_p) with e = ids[p], read from DEVICE memory at run time, so
  * the ids may come straight from gufo_cuda_route_device. ids[p] < 0 skips the
  * pair and leaves y[p] untouched (expert-parallel ranks pass -1 for experts
- * they do not hold). x_p = x + p * x_stride; x_stride 0 shares one input.
- * Scratch: ffn [pairs][2 * expert_ffn], act [pairs][expert_ffn]. */
+ * they do not hold). x_p = x + (p / pairs_per_input) * x_stride: a batch of
+ * tokens with k slots each passes x_stride = hidden and pairs_per_input = k;
+ * x_stride 0 shares one input. Scratch: ffn [pairs][2 * expert_ffn], act
+ * [pairs][expert_ffn]. */
 int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx,
                                 const gufo_cuda_expert_bank* bank,
                                 const int* ids, int pairs, const float* x,
-                                int64_t x_stride, float* ffn, float* act,
-                                float* y);
+                                int64_t x_stride, int pairs_per_input,
+                                float* ffn, float* act, float* y);
 
 /* out[t] = shared[t] * scale[t] + sum over slots, in slot order, of
  * weights[t][slot] * expert_out[t][slot] (decoder.cpp:541-556). out may be
