@@ -334,13 +334,21 @@ def run_ours(args):
                 "ms_per_step": ms_e2e},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": lm["achieved"], "peak": peak, "unit": "GB/s",
-                     "frac": lm["frac"], "traffic": None, "peak_kind": peak_kind, "kernel": lm["kernel"],
+                     "frac": lm["frac"], "traffic": LM_HEAD_TRAFFIC_BYTES_PER_ROW * cfg.vocab,
+                     "traffic_source": "ncu capture of the 131072-row case scaled by rows", "peak_kind": peak_kind, "kernel": lm["kernel"],
                      "shape": lm["shape"], "bytes_per_launch": lm["bytes"], "us_per_launch": lm["us"]},
         "roofline_more": {k: v for k, v in probes.items() if k != "lm_head"},
         "cpu_baseline": base,
         "clocks": clocks.summary(),
     }
     print(json.dumps(line))
+
+
+# DRAM traffic of one LM-head launch: dram__bytes_read.sum + dram__bytes_write.sum of GemvQ6KMma
+# from one ncu capture of `bench.py --probe q6k` (131072 rows: 220.26 MB read, 5.63 MB written on
+# average), scaled by rows to the 248320-row launch (every row is read once, so traffic grows in
+# proportion). The summary with the command is profiles/gemv_q6k_mma_131072x2048.md.
+LM_HEAD_TRAFFIC_BYTES_PER_ROW = (220.26e6 + 5.63e6) / 131072
 
 
 def run_probe(which: str) -> None:
