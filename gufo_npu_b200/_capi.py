@@ -39,6 +39,13 @@ class LinearSeq(C.Structure):
                 ("ssm", C.c_void_p), ("ssm_out", C.c_void_p), ("y", C.c_void_p)]
 
 
+class DeltaNetStepSeq(C.Structure):
+    _fields_ = [("n_tokens", C.c_int), ("in_", C.c_void_p), ("in_stride", C.c_int64), ("h", C.c_void_p),
+                ("h_stride", C.c_int64), ("conv_in", C.c_void_p), ("conv_out", C.c_void_p),
+                ("conv_saved", C.c_void_p), ("ssm", C.c_void_p), ("ssm_spec", C.c_void_p), ("y", C.c_void_p),
+                ("y_stride", C.c_int64)]
+
+
 class DeltaNetParams(C.Structure):
     _fields_ = [("key_heads", C.c_int), ("value_heads", C.c_int), ("head_dim", C.c_int),
                 ("conv_kernel", C.c_int), ("rms_eps", C.c_float), ("conv", _f32p), ("ssm_a", _f32p),
@@ -113,6 +120,8 @@ SIGNATURES = {
                                                   C.POINTER(C.c_int64)]),
     "gufo_cuda_deltanet_layer_free": (C.c_int, [C.c_void_p, C.c_int64]),
     "gufo_cuda_deltanet_linear_device": (C.c_int, [C.c_void_p, C.c_int64, C.POINTER(LinearSeq), C.c_int]),
+    "gufo_cuda_deltanet_step_device": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_float,
+                                                 C.POINTER(DeltaNetStepSeq), C.c_int]),
     "gufo_cuda_embed_device": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "gufo_cuda_add_rms_norm_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int,
                                                 C.c_void_p, C.c_void_p]),

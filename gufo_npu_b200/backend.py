@@ -463,6 +463,7 @@ class CudaMixer:
         self.ctx = ctx
         self.config = cfg
         self.layers: Dict[int, int] = {}
+        self.gates: Dict[int, tuple] = {}
         for il in range(cfg.layers):
             if cfg.is_full_attention(il):
                 continue
@@ -473,6 +474,12 @@ class CudaMixer:
             self.layers[il] = ctx.deltanet_layer_create(
                 cfg.linear_key_heads, cfg.linear_value_heads, cfg.linear_head_dim, cfg.conv_kernel, cfg.rms_eps,
                 f32("ssm_conv1d.weight"), f32("ssm_a"), f32("ssm_dt.bias"), f32("ssm_norm.weight"))
+            # For Run (the gates from the residual stream): the F32 alpha / beta rows and the norm.
+            alpha, beta = tensors[p + "ssm_alpha.weight"], tensors[p + "ssm_beta.weight"]
+            norm = ctx.malloc(cfg.hidden * 4)
+            ctx.upload(norm, f32("attn_norm.weight"))
+            self.gates[il] = (ctx.matrix_upload(alpha.ggml_type, alpha.data.cpu().numpy(), alpha.rows, alpha.cols),
+                              ctx.matrix_upload(beta.ggml_type, beta.data.cpu().numpy(), beta.rows, beta.cols), norm)
 
     def conv_values(self) -> int:
         return (self.config.conv_kernel - 1) * self.config.conv_channels
@@ -486,6 +493,27 @@ class CudaMixer:
         if layer not in self.layers:
             raise ValueError(f"deltanet: layer {layer} is not a DeltaNet layer")
         self.ctx.deltanet_linear_device(self.layers[layer], seqs)
+
+
+def _deltanet_run(self, layer: int, seqs: List[dict]) -> None:
+    """DeltaNetStep::Run (src/models/qwen35_2b/deltanet.hpp:42-44) for each sequence in `seqs`:
+    dicts with n_tokens, in [n, in_stride], h [n, h_stride], conv_in, conv_out, conv_saved, ssm,
+    ssm_spec, y [n, y_stride] (device tensors; conv_saved / ssm_spec may be None for one token)."""
+    if layer not in self.layers:
+        raise ValueError(f"deltanet: layer {layer} is not a DeltaNet layer")
+    arr = (_capi.DeltaNetStepSeq * max(len(seqs), 1))()
+    for i, q in enumerate(seqs):
+        arr[i] = _capi.DeltaNetStepSeq(q["n_tokens"], _ptr(q["in"]), q["in"].stride(0), _ptr(q["h"]),
+                                       q["h"].stride(0), _ptr(q["conv_in"]), _ptr(q["conv_out"]),
+                                       _ptr(q.get("conv_saved")), _ptr(q["ssm"]), _ptr(q.get("ssm_spec")),
+                                       _ptr(q["y"]), q["y"].stride(0))
+    alpha, beta, norm = self.gates[layer]
+    self.ctx._check(self.ctx.lib.gufo_cuda_deltanet_step_device(self.ctx.handle, self.layers[layer], alpha, beta,
+                                                                C.c_void_p(norm), self.config.rms_eps, arr,
+                                                                len(seqs)))
+
+
+CudaMixer.Run = _deltanet_run
 
 
 class CudaDecoder:

@@ -173,8 +173,24 @@ bool Q4KFastFits(int cols, int tokens);
 // One Mixer::Linear step per sequence; the caller holds ctx->mu.
 // `early_state`: the states were not written by the kernels just before this
 // one in the stream, so their loads may run ahead of the dependency wait.
+// The F32 alpha / beta rows of a DeltaNet layer's input product, for a step
+// that computes the two gates inside the mixer kernel instead of reading them
+// from the product's output: a = alpha_w[head] . x, b = beta_w[head] . x.
+struct DeltaNetGateRows {
+  const float* x;         // the layer's normed input [cols] (every sequence's, unless xs is given)
+  const float* alpha_w;   // [value heads][cols]
+  const float* beta_w;
+  int cols;               // a multiple of 4
+  // Non-null norm_w: x holds the residual stream instead and the kernel applies
+  // vec::RmsNorm (src/core/vec.hpp:57-63) with these weights first.
+  const float* norm_w;
+  float eps;
+  // Per-sequence inputs (launch order), overriding x when non-null.
+  const float* const* xs;
+};
 int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& layer,
-                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state);
+                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state,
+                          const DeltaNetGateRows* gate_rows = nullptr);
 // The same for Q6_K parts (image with group sums of 16).
 int LaunchGemvQ6KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 bool Q6KFastFits(int cols, int tokens);

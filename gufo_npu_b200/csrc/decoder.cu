@@ -456,6 +456,7 @@ struct gufo_cuda_decoder {
     gufo::GemvArgs router;             // MoE: router rows and the shared expert's gate
     gufo::ExpertBank bank;             // MoE: the stacked expert tensors
     gufo::DeltaNetLayer linear;        // small weights (device), DeltaNet layers
+    gufo::DeltaNetGateRows gate_rows{};  // F32 alpha / beta rows, computed inside the mixer kernel
     float* attn_norm = nullptr;
     float* post_norm = nullptr;
     float* q_norm = nullptr;
@@ -692,7 +693,10 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
       Mark(d, GUFO_CUDA_TIMELINE_ATTENTION);
     } else {
       gufo_cuda_linear_seq seq{d->in, l.conv[parity], l.conv[parity ^ 1], l.ssm, nullptr, d->mixed};
-      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1, true));
+      gufo::DeltaNetGateRows gate_rows = l.gate_rows;
+      gate_rows.x = d->normed;
+      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1, true,
+                                          gate_rows.alpha_w != nullptr ? &gate_rows : nullptr));
       Mark(d, GUFO_CUDA_TIMELINE_DELTANET);
     }
     Input plain{kProloguePlain};
@@ -828,6 +832,18 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
       const int64_t rows[4] = {channels, value_dim, c.linear_value_heads, c.linear_value_heads};
       if ((rc = gufo::Stack(ctx, in, rows, 4, c.hidden, "attn_qkv/gate/ssm_alpha/ssm_beta", &l.in)) != GUFO_CUDA_OK) {
         return fail(rc);
+      }
+      // F32 alpha / beta rows (the usual case) are multiplied inside the mixer
+      // kernel: the input product then stops after [qkv | z], one launch less.
+      const gufo::Matrix* alpha = ctx->FindMatrix(w.ssm_alpha);
+      const gufo::Matrix* beta = ctx->FindMatrix(w.ssm_beta);
+      if (alpha->type == GUFO_CUDA_F32 && beta->type == GUFO_CUDA_F32 && c.hidden % 4 == 0) {
+        if ((rc = gufo::Stack(ctx, in, rows, 2, c.hidden, "attn_qkv/gate", &l.in)) != GUFO_CUDA_OK) {
+          return fail(rc);
+        }
+        l.gate_rows.alpha_w = reinterpret_cast<const float*>(alpha->data);
+        l.gate_rows.beta_w = reinterpret_cast<const float*>(beta->data);
+        l.gate_rows.cols = c.hidden;
       }
       const int64_t out_rows = c.hidden;
       if ((rc = gufo::Stack(ctx, &w.ssm_out, &out_rows, 1, value_dim, "ssm_out", &l.out)) != GUFO_CUDA_OK) {

@@ -19,6 +19,8 @@
 // dk outputs.
 #include "common.cuh"
 
+#include <vector>
+
 namespace gufo {
 
 constexpr int kTileCols = 32;
@@ -50,6 +52,9 @@ struct LinearArgs {
   // When the caller knows that no kernel shortly before this one in the stream
   // wrote the states, their loads may start ahead of the dependency wait.
   int early_state;
+  // Non-null alpha_w: the gates come from these rows instead of the input row.
+  DeltaNetGateRows gate_rows;
+  const float* gate_x[kMaxSeqs];   // per sequence, or null for gate_rows.x
 };
 
 namespace {
@@ -285,8 +290,45 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   fetch(kh * dk + tid, tq);
   fetch(key_dim + kh * dk + tid, tk);
   fetch(2 * key_dim + head * dk + tid, tv);
-  const float* gates = x + channels + value_dim;  // alpha | beta follow z
-  const float alpha = gates[head], beta = gates[hv + head];
+  float alpha, beta;
+  if (args.gate_rows.alpha_w != nullptr) {
+    // The head's alpha and beta rows against the normed input, one float4 per
+    // thread and pass (GgufProjections serves these F32 rows through its own
+    // dot, src/models/qwen35/gguf_projections.cpp:162-170). With norm weights
+    // the input is the residual stream and the RMS norm is applied on the way
+    // (DeltaNetStep::Run, src/models/qwen35_2b/deltanet.cpp:358-392).
+    const DeltaNetGateRows& g = args.gate_rows;
+    const float* gx = args.gate_x[blockIdx.y] != nullptr ? args.gate_x[blockIdx.y] : g.x;
+    const float4* xa = reinterpret_cast<const float4*>(gx);
+    const float4* wa = reinterpret_cast<const float4*>(g.alpha_w + static_cast<size_t>(head) * g.cols);
+    const float4* wb = reinterpret_cast<const float4*>(g.beta_w + static_cast<size_t>(head) * g.cols);
+    float inv = 1.0f;
+    if (g.norm_w != nullptr) {
+      float sq = 0.f;
+      for (int i = tid; i < g.cols / 4; i += dk) {
+        const float4 xv = xa[i];
+        sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+      }
+      inv = 1.0f / sqrtf(BlockSum(sq, sh, warps) / static_cast<float>(g.cols) + g.eps);
+    }
+    float pa = 0.f, pb = 0.f;
+    for (int i = tid; i < g.cols / 4; i += dk) {
+      float4 xv = xa[i];
+      if (g.norm_w != nullptr) {
+        const float4 nw = reinterpret_cast<const float4*>(g.norm_w)[i];
+        xv = make_float4(xv.x * inv * nw.x, xv.y * inv * nw.y, xv.z * inv * nw.z, xv.w * inv * nw.w);
+      }
+      const float4 av = wa[i], bv = wb[i];
+      pa += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
+      pb += bv.x * xv.x + bv.y * xv.y + bv.z * xv.z + bv.w * xv.w;
+    }
+    alpha = BlockSum(pa, sh, warps);
+    beta = BlockSum(pb, sh, warps);
+  } else {
+    const float* gates = x + channels + value_dim;  // alpha | beta follow z
+    alpha = gates[head];
+    beta = gates[hv + head];
+  }
   const float ssm_a = args.ssm_a[head], dt_bias = args.dt_bias[head];
   const float qv = conv(kh * dk + tid, tq, head < hk);
   const float kv = conv(key_dim + kh * dk + tid, tk, head < hk);
@@ -471,12 +513,92 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
   return gufo::EnqueueDeltaNetLinear(ctx, it->second, seqs, nseq, ctx->early_state);
 }
 
+int gufo_cuda_deltanet_step_device(gufo_cuda_ctx* ctx, gufo_cuda_deltanet_layer layer, gufo_cuda_matrix ssm_alpha,
+                                   gufo_cuda_matrix ssm_beta, const float* attn_norm, float rms_eps,
+                                   const gufo_cuda_deltanet_step_seq* seqs, int nseq) {
+  if (ctx == nullptr || attn_norm == nullptr || (seqs == nullptr && nseq > 0)) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: null pointer");
+  }
+  if (nseq < 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: negative sequence count");
+  }
+  int most = 0;
+  for (int s = 0; s < nseq; ++s) {
+    const gufo_cuda_deltanet_step_seq& q = seqs[s];
+    if (q.n_tokens < 1 || q.n_tokens > 4) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: 1 to 4 tokens per sequence");
+    }
+    if (q.in == nullptr || q.h == nullptr || q.conv_in == nullptr || q.conv_out == nullptr || q.ssm == nullptr ||
+        q.y == nullptr || (q.n_tokens >= 2 && (q.conv_saved == nullptr || q.ssm_spec == nullptr))) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: null pointer in a sequence");
+    }
+    if (q.conv_in == q.conv_out || q.conv_in == q.conv_saved || q.conv_out == q.conv_saved) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: the conv windows must be distinct buffers");
+    }
+    if ((reinterpret_cast<uintptr_t>(q.h) & 15) != 0 || q.h_stride % 4 != 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: residual rows must be 16-byte aligned");
+    }
+    most = q.n_tokens > most ? q.n_tokens : most;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->deltanet_layers.find(layer);
+  if (it == ctx->deltanet_layers.end()) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "deltanet_step: unknown layer handle");
+  }
+  const gufo::Matrix* alpha = ctx->FindMatrix(ssm_alpha);
+  const gufo::Matrix* beta = ctx->FindMatrix(ssm_beta);
+  if (alpha == nullptr || beta == nullptr || alpha->type != GUFO_CUDA_F32 || beta->type != GUFO_CUDA_F32 ||
+      alpha->rows != it->second.value_heads || beta->rows != alpha->rows || beta->cols != alpha->cols ||
+      alpha->cols % 4 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "deltanet_step: ssm_alpha / ssm_beta must be F32 [hidden, value heads]");
+  }
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::DeltaNetGateRows gates{};
+  gates.alpha_w = reinterpret_cast<const float*>(alpha->data);
+  gates.beta_w = reinterpret_cast<const float*>(beta->data);
+  gates.cols = static_cast<int>(alpha->cols);
+  gates.norm_w = attn_norm;
+  gates.eps = rms_eps;
+  // Token t of every sequence that has one, in one launch per t. Windows
+  // alternate between conv_out and conv_saved so that the last token reads
+  // conv_saved and writes conv_out; the last of two or more tokens leaves ssm
+  // alone and writes ssm_spec.
+  std::vector<gufo_cuda_linear_seq> step;
+  std::vector<const float*> xs;
+  for (int t = 0; t < most; ++t) {
+    step.clear();
+    xs.clear();
+    for (int s = 0; s < nseq; ++s) {
+      const gufo_cuda_deltanet_step_seq& q = seqs[s];
+      if (t >= q.n_tokens) {
+        continue;
+      }
+      const int from_end = q.n_tokens - 1 - t;   // 0 for the last token
+      float* dst = from_end % 2 == 0 ? q.conv_out : q.conv_saved;
+      const float* src = t == 0 ? q.conv_in : (from_end % 2 == 0 ? q.conv_saved : q.conv_out);
+      const bool speculative = q.n_tokens >= 2 && from_end == 0;
+      step.push_back({q.in + static_cast<size_t>(t) * q.in_stride, src, dst, q.ssm, speculative ? q.ssm_spec : nullptr,
+                      q.y + static_cast<size_t>(t) * q.y_stride});
+      xs.push_back(q.h + static_cast<size_t>(t) * q.h_stride);
+    }
+    gates.xs = xs.data();
+    // States are written by the launch before this one: no early state loads.
+    const int rc = gufo::EnqueueDeltaNetLinear(ctx, it->second, step.data(), static_cast<int>(step.size()), false,
+                                               &gates);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+  }
+  return GUFO_CUDA_OK;
+}
+
 }  // extern "C"
 
 namespace gufo {
 
 int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
-                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state) {
+                          const gufo_cuda_linear_seq* seqs, int nseq, bool early_state,
+                          const DeltaNetGateRows* gate_rows) {
   for (int s0 = 0; s0 < nseq; s0 += gufo::kMaxSeqs) {
     const int n = nseq - s0 < gufo::kMaxSeqs ? nseq - s0 : gufo::kMaxSeqs;
     gufo::LinearArgs args{};
@@ -493,6 +615,13 @@ int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
     args.dt_bias = l.dt_bias;
     args.ssm_norm = l.ssm_norm;
     args.early_state = early_state ? 1 : 0;
+    if (gate_rows != nullptr) {
+      args.gate_rows = *gate_rows;
+      for (int s = 0; s < n; ++s) {
+        args.gate_x[s] = gate_rows->xs != nullptr ? gate_rows->xs[s0 + s] : nullptr;
+      }
+      args.gate_rows.xs = nullptr;
+    }
     GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaNetLinearKernel, dim3(l.value_heads, n),
                                          dim3(l.head_dim), 0, ctx->stream, 1, args));
     ctx->launches.fetch_add(1);

@@ -272,7 +272,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 1.0f / 16.0f, a.x + static_cast<size_t>(group / (a.x_group_div > 1 ? a.x_group_div : 1)) * a.x_group_stride);
+    FillImage(a, l, smem, 1.0f / 16.0f, a.x + static_cast<size_t>(group / (a.x_group_div > 1 ? a.x_group_div : 1)) * a.x_group_stride, rank, ks, kSlabBlocks);
   }
 
   Accum<TOKENS> acc;

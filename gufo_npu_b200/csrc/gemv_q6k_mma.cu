@@ -289,7 +289,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 1.0f, a.x);
+    FillImage(a, l, smem, 1.0f, a.x, rank, ks, kSlabBlocks);
   }
 
   Accum<TOKENS> acc;

@@ -173,16 +173,20 @@ __device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + 
 // Builds the one-token image in shared memory at `image` from the launch's
 // fused input (prologue != kPrologueImage). Warp w converts blocks w, w + 8,
 // ...; a lane holds eight adjacent values, so nothing is staged in between.
-// `x` is the plain / SwiGLU input (a.x, or a group's part of it). Ends with a
-// __syncthreads. kFastThreads threads.
+// `x` is the plain / SwiGLU input (a.x, or a group's part of it). A block that
+// shares its tiles with a cluster (rank `rank` of `ks`, slabs of `slab_blocks`
+// blocks dealt round-robin) converts only the blocks of its own slabs; the
+// others are never read. Ends with a __syncthreads. kFastThreads threads.
 __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
-                                          uint8_t* image, float extra, const float* x) {
+                                          uint8_t* image, float extra, const float* x,
+                                          int rank, int ks, int slab_blocks) {
   __shared__ float reduce[kFastWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n = a.cols;
   const int blocks = n / kSuperBlock;
   const bool first = blockIdx.x == 0;
+  auto mine = [&](int b) { return ks == 1 || (b / slab_blocks) % ks == rank; };
   auto load8 = [&](const float* p, float (&v)[8]) {
     const float4 v0 = *reinterpret_cast<const float4*>(p);
     const float4 v1 = *reinterpret_cast<const float4*>(p + 4);
@@ -241,6 +245,10 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     }
     const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + a.eps);
     for (int b = warp; b < blocks; b += kFastWarps) {
+      // Block 0 writes the whole residual stream and normed vector.
+      if (!first && !mine(b)) {
+        continue;
+      }
       const int at = b * kSuperBlock + lane * 8;
       float v[8], w[8], out[8];
       if (b == warp) {
@@ -269,6 +277,9 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     }
   } else {
     for (int b = warp; b < blocks; b += kFastWarps) {
+      if (!mine(b)) {
+        continue;
+      }
       const int at = b * kSuperBlock + lane * 8;
       float v[8];
       load8(x + at, v);

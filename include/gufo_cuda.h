@@ -245,6 +245,41 @@ int gufo_cuda_deltanet_linear_device(gufo_cuda_ctx* ctx,
                                      const gufo_cuda_linear_seq* seqs,
                                      int nseq);
 
+/* DeltaNetStep::Run (src/models/qwen35_2b/deltanet.hpp:42-44,
+ * deltanet.cpp:358-392): 1 to 4 tokens of a sequence through the layer, the
+ * gates taken from the residual stream. Per token t: normed = RMSNorm(h[t]) *
+ * attn_norm, alpha / beta = the F32 ssm_alpha / ssm_beta rows times normed,
+ * then Mixer::Linear on in[t] (only its [qkv | z] part is read). Tokens before
+ * the last advance ssm in place. With two or more tokens the last one is a
+ * draft: ssm keeps the state before it and ssm_spec gets the state after it,
+ * conv_saved the window before it and conv_out the window after it (the
+ * reference's two-token form; accepting the draft is ssm <- ssm_spec, rejecting
+ * it conv <- conv_saved). With one token: ssm in place, conv_in -> conv_out,
+ * conv_saved / ssm_spec unused (may be NULL). conv_in, conv_out and conv_saved
+ * are distinct buffers. One launch per token index over all sequences. */
+typedef struct gufo_cuda_deltanet_step_seq {
+  int n_tokens;          /* 1 .. 4 */
+  const float* in;       /* [n_tokens] rows, in_stride floats apart */
+  int64_t in_stride;
+  const float* h;        /* [n_tokens] residual rows, h_stride floats apart */
+  int64_t h_stride;
+  const float* conv_in;
+  float* conv_out;
+  float* conv_saved;
+  float* ssm;
+  float* ssm_spec;
+  float* y;              /* [n_tokens] rows of value_dim values, y_stride apart */
+  int64_t y_stride;
+} gufo_cuda_deltanet_step_seq;
+
+int gufo_cuda_deltanet_step_device(gufo_cuda_ctx* ctx,
+                                   gufo_cuda_deltanet_layer layer,
+                                   gufo_cuda_matrix ssm_alpha,
+                                   gufo_cuda_matrix ssm_beta,
+                                   const float* attn_norm, float rms_eps,
+                                   const gufo_cuda_deltanet_step_seq* seqs,
+                                   int nseq);
+
 /* ---- the small steps between the products ------------------------------- */
 
 /* The CPU work Decoder::Step does between its Projections calls, as device

@@ -352,6 +352,89 @@ def test_deltanet_linear_matches_reference_outputs(ctx, golden):
     assert rel_l2(ssm.cpu().numpy(), g["linear_ssm"]) <= DELTA_TOL
 
 
+def test_deltanet_run_matches_reference_outputs(ctx, golden):
+    """DeltaNetStep::Run (1 or 2 tokens, gates from the residual stream, draft state and saved
+    window) over 6 steps, against the committed outputs of the reference's fused step; the draft
+    is kept on even steps and dropped on odd ones, as when the goldens were made."""
+    dev = torch.device("cuda:0")
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    mixer = CudaMixer(ctx, cfg, tensors)
+    g = golden("deltanet")
+    rows = cfg.conv_channels + cfg.value_dim
+    width = rows + 2 * cfg.linear_value_heads
+    conv = torch.zeros(mixer.conv_values(), device=dev)
+    ssm = torch.zeros(mixer.ssm_values(), device=dev)
+    for step in range(6):
+        count = 1 if step % 3 == 0 else 2
+        x_in = torch.from_numpy(G.normal(5000 + step, count, width)).to(dev)
+        x_in[:, rows:] = float("nan")            # the alpha / beta slots of the rows are not read
+        h = torch.from_numpy(4.0 * G.normal(6000 + step, count, cfg.hidden)).to(dev)
+        conv_out, saved = torch.zeros_like(conv), torch.zeros_like(conv)
+        spec = torch.zeros_like(ssm)
+        y = torch.empty(count, cfg.value_dim, device=dev)
+        torch.cuda.synchronize()
+        mixer.Run(0, [{"n_tokens": count, "in": x_in, "h": h, "conv_in": conv, "conv_out": conv_out,
+                       "conv_saved": saved if count == 2 else None, "ssm": ssm,
+                       "ssm_spec": spec if count == 2 else None, "y": y}])
+        ctx.synchronize()
+        assert rel_l2(y.cpu().numpy(), g[f"fused_y_{step}"]) <= DELTA_TOL, step
+        conv = conv_out
+        if count == 2:
+            assert rel_l2(spec.cpu().numpy()[::G.SAMPLE], g[f"fused_spec_{step}"]) <= DELTA_TOL
+            assert np.array_equal(bits(saved.cpu().numpy()[::7]), bits(g[f"fused_saved_{step}"]))
+            if step % 2 == 0:
+                ssm = spec.clone()
+            else:
+                conv = saved.clone()
+    assert np.array_equal(bits(conv.cpu().numpy()), bits(g["fused_conv"]))
+    assert rel_l2(ssm.cpu().numpy(), g["fused_ssm"]) <= DELTA_TOL
+
+
+def test_deltanet_run_ragged_token_counts(ctx):
+    """Sequences of 1 to 4 tokens in one call equal the same tokens one call at a time: the
+    tokens before the last advance the state, the last of several is a draft."""
+    dev = torch.device("cuda:0")
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    mixer = CudaMixer(ctx, cfg, tensors)
+    width = cfg.conv_channels + cfg.value_dim + 2 * cfg.linear_value_heads
+    counts = [3, 1, 4, 2, 1]
+    gen = torch.Generator(device=dev).manual_seed(10)
+    z = lambda *shape: torch.zeros(*shape, device=dev)
+    x_in = [torch.randn(n, width, device=dev, generator=gen) for n in counts]
+    h = [torch.randn(n, cfg.hidden, device=dev, generator=gen) * 3 for n in counts]
+    conv0 = [torch.randn(mixer.conv_values(), device=dev, generator=gen) for _ in counts]
+    ssm0 = [torch.randn(mixer.ssm_values(), device=dev, generator=gen) * 0.1 for _ in counts]
+
+    def seq(s, n, x, hh, conv_in, ssm):
+        return {"n_tokens": n, "in": x, "h": hh, "conv_in": conv_in, "conv_out": z(mixer.conv_values()),
+                "conv_saved": z(mixer.conv_values()), "ssm": ssm, "ssm_spec": z(mixer.ssm_values()),
+                "y": z(n, cfg.value_dim)}
+    together = [seq(s, n, x_in[s], h[s], conv0[s], ssm0[s].clone()) for s, n in enumerate(counts)]
+    torch.cuda.synchronize()
+    mixer.Run(0, together)
+    ctx.synchronize()
+    for s, n in enumerate(counts):
+        conv, ssm = conv0[s], ssm0[s].clone()
+        for t in range(n):
+            last_of_many = n >= 2 and t == n - 1
+            one = seq(s, 1, x_in[s][t:t + 1], h[s][t:t + 1], conv, ssm)
+            before = ssm.clone()
+            torch.cuda.synchronize()
+            mixer.Run(0, [one])
+            ctx.synchronize()
+            assert torch.equal(one["y"][0], together[s]["y"][t]), (s, t)
+            if last_of_many:
+                assert torch.equal(conv, together[s]["conv_saved"])
+                assert torch.equal(ssm, together[s]["ssm_spec"])       # the draft state
+                assert torch.equal(before, together[s]["ssm"])         # ssm kept the state before it
+            conv = one["conv_out"]
+        assert torch.equal(conv, together[s]["conv_out"])
+        if n == 1:
+            assert torch.equal(ssm, together[s]["ssm"])
+
+
 def test_deltanet_linear_batched_sequences(ctx, oracle):
     """Several sequences in one launch equal the same sequences one by one."""
     dev = torch.device("cuda:0")
