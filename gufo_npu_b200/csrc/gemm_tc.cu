@@ -10,15 +10,18 @@
 // per 64 columns. The tokens sit on the MMA's M (the tensor core spends M cycles
 // per instruction whatever N is, measured here: 128 x 32 x 16 took as long as
 // 128 x 128 x 16), the weight rows fill its N = 256.
-//   - two loader warps copy one Q4_K block (144 B) of each of the 256 rows per
-//     stage with 16-byte cp.async whose completion arrives on an mbarrier
-//     (tiled TMA boxes this narrow, 144 B wide, ran no faster);
+//   - two loader warps copy one block of each of the 256 rows per stage (Q4_K:
+//     its 144 bytes; Q6_K: 208 bytes from the three planes of the device
+//     arrangement plus the slab's d values) with 16-byte cp.async whose
+//     completion arrives on an mbarrier (tiled TMA boxes this narrow, 144 B wide,
+//     ran no faster);
 //   - one loader thread brings the activation tiles with one bulk copy
 //     (cp.async.bulk) each: the activations were converted once per product into
 //     fp16 tile images that already carry the shared-memory swizzle;
-//   - sixteen dequant warps, two threads per weight row: w = d*sc*q - dmin*m in fp32
-//     (DequantQ4_K, src/core/quant.cpp:33-59), rounded once to fp16 and stored
-//     in the 128-byte-swizzled K-major layout the MMA reads;
+//   - sixteen dequant warps, two threads per weight row: w = d*sc*q - dmin*m
+//     (DequantQ4_K, src/core/quant.cpp:33-59) or w = d*sc*(q - 32) (DequantQ6_K,
+//     :98-125) in fp32, rounded once to fp16 and stored in the
+//     128-byte-swizzled K-major layout the MMA reads;
 //   - one thread issues tcgen05.mma (kind::f16, M = 128, N = 256, K = 16, four
 //     per tile) and tcgen05.commit hands the tile buffers back;
 //   - four epilogue warps read the accumulator with tcgen05.ld (lane = token,
@@ -48,6 +51,8 @@
 
 #include <cuda_fp16.h>
 
+#include <vector>
+
 namespace gufo {
 
 namespace {
@@ -57,10 +62,47 @@ constexpr int kTokenRows = 128;            // token rows per tile image (the MMA
 constexpr int kTileK = 64;                 // values per tile (one swizzle row of fp16)
 constexpr int kWTileBytes = kTileRows * kTileK * 2;    // 32 KiB
 constexpr int kXTileBytes = kTokenRows * kTileK * 2;   // 16 KiB
-constexpr int kWStages = 3;
-constexpr int kXStages = 3;
-constexpr int kRawStages = 2;
-constexpr int kRawBytes = kTileRows * kQ4KBytes;       // one Q4_K block of every row
+// What differs between the block formats: how one block of a row is copied into
+// shared memory (16-byte chunks) and how deep the rings are.
+template <int TYPE>
+struct Quant;
+
+template <>
+struct Quant<GUFO_CUDA_Q4_K> {
+  static constexpr int kRowBytes = kQ4KBytes;   // shared memory per row and block
+  static constexpr int kWStages = 3, kXStages = 3, kRawStages = 2;
+  // Chunk `chunk` of block `block` of a row: the GGUF bytes as they are.
+  __device__ static const uint8_t* Source(const uint8_t* row, int blocks, int block, int chunk) {
+    (void)blocks;
+    return row + static_cast<size_t>(block) * kQ4KBytes + chunk * 16;
+  }
+};
+
+template <>
+struct Quant<GUFO_CUDA_Q6_K> {
+  // ql 128 | qh 64 | scales 16 | the 16 bytes that hold the slab's d values.
+  static constexpr int kRowBytes = 224;
+  static constexpr int kWStages = 2, kXStages = 2, kRawStages = 2;
+  // The planar device arrangement (Q6KBlockAt): a slab of n blocks stores
+  // ql n x 128 | qh n x 64 | scales n x 16 | d n x 2.
+  __device__ static const uint8_t* Source(const uint8_t* row, int blocks, int block, int chunk) {
+    const int slab = block / kQ6KSlabBlocks;
+    const int j = block - slab * kQ6KSlabBlocks;
+    const int left = blocks - slab * kQ6KSlabBlocks;
+    const int n = left < kQ6KSlabBlocks ? left : kQ6KSlabBlocks;
+    const uint8_t* base = row + static_cast<size_t>(slab) * kQ6KSlabBlocks * kQ6KBytes;
+    if (chunk < 8) {
+      return base + 128 * j + 16 * chunk;
+    }
+    if (chunk < 12) {
+      return base + 128 * n + 64 * j + 16 * (chunk - 8);
+    }
+    if (chunk == 12) {
+      return base + 192 * n + 16 * j;
+    }
+    return base + 208 * n;   // all of the slab's d values; the row stride covers the 16 bytes
+  }
+};
 constexpr int kDequantThreads = 2 * kTileRows;         // two threads per weight row
 constexpr int kEpilogueWarp = kDequantThreads / 32;    // four epilogue warps, one per lane quarter
 constexpr int kEpilogueWarps = 4;
@@ -72,19 +114,22 @@ constexpr int kTmemColumns = 512;                      // two accumulators of 25
 constexpr long long kWaitCycles = 1ll << 31;   // about a second of SM clocks
 
 // Dynamic shared memory, from a 1024-byte aligned base.
+template <int TYPE>
 struct Smem {
+  using Q = Quant<TYPE>;
+  static constexpr int kRawBytes = kTileRows * Q::kRowBytes;   // one block of every row
   static constexpr int kW = 0;
-  static constexpr int kX = kW + kWStages * kWTileBytes;
-  static constexpr int kRaw = kX + kXStages * kXTileBytes;
-  static constexpr int kBars = kRaw + kRawStages * kRawBytes;
-  // raw_full[2], raw_empty[2], w_full[3], w_empty[3], x_full[3], x_empty[3], acc_full[2], acc_empty[2]
-  static constexpr int kBarCount = 2 * kRawStages + 2 * kWStages + 2 * kXStages + 4;
+  static constexpr int kX = kW + Q::kWStages * kWTileBytes;
+  static constexpr int kRaw = kX + Q::kXStages * kXTileBytes;
+  static constexpr int kBars = kRaw + Q::kRawStages * kRawBytes;
+  // raw_full, raw_empty, w_full, w_empty, x_full, x_empty (per stage), acc_full[2], acc_empty[2]
+  static constexpr int kBarCount = 2 * Q::kRawStages + 2 * Q::kWStages + 2 * Q::kXStages + 4;
   static constexpr int kTmemSlot = kBars + kBarCount * 8;
   static constexpr int kAbort = kTmemSlot + 4;
   static constexpr int kBytes = kAbort + 4 + 1024;   // + room to align the base
+  static_assert(kX % 1024 == 0 && kRaw % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  static_assert(kBytes <= 227 * 1024, "beyond the shared memory of a thread block");
 };
-static_assert(Smem::kX % 1024 == 0 && Smem::kRaw % 1024 == 0, "swizzled tiles need 1024-byte alignment");
-static_assert(Smem::kBytes <= 227 * 1024, "beyond the shared memory of a thread block");
 
 constexpr int kTcMaxParts = 4;
 
@@ -236,6 +281,32 @@ __device__ __forceinline__ void SixteenWeights(uint32_t w0, uint32_t w1, float a
   high->w = pack(fmaf(Nibble<2>(s1), a_hi, -b_hi), fmaf(Nibble<4>(s1), a_hi, -b_hi));
 }
 
+// Byte I of `w` (a code below 64) minus 32 as a float, exactly: bytes 0 to 2
+// are masked in place under the exponent whose mantissa bit 8I is worth 1
+// (2^(23 - 8I) + code) and the power of two and the 32 are subtracted together;
+// byte 3 is read as byte 1 of the word shifted down by 16.
+template <int I>
+__device__ __forceinline__ float CodeMinus32(uint32_t w) {
+  static_assert(I >= 0 && I <= 2, "the byte must sit below the exponent");
+  constexpr uint32_t kExponent = static_cast<uint32_t>(127 + 23 - 8 * I) << 23;
+  constexpr float kBias = static_cast<float>(1u << (23 - 8 * I)) + 32.0f;
+  return __uint_as_float((w & (0x3Fu << (8 * I))) | kExponent) - kBias;
+}
+
+// Eight Q6_K weights from the codes in the bytes of two words, as four fp16
+// pairs in byte order: w = scale * (code - 32), rounded once.
+__device__ __forceinline__ uint4 EightCodes(uint32_t w0, uint32_t w1, float scale) {
+  const uint32_t s0 = w0 >> 16, s1 = w1 >> 16;
+  auto pack = [](float x, float y) {
+    const __half2 h = __floats2half2_rn(x, y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  };
+  return make_uint4(pack(CodeMinus32<0>(w0) * scale, CodeMinus32<1>(w0) * scale),
+                    pack(CodeMinus32<0>(s0) * scale, CodeMinus32<1>(s0) * scale),
+                    pack(CodeMinus32<0>(w1) * scale, CodeMinus32<1>(w1) * scale),
+                    pack(CodeMinus32<0>(s1) * scale, CodeMinus32<1>(s1) * scale));
+}
+
 // Where unit `u` of a launch works: its part, weight rows and K range.
 struct Unit {
   int part;
@@ -268,8 +339,13 @@ __device__ __forceinline__ Unit LocateUnit(const TcGemmArgs& a, int u) {
 // can read one quarter) share the work of a small batch.
 __host__ __device__ __forceinline__ int TokenRow(int t) { return (t & 3) * 32 + (t >> 2); }
 
+template <int TYPE>
 __global__ void __launch_bounds__(kTcThreads, 1)
-GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
+GemmTc(const __grid_constant__ TcGemmArgs a) {
+  using Q = Quant<TYPE>;
+  using Smem = Smem<TYPE>;
+  constexpr int kWStages = Q::kWStages, kXStages = Q::kXStages, kRawStages = Q::kRawStages;
+  constexpr int kRawBytes = Smem::kRawBytes;
   extern __shared__ uint8_t smem_raw[];
   // The swizzled tiles need a 1024-byte aligned base.
   const uint32_t base = (SharedAddress(smem_raw) + 1023u) & ~1023u;
@@ -328,11 +404,11 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
   // the stage counters run on across units, so the pipeline never drains
   // between them.
   if (warp == kLoaderWarp || warp == kLoaderWarp + 1) {
-    // ---- weight loaders: 2304 16-byte chunks per block (9 per row), split
-    // between the two warps; consecutive lanes take consecutive chunks, so one
-    // instruction touches the 144-byte runs of three or four rows ---------------
+    // ---- weight loaders: the 16-byte chunks of one block of every row (Q4_K: 9
+    // per row, one 144-byte run; Q6_K: 14 per row from its four planes), split
+    // between the two warps; consecutive lanes take consecutive chunks ----------
     const int which = warp - kLoaderWarp;
-    constexpr int kChunksPerRow = kQ4KBytes / 16;
+    constexpr int kChunksPerRow = Q::kRowBytes / 16;
     constexpr int kChunks = kTileRows * kChunksPerRow;
     int i = 0;   // blocks requested so far
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
@@ -343,7 +419,6 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
         const uint32_t phase = (i / kRawStages) & 1u;
         BoundedWait(raw_empty(s), phase ^ 1u, abort_flag, a.error, 1);
         const uint32_t to = base + Smem::kRaw + s * kRawBytes;
-        const size_t column = static_cast<size_t>(unit.first_block + b) * kQ4KBytes;
 #pragma unroll 6
         for (int c = which * 32 + lane; c < kChunks; c += 64) {
           const int r = c / kChunksPerRow;
@@ -351,7 +426,8 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
           // Rows past the end repeat the last row; their sums are never stored.
           const int row = min(unit.row0 + r, part.rows - 1);
           asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to + c * 16),
-                       "l"(part.w + static_cast<size_t>(row) * part.row_bytes + column + chunk * 16) : "memory");
+                       "l"(Q::Source(part.w + static_cast<size_t>(row) * part.row_bytes, a.blocks,
+                                     unit.first_block + b, chunk)) : "memory");
         }
         // Arrives on the stage's barrier once this thread's copies have landed.
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(s)) : "memory");
@@ -485,40 +561,95 @@ GemmQ4KTc(const __grid_constant__ TcGemmArgs a) {
         const int s = i % kRawStages;
         const uint32_t phase = (i / kRawStages) & 1u;
         BoundedWait(raw_full(s), phase, abort_flag, a.error, 4);
-        const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * kQ4KBytes;
-        const uint4 head = *reinterpret_cast<const uint4*>(block);
-        const float d = HalfBitsToFloat(static_cast<uint16_t>(head.x & 0xFFFF));
-        const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head.x >> 16));
-#pragma unroll
-        for (int tt = 0; tt < 2; ++tt) {
-          const int t = 2 * half + tt;
-          const int g = 4 * i + t;
-          const int ws = g % kWStages;
-          const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
-          int sc_lo, m_lo, sc_hi, m_hi;
-          ScaleMinK4(2 * t, head.y, head.z, head.w, &sc_lo, &m_lo);
-          ScaleMinK4(2 * t + 1, head.y, head.z, head.w, &sc_hi, &m_hi);
-          const float a_lo = d * static_cast<float>(sc_lo), a_hi = d * static_cast<float>(sc_hi);
-          const float b_lo = dmin * static_cast<float>(m_lo), b_hi = dmin * static_cast<float>(m_hi);
-          const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t);
-          const uint4 q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
-          const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-          BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
-          uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
-            uint4 low, high;
-            SixteenWeights(words[2 * c], words[2 * c + 1], a_lo, b_lo, a_hi, b_hi, &low, &high);
-            *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) = low;
-            *reinterpret_cast<uint4*>(tile_row + (((4 + c) ^ (r & 7)) << 4)) = high;
+        if constexpr (TYPE == GUFO_CUDA_Q4_K) {
+          const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * Q::kRowBytes;
+          const uint4 head = *reinterpret_cast<const uint4*>(block);
+          const float d = HalfBitsToFloat(static_cast<uint16_t>(head.x & 0xFFFF));
+          const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head.x >> 16));
+  #pragma unroll
+          for (int tt = 0; tt < 2; ++tt) {
+            const int t = 2 * half + tt;
+            const int g = 4 * i + t;
+            const int ws = g % kWStages;
+            const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
+            int sc_lo, m_lo, sc_hi, m_hi;
+            ScaleMinK4(2 * t, head.y, head.z, head.w, &sc_lo, &m_lo);
+            ScaleMinK4(2 * t + 1, head.y, head.z, head.w, &sc_hi, &m_hi);
+            const float a_lo = d * static_cast<float>(sc_lo), a_hi = d * static_cast<float>(sc_hi);
+            const float b_lo = dmin * static_cast<float>(m_lo), b_hi = dmin * static_cast<float>(m_hi);
+            const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
+            const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
+            uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
+  #pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
+              uint4 low, high;
+              SixteenWeights(words[2 * c], words[2 * c + 1], a_lo, b_lo, a_hi, b_hi, &low, &high);
+              *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) = low;
+              *reinterpret_cast<uint4*>(tile_row + (((4 + c) ^ (r & 7)) << 4)) = high;
+            }
+            // Make the generic-proxy stores visible to the tensor core's reads; one
+            // lane then arrives for the warp.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              MbarArrive(w_full(ws));
+            }
           }
-          // Make the generic-proxy stores visible to the tensor core's reads; one
-          // lane then arrives for the warp.
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) {
-            MbarArrive(w_full(ws));
+        } else {
+          // Thread (row r, half n) turns the 128 values of its half of the block
+          // into tiles 2n (low nibbles) and 2n + 1 (high nibbles): w = d * sc *
+          // (code - 32), code = nibble | two bits of qh << 4 (DequantQ6_K,
+          // src/core/quant.cpp:98-125).
+          const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * Q::kRowBytes;
+          const uint4 l0 = *reinterpret_cast<const uint4*>(block + 64 * half);
+          const uint4 l1 = *reinterpret_cast<const uint4*>(block + 64 * half + 16);
+          const uint4 l2 = *reinterpret_cast<const uint4*>(block + 64 * half + 32);
+          const uint4 l3 = *reinterpret_cast<const uint4*>(block + 64 * half + 48);
+          const uint4 h0 = *reinterpret_cast<const uint4*>(block + 128 + 32 * half);
+          const uint4 h1 = *reinterpret_cast<const uint4*>(block + 128 + 32 * half + 16);
+          const uint2 sc8 = *reinterpret_cast<const uint2*>(block + 192 + 8 * half);
+          const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(
+              block + 208 + 2 * ((unit.first_block + b) % kQ6KSlabBlocks)));
+          const uint32_t ql[16] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w,
+                                   l2.x, l2.y, l2.z, l2.w, l3.x, l3.y, l3.z, l3.w};
+          const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+          // Scale of 16-value group i of this half (int8).
+          auto scale = [&](int i) {
+            const uint32_t word = i < 4 ? sc8.x : sc8.y;
+            return d * static_cast<float>(static_cast<int>(word << (24 - 8 * (i & 3))) >> 24);
+          };
+#pragma unroll
+          for (int tt = 0; tt < 2; ++tt) {
+            const int t = 2 * half + tt;
+            const int g = 4 * i + t;
+            const int ws = g % kWStages;
+            const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
+            BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
+            uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              // Chunk c < 4: values 8c .. 8c + 7 from ql bytes 8c .., chunk c >= 4: from ql
+              // bytes 32 + 8(c - 4) ..; both take their two high bits from qh bytes
+              // 8(c & 3) .., at bit 2 * (2 tt + (c >> 2)).
+              const int k = c & 3;
+              const int shift = 2 * (2 * tt + (c >> 2));   // where the two bits sit in qh
+              const uint32_t q0 = ql[(c >> 2) * 8 + 2 * k], q1 = ql[(c >> 2) * 8 + 2 * k + 1];
+              const uint32_t n0 = tt == 0 ? (q0 & 0x0F0F0F0Fu) : ((q0 >> 4) & 0x0F0F0F0Fu);
+              const uint32_t n1 = tt == 0 ? (q1 & 0x0F0F0F0Fu) : ((q1 >> 4) & 0x0F0F0F0Fu);
+              const uint32_t b0 = shift <= 4 ? (qh[2 * k] << (4 - shift)) : (qh[2 * k] >> (shift - 4));
+              const uint32_t b1 = shift <= 4 ? (qh[2 * k + 1] << (4 - shift)) : (qh[2 * k + 1] >> (shift - 4));
+              const float sc = scale(4 * tt + 2 * (c >> 2) + (k >> 1));
+              *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) =
+                  EightCodes(n0 | (b0 & 0x30303030u), n1 | (b1 & 0x30303030u), sc);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              MbarArrive(w_full(ws));
+            }
           }
         }
         __syncwarp();
@@ -635,8 +766,8 @@ int ReserveTc(gufo_cuda_ctx* ctx, size_t bytes) {
 }  // namespace
 
 bool TcGemmRuns(const gufo_cuda_ctx* ctx, int type, int cols, int tokens) {
-  return !ctx->force_general && ctx->tc_gemm && type == GUFO_CUDA_Q4_K && cols % kSuperBlock == 0 &&
-         tokens >= kTcMinTokens;
+  return !ctx->force_general && ctx->tc_gemm && (type == GUFO_CUDA_Q4_K || type == GUFO_CUDA_Q6_K) &&
+         cols % kSuperBlock == 0 && tokens >= kTcMinTokens;
 }
 
 // Scratch layout: [0, 256) error word; then the tile images, the unscale
@@ -646,12 +777,31 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
   const int blocks = cols / kSuperBlock;
   static bool configured[16] = {};
   if (!configured[ctx->device & 15]) {
-    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemmQ4KTc, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem::kBytes));
+    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemmTc<GUFO_CUDA_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Smem<GUFO_CUDA_Q4_K>::kBytes));
+    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemmTc<GUFO_CUDA_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Smem<GUFO_CUDA_Q6_K>::kBytes));
     configured[ctx->device & 15] = true;
   }
-  for (int p = 0; p < base.nparts; ++p) {
-    if ((reinterpret_cast<uintptr_t>(base.parts[p].data) & 15) != 0 || base.parts[p].row_bytes % 16 != 0) {
-      return Fail(GUFO_CUDA_BAD_ARGUMENT, "tcgen05 gemm: weight rows must be 16-byte aligned");
+  // Launch groups: parts of one block format, up to kTcMaxParts each.
+  std::vector<std::vector<int>> groups;
+  for (int type : {GUFO_CUDA_Q4_K, GUFO_CUDA_Q6_K}) {
+    std::vector<int> group;
+    for (int p = 0; p < base.nparts; ++p) {
+      if ((reinterpret_cast<uintptr_t>(base.parts[p].data) & 15) != 0 || base.parts[p].row_bytes % 16 != 0) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "tcgen05 gemm: weight rows must be 16-byte aligned");
+      }
+      if (base.parts[p].type != type) {
+        continue;
+      }
+      group.push_back(p);
+      if (static_cast<int>(group.size()) == kTcMaxParts) {
+        groups.push_back(group);
+        group.clear();
+      }
+    }
+    if (!group.empty()) {
+      groups.push_back(group);
     }
   }
   // K ranges per 256-row tile; up to kTcMaxParts parts share a launch and its split.
@@ -684,10 +834,10 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     const size_t image_bytes = static_cast<size_t>(blocks) * 4 * kXTileBytes;
     // Worst case for the partial sums: every part split into blocks / 2 ranges.
     size_t partial_floats = 0;
-    for (int p0 = 0; p0 < base.nparts; p0 += kTcMaxParts) {
+    for (const std::vector<int>& group : groups) {
       int tiles = 0;
       size_t rows = 0;
-      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+      for (int p : group) {
         tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
         rows += base.parts[p].rows;
       }
@@ -711,7 +861,7 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     GUFO_CUDA_TRY(LaunchOverlapped(StageHalfKernel, dim3(kTokenRows), dim3(256), 0, ctx->stream, 1, x, m, cols,
                                    kTokenRows, xh, unscale));
     ctx->launches.fetch_add(1);
-    for (int p0 = 0; p0 < base.nparts; p0 += kTcMaxParts) {
+    for (const std::vector<int>& group : groups) {
       TcGemmArgs args{};
       args.blocks = blocks;
       args.xh = xh;
@@ -719,13 +869,13 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
       args.tokens = m;
       args.error = reinterpret_cast<int*>(ctx->tc_scratch);
       int tiles = 0;
-      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+      for (int p : group) {
         tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
       }
       args.ksplit = splits_for(tiles, m);
       args.blocks_per_unit = (blocks + args.ksplit - 1) / args.ksplit;
       float* next_partial = partial;
-      for (int p = p0; p < base.nparts && p < p0 + kTcMaxParts; ++p) {
+      for (int p : group) {
         const GemvPart& part = base.parts[p];
         TcPart& to = args.parts[args.nparts++];
         to.w = part.data;
@@ -745,11 +895,17 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
       }
       args.total_units = tiles * args.ksplit;
       const int grid = args.total_units < ctx->sm_count ? args.total_units : ctx->sm_count;
-      GUFO_CUDA_TRY(LaunchOverlapped(GemmQ4KTc, dim3(grid), dim3(kTcThreads), Smem::kBytes, ctx->stream, 1, args));
+      if (base.parts[group[0]].type == GUFO_CUDA_Q4_K) {
+        GUFO_CUDA_TRY(LaunchOverlapped(GemmTc<GUFO_CUDA_Q4_K>, dim3(grid), dim3(kTcThreads),
+                                       Smem<GUFO_CUDA_Q4_K>::kBytes, ctx->stream, 1, args));
+      } else {
+        GUFO_CUDA_TRY(LaunchOverlapped(GemmTc<GUFO_CUDA_Q6_K>, dim3(grid), dim3(kTcThreads),
+                                       Smem<GUFO_CUDA_Q6_K>::kBytes, ctx->stream, 1, args));
+      }
       ctx->launches.fetch_add(1);
       if (args.ksplit > 1) {
         for (int i = 0; i < args.nparts; ++i) {
-          const GemvPart& part = base.parts[p0 + i];
+          const GemvPart& part = base.parts[group[i]];
           float* y = base.y + static_cast<size_t>(t0) * base.y_stride + part.out_offset;
           GUFO_CUDA_TRY(LaunchOverlapped(SumSplitsKernel, dim3((part.rows + 255) / 256, m), dim3(256), 0, ctx->stream,
                                          1, static_cast<const float*>(args.parts[i].out), args.ksplit,

@@ -221,6 +221,13 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
       }
     };
     float keep[8] = {};
+    // The norm weights of the warp's first block never depend on an earlier
+    // kernel: their load rides with the first pass instead of following the
+    // barrier.
+    float keep_w[8] = {};
+    if (warp < blocks) {
+      load8(a.norm_w + warp * kSuperBlock + lane * 8, keep_w);
+    }
     float sq = 0.f;
     for (int b = warp; b < blocks; b += kFastWarps) {
       float v[8];
@@ -256,10 +263,13 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
         for (int i = 0; i < 8; ++i) {
           v[i] = keep[i];
         }
+        for (int i = 0; i < 8; ++i) {
+          w[i] = keep_w[i];
+        }
       } else {
         residual(at, v);
+        load8(a.norm_w + at, w);
       }
-      load8(a.norm_w + at, w);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         out[i] = v[i] * inv * w[i];

@@ -32,19 +32,21 @@ def _weights(seed, rows, cols, ggml_type=Q.GGML_Q4_K):
     return raw.reshape(rows, -1)
 
 
+@pytest.mark.parametrize("ggml_type", [Q.GGML_Q4_K, Q.GGML_Q6_K])
 @pytest.mark.parametrize("rows,cols", [(256, 512), (130, 256), (1000, 2560), (2560, 9728)])
 @pytest.mark.parametrize("tokens", [16, 17, 33, 128, 131])
-def test_gemm_matches_oracle(ctx, oracle, rows, cols, tokens):
-    """One Q4_K part: row counts off the 128-row tile, K split over thread blocks (2560 x 9728),
-    token counts off the MMA's N granule and past one pass."""
+def test_gemm_matches_oracle(ctx, oracle, ggml_type, rows, cols, tokens):
+    """One Q4_K or Q6_K part: row counts off the 256-row tile, K split over thread blocks
+    (2560 x 9728), block counts that leave a partial slab in the Q6_K device arrangement (10, 38),
+    token counts off the tile granule and past one pass."""
     if rows * cols * tokens > 1.5e9:
         tokens = min(tokens, 33)
-    raw = _weights(40 + rows % 7, rows, cols)
+    raw = _weights(40 + rows % 7, rows, cols, ggml_type)
     x = G.normal(50 + tokens, tokens, cols)
-    m = ctx.matrix_upload(Q.GGML_Q4_K, raw, rows, cols)
+    m = ctx.matrix_upload(ggml_type, raw, rows, cols)
     got = ctx.matmul([(m, 0, rows)], x, tokens, rows)
     ctx.synchronize()
-    want = oracle.matmul([(raw, Q.GGML_Q4_K, 0, rows)], cols, x)
+    want = oracle.matmul([(raw, ggml_type, 0, rows)], cols, x)
     err = rel_l2(got, want)
     assert err <= GEMM_TOL, err
     assert err <= 4e-4, err
@@ -73,18 +75,18 @@ def test_gemm_agrees_with_the_eight_token_passes(ctx):
 
 
 def test_gemm_stacked_parts_and_row_ranges(ctx, oracle):
-    """Gate and up stacked, a row range inside a matrix, an F32 part beside them (it takes the
-    other kernels), every output column in its place."""
+    """Gate and up stacked (one Q4_K, one Q6_K: two launches), a row range inside a matrix, an
+    F32 part beside them (it takes the other kernels), every output column in its place."""
     cols, tokens = 768, 24
-    gate, up = _weights(63, 300, cols), _weights(64, 300, cols)
+    gate, up = _weights(63, 300, cols), _weights(64, 300, cols, Q.GGML_Q6_K)
     extra = G.normal(65, 5, cols)
     mg = ctx.matrix_upload(Q.GGML_Q4_K, gate, 300, cols)
-    mu = ctx.matrix_upload(Q.GGML_Q4_K, up, 300, cols)
+    mu = ctx.matrix_upload(Q.GGML_Q6_K, up, 300, cols)
     mf = ctx.matrix_upload(Q.GGML_F32, extra.view(np.uint8), 5, cols)
     x = G.normal(66, tokens, cols)
     got = ctx.matmul([(mg, 0, 300), (mf, 0, 5), (mu, 17, 200)], x, tokens, 505)
     want = oracle.matmul([(gate, Q.GGML_Q4_K, 0, 300), (extra.view(np.uint8).reshape(5, -1), Q.GGML_F32, 0, 5),
-                          (up, Q.GGML_Q4_K, 17, 200)], cols, x)
+                          (up, Q.GGML_Q6_K, 17, 200)], cols, x)
     assert rel_l2(got[:, :300], want[:, :300]) <= 4e-4
     assert rel_l2(got[:, 300:305], want[:, 300:305]) <= 1e-5
     assert rel_l2(got[:, 305:], want[:, 305:]) <= 4e-4
