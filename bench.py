@@ -444,6 +444,22 @@ def probe_gemm(ctx, stream, dev, gen) -> None:
         out["results"].append({"tokens": m, "us": us, "GB/s": algorithmic / us / 1e3,
                                "hbm_frac": algorithmic / us / 1e3 / peak,
                                "TFLOP/s": 2.0 * m * 2 * rows * cols / us / 1e6})
+    # The verify batch's LM head at 4B-class shapes: 248320 x 2560 Q6_K (521 MB, one copy: larger
+    # than L2 by itself).
+    del sets, keep
+    rows = 248320
+    raw = Q.quantize(Q.GGML_Q6_K, torch.randn(rows, cols, device=dev, generator=gen) * 0.02)
+    head = Context._parts([(ctx.matrix_from_device(Q.GGML_Q6_K, raw.data_ptr(), rows, cols), 0, rows)])
+    weight_bytes = rows * Q.row_bytes(Q.GGML_Q6_K, cols)
+    out["lm_head"] = {"shape": f"{rows} x {cols} Q6_K", "results": []}
+    for m in (32, 128):
+        x = torch.randn(m, cols, device=dev, generator=gen)
+        y = torch.empty(m, rows, device=dev)
+        us = graph_us(stream, lambda: ctx.matmul_device(head, 1, x, m, y))
+        algorithmic = weight_bytes + 4 * m * cols + 4 * m * rows
+        out["lm_head"]["results"].append({"tokens": m, "us": us, "GB/s": algorithmic / us / 1e3,
+                                          "hbm_frac": algorithmic / us / 1e3 / peak,
+                                          "TFLOP/s": 2.0 * m * rows * cols / us / 1e6})
     ctx.synchronize()
     out["launches"] = ctx.launch_count()
     print(json.dumps(out))

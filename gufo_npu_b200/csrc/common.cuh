@@ -219,6 +219,7 @@ struct gufo_cuda_ctx {
   size_t tc_scratch_bytes = 0;
   // Products of 16 or more token rows run on the tcgen05 GEMM (option "tc_gemm").
   bool tc_gemm = true;
+  bool tc_gemm_all = false;   // option value 2: from 16 rows on, whatever is faster
   std::atomic<int64_t> launches{0};
   // Test hook: route every product through the general kernel.
   bool force_general = false;

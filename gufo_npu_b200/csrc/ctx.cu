@@ -237,6 +237,7 @@ int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value) {
   }
   if (std::strcmp(name, "tc_gemm") == 0) {
     ctx->tc_gemm = value != 0;
+    ctx->tc_gemm_all = value == 2;
     return GUFO_CUDA_OK;
   }
   if (std::strcmp(name, "reuse_image") == 0) {

@@ -766,8 +766,12 @@ int ReserveTc(gufo_cuda_ctx* ctx, size_t bytes) {
 }  // namespace
 
 bool TcGemmRuns(const gufo_cuda_ctx* ctx, int type, int cols, int tokens) {
-  return !ctx->force_general && ctx->tc_gemm && (type == GUFO_CUDA_Q4_K || type == GUFO_CUDA_Q6_K) &&
-         cols % kSuperBlock == 0 && tokens >= kTcMinTokens;
+  if (ctx->force_general || !ctx->tc_gemm || cols % kSuperBlock != 0) {
+    return false;
+  }
+  // "tc_gemm" = 2 sends every product of 16 or more rows here (tests).
+  const int least = ctx->tc_gemm_all ? 16 : (type == GUFO_CUDA_Q6_K ? kTcMinTokensQ6K : kTcMinTokens);
+  return (type == GUFO_CUDA_Q4_K || type == GUFO_CUDA_Q6_K) && tokens >= least;
 }
 
 // Scratch layout: [0, 256) error word; then the tile images, the unscale

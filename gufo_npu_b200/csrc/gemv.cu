@@ -173,7 +173,7 @@ void LaunchRows(const GemvArgs& args, cudaStream_t stream) {
 // kernels (x staged once per block format, one launch per part), the rest
 // together on the general kernel; at most kMaxTokens tokens per pass.
 int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
-  if (tokens >= kTcMinTokens && (reinterpret_cast<uintptr_t>(base.x) & 15) == 0) {
+  if (tokens >= 16 && (reinterpret_cast<uintptr_t>(base.x) & 15) == 0) {
     // Many token rows: the parts the tcgen05 GEMM runs read their weights once
     // for all rows; the other parts take the 8-token passes below.
     GemvArgs tc = base, other = base;

@@ -159,9 +159,9 @@ def test_activation_extremes(ctx, oracle):
 @pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8, 9, 19])
 def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
     """Results do not depend on how many tokens come together
-    (src/models/qwen35/gguf_projections.cpp:241-243): to fp32 summation order below 16 tokens, and
-    to the fp16 rounding of the tcgen05 path (Q4_K, 16 tokens and more) above, both far inside
-    the 1e-3 bound."""
+    (src/models/qwen35/gguf_projections.cpp:241-243): to fp32 summation order on the GEMV kernels;
+    a product that the dispatcher sends to the tcgen05 path differs by that path's fp16 rounding,
+    hence the wider bound from 16 tokens on. Both are far inside the 1e-3 bound."""
     rows, cols = 96, 768
     x = G.normal(50 + tokens, tokens, cols)
     exact_tol, same_tol = (1e-5, 1e-6) if tokens < 16 else (4e-4, 4e-4)
