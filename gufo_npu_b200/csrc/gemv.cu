@@ -234,9 +234,10 @@ int LaunchGemv(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
         }
         if (args.prologue == kPrologueImage && !staged) {
           staged = true;
-          // High nibbles of Q4_K reach the MMA as 16 q: fold 1/16 into the factors.
+          // High nibbles of Q4_K reach the MMA as 16 q, Q6_K codes as 4 (q - 32): the
+          // factors carry 1/16 and 1/4.
           const int rc = StageActivations(ctx, x, m, base.cols, type == GUFO_CUDA_Q4_K ? 32 : 16,
-                                          type == GUFO_CUDA_Q4_K ? 1.0f / 16.0f : 1.0f, &args.image);
+                                          type == GUFO_CUDA_Q4_K ? 1.0f / 16.0f : 0.25f, &args.image);
           if (rc != GUFO_CUDA_OK) {
             return rc;
           }
