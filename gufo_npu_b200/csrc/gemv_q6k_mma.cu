@@ -98,6 +98,25 @@ __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&h
   }
   const int s0g = ScaleOf<8 * H + 2 * K>(u.sc[0]), s1g = ScaleOf<8 * H + 2 * K + 1>(u.sc[0]);
   const int s0h = ScaleOf<8 * H + 2 * K>(u.sc[1]), s1h = ScaleOf<8 * H + 2 * K + 1>(u.sc[1]);
+  if constexpr (TOKENS == 1) {
+    // One token fills three of the eight MMA columns, so one product serves both
+    // groups of the run: columns 0..2 carry the planes for values 0..15 only,
+    // columns 4..6 for values 16..31 only (at_first is this lane's share of that
+    // arrangement, zeros elsewhere). A lane's two output columns, 2t and 2t + 1,
+    // then belong to the first group for t < 2 and to the second for t >= 2.
+    const uint2 x = *reinterpret_cast<const uint2*>(at_first + 128 * H + 32 * K);
+    int c[4];
+    MmaS8S8(c, a, x.x, x.y);
+    const bool second = stride_second != 0;   // set for lanes t >= 2
+    const int sg = second ? s1g : s0g, sh = second ? s1h : s0h;
+    sum[0][0] += sg * c[0];
+    sum[0][1] += sg * c[1];
+    sum[0][2] += sh * c[2];
+    sum[0][3] += sh * c[3];
+    (void)at_second;
+    (void)g;
+    (void)stride_first;
+  } else {
 #pragma unroll
   for (int nb = 0; nb < kNB; ++nb) {
     // Further column groups lie 8 planes on; the plane of zeros has no such
@@ -116,6 +135,7 @@ __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&h
     sum[nb][1] += s1g * c[1];
     sum[nb][2] += s1h * c[2];
     sum[nb][3] += s1h * c[3];
+  }
   }
 }
 
@@ -167,7 +187,9 @@ __device__ __forceinline__ void MultiplyUnit(const Q6KUnit& u, int b, int g, int
   const float d1 = HalfBitsToFloat(static_cast<uint16_t>(u.d[1]));
 #pragma unroll
   for (int nb = 0; nb < kNB; ++nb) {
-    const float2 cs = *reinterpret_cast<const float2*>(&col_scale[b * l.kcols + nb * 8 + 2 * t]);
+    // One token: lanes t >= 2 hold the second groups' sums of columns 2 (t - 2).
+    const int col = TOKENS == 1 ? 2 * (t & 1) : nb * 8 + 2 * t;
+    const float2 cs = *reinterpret_cast<const float2*>(&col_scale[b * l.kcols + col]);
     acc.out[nb][0] = fmaf(static_cast<float>(sum[nb][0]), d0 * cs.x, acc.out[nb][0]);
     acc.out[nb][1] = fmaf(static_cast<float>(sum[nb][1]), d0 * cs.y, acc.out[nb][1]);
     acc.out[nb][2] = fmaf(static_cast<float>(sum[nb][2]), d1 * cs.x, acc.out[nb][2]);
@@ -208,7 +230,12 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
   // stored.
   const uint8_t* plane = smem + (g % kNCols) * l.plane_stride + 8 * t;
   const uint8_t* none = zeros + 8 * t;
-  const uint8_t* lane_first = t < 2 ? plane : none;
+  // One token (see MultiplyRun): column g < 4 carries plane g for the lanes of
+  // values 0..15 (t < 2), column g >= 4 carries plane g - 4 for the lanes of
+  // values 16..31; columns 3 and 7 and the other lanes read zeros.
+  const bool one_live = (g & 3) < kNCols && ((g < 4) == (t < 2));
+  const uint8_t* lane_first = TOKENS == 1 ? (one_live ? smem + (g & 3) * l.plane_stride + 8 * t : none)
+                                          : (t < 2 ? plane : none);
   const uint8_t* lane_second = t < 2 ? none : plane;
   const int row_tiles = TotalTiles(a);
   // With ksplit > 1 a cluster of ksplit blocks shares each tile.
@@ -351,6 +378,13 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     if (s == slabs_mine - 1) {
       // Hand this tile's partial sums to the block.
+      if constexpr (TOKENS == 1) {
+        // The second groups' sums sit two lanes on, in the same columns.
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc.out[0][j] += __shfl_xor_sync(0xFFFFFFFFu, acc.out[0][j], 2);
+        }
+      }
       float* tile = exchange + ((n & 1) * kFastWarps + warp) * kTileFloats;
 #pragma unroll
       for (int nb = 0; nb < kNB; ++nb) {
