@@ -135,6 +135,9 @@ struct FastGemvArgs {
   int groups;
   int x_group_stride;     // floats between the inputs (0: shared)
   int x_group_div;        // groups per input: group g reads input g / x_group_div (0 counts as 1)
+  // Timing experiments (context option "gemv_variant"; wrong results): 1 skips
+  // the multiplies and leaves only the data movement.
+  int variant;
   int y_group_stride;     // floats between the groups' outputs
 };
 

@@ -31,7 +31,7 @@ constexpr int kSlabBlocks = kQ6KSlabBlocks;                    // blocks per sla
 constexpr int kSlabDataBytes = kSlabBlocks * kQ6KBytes;        // 1680
 constexpr int kSlabRowBytes = kSlabDataBytes + 16;             // 424 words: 8 mod 32
 constexpr int kSlabBytes = 16 * kSlabRowBytes;
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 
 struct Q6KUnit {
   uint2 ql[2][2][2];   // [row][half][run parity]: bytes 8t..8t+7 of ql[32 * parity ..]
@@ -371,7 +371,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     const int slab = rank + s * ks;
     const int b = slab * kSlabBlocks + warp;
-    if (b < blocks) {
+    if (b < blocks && a.variant != 1) {
       Q6KUnit unit;
       LoadUnit(unit, ring + (q % kStages) * kSlabBytes, warp, min(kSlabBlocks, blocks - slab * kSlabBlocks), g, t);
       MultiplyUnit<TOKENS>(unit, b, g, t, lane_first, lane_second, l, col_scale, sums, acc);
@@ -429,7 +429,7 @@ size_t SharedBytes(int cols) {
 
 template <int TOKENS>
 int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
-  constexpr int kPerSm = 2;
+  constexpr int kPerSm = TOKENS == 1 ? 3 : 2;
   const size_t smem = SharedBytes<TOKENS>(args.cols);
   if (smem > static_cast<size_t>(kFastMaxShared)) {
     return GUFO_CUDA_TOO_LARGE;
@@ -452,6 +452,7 @@ int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   }
   // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
   FastGemvArgs launch = args;
+  launch.variant = ctx->gemv_variant;
   const int slabs = (args.cols / kSuperBlock + kSlabBlocks - 1) / kSlabBlocks;
   int grid = 1;
   PlanFastGrid(GemvQ6KMma<TOKENS, kPerSm>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit, &grid);
