@@ -345,10 +345,10 @@ def run_ours(args):
 
 
 # DRAM traffic of one LM-head launch: dram__bytes_read.sum + dram__bytes_write.sum of GemvQ6KMma
-# from one ncu capture of `bench.py --probe q6k` (131072 rows: 220.26 MB read, 5.63 MB written on
+# from one ncu capture of `bench.py --probe q6k` (131072 rows: 220.26 MB read, 4.04 MB written on
 # average), scaled by rows to the 248320-row launch (every row is read once, so traffic grows in
 # proportion). The summary with the command is profiles/gemv_q6k_mma_131072x2048.md.
-LM_HEAD_TRAFFIC_BYTES_PER_ROW = (220.26e6 + 5.63e6) / 131072
+LM_HEAD_TRAFFIC_BYTES_PER_ROW = (220.26e6 + 4.04e6) / 131072
 
 
 def run_probe(which: str) -> None:
