@@ -343,7 +343,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
     }
     const int slab = rank + s * ks;
     const int b = slab * kSlabBlocks + warp;
-    if (b < blocks) {
+    if (b < blocks && a.variant != 1) {
       Q4KUnit unit;
       LoadUnit(unit, ring + (q % kStages) * kSlabBytes, warp, g, t);
       MultiplyUnit<TOKENS>(unit, b, g, t, lane_plane, l, col_scale, sums, acc);
@@ -413,6 +413,7 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   }
   // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
   FastGemvArgs launch = args;
+  launch.variant = ctx->gemv_variant;
   const int slabs = (args.cols / kSuperBlock + kSlabBlocks - 1) / kSlabBlocks;
   int grid = 1;
   if (args.group_ids != nullptr) {
