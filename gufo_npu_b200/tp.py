@@ -222,7 +222,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64)
     del tensors
     rng = np.random.default_rng(7)
-    tokens = iter(rng.integers(0, cfg.vocab, size=2 * (steps + warmup) + 8).tolist())
+    tokens = iter(rng.integers(0, cfg.vocab, size=4 * (steps + warmup) + 16).tolist())
     host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
     for _ in range(warmup):
         dec.step(next(tokens), stream)
@@ -250,6 +250,18 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         host.copy_(logits, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     ms_e2e = timed(e2e_step)
+    # For context beside the row-split number: the same GPUs as independent replicas, every rank
+    # decoding its own sequence with the single-GPU resident decoder at the same time (no
+    # collective on the data path). Timed the same way: barrier, device events, max over ranks.
+    from .backend import CudaDecoder, CudaProjections
+    full = synth.build_model(cfg, seed=1, device=f"cuda:{local}")
+    replica = CudaDecoder(CudaProjections(ctx, cfg, full), full, max_positions=2 * (steps + warmup) + 64,
+                          use_graph=True)
+    del full
+    for _ in range(warmup):
+        replica.step_device(next(tokens))
+    torch.cuda.synchronize()
+    ms_replica = timed(lambda: replica.step_device(next(tokens)))
     if rank == 0:
         print(json.dumps({
             "metric": metric, "value": 1e3 / ms_resident, "unit": unit, "n_gpus": world, "steps": steps,
@@ -262,6 +274,9 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
+            "replicas": {"value": world * 1e3 / ms_replica, "unit": unit, "ms_per_step": ms_replica,
+                         "note": "the same GPUs as independent sequences, one resident decoder per GPU, no "
+                                 "collective; not the metric's row-split configuration"},
             "roofline": None, "cpu_baseline": None,
         }))
     dist.barrier()
