@@ -19,6 +19,9 @@ namespace gufo {
 constexpr int kSuperBlock = 256;   // values per K-quant super-block
 constexpr int kQ4KBytes = 144;     // d, dmin (fp16), 12 scale bytes, 128 nibble bytes
 constexpr int kQ6KBytes = 210;     // 128 ql, 64 qh, 16 int8 scales, d (fp16)
+constexpr int kQ5KBytes = 176;     // d, dmin (fp16), 12 scale bytes, 32 qh, 128 nibble bytes
+constexpr int kQ8Block = 32;       // values per Q8_0 block
+constexpr int kQ8Bytes = 34;       // d (fp16), 32 int8
 
 // Q6_K rows are kept on the device in a planar arrangement of the same bytes:
 // GGUF blocks are 210 bytes, so inside a row they sit on 2-byte boundaries and

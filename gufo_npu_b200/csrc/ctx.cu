@@ -35,6 +35,13 @@ size_t RowBytes(int type, int64_t cols) {
       return cols % kSuperBlock ? 0 : static_cast<size_t>(cols / kSuperBlock) * kQ4KBytes;
     case GUFO_CUDA_Q6_K:
       return cols % kSuperBlock ? 0 : static_cast<size_t>(cols / kSuperBlock) * kQ6KBytes;
+    case GUFO_CUDA_Q5_K:
+      return cols % kSuperBlock ? 0 : static_cast<size_t>(cols / kSuperBlock) * kQ5KBytes;
+    case GUFO_CUDA_Q8_0:
+      return cols % kQ8Block ? 0 : static_cast<size_t>(cols / kQ8Block) * kQ8Bytes;
+    case GUFO_CUDA_F16:
+    case GUFO_CUDA_BF16:
+      return static_cast<size_t>(cols) * 2;
     default:
       return 0;
   }
@@ -343,10 +350,11 @@ static int CheckMatrixArgs(const gufo_cuda_ctx* ctx, int type, const void* bytes
   if (ctx == nullptr || bytes == nullptr || out == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "matrix: null pointer");
   }
-  if (type != GUFO_CUDA_F32 && type != GUFO_CUDA_Q4_K && type != GUFO_CUDA_Q6_K) {
+  if (type != GUFO_CUDA_F32 && type != GUFO_CUDA_Q4_K && type != GUFO_CUDA_Q6_K && type != GUFO_CUDA_Q5_K &&
+      type != GUFO_CUDA_Q8_0 && type != GUFO_CUDA_F16 && type != GUFO_CUDA_BF16) {
     return Fail(GUFO_CUDA_UNSUPPORTED_TYPE,
                 "matrix: ggml type " + std::to_string(type) +
-                    " is not run by this backend (Q4_K, Q6_K, F32)");
+                    " is not run by this backend (Q4_K, Q5_K, Q6_K, Q8_0, F32, F16, BF16)");
   }
   if (rows <= 0 || cols <= 0) {
     return Fail(GUFO_CUDA_SHAPE, "matrix: rows and cols must be positive");

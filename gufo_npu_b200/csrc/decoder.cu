@@ -394,6 +394,9 @@ int gufo_cuda_embed_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix, const in
   if (m == nullptr) {
     return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT, "embed: unknown matrix handle");
   }
+  if (m->type != GUFO_CUDA_Q4_K && m->type != GUFO_CUDA_Q6_K && m->type != GUFO_CUDA_F32) {
+    return gufo::Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "embed: the lookup runs Q4_K, Q6_K and F32 rows");
+  }
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
   gufo::EmbedArgs a{m->data, m->type, static_cast<int>(m->row_bytes), static_cast<int>(m->cols), device_token, h};
   GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::EmbedKernel, dim3(1), dim3(gufo::kSmallThreads), 0, ctx->stream, 1, a));
@@ -783,6 +786,9 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
   const gufo::Matrix* embed = ctx->FindMatrix(weights->token_embd);
   if (embed == nullptr || embed->cols != c.hidden || embed->rows != c.vocab) {
     return fail(Fail(GUFO_CUDA_SHAPE, "decoder_create: token_embd must be [hidden, vocab]"));
+  }
+  if (embed->type != GUFO_CUDA_Q4_K && embed->type != GUFO_CUDA_Q6_K && embed->type != GUFO_CUDA_F32) {
+    return fail(Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "decoder_create: token_embd must be Q4_K, Q6_K or F32 here"));
   }
   d->embed = *embed;
   {

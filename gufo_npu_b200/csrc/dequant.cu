@@ -1,5 +1,7 @@
 // Bit-exact dequantization of GGUF Q4_K and Q6_K rows to fp32
-// (quant::Dequantize, src/core/quant.cpp:33-59 and 98-125 in the reference).
+// (quant::Dequantize, src/core/quant.cpp:33-59 and 98-125 in the reference),
+// and of the other formats real files carry: Q8_0 (:21-30), Q5_K (:61-95), F16
+// and BF16.
 //
 // HBM-bound on the fp32 writes (4 bytes out per 0.56 / 0.82 bytes in). Each
 // product below is exact in fp32 (d: 11 significant bits, 6- or 7-bit scale,
@@ -81,6 +83,71 @@ DequantQ6K(const uint8_t* __restrict__ src, float* __restrict__ dst,
   }
 }
 
+// One thread per value: w = d * q (DequantQ8_0, quant.cpp:21-30). Blocks are
+// 34 bytes, so the scale sits on a 2-byte boundary.
+__global__ void __launch_bounds__(256)
+DequantQ8_0(const uint8_t* __restrict__ src, float* __restrict__ dst, int64_t values) {
+  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < values;
+       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint8_t* block = src + (item >> 5) * kQ8Bytes;
+    const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(block));
+    const int q = static_cast<int8_t>(block[2 + (item & 31)]);
+    dst[item] = __fmul_rn(d, static_cast<float>(q));
+  }
+}
+
+// One thread per (block, sub-block pair p, l): values l of sub-blocks 2p and
+// 2p + 1; the fifth bit of a code is bit 2p / 2p + 1 of qh[l] (DequantQ5_K,
+// quant.cpp:61-95).
+__global__ void __launch_bounds__(256)
+DequantQ5K(const uint8_t* __restrict__ src, float* __restrict__ dst, int64_t blocks) {
+  const int64_t items = blocks * 128;
+  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < items;
+       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t b = item >> 7;
+    const int p = static_cast<int>((item >> 5) & 3);
+    const int l = static_cast<int>(item & 31);
+    const uint8_t* bytes = src + b * kQ5KBytes;
+    const uint32_t* block = reinterpret_cast<const uint32_t*>(bytes);
+    const uint32_t dd = __ldg(block);
+    const float d = HalfBitsToFloat(static_cast<uint16_t>(dd & 0xFFFF));
+    const float dmin = HalfBitsToFloat(static_cast<uint16_t>(dd >> 16));
+    int sc_lo, m_lo, sc_hi, m_hi;
+    ScaleMinK4(2 * p, __ldg(block + 1), __ldg(block + 2), __ldg(block + 3), &sc_lo, &m_lo);
+    ScaleMinK4(2 * p + 1, __ldg(block + 1), __ldg(block + 2), __ldg(block + 3), &sc_hi, &m_hi);
+    const int h = bytes[16 + l];
+    const int a = bytes[48 + 32 * p + l];
+    const int lo = (a & 0xF) + (((h >> (2 * p)) & 1) << 4);
+    const int hi = (a >> 4) + (((h >> (2 * p + 1)) & 1) << 4);
+    float* out = dst + b * kSuperBlock + 64 * p + l;
+    out[0] = __fsub_rn(__fmul_rn(__fmul_rn(d, static_cast<float>(sc_lo)), static_cast<float>(lo)),
+                       __fmul_rn(dmin, static_cast<float>(m_lo)));
+    out[32] = __fsub_rn(__fmul_rn(__fmul_rn(d, static_cast<float>(sc_hi)), static_cast<float>(hi)),
+                        __fmul_rn(dmin, static_cast<float>(m_hi)));
+  }
+}
+
+// fp16 or bf16 values to fp32.
+__global__ void __launch_bounds__(256)
+DequantHalf(const uint16_t* __restrict__ src, float* __restrict__ dst, int64_t values, int bf16) {
+  for (int64_t item = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; item < values;
+       item += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint16_t bits = src[item];
+    float value;
+    if (bf16) {
+      value = __uint_as_float(static_cast<uint32_t>(bits) << 16);
+    } else if ((bits & 0x7C00u) == 0x7C00u) {
+      // Infinities and NaNs keep their payload as quant::HalfToFloat does
+      // (src/core/quant.cpp:148-149); the hardware conversion would quiet them.
+      value = __uint_as_float((static_cast<uint32_t>(bits & 0x8000u) << 16) | 0x7F800000u |
+                              (static_cast<uint32_t>(bits & 0x3FFu) << 13));
+    } else {
+      value = HalfBitsToFloat(bits);
+    }
+    dst[item] = value;
+  }
+}
+
 }  // namespace
 }  // namespace gufo
 
@@ -113,11 +180,21 @@ int gufo_cuda_dequantize_device(gufo_cuda_ctx* ctx, gufo_cuda_matrix matrix,
     return GUFO_CUDA_OK;
   }
   const int64_t blocks = values / gufo::kSuperBlock;
-  const int64_t items = blocks * (m->type == GUFO_CUDA_Q4_K ? 32 : 64);
+  const int64_t items = m->type == GUFO_CUDA_Q4_K   ? blocks * 32
+                        : m->type == GUFO_CUDA_Q6_K ? blocks * 64
+                        : m->type == GUFO_CUDA_Q5_K ? blocks * 128
+                                                    : values;
   const int64_t want = (items + 255) / 256;
   const int grid = static_cast<int>(want < ctx->sm_count * 8 ? want : ctx->sm_count * 8);
   if (m->type == GUFO_CUDA_Q4_K) {
     gufo::DequantQ4K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, blocks);
+  } else if (m->type == GUFO_CUDA_Q5_K) {
+    gufo::DequantQ5K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, blocks);
+  } else if (m->type == GUFO_CUDA_Q8_0) {
+    gufo::DequantQ8_0<<<grid, 256, 0, ctx->stream>>>(src, device_dst, values);
+  } else if (m->type == GUFO_CUDA_F16 || m->type == GUFO_CUDA_BF16) {
+    gufo::DequantHalf<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<const uint16_t*>(src), device_dst, values,
+                                                     m->type == GUFO_CUDA_BF16 ? 1 : 0);
   } else {
     gufo::DequantQ6K<<<grid, 256, 0, ctx->stream>>>(src, device_dst, rows,
                                                      static_cast<int>(m->cols / gufo::kSuperBlock), m->row_bytes);

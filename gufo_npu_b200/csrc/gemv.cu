@@ -97,6 +97,69 @@ __device__ __forceinline__ void RowQ6K(const uint8_t* __restrict__ row, int cols
   }
 }
 
+// Q5_K: Q4_K's layout with a fifth code bit per value in 32 bytes of qh
+// (gguf_dot::DotK4<true>, src/models/qwen35/gguf_dot.hpp:115-193).
+template <int M>
+__device__ __forceinline__ void RowQ5K(const uint8_t* __restrict__ row, int cols,
+                                       const float* __restrict__ x, int lane,
+                                       float (&acc)[M]) {
+  const int p = lane >> 3;        // sub-block pair of this lane's word
+  const int c = (lane & 7) * 4;   // first value inside the sub-blocks
+  const int blocks = cols / kSuperBlock;
+  for (int b = 0; b < blocks; ++b) {
+    const uint32_t* block = reinterpret_cast<const uint32_t*>(row + b * kQ5KBytes);
+    const uint32_t dd = __ldg(block);
+    const uint32_t s0 = __ldg(block + 1), s1 = __ldg(block + 2), s2 = __ldg(block + 3);
+    const uint32_t h = __ldg(block + 4 + (lane & 7)) >> (2 * p);   // qh bytes c .. c + 3, this pair's bits low
+    const uint32_t q = __ldg(block + 12 + lane);
+    const float d = HalfBitsToFloat(static_cast<uint16_t>(dd & 0xFFFF));
+    const float dmin = HalfBitsToFloat(static_cast<uint16_t>(dd >> 16));
+    int sc_lo, m_lo, sc_hi, m_hi;
+    ScaleMinK4(2 * p, s0, s1, s2, &sc_lo, &m_lo);
+    ScaleMinK4(2 * p + 1, s0, s1, s2, &sc_hi, &m_hi);
+    const float d_lo = d * static_cast<float>(sc_lo), o_lo = dmin * static_cast<float>(m_lo);
+    const float d_hi = d * static_cast<float>(sc_hi), o_hi = dmin * static_cast<float>(m_hi);
+    const float l0 = static_cast<float>((q & 0xF) + ((h & 1) << 4));
+    const float l1 = static_cast<float>(((q >> 8) & 0xF) + (((h >> 8) & 1) << 4));
+    const float l2 = static_cast<float>(((q >> 16) & 0xF) + (((h >> 16) & 1) << 4));
+    const float l3 = static_cast<float>(((q >> 24) & 0xF) + (((h >> 24) & 1) << 4));
+    const float h0 = static_cast<float>(((q >> 4) & 0xF) + (((h >> 1) & 1) << 4));
+    const float h1 = static_cast<float>(((q >> 12) & 0xF) + (((h >> 9) & 1) << 4));
+    const float h2 = static_cast<float>(((q >> 20) & 0xF) + (((h >> 17) & 1) << 4));
+    const float h3 = static_cast<float>((q >> 28) + (((h >> 25) & 1) << 4));
+    const int at = b * kSuperBlock + 64 * p + c;
+#pragma unroll
+    for (int t = 0; t < M; ++t) {
+      const float4 xl = __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(t) * cols + at));
+      const float4 xh = __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(t) * cols + at + 32));
+      const float dot_lo = l0 * xl.x + l1 * xl.y + l2 * xl.z + l3 * xl.w;
+      const float dot_hi = h0 * xh.x + h1 * xh.y + h2 * xh.z + h3 * xh.w;
+      const float sum_lo = (xl.x + xl.y) + (xl.z + xl.w);
+      const float sum_hi = (xh.x + xh.y) + (xh.z + xh.w);
+      acc[t] += d_lo * dot_lo - o_lo * sum_lo;
+      acc[t] += d_hi * dot_hi - o_hi * sum_hi;
+    }
+  }
+}
+
+// Q8_0: 32 int8 codes and one fp16 scale per 34-byte block; lane l takes value l
+// of every block (gguf_dot::DotQ8_0, gguf_dot.hpp:31-69).
+template <int M>
+__device__ __forceinline__ void RowQ8_0(const uint8_t* __restrict__ row, int cols,
+                                        const float* __restrict__ x, int lane,
+                                        float (&acc)[M]) {
+  const int blocks = cols / kQ8Block;
+  for (int b = 0; b < blocks; ++b) {
+    const uint8_t* block = row + b * kQ8Bytes;
+    const float d = HalfBitsToFloat(__ldg(reinterpret_cast<const uint16_t*>(block)));
+    const float w = d * static_cast<float>(static_cast<int>(static_cast<int8_t>(__ldg(block + 2 + lane))));
+#pragma unroll
+    for (int t = 0; t < M; ++t) {
+      acc[t] = fmaf(w, __ldg(x + static_cast<size_t>(t) * cols + b * kQ8Block + lane), acc[t]);
+    }
+  }
+}
+
 template <int M>
 __device__ __forceinline__ void RowF32(const uint8_t* __restrict__ row, int cols,
                                        const float* __restrict__ x, int lane,
@@ -148,6 +211,10 @@ GemvRows(const __grid_constant__ GemvArgs args) {
     RowQ4K<M>(data, args.cols, x, lane, acc);
   } else if (part.type == GUFO_CUDA_Q6_K) {
     RowQ6K<M>(data, args.cols, x, lane, acc);
+  } else if (part.type == GUFO_CUDA_Q5_K) {
+    RowQ5K<M>(data, args.cols, x, lane, acc);
+  } else if (part.type == GUFO_CUDA_Q8_0) {
+    RowQ8_0<M>(data, args.cols, x, lane, acc);
   } else {
     RowF32<M>(data, args.cols, x, lane, acc);
   }
@@ -387,6 +454,9 @@ int BuildGemvArgs(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
     if (parts[p].first < 0 || parts[p].rows <= 0 ||
         parts[p].first + parts[p].rows > m->rows) {
       return Fail(GUFO_CUDA_SHAPE, "matmul: row range outside the matrix");
+    }
+    if (m->type == GUFO_CUDA_F16 || m->type == GUFO_CUDA_BF16) {
+      return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "matmul: F16 / BF16 rows are dequantized only, not multiplied");
     }
     if (p == 0) {
       cols = m->cols;

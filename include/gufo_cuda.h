@@ -47,8 +47,12 @@ typedef enum gufo_cuda_status {
  * (src/core/gguf.hpp:16-24). */
 enum {
   GUFO_CUDA_F32 = 0,
+  GUFO_CUDA_F16 = 1,   /* dequantization only (embeddings) */
+  GUFO_CUDA_Q8_0 = 8,
   GUFO_CUDA_Q4_K = 12,
-  GUFO_CUDA_Q6_K = 14
+  GUFO_CUDA_Q5_K = 13,
+  GUFO_CUDA_Q6_K = 14,
+  GUFO_CUDA_BF16 = 30  /* dequantization only */
 };
 
 typedef struct gufo_cuda_ctx gufo_cuda_ctx;
@@ -110,7 +114,11 @@ int gufo_cuda_memset_zero(gufo_cuda_ctx* ctx, void* device_ptr, size_t bytes);
  * host bytes are not referenced after the call. `cols` must be a whole number
  * of blocks of `ggml_type` (quant::RowBytes, src/core/quant.cpp:221-227).
  * Types: Q4_K, Q6_K and F32 (the alpha/beta and router rows,
- * src/models/qwen35/gguf_projections.cpp:126-131,162-170). */
+ * src/models/qwen35/gguf_projections.cpp:126-131,162-170) on every path; Q8_0
+ * and Q5_K (the other row formats of real UD-Q4_K_XL files,
+ * src/models/qwen35/gguf_dot.hpp:31-69,190-193) for products on the general
+ * kernel and dequantization; F16 and BF16 for dequantization only
+ * (src/core/quant.cpp:221-260). */
 int gufo_cuda_matrix_upload(gufo_cuda_ctx* ctx, int ggml_type,
                             const void* host_bytes, int64_t rows, int64_t cols,
                             gufo_cuda_matrix* out);

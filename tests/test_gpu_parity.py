@@ -564,3 +564,61 @@ def test_reference_decoder_with_cuda_adapter(tmp_path, tag, kwargs, seed):
     run = subprocess.run([binary, str(path), "6"], capture_output=True, text=True, timeout=300)
     assert run.returncode == 0, run.stdout + run.stderr
     assert "PASS" in run.stdout
+
+
+# ---- the other row formats of real files: Q8_0, Q5_K (products and dequantization), F16, BF16 ----
+
+@pytest.mark.parametrize("name,ggml_type", [("Q5_K", Q.GGML_Q5_K), ("Q8_0", Q.GGML_Q8_0), ("BF16", Q.GGML_BF16)])
+def test_dequantize_other_reference_fixtures_bit_exact(ctx, golden, name, ggml_type):
+    raw = np.fromfile(golden.path("quant", name + ".bin"), dtype=np.uint8)
+    want = np.fromfile(golden.path("quant", name + ".f32"), dtype=np.float32)
+    m = ctx.matrix_upload(ggml_type, raw, 1, want.size)
+    got = ctx.dequantize(m, 0, 1, want.size)
+    assert np.array_equal(bits(got.ravel()), bits(want))
+    ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("ggml_type", [Q.GGML_Q5_K, Q.GGML_Q8_0, Q.GGML_F16, Q.GGML_BF16])
+def test_dequantize_other_types_match_oracle_bit_exact(ctx, oracle, ggml_type):
+    rows, cols = 19, 768
+    if ggml_type in (Q.GGML_F16, Q.GGML_BF16):
+        # Every 16-bit pattern once (NaN payloads included: compared as bits).
+        raw = np.arange(65536, dtype=np.uint16).view(np.uint8)
+        rows, cols = 64, 1024
+    else:
+        raw = Q.random_blocks(ggml_type, rows, cols, seed=23).numpy()
+    m = ctx.matrix_upload(ggml_type, raw, rows, cols)
+    got = ctx.dequantize(m, 0, rows, cols)
+    want = oracle.dequantize(ggml_type, raw, rows * cols).reshape(rows, cols)
+    assert np.array_equal(bits(got), bits(want))
+    ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("ggml_type", [Q.GGML_Q5_K, Q.GGML_Q8_0])
+@pytest.mark.parametrize("tokens", [1, 3, 9])
+def test_gemv_other_types_match_oracle(ctx, oracle, ggml_type, tokens):
+    """Q5_K and Q8_0 rows on the general kernel against the oracle's fused row dots, alone and
+    stacked beside a Q4_K part."""
+    rows, cols = 77, 1024
+    raw = Q.random_blocks(ggml_type, rows, cols, seed=24).numpy()
+    other = Q.random_blocks(Q.GGML_Q4_K, 40, cols, seed=25).numpy()
+    x = G.normal(26 + tokens, tokens, cols)
+    m = ctx.matrix_upload(ggml_type, raw, rows, cols)
+    mo = ctx.matrix_upload(Q.GGML_Q4_K, other, 40, cols)
+    got = ctx.matmul([(mo, 0, 40), (m, 5, 70)], x, tokens, 110)
+    want = oracle.matmul([(other, Q.GGML_Q4_K, 0, 40), (raw, ggml_type, 5, 70)], cols, x)
+    exact = oracle.matmul([(other, Q.GGML_Q4_K, 0, 40), (raw, ggml_type, 5, 70)], cols, x, exact=True)
+    assert rel_l2(got, want) <= 1e-5
+    assert rel_l2(got, exact) <= 1e-5
+    ctx.matrix_free(m)
+    ctx.matrix_free(mo)
+
+
+def test_half_rows_are_not_multiplied(ctx):
+    from gufo_npu_b200._capi import GufoCudaError
+    raw = np.zeros(8 * 256 * 2, dtype=np.uint8)
+    m = ctx.matrix_upload(Q.GGML_F16, raw, 8, 256)
+    with pytest.raises(GufoCudaError) as e:
+        ctx.matmul([(m, 0, 8)], np.zeros((1, 256), dtype=np.float32), 1, 8)
+    assert e.value.status == 3
+    ctx.matrix_free(m)
