@@ -301,6 +301,45 @@ def test_delta_rule_matches_oracle_over_steps(ctx, oracle, hk, hv, dk):
     assert checked >= nseq
 
 
+def test_delta_rule_config3_context_lengths(ctx, oracle):
+    """Config 3 as BASELINE states it: 16 heads of 128 x 128, 8 sequences whose states have seen
+    a seeded draw of 1 to 4096 steps each. All heads run on the device; two heads of every
+    sequence are followed on the CPU and compared after the first, a middle and the last step."""
+    dev = torch.device("cuda:0")
+    hk = hv = 16
+    dk, nseq = 128, 8
+    lengths = np.random.default_rng(33).integers(1, 4097, size=nseq)
+    watched = (0, 9)
+    gen = torch.Generator(device=dev).manual_seed(34)
+    states = torch.zeros(nseq, hv, dk, dk, device=dev)
+    y = torch.empty(nseq, hv, dk, device=dev)
+    ref = np.zeros((nseq, len(watched), dk, dk), dtype=np.float32)
+    worst = 0.0
+    for step in range(int(lengths.max())):
+        live = [s for s in range(nseq) if step < lengths[s]]
+        n = len(live)
+        q = torch.nn.functional.normalize(torch.randn(n, hk, dk, device=dev, generator=gen), dim=-1)
+        k = torch.nn.functional.normalize(torch.randn(n, hk, dk, device=dev, generator=gen), dim=-1)
+        v = torch.randn(n, hv, dk, device=dev, generator=gen)
+        beta = torch.sigmoid(torch.randn(n, hv, device=dev, generator=gen))
+        decay = torch.exp(-torch.nn.functional.softplus(torch.randn(n, hv, device=dev, generator=gen)))
+        seqs = [{"q": q[i], "k": k[i], "v": v[i], "decay": decay[i], "beta": beta[i], "y": y[s], "state": states[s]}
+                for i, s in enumerate(live)]
+        torch.cuda.synchronize()
+        ctx.delta_rule_device(seqs, hk, hv, dk)
+        ctx.synchronize()
+        qc, kc, vc, bc, dc = (t.cpu().numpy() for t in (q, k, v, beta, decay))
+        for i, s in enumerate(live):
+            for j, h in enumerate(watched):
+                ref[s, j], want_y = oracle.delta_rule(ref[s, j], kc[i, h], qc[i, h], vc[i, h], float(dc[i, h]),
+                                                      float(bc[i, h]))
+                if step in (0, lengths[s] // 2, lengths[s] - 1):
+                    err = max(rel_l2(y[s, h].cpu().numpy(), want_y), rel_l2(states[s, h].cpu().numpy(), ref[s, j]))
+                    worst = max(worst, err)
+                    assert err <= DELTA_TOL, (s, h, step, err)
+    assert worst > 0.0
+
+
 def test_delta_rule_alternate_output_leaves_state(ctx, oracle):
     dev = torch.device("cuda:0")
     hk = hv = 4
