@@ -49,7 +49,7 @@ struct CudaProjections::Layer {
   Rows gate_exps, up_exps, down_exps;
 };
 
-CudaProjections::Rows CudaProjections::Upload(const TensorInfo& t) {
+CudaProjections::Rows CudaProjections::Upload(const TensorInfo& t) const {
   gufo_cuda_matrix handle = 0;
   Check(ctx_, gufo_cuda_matrix_upload(ctx_, static_cast<int>(t.type), t.data,
                                       static_cast<long long>(t.Rows()),
@@ -113,6 +113,37 @@ CudaProjections::CudaProjections(const gguf::File& file, int device)
 }
 
 CudaProjections::~CudaProjections() { gufo_cuda_ctx_destroy(ctx_); }
+
+CudaProjections::LayerHandles CudaProjections::Handles(int layer) const {
+  const Layer& l = layers_.at(static_cast<std::size_t>(layer));
+  LayerHandles h;
+  const std::vector<Rows>& in = l.linear_in.empty() ? l.attention_in : l.linear_in;
+  for (std::size_t i = 0; i < in.size() && i < 4; ++i) {
+    h.in[i] = in[i].w;
+  }
+  h.out = l.mixer_out.at(0).w;
+  h.ffn_gate = l.ffn_in.at(0).w;
+  h.ffn_up = l.ffn_in.at(1).w;
+  h.ffn_down = l.ffn_down.at(0).w;
+  if (!l.router.empty()) {
+    h.router[0] = l.router.at(0).w;
+    h.router[1] = l.router.at(1).w;
+    h.gate_exps = l.gate_exps.w;
+    h.up_exps = l.up_exps.w;
+    h.down_exps = l.down_exps.w;
+  }
+  return h;
+}
+
+long long CudaProjections::EmbeddingHandle(const gguf::File& file) const {
+  if (config_.tied_embeddings) {
+    return lm_head_.w;
+  }
+  if (embedding_.w == 0) {
+    embedding_ = Upload(file.Tensor("token_embd.weight"));
+  }
+  return embedding_.w;
+}
 
 void CudaProjections::MatMul(const std::vector<Rows>& parts, const float* x,
                              int tokens, float* y) const {

@@ -4,7 +4,8 @@
 // GgufProjections (fp32) and once with the CUDA adapter
 // (integration/src_cuda/cuda_projections.cpp over libgufo_cuda.so) plugged in
 // behind the same Projections interface, and compares the logits of every
-// step. Built by oracle/Makefile from the reference's sources where they lie;
+// step; a third run takes the same tokens through the device-resident
+// cuda::Decoder (integration/src_cuda/cuda_decoder.cpp). Built by oracle/Makefile from the reference's sources where they lie;
 // the mixers, norms and sampling stay the reference's CPU code in both runs.
 //
 //   adapter_parity <model.gguf> <tokens>     exit 0 when every step agrees
@@ -14,6 +15,7 @@
 #include <vector>
 
 #include "core/gguf.hpp"
+#include "cuda/cuda_decoder.hpp"
 #include "cuda/cuda_projections.hpp"
 #include "models/qwen35/decoder.hpp"
 #include "models/qwen35/gguf_projections.hpp"
@@ -30,6 +32,7 @@ int main(int argc, char** argv) {
   gufo_npu::cuda::CudaProjections gpu(*file, 0);
   qwen35::Decoder a(*file, cpu);
   qwen35::Decoder b(*file, gpu);
+  gufo_npu::cuda::Decoder resident(*file, gpu, steps + 8);
   auto sa = a.NewState();
   auto sb = b.NewState();
   const int vocab = a.config().vocab;
@@ -50,6 +53,21 @@ int main(int argc, char** argv) {
     worst = err > worst ? err : worst;
     std::printf("step %d: logits rel-L2 %.3e argmax %d/%d\n", s, err, arg_got, arg_want);
     if (err > 2e-3 || arg_want != arg_got) {
+      std::printf("FAIL\n");
+      return 1;
+    }
+    // The same token through the device-resident decoder.
+    const std::vector<float>& on_device = resident.Step(token);
+    double num2 = 0;
+    int arg_device = 0;
+    for (int i = 0; i < vocab; ++i) {
+      num2 += (double(on_device[i]) - want[i]) * (double(on_device[i]) - want[i]);
+      if (on_device[i] > on_device[arg_device]) arg_device = i;
+    }
+    const double err2 = std::sqrt(num2 / den);
+    worst = err2 > worst ? err2 : worst;
+    std::printf("step %d: resident decoder rel-L2 %.3e argmax %d/%d\n", s, err2, arg_device, arg_want);
+    if (err2 > 2e-3 || arg_want != arg_device || resident.position() != s + 1) {
       std::printf("FAIL\n");
       return 1;
     }
