@@ -1,3 +1,4 @@
+#include "cuda/cuda_decoder.hpp"
 #include "cuda/cuda_projections.hpp"
 
 #include <stdexcept>
@@ -20,6 +21,16 @@ void CudaProjections::ApplyExpert(qwen35::Stage, int, int, const float*, int, fl
   throw std::runtime_error("gufo-npu was built without CUDA");
 }
 void CudaProjections::MatMul(const std::vector<Rows>&, const float*, int, float*) const {}
-CudaProjections::Rows CudaProjections::Upload(const gguf::TensorInfo&) { return {}; }
+CudaProjections::Rows CudaProjections::Upload(const gguf::TensorInfo&) const { return {}; }
+CudaProjections::LayerHandles CudaProjections::Handles(int) const { return {}; }
+long long CudaProjections::EmbeddingHandle(const gguf::File&) const { return 0; }
+
+Decoder::Decoder(const gguf::File&, const CudaProjections& projections, int) : projections_(projections) {
+  throw std::runtime_error("gufo-npu was built without CUDA");
+}
+Decoder::~Decoder() = default;
+const std::vector<float>& Decoder::Step(int) { throw std::runtime_error("gufo-npu was built without CUDA"); }
+void Decoder::Reset() { throw std::runtime_error("gufo-npu was built without CUDA"); }
+int Decoder::position() const { return 0; }
 
 }  // namespace gufo_npu::cuda
