@@ -189,7 +189,7 @@ def test_empty_and_bad_products(ctx):
             ctx.matmul(bad, x, 1, 8)
         assert e.value.status == status
     with pytest.raises(GufoCudaError) as e:
-        ctx.matrix_upload(13, raw, 8, 256)          # Q5_K: not run by this backend
+        ctx.matrix_upload(10, raw, 8, 256)          # Q2_K: not run by this backend
     assert e.value.status == 3
     with pytest.raises(GufoCudaError) as e:
         ctx.matrix_upload(Q.GGML_Q4_K, raw, 8, 250)
