@@ -296,10 +296,10 @@ def run_ours(args):
     total_bytes = weight_bytes(tensors)
     ctx = Context(local, stream.cuda_stream)
     proj = CudaProjections(ctx, cfg, tensors)
-    dec = CudaDecoder(proj, tensors, max_positions=max(4096, 4 * (args.steps + args.warmup) + 64), use_graph=True)
+    dec = CudaDecoder(proj, tensors, max_positions=max(4096, 6 * (args.steps + args.warmup) + 64), use_graph=True)
     peak, peak_kind = measured_peaks()
     rng = np.random.default_rng(7)
-    tokens = rng.integers(0, cfg.vocab, size=4 * (args.steps + args.warmup) + 8).tolist()
+    tokens = rng.integers(0, cfg.vocab, size=6 * (args.steps + args.warmup) + 64).tolist()
     cursor = iter(tokens)
     logits_host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
 
@@ -316,6 +316,16 @@ def run_ours(args):
             dec.Step(next(cursor), logits_host.numpy())
         ms_e2e = time_on_stream(lambda i: dec.Step(next(cursor), logits_host.numpy()), args.steps)
         probes = roofline_probes(ctx, proj, cfg, stream, peak)
+        # Two-token steps (a token and a draft, the weights read once for both), drafts kept
+        # or rolled back: what speculative decoding pays per step on this path.
+        pair_ms = {}
+        for keep in (True, False):
+            def pair_step(i, keep=keep):
+                dec.step_tokens_device([next(cursor), next(cursor)])
+                dec.Resolve(keep)
+            for _ in range(3):
+                pair_step(0)
+            pair_ms[keep] = time_on_stream(pair_step, max(args.steps // 2, 8))
     assert np.isfinite(logits_host.numpy()).all()
     host = {k: synth.Tensor(t.shape, t.ggml_type, t.data.cpu()) for k, t in tensors.items()}
     del tensors
@@ -338,6 +348,10 @@ def run_ours(args):
                      "traffic_source": "ncu capture of the 131072-row case scaled by rows", "peak_kind": peak_kind, "kernel": lm["kernel"],
                      "shape": lm["shape"], "bytes_per_launch": lm["bytes"], "us_per_launch": lm["us"]},
         "roofline_more": {k: v for k, v in probes.items() if k != "lm_head"},
+        "pair_step": {"ms_kept": pair_ms[True], "ms_rolled_back": pair_ms[False],
+                      "tok_s_all_kept": 2e3 / pair_ms[True], "tok_s_all_rolled_back": 1e3 / pair_ms[False],
+                      "note": "NpuDecoder::Step(tokens, 2) + Resolve through gufo_cuda_decoder_step_tokens; "
+                              "not the headline metric"},
         "cpu_baseline": base,
         "clocks": clocks.summary(),
     }

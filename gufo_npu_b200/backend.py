@@ -596,6 +596,37 @@ class CudaDecoder:
         self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step(self.handle, token, C.c_void_p(_ptr(logits))))
         return logits
 
+    def StepTokens(self, tokens: Sequence[int], logits: bool = True) -> Optional[np.ndarray]:
+        """NpuDecoder::Step(tokens, count, state, logits) (src/models/qwen35_2b/npu_decoder.hpp:57-65):
+        one or two tokens from the current position in one pass; returns [count, vocab] logits, or
+        None with `logits` off (prompt passes). After two tokens the second is a draft until
+        `Resolve`."""
+        count = len(tokens)
+        ids = (C.c_int * max(count, 1))(*tokens)
+        out = np.empty((count, self.config.vocab), dtype=np.float32) if logits else None
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step_tokens(
+            self.handle, ids, count, int(logits), C.c_void_p(_ptr(out)) if logits else None))
+        return out
+
+    def step_tokens_device(self, tokens: Sequence[int]) -> int:
+        """`StepTokens` leaving the [count, vocab] logits on the device; returns their address."""
+        ids = (C.c_int * len(tokens))(*tokens)
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step_tokens(self.handle, ids, len(tokens), 1, None))
+        out = C.c_void_p()
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_logits_device(self.handle, C.byref(out)))
+        return int(out.value)
+
+    def Resolve(self, keep_second: bool) -> None:
+        """NpuDecoder::Resolve (src/models/qwen35_2b/npu_decoder.cpp:630-650): keeps the draft of
+        the last two-token step, or rolls the decoder back to just after its first token."""
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_resolve(self.handle, int(keep_second)))
+
+    def hidden(self, t: int = 0) -> np.ndarray:
+        """NpuDecoder::hidden(t): the final residual (before output_norm) of token t of the last step."""
+        out = C.c_void_p()
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_hidden_device(self.handle, t, C.byref(out)))
+        return self.ctx.download(int(out.value), self.config.hidden)
+
     def step_device(self, token: int) -> int:
         """Runs `token` leaving the logits on the device; returns their device address."""
         self.ctx._check(self.ctx.lib.gufo_cuda_decoder_step(self.handle, token, None))

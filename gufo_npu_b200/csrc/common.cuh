@@ -93,7 +93,7 @@ int CudaFail(cudaError_t e, const char* what);
 // weight read.
 enum FastPrologue {
   kPrologueImage = 0,    // a fixed-point image staged earlier (any token count)
-  kProloguePlain = 1,    // x fp32 [cols], staged by every thread block
+  kProloguePlain = 1,    // x fp32 rows, staged by every thread block
   kPrologueResNorm = 2,  // x = RMS(h_in + delta) * norm_w; block 0 also writes h_out and normed_out
   kPrologueSwiGlu = 3,   // x[i] = silu(x_in[i]) * x_in[cols + i]
 };
@@ -115,17 +115,17 @@ struct FastGemvArgs {
   int row_bytes;
   float* y;              // [tokens][y_stride]
   int y_stride;
-  int tokens;            // fused prologues: 1
+  int tokens;            // rows of x and y (grouped launches: 1)
   int prologue;
   const uint8_t* image;  // kPrologueImage
-  const float* x;        // kProloguePlain: [cols]; kPrologueSwiGlu: [2 * cols]
-  const float* h_in;     // kPrologueResNorm: the residual stream [cols] ...
-  const float* delta;    //   ... plus this (may be null)
+  const float* x;        // kProloguePlain: [tokens][cols]; kPrologueSwiGlu: [tokens][2 * cols]
+  const float* h_in;     // kPrologueResNorm: the residual stream [tokens][cols] ...
+  const float* delta;    //   ... plus this, [tokens][cols] (may be null)
   const float* norm_w;
   float eps;
   float* h_out;          //   h_in + delta, written by block 0 (must not alias h_in)
-  float* normed_out;     //   the normed vector, written by block 0 (may be null)
-  int* advance;          //   incremented once by block 0 (may be null)
+  float* normed_out;     //   the normed rows, written by block 0 (may be null)
+  int* advance;          //   incremented by `tokens` by block 0 (may be null)
   // Thread blocks per 16-row tile (a cluster): block r of a cluster takes the
   // slabs r, r + ksplit, ... and the partial sums meet in block 0's shared
   // memory. Set by the launcher for matrices with few rows.

@@ -8,6 +8,10 @@
 // logits). The position lives in device memory so that the whole step can be
 // replayed as a CUDA graph: two graphs, because the DeltaNet conv window
 // alternates between two buffers from step to step.
+//
+// A step can also take two tokens, the weights read once for both, the second
+// a draft that Resolve keeps or rolls back (qwen35_2b::NpuDecoder::Step and
+// Resolve, src/models/qwen35_2b/npu_decoder.hpp:57-68).
 #include <cuda_fp16.h>
 
 #include <algorithm>
@@ -24,6 +28,7 @@ constexpr int kSmallThreads = 256;
 constexpr int kAttnSplits = 8;      // position slices per KV head
 constexpr int kMaxGroup = 8;        // query heads per KV head
 constexpr int kMaxPerLane = 8;      // head_dim / 32
+constexpr int kStepTokens = 2;      // tokens of a pair step
 
 __device__ __forceinline__ float SigmoidF(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float SiluF(float x) { return x * SigmoidF(x); }
@@ -157,6 +162,7 @@ struct AttnArgs {
   float* queries;           // [heads][hd]
   float* partials;          // [kv_heads][splits][group][hd + 2]
   float* ctx;               // [heads][hd]
+  int offset = 0;           // the token sits at *position + offset
 };
 
 // q/k RMSNorm and RoPE; appends k and v to the cache in fp16
@@ -169,7 +175,7 @@ AttnPrepKernel(const __grid_constant__ AttnArgs a) {
   GridDependencyWait();
   const int hd = a.head_dim;
   const int half = a.rope_dim / 2;
-  const int pos = *a.position;
+  const int pos = *a.position + a.offset;
   const int head = blockIdx.x;
   const bool is_query = head < a.heads;
   const int kh = head - a.heads;
@@ -220,7 +226,7 @@ AttnSliceKernel(const __grid_constant__ AttnArgs a) {
   const int per = hd / 32;
   const int group = a.heads / a.kv_heads;
   const int kh = blockIdx.y;
-  const int length = *a.position + 1;
+  const int length = *a.position + a.offset + 1;
   const int slice = (length + kAttnSplits - 1) / kAttnSplits;
   const int begin = blockIdx.x * slice;
   const int end = min(length, begin + slice);
@@ -465,7 +471,9 @@ struct gufo_cuda_decoder {
     float* q_norm = nullptr;
     float* k_norm = nullptr;
     float* conv[2] = {nullptr, nullptr};
+    float* conv_saved = nullptr;       // the window after the first token of a pair
     float* ssm = nullptr;
+    float* ssm_spec = nullptr;         // the state after the second token of a pair
     __half* keys = nullptr;
     __half* values = nullptr;
   };
@@ -483,11 +491,18 @@ struct gufo_cuda_decoder {
   float *expert_ffn = nullptr, *expert_act = nullptr, *expert_out = nullptr;
   int* chosen = nullptr;
   int* position_dev = nullptr;
-  int* token_dev = nullptr;
-  int* token_pinned = nullptr;
+  int* token_dev = nullptr;      // [kStepTokens]
+  int* token_pinned = nullptr;   // [kStepTokens] tokens, then the position (Resolve)
   int position = 0;
+  int conv_cur = 0;              // which of a layer's conv windows is current
+  int pending = 0;               // tokens of the last step that await Resolve (0 or 2)
+  const float* final_h = nullptr;   // final residual rows of the last step (before output_norm)
+  // Every DeltaNet layer's windows and states sit in one allocation per kind, so
+  // that Resolve moves all layers with one copy.
+  float* conv_all[3] = {nullptr, nullptr, nullptr};   // windows 0, 1, saved
+  float* ssm_all[2] = {nullptr, nullptr};             // states, draft states
+  size_t conv_all_bytes = 0, ssm_all_bytes = 0;
   int steps = 0;
-  int64_t kernels_per_step = 0;
   // Per-stage device time (the reference keeps the same kind of split,
   // NpuDecoder::Timeline, src/models/qwen35_2b/npu_decoder.hpp:121-154).
   bool timeline = false;
@@ -495,7 +510,12 @@ struct gufo_cuda_decoder {
   std::vector<int> mark_kind;
   double stage_ms[GUFO_CUDA_TIMELINE_KINDS] = {};
   int timeline_steps = 0;
-  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  // One graph per (tokens - 1, current conv window, with logits); each kind of
+  // step runs eagerly twice first (that sizes staging buffers and sets kernel
+  // attributes, which a capture cannot).
+  cudaGraphExec_t graph[2][2][2] = {};
+  int64_t graph_kernels[2][2][2] = {};
+  int eager_runs[2][2] = {};
   std::vector<void*> owned;   // every device allocation, for destroy
 
   int in_width(const Layer& l) const { return l.in.total_rows; }
@@ -551,10 +571,12 @@ int Stack(gufo_cuda_ctx* ctx, const gufo_cuda_matrix* handles, const int64_t* wa
     }                                 \
   } while (0)
 
-// Where a product's input comes from (FastPrologue, common.cuh).
+// Where a product's input comes from (FastPrologue, common.cuh). With several
+// tokens every pointer is the first of `tokens` rows: residual, pending add and
+// plain x `cols` floats apart, a SwiGLU input 2 * cols apart.
 struct Input {
   int prologue;
-  const float* x = nullptr;        // plain: the vector; SwiGLU: [gate | up]
+  const float* x = nullptr;        // plain: the rows; SwiGLU: [gate | up] rows
   const float* h_in = nullptr;     // residual + norm
   const float* delta = nullptr;
   const float* norm_w = nullptr;
@@ -562,10 +584,11 @@ struct Input {
   int* advance = nullptr;
 };
 
-// One stage's product with its input fused into the GEMV kernels where every
-// part allows it; otherwise the input is materialised by the small kernels
-// first. `scratch` holds the materialised / normed vector.
-int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y) {
+// One stage's product for `tokens` rows with its input fused into the GEMV
+// kernels where every part allows it; otherwise the input is materialised by the
+// small kernels first. `scratch` holds the materialised / normed rows.
+int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y,
+                 int tokens) {
   gufo_cuda_ctx* ctx = d->ctx;
   const gufo_cuda_decoder_config& c = d->c;
   const dim3 block(kSmallThreads);
@@ -574,32 +597,38 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
   for (int p = 0; p < stage.nparts; ++p) {
     const int type = stage.parts[p].type;
     if (type == GUFO_CUDA_Q4_K) {
-      fused = fused && Q4KFastFits(stage.cols, 1);
+      fused = fused && Q4KFastFits(stage.cols, tokens);
       ++fast_parts;
     } else if (type == GUFO_CUDA_Q6_K) {
-      fused = fused && Q6KFastFits(stage.cols, 1);
+      fused = fused && Q6KFastFits(stage.cols, tokens);
       ++fast_parts;
     } else if (in.prologue == kPrologueSwiGlu) {
       fused = false;   // other rows would need the activated vector in memory
     }
   }
+  const size_t cols = static_cast<size_t>(stage.cols);
   if (!fused || fast_parts == 0) {
     const float* x = in.x;
     if (in.prologue == kPrologueResNorm) {
-      GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, dim3(1), block, 0, ctx->stream, 1, in.h_in, in.h_out, in.delta,
-                                     in.norm_w, c.rms_eps, stage.cols, scratch, in.advance));
-      ctx->launches.fetch_add(1);
+      for (int t = 0; t < tokens; ++t) {
+        GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, dim3(1), block, 0, ctx->stream, 1, in.h_in + t * cols,
+                                       in.h_out + t * cols, in.delta != nullptr ? in.delta + t * cols : nullptr,
+                                       in.norm_w, c.rms_eps, stage.cols, scratch + t * cols, in.advance));
+      }
+      ctx->launches.fetch_add(tokens);
       x = scratch;
     } else if (in.prologue == kPrologueSwiGlu) {
-      GUFO_CUDA_TRY(LaunchOverlapped(SwiGluKernel, dim3((stage.cols + kSmallThreads - 1) / kSmallThreads), block, 0,
-                                     ctx->stream, 1, in.x, stage.cols, scratch));
-      ctx->launches.fetch_add(1);
+      for (int t = 0; t < tokens; ++t) {
+        GUFO_CUDA_TRY(LaunchOverlapped(SwiGluKernel, dim3((stage.cols + kSmallThreads - 1) / kSmallThreads), block, 0,
+                                       ctx->stream, 1, in.x + t * 2 * cols, stage.cols, scratch + t * cols));
+      }
+      ctx->launches.fetch_add(tokens);
       x = scratch;
     }
     GemvArgs args = stage;
     args.x = x;
     args.y = y;
-    return LaunchGemv(ctx, args, 1);
+    return LaunchGemv(ctx, args, tokens);
   }
   bool first = true;
   for (int type : {GUFO_CUDA_Q4_K, GUFO_CUDA_Q6_K}) {
@@ -607,7 +636,7 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
     args.cols = stage.cols;
     args.y = y;
     args.y_stride = stage.y_stride;
-    args.tokens = 1;
+    args.tokens = tokens;
     args.prologue = in.prologue;
     args.x = in.x;
     args.h_in = in.h_in;
@@ -631,7 +660,7 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
     first = false;
     GUFO_STEP_TRY(type == GUFO_CUDA_Q4_K ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args));
   }
-  // Rows of other formats (the F32 alpha / beta rows) read the vector block 0 wrote.
+  // Rows of other formats (the F32 alpha / beta rows) read the rows block 0 wrote.
   GemvArgs rest = stage;
   rest.nparts = 0;
   rest.total_rows = 0;
@@ -644,7 +673,7 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
   if (rest.nparts > 0) {
     rest.x = in.prologue == kPrologueResNorm ? scratch : in.x;
     rest.y = y;
-    GUFO_STEP_TRY(LaunchGemv(ctx, rest, 1));
+    GUFO_STEP_TRY(LaunchGemv(ctx, rest, tokens));
   }
   return GUFO_CUDA_OK;
 }
@@ -665,16 +694,26 @@ void Mark(gufo_cuda_decoder* d, int kind) {
   d->mark_kind.push_back(kind);
 }
 
-int EnqueueStep(gufo_cuda_decoder* d, int parity) {
+// `tokens` (1 or 2) rows from the current position in one pass: every product
+// runs once for all rows, the mixers token by token (the second sees the
+// first's cache row and state). With two tokens the DeltaNet layers leave the
+// state after the first token in ssm and the window after it in conv_saved; the
+// second token's go to ssm_spec and the other conv window (DeltaNetStep::Run,
+// src/models/qwen35_2b/deltanet.hpp:35-44). Token t's rows sit at t * width in
+// every activation buffer.
+int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) {
   gufo_cuda_ctx* ctx = d->ctx;
   const gufo_cuda_decoder_config& c = d->c;
   cudaStream_t st = ctx->stream;
   const dim3 one(1), block(kSmallThreads);
+  const size_t hidden = static_cast<size_t>(c.hidden);
   int cur = 0;   // which residual buffer is current
-  EmbedArgs embed{d->embed.data, d->embed.type, static_cast<int>(d->embed.row_bytes), c.hidden,
-                  d->token_dev, d->h[0]};
-  GUFO_CUDA_TRY(LaunchOverlapped(EmbedKernel, one, block, 0, st, 1, embed));
-  ctx->launches.fetch_add(1);
+  for (int t = 0; t < tokens; ++t) {
+    EmbedArgs embed{d->embed.data, d->embed.type, static_cast<int>(d->embed.row_bytes), c.hidden,
+                    d->token_dev + t, d->h[0] + t * hidden};
+    GUFO_CUDA_TRY(LaunchOverlapped(EmbedKernel, one, block, 0, st, 1, embed));
+  }
+  ctx->launches.fetch_add(tokens);
   Mark(d, -1);
   Mark(d, GUFO_CUDA_TIMELINE_EMBED);
   const float* pending = nullptr;   // projection output not yet added to the residual
@@ -685,50 +724,61 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
     norm1.delta = pending;
     norm1.norm_w = l.attn_norm;
     norm1.h_out = d->h[cur ^ 1];
-    GUFO_STEP_TRY(FusedProduct(d, l.in, norm1, d->normed, d->in));
+    GUFO_STEP_TRY(FusedProduct(d, l.in, norm1, d->normed, d->in, tokens));
     Mark(d, GUFO_CUDA_TIMELINE_IN);
     cur ^= 1;
-    if (l.attention) {
-      AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps,
-                 d->position_dev, d->in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values,
-                 d->queries, d->partials, d->mixed};
-      GUFO_STEP_TRY(EnqueueAttention(ctx, a));
-      Mark(d, GUFO_CUDA_TIMELINE_ATTENTION);
-    } else {
-      gufo_cuda_linear_seq seq{d->in, l.conv[parity], l.conv[parity ^ 1], l.ssm, nullptr, d->mixed};
-      gufo::DeltaNetGateRows gate_rows = l.gate_rows;
-      gate_rows.x = d->normed;
-      GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1, true,
-                                          gate_rows.alpha_w != nullptr ? &gate_rows : nullptr));
-      Mark(d, GUFO_CUDA_TIMELINE_DELTANET);
+    const size_t in_width = static_cast<size_t>(l.in.y_stride);
+    const size_t mixed_width = static_cast<size_t>(l.out.cols);
+    for (int t = 0; t < tokens; ++t) {
+      const float* in = d->in + t * in_width;
+      float* mixed = d->mixed + t * mixed_width;
+      if (l.attention) {
+        AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps,
+                   d->position_dev, in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values,
+                   d->queries, d->partials, mixed, t};
+        GUFO_STEP_TRY(EnqueueAttention(ctx, a));
+      } else {
+        // One token: window to window, state in place. Two: the first goes to
+        // conv_saved, the second from there to the other window and ssm_spec.
+        const bool last = t == tokens - 1;
+        const float* conv_from = t == 0 ? l.conv[parity] : l.conv_saved;
+        float* conv_to = last ? l.conv[parity ^ 1] : l.conv_saved;
+        gufo_cuda_linear_seq seq{in, conv_from, conv_to, l.ssm, t > 0 ? l.ssm_spec : nullptr, mixed};
+        gufo::DeltaNetGateRows gate_rows = l.gate_rows;
+        gate_rows.x = d->normed + t * hidden;
+        // A second token reads the state the launch before it wrote: no early loads.
+        GUFO_STEP_TRY(EnqueueDeltaNetLinear(ctx, l.linear, &seq, 1, t == 0,
+                                            gate_rows.alpha_w != nullptr ? &gate_rows : nullptr));
+      }
     }
+    Mark(d, l.attention ? GUFO_CUDA_TIMELINE_ATTENTION : GUFO_CUDA_TIMELINE_DELTANET);
     Input plain{kProloguePlain};
     plain.x = d->mixed;
-    GUFO_STEP_TRY(FusedProduct(d, l.out, plain, d->act, d->out));
+    GUFO_STEP_TRY(FusedProduct(d, l.out, plain, d->act, d->out, tokens));
     Mark(d, GUFO_CUDA_TIMELINE_OUT);
     Input norm2{kPrologueResNorm};
     norm2.h_in = d->h[cur];
     norm2.delta = d->out;
     norm2.norm_w = l.post_norm;
     norm2.h_out = d->h[cur ^ 1];
-    GUFO_STEP_TRY(FusedProduct(d, l.ffn_in, norm2, d->normed, d->ffn));
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_in, norm2, d->normed, d->ffn, tokens));
     Mark(d, GUFO_CUDA_TIMELINE_FFN_IN);
     cur ^= 1;
     Input swiglu{kPrologueSwiGlu};
     swiglu.x = d->ffn;
-    GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, swiglu, d->act, d->out));
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, swiglu, d->act, d->out, tokens));
     if (c.experts > 0) {
       // Decoder::MoeFfn (decoder.cpp:535-557): d->out holds the shared
       // expert's output, d->normed the layer's normed input.
       GemvArgs router = l.router;
       router.x = d->normed;
       router.y = d->router;
-      GUFO_STEP_TRY(LaunchGemv(ctx, router, 1));
-      GUFO_STEP_TRY(EnqueueRoute(ctx, d->router, c.experts + 1, 1, c.experts, c.experts_used, d->chosen,
+      GUFO_STEP_TRY(LaunchGemv(ctx, router, tokens));
+      GUFO_STEP_TRY(EnqueueRoute(ctx, d->router, c.experts + 1, tokens, c.experts, c.experts_used, d->chosen,
                                  d->route_weights, d->shared_scale));
-      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, c.experts_used, d->normed, 0, 1, d->expert_ffn,
-                                     d->expert_act, d->expert_out));
-      GUFO_STEP_TRY(EnqueueMoeCombine(ctx, d->out, d->shared_scale, d->route_weights, d->expert_out, 1,
+      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, tokens * c.experts_used, d->normed, c.hidden,
+                                     c.experts_used, d->expert_ffn, d->expert_act, d->expert_out));
+      GUFO_STEP_TRY(EnqueueMoeCombine(ctx, d->out, d->shared_scale, d->route_weights, d->expert_out, tokens,
                                       c.experts_used, c.hidden, d->out));
     }
     Mark(d, GUFO_CUDA_TIMELINE_FFN_DOWN);
@@ -740,7 +790,18 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity) {
   last.norm_w = d->output_norm;
   last.h_out = d->h[cur ^ 1];
   last.advance = d->position_dev;
-  GUFO_STEP_TRY(FusedProduct(d, d->lm_head, last, d->normed, d->logits));
+  d->final_h = last.h_out;
+  if (want_logits) {
+    GUFO_STEP_TRY(FusedProduct(d, d->lm_head, last, d->normed, d->logits, tokens));
+  } else {
+    // A prompt pass whose logits nobody reads: only the final residuals.
+    for (int t = 0; t < tokens; ++t) {
+      GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, one, block, 0, st, 1, last.h_in + t * hidden,
+                                     last.h_out + t * hidden, last.delta + t * hidden, last.norm_w, c.rms_eps,
+                                     c.hidden, d->normed + t * hidden, last.advance));
+    }
+    ctx->launches.fetch_add(tokens);
+  }
   Mark(d, GUFO_CUDA_TIMELINE_LM_HEAD);
   return GUFO_CUDA_OK;
 }
@@ -802,6 +863,7 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
     return fail(rc);
   }
   size_t in_max = 0;
+  int linear_layers = 0;
   d->layers.resize(c.layers);
   for (int il = 0; il < c.layers; ++il) {
     const gufo_cuda_layer_weights& w = weights->layers[il];
@@ -866,13 +928,7 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
           (rc = gufo::UploadVec(d, w.ssm_norm, c.linear_head_dim, &l.linear.ssm_norm, "ssm_norm")) != GUFO_CUDA_OK) {
         return fail(rc);
       }
-      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
-      const size_t ssm_bytes = static_cast<size_t>(value_dim) * c.linear_head_dim * 4;
-      if ((rc = gufo::Alloc(d, conv_bytes, reinterpret_cast<void**>(&l.conv[0]))) != GUFO_CUDA_OK ||
-          (rc = gufo::Alloc(d, conv_bytes, reinterpret_cast<void**>(&l.conv[1]))) != GUFO_CUDA_OK ||
-          (rc = gufo::Alloc(d, ssm_bytes, reinterpret_cast<void**>(&l.ssm))) != GUFO_CUDA_OK) {
-        return fail(rc);
-      }
+      ++linear_layers;
     }
     const gufo_cuda_matrix gate_up[2] = {w.ffn_gate, w.ffn_up};
     const int64_t ffn_rows[2] = {c.ffn, c.ffn};
@@ -894,6 +950,37 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
     }
     in_max = std::max(in_max, static_cast<size_t>(l.in.total_rows));
   }
+  // The DeltaNet layers' windows and states: one allocation per kind.
+  {
+    const size_t conv_floats = static_cast<size_t>(c.conv_kernel - 1) * channels;
+    const size_t ssm_floats = static_cast<size_t>(value_dim) * c.linear_head_dim;
+    d->conv_all_bytes = conv_floats * 4 * linear_layers;
+    d->ssm_all_bytes = ssm_floats * 4 * linear_layers;
+    if (linear_layers > 0) {
+      for (float*& block : d->conv_all) {
+        if ((rc = gufo::Alloc(d, d->conv_all_bytes, reinterpret_cast<void**>(&block))) != GUFO_CUDA_OK) {
+          return fail(rc);
+        }
+      }
+      for (float*& block : d->ssm_all) {
+        if ((rc = gufo::Alloc(d, d->ssm_all_bytes, reinterpret_cast<void**>(&block))) != GUFO_CUDA_OK) {
+          return fail(rc);
+        }
+      }
+    }
+    size_t at = 0;
+    for (auto& l : d->layers) {
+      if (l.attention) {
+        continue;
+      }
+      l.conv[0] = d->conv_all[0] + at * conv_floats;
+      l.conv[1] = d->conv_all[1] + at * conv_floats;
+      l.conv_saved = d->conv_all[2] + at * conv_floats;
+      l.ssm = d->ssm_all[0] + at * ssm_floats;
+      l.ssm_spec = d->ssm_all[1] + at * ssm_floats;
+      ++at;
+    }
+  }
   std::vector<float> inv_freq(c.rope_dim / 2 > 0 ? c.rope_dim / 2 : 1);
   for (int i = 0; i < c.rope_dim / 2; ++i) {
     // The reference's table (decoder.cpp:85-90).
@@ -905,46 +992,44 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
   }
   const size_t mixed = static_cast<size_t>(std::max<int64_t>(value_dim, attn_dim));
   const int group = c.heads / c.kv_heads;
+  // Activations for the two rows of a pair step; a one-token step uses the first.
+  const size_t two = gufo::kStepTokens;
   struct Buf {
     float** p;
     size_t n;
-  } bufs[] = {{&d->h[0], static_cast<size_t>(c.hidden)}, {&d->h[1], static_cast<size_t>(c.hidden)},
-              {&d->normed, static_cast<size_t>(c.hidden)},
-              {&d->in, in_max}, {&d->mixed, mixed}, {&d->out, static_cast<size_t>(c.hidden)},
-              {&d->ffn, static_cast<size_t>(2) * c.ffn}, {&d->act, static_cast<size_t>(c.ffn)},
-              {&d->logits, static_cast<size_t>(c.vocab)}, {&d->queries, static_cast<size_t>(attn_dim)},
+  } bufs[] = {{&d->h[0], two * c.hidden}, {&d->h[1], two * c.hidden},
+              {&d->normed, two * c.hidden},
+              {&d->in, two * in_max}, {&d->mixed, two * mixed}, {&d->out, two * c.hidden},
+              {&d->ffn, two * 2 * c.ffn}, {&d->act, two * c.ffn},
+              {&d->logits, two * c.vocab}, {&d->queries, static_cast<size_t>(attn_dim)},
               {&d->partials, static_cast<size_t>(c.kv_heads) * gufo::kAttnSplits * group * (c.head_dim + 2)},
               // MoE scratch (a few floats for a dense model).
-              {&d->router, static_cast<size_t>(c.experts) + 1},
-              {&d->route_weights, static_cast<size_t>(c.experts_used) + 1},
-              {&d->shared_scale, 1},
-              {&d->expert_ffn, static_cast<size_t>(c.experts_used) * 2 * c.expert_ffn + 1},
-              {&d->expert_act, static_cast<size_t>(c.experts_used) * c.expert_ffn + 1},
-              {&d->expert_out, static_cast<size_t>(c.experts_used) * c.hidden + 1}};
+              {&d->router, two * (static_cast<size_t>(c.experts) + 1)},
+              {&d->route_weights, two * c.experts_used + 1},
+              {&d->shared_scale, two},
+              {&d->expert_ffn, two * c.experts_used * 2 * c.expert_ffn + 1},
+              {&d->expert_act, two * c.experts_used * c.expert_ffn + 1},
+              {&d->expert_out, two * c.experts_used * c.hidden + 1}};
   for (auto& b : bufs) {
     if ((rc = gufo::Alloc(d, b.n * 4, reinterpret_cast<void**>(b.p))) != GUFO_CUDA_OK) {
       return fail(rc);
     }
   }
-  if ((rc = gufo::Alloc(d, 4 * (static_cast<size_t>(c.experts_used) + 1), reinterpret_cast<void**>(&d->chosen))) !=
-          GUFO_CUDA_OK ||
+  if ((rc = gufo::Alloc(d, 4 * (two * c.experts_used + 1), reinterpret_cast<void**>(&d->chosen))) != GUFO_CUDA_OK ||
       (rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->position_dev))) != GUFO_CUDA_OK ||
-      (rc = gufo::Alloc(d, 4, reinterpret_cast<void**>(&d->token_dev))) != GUFO_CUDA_OK) {
+      (rc = gufo::Alloc(d, 4 * two, reinterpret_cast<void**>(&d->token_dev))) != GUFO_CUDA_OK) {
     return fail(rc);
   }
-  cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&d->token_pinned), 4);
+  cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&d->token_pinned), 4 * (two + 1));
   if (e != cudaSuccess) {
     return fail(gufo::CudaFail(e, "cudaMallocHost"));
   }
   *out = d;
   // Zero states (the lock is already held: reset's body inline).
-  for (auto& l : d->layers) {
-    if (!l.attention) {
-      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
-      cudaMemsetAsync(l.conv[0], 0, conv_bytes, ctx->stream);
-      cudaMemsetAsync(l.conv[1], 0, conv_bytes, ctx->stream);
-      cudaMemsetAsync(l.ssm, 0, static_cast<size_t>(value_dim) * c.linear_head_dim * 4, ctx->stream);
-    }
+  if (d->conv_all_bytes > 0) {
+    cudaMemsetAsync(d->conv_all[0], 0, d->conv_all_bytes, ctx->stream);
+    cudaMemsetAsync(d->conv_all[1], 0, d->conv_all_bytes, ctx->stream);
+    cudaMemsetAsync(d->ssm_all[0], 0, d->ssm_all_bytes, ctx->stream);
   }
   cudaMemsetAsync(d->position_dev, 0, 4, ctx->stream);
   GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
@@ -957,9 +1042,13 @@ int gufo_cuda_decoder_destroy(gufo_cuda_decoder* d) {
   }
   cudaSetDevice(d->ctx->device);
   cudaStreamSynchronize(d->ctx->stream);
-  for (auto& g : d->graph) {
-    if (g != nullptr) {
-      cudaGraphExecDestroy(g);
+  for (auto& per_count : d->graph) {
+    for (auto& per_window : per_count) {
+      for (cudaGraphExec_t g : per_window) {
+        if (g != nullptr) {
+          cudaGraphExecDestroy(g);
+        }
+      }
     }
   }
   for (void* p : d->owned) {
@@ -982,47 +1071,58 @@ int gufo_cuda_decoder_reset(gufo_cuda_decoder* d) {
   gufo_cuda_ctx* ctx = d->ctx;
   std::lock_guard<std::mutex> lock(ctx->mu);
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
-  const gufo_cuda_decoder_config& c = d->c;
-  const size_t channels = static_cast<size_t>(2 * c.linear_key_heads + c.linear_value_heads) * c.linear_head_dim;
-  for (auto& l : d->layers) {
-    if (!l.attention) {
-      const size_t conv_bytes = static_cast<size_t>(c.conv_kernel - 1) * channels * 4;
-      GUFO_CUDA_TRY(cudaMemsetAsync(l.conv[0], 0, conv_bytes, ctx->stream));
-      GUFO_CUDA_TRY(cudaMemsetAsync(l.conv[1], 0, conv_bytes, ctx->stream));
-      GUFO_CUDA_TRY(cudaMemsetAsync(l.ssm, 0, static_cast<size_t>(c.linear_value_heads) * c.linear_head_dim *
-                                                  c.linear_head_dim * 4, ctx->stream));
-    }
+  if (d->conv_all_bytes > 0) {
+    GUFO_CUDA_TRY(cudaMemsetAsync(d->conv_all[0], 0, d->conv_all_bytes, ctx->stream));
+    GUFO_CUDA_TRY(cudaMemsetAsync(d->conv_all[1], 0, d->conv_all_bytes, ctx->stream));
+    GUFO_CUDA_TRY(cudaMemsetAsync(d->ssm_all[0], 0, d->ssm_all_bytes, ctx->stream));
   }
   GUFO_CUDA_TRY(cudaMemsetAsync(d->position_dev, 0, 4, ctx->stream));
   d->position = 0;
+  d->conv_cur = 0;
+  d->pending = 0;
   return GUFO_CUDA_OK;
 }
 
-int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) {
-  if (d == nullptr) {
-    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: null decoder");
+int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int count, int want_logits,
+                                  float* host_logits) {
+  if (d == nullptr || tokens == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: null pointer");
   }
-  if (token < 0 || token >= d->c.vocab) {
-    return Fail(GUFO_CUDA_BAD_ARGUMENT, "qwen35: token id out of range");
+  if (count < 1 || count > gufo::kStepTokens) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: 1 or 2 tokens per step");
   }
-  if (d->position >= d->c.max_positions) {
+  for (int t = 0; t < count; ++t) {
+    if (tokens[t] < 0 || tokens[t] >= d->c.vocab) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "qwen35: token id out of range");
+    }
+  }
+  if (d->pending != 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: the last two-token step awaits decoder_resolve");
+  }
+  if (d->position + count > d->c.max_positions) {
     return Fail(GUFO_CUDA_TOO_LARGE, "decoder_step: the attention cache is full");
+  }
+  if (host_logits != nullptr && want_logits == 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step: logits asked for and switched off");
   }
   gufo_cuda_ctx* ctx = d->ctx;
   std::lock_guard<std::mutex> lock(ctx->mu);
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
-  *d->token_pinned = token;
-  GUFO_CUDA_TRY(cudaMemcpyAsync(d->token_dev, d->token_pinned, 4, cudaMemcpyHostToDevice, ctx->stream));
-  const int parity = d->position & 1;
-  // The first steps run eagerly (they size the staging buffer and set kernel
-  // attributes); later ones replay a captured graph per parity.
-  if (d->c.use_graph && d->steps >= 2 && !d->timeline) {
-    if (d->graph[parity] == nullptr) {
+  for (int t = 0; t < count; ++t) {
+    d->token_pinned[t] = tokens[t];
+  }
+  GUFO_CUDA_TRY(cudaMemcpyAsync(d->token_dev, d->token_pinned, 4 * count, cudaMemcpyHostToDevice, ctx->stream));
+  const int parity = d->conv_cur;
+  const int pair = count - 1, with = want_logits != 0 ? 1 : 0;
+  auto enqueue = [&]() { return gufo::EnqueueStep(d, parity, with != 0, count); };
+  if (d->c.use_graph && d->eager_runs[pair][with] >= 2 && !d->timeline) {
+    cudaGraphExec_t& exec = d->graph[pair][parity][with];
+    if (exec == nullptr) {
       cudaGraph_t graph = nullptr;
       GUFO_CUDA_TRY(cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
       const int64_t before = ctx->launches.load();
-      const int rc = gufo::EnqueueStep(d, parity);
-      d->kernels_per_step = ctx->launches.load() - before;
+      const int rc = enqueue();
+      d->graph_kernels[pair][parity][with] = ctx->launches.load() - before;
       ctx->launches.store(before);   // counted at every replay instead
       const cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
       if (rc != GUFO_CUDA_OK || e != cudaSuccess) {
@@ -1031,22 +1131,25 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) 
         }
         return rc != GUFO_CUDA_OK ? rc : gufo::CudaFail(e, "cudaStreamEndCapture");
       }
-      const cudaError_t ei = cudaGraphInstantiate(&d->graph[parity], graph, 0);
+      const cudaError_t ei = cudaGraphInstantiate(&exec, graph, 0);
       cudaGraphDestroy(graph);
       if (ei != cudaSuccess) {
-        d->graph[parity] = nullptr;
+        exec = nullptr;
         return gufo::CudaFail(ei, "cudaGraphInstantiate");
       }
     }
-    GUFO_CUDA_TRY(cudaGraphLaunch(d->graph[parity], ctx->stream));
-    ctx->launches.fetch_add(d->kernels_per_step);
+    GUFO_CUDA_TRY(cudaGraphLaunch(exec, ctx->stream));
+    ctx->launches.fetch_add(d->graph_kernels[pair][parity][with]);
   } else {
-    const int rc = gufo::EnqueueStep(d, parity);
+    const int rc = enqueue();
     if (rc != GUFO_CUDA_OK) {
       return rc;
     }
+    ++d->eager_runs[pair][with];
   }
-  ++d->position;
+  d->position += count;
+  d->conv_cur ^= 1;
+  d->pending = count == 2 ? 2 : 0;
   ++d->steps;
   if (d->timeline) {
     // Fold this step's marks into the per-stage totals.
@@ -1062,10 +1165,57 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) 
     ++d->timeline_steps;
   }
   if (host_logits != nullptr) {
-    GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(d->c.vocab) * 4,
+    GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(count) * d->c.vocab * 4,
                                   cudaMemcpyDeviceToHost, ctx->stream));
     GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
   }
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_step(gufo_cuda_decoder* d, int token, float* host_logits) {
+  return gufo_cuda_decoder_step_tokens(d, &token, 1, 1, host_logits);
+}
+
+int gufo_cuda_decoder_resolve(gufo_cuda_decoder* d, int keep_second) {
+  if (d == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_resolve: null decoder");
+  }
+  if (d->pending != 2) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_resolve: the last step was not a two-token step");
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  if (keep_second != 0) {
+    // The draft's states become the states (ssm <-> ssm_spec in the reference).
+    if (d->ssm_all_bytes > 0) {
+      GUFO_CUDA_TRY(cudaMemcpyAsync(d->ssm_all[0], d->ssm_all[1], d->ssm_all_bytes, cudaMemcpyDeviceToDevice,
+                                    ctx->stream));
+    }
+  } else {
+    // Back to just after the first token: its conv windows, one position less;
+    // the second token's cache rows are overwritten by the next step.
+    if (d->conv_all_bytes > 0) {
+      GUFO_CUDA_TRY(cudaMemcpyAsync(d->conv_all[d->conv_cur], d->conv_all[2], d->conv_all_bytes,
+                                    cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    --d->position;
+    d->token_pinned[gufo::kStepTokens] = d->position;
+    GUFO_CUDA_TRY(cudaMemcpyAsync(d->position_dev, d->token_pinned + gufo::kStepTokens, 4, cudaMemcpyHostToDevice,
+                                  ctx->stream));
+    // The pinned word is read when the copy runs: wait, so that a later
+    // Resolve cannot overwrite it first.
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  }
+  d->pending = 0;
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_hidden_device(gufo_cuda_decoder* d, int t, const float** hidden) {
+  if (d == nullptr || hidden == nullptr || t < 0 || t >= gufo::kStepTokens || d->final_h == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_hidden_device: no such row");
+  }
+  *hidden = d->final_h + static_cast<size_t>(t) * d->c.hidden;
   return GUFO_CUDA_OK;
 }
 
@@ -1112,7 +1262,7 @@ int gufo_cuda_decoder_linear_state(gufo_cuda_decoder* d, int layer, float* host_
   const auto& l = d->layers[layer];
   const size_t channels = static_cast<size_t>(2 * c.linear_key_heads + c.linear_value_heads) * c.linear_head_dim;
   if (host_conv != nullptr) {
-    GUFO_CUDA_TRY(cudaMemcpyAsync(host_conv, l.conv[d->position & 1], (c.conv_kernel - 1) * channels * 4,
+    GUFO_CUDA_TRY(cudaMemcpyAsync(host_conv, l.conv[d->conv_cur], (c.conv_kernel - 1) * channels * 4,
                                   cudaMemcpyDeviceToHost, ctx->stream));
   }
   if (host_ssm != nullptr) {

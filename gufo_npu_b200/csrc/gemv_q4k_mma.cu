@@ -272,7 +272,7 @@ GemvQ4KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 1.0f / 16.0f, a.x + static_cast<size_t>(group / (a.x_group_div > 1 ? a.x_group_div : 1)) * a.x_group_stride, rank, ks, kSlabBlocks);
+    FillImage<TOKENS>(a, l, smem, 1.0f / 16.0f, a.x + static_cast<size_t>(group / (a.x_group_div > 1 ? a.x_group_div : 1)) * a.x_group_stride, rank, ks, kSlabBlocks);
   }
 
   Accum<TOKENS> acc;
@@ -407,9 +407,6 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   int row_tiles = 0;
   for (int p = 0; p < args.nparts; ++p) {
     row_tiles += (args.parts[p].rows + 15) / 16;
-  }
-  if (args.prologue != kPrologueImage && args.tokens != 1) {
-    return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: fused prologues take one token");
   }
   // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
   FastGemvArgs launch = args;

@@ -301,7 +301,7 @@ GemvQ6KMma(const __grid_constant__ FastGemvArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   } else {
-    FillImage(a, l, smem, 0.25f, a.x, rank, ks, kSlabBlocks);
+    FillImage<TOKENS>(a, l, smem, 0.25f, a.x, rank, ks, kSlabBlocks);
   }
 
   Accum<TOKENS> acc;
@@ -443,9 +443,6 @@ int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   int row_tiles = 0;
   for (int p = 0; p < args.nparts; ++p) {
     row_tiles += (args.parts[p].rows + 15) / 16;
-  }
-  if (args.prologue != kPrologueImage && args.tokens != 1) {
-    return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: fused prologues take one token");
   }
   if (args.group_ids != nullptr) {
     return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "fast gemv: grouped launches run Q4_K only");

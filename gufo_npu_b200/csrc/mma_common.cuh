@@ -180,13 +180,17 @@ __device__ __forceinline__ void StageBlock(const float (&v)[8], int lane, int to
 
 __device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + expf(-x))); }
 
-// Builds the one-token image in shared memory at `image` from the launch's
-// fused input (prologue != kPrologueImage). Warp w converts blocks w, w + 8,
-// ...; a lane holds eight adjacent values, so nothing is staged in between.
-// `x` is the plain / SwiGLU input (a.x, or a group's part of it). A block that
-// shares its tiles with a cluster (rank `rank` of `ks`, slabs of `slab_blocks`
-// blocks dealt round-robin) converts only the blocks of its own slabs; the
-// others are never read. Ends with a __syncthreads. kFastThreads threads.
+// Builds the image of the launch's TOKENS rows in shared memory at `image` from
+// the launch's fused input (prologue != kPrologueImage). Warp w converts blocks
+// w, w + 8, ...; a lane holds eight adjacent values, so nothing is staged in
+// between. `x` is the plain / SwiGLU input (a.x, or a group's part of it). Rows
+// of several tokens follow one another: the residual, its pending add, the
+// normed vector and a plain x `cols` floats apart, a SwiGLU input [gate | up]
+// 2 * cols apart. A block that shares its tiles with a cluster (rank `rank` of
+// `ks`, slabs of `slab_blocks` blocks dealt round-robin) converts only the
+// blocks of its own slabs; the others are never read. Ends with a
+// __syncthreads. kFastThreads threads.
+template <int TOKENS>
 __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
                                           uint8_t* image, float extra, const float* x,
                                           int rank, int ks, int slab_blocks) {
@@ -210,7 +214,7 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
   // Columns without a token keep a zero factor.
   float* scale = reinterpret_cast<float*>(image + l.scale_at);
   for (int i = threadIdx.x; i < blocks * l.kcols; i += kFastThreads) {
-    if (i % l.kcols >= kLimbs) {
+    if (i % l.kcols >= kLimbs * TOKENS) {
       scale[i] = 0.f;
     }
   }
@@ -219,18 +223,6 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     // pending add (src/models/qwen35/decoder.cpp:493,504-508). The first pass
     // sums the squares; the second reads the same values again (they sit in
     // L2, and the warp's first block is still in registers).
-    auto residual = [&](int at, float (&v)[8]) {
-      load8(a.h_in + at, v);
-      if (a.delta != nullptr) {
-        float d[8];
-        load8(a.delta + at, d);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[i] += d[i];
-        }
-      }
-    };
-    float keep[8] = {};
     // The norm weights of the warp's first block never depend on an earlier
     // kernel: their load rides with the first pass instead of following the
     // barrier.
@@ -238,80 +230,104 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     if (warp < blocks) {
       load8(a.norm_w + warp * kSuperBlock + lane * 8, keep_w);
     }
-    float sq = 0.f;
-    for (int b = warp; b < blocks; b += kFastWarps) {
-      float v[8];
-      residual(b * kSuperBlock + lane * 8, v);
+#pragma unroll 1
+    for (int tok = 0; tok < TOKENS; ++tok) {
+      const size_t row = static_cast<size_t>(tok) * n;
+      auto residual = [&](int at, float (&v)[8]) {
+        load8(a.h_in + row + at, v);
+        if (a.delta != nullptr) {
+          float d[8];
+          load8(a.delta + row + at, d);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        sq = fmaf(v[i], v[i], sq);
+          for (int i = 0; i < 8; ++i) {
+            v[i] += d[i];
+          }
+        }
+      };
+      if (tok > 0) {
+        __syncthreads();   // the sums of the token before have been read
+      }
+      float keep[8] = {};
+      float sq = 0.f;
+      for (int b = warp; b < blocks; b += kFastWarps) {
+        float v[8];
+        residual(b * kSuperBlock + lane * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          sq = fmaf(v[i], v[i], sq);
+          if (b == warp) {
+            keep[i] = v[i];
+          }
+        }
+      }
+      sq = WarpSum(sq);
+      if (lane == 0) {
+        reduce[warp] = sq;
+      }
+      __syncthreads();
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kFastWarps; ++w) {
+        total += reduce[w];
+      }
+      const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + a.eps);
+      for (int b = warp; b < blocks; b += kFastWarps) {
+        // Block 0 writes the whole residual stream and normed vector.
+        if (!first && !mine(b)) {
+          continue;
+        }
+        const int at = b * kSuperBlock + lane * 8;
+        float v[8], w[8], out[8];
         if (b == warp) {
-          keep[i] = v[i];
-        }
-      }
-    }
-    sq = WarpSum(sq);
-    if (lane == 0) {
-      reduce[warp] = sq;
-    }
-    __syncthreads();
-    float total = 0.f;
 #pragma unroll
-    for (int w = 0; w < kFastWarps; ++w) {
-      total += reduce[w];
-    }
-    const float inv = 1.0f / sqrtf(total / static_cast<float>(n) + a.eps);
-    for (int b = warp; b < blocks; b += kFastWarps) {
-      // Block 0 writes the whole residual stream and normed vector.
-      if (!first && !mine(b)) {
-        continue;
-      }
-      const int at = b * kSuperBlock + lane * 8;
-      float v[8], w[8], out[8];
-      if (b == warp) {
+          for (int i = 0; i < 8; ++i) {
+            v[i] = keep[i];
+          }
+          for (int i = 0; i < 8; ++i) {
+            w[i] = keep_w[i];
+          }
+        } else {
+          residual(at, v);
+          load8(a.norm_w + at, w);
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          v[i] = keep[i];
+          out[i] = v[i] * inv * w[i];
         }
-        for (int i = 0; i < 8; ++i) {
-          w[i] = keep_w[i];
+        if (first) {
+          store8(a.h_out + row + at, v);
+          if (a.normed_out != nullptr) {
+            store8(a.normed_out + row + at, out);
+          }
         }
-      } else {
-        residual(at, v);
-        load8(a.norm_w + at, w);
+        StageBlock(out, lane, tok, b, l, image, extra);
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        out[i] = v[i] * inv * w[i];
-      }
-      if (first) {
-        store8(a.h_out + at, v);
-        if (a.normed_out != nullptr) {
-          store8(a.normed_out + at, out);
-        }
-      }
-      StageBlock(out, lane, 0, b, l, image, extra);
     }
     if (first && threadIdx.x == 0 && a.advance != nullptr) {
-      *a.advance += 1;
+      *a.advance += TOKENS;
     }
   } else {
-    for (int b = warp; b < blocks; b += kFastWarps) {
-      if (!mine(b)) {
-        continue;
-      }
-      const int at = b * kSuperBlock + lane * 8;
-      float v[8];
-      load8(x + at, v);
-      if (a.prologue == kPrologueSwiGlu) {
-        float up[8];
-        load8(x + n + at, up);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          v[i] = SiluFast(v[i]) * up[i];
+    const size_t stride = a.prologue == kPrologueSwiGlu ? 2 * static_cast<size_t>(n) : static_cast<size_t>(n);
+#pragma unroll 1
+    for (int tok = 0; tok < TOKENS; ++tok) {
+      const float* xt = x + tok * stride;
+      for (int b = warp; b < blocks; b += kFastWarps) {
+        if (!mine(b)) {
+          continue;
         }
+        const int at = b * kSuperBlock + lane * 8;
+        float v[8];
+        load8(xt + at, v);
+        if (a.prologue == kPrologueSwiGlu) {
+          float up[8];
+          load8(xt + n + at, up);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[i] = SiluFast(v[i]) * up[i];
+          }
+        }
+        StageBlock(v, lane, tok, b, l, image, extra);
       }
-      StageBlock(v, lane, 0, b, l, image, extra);
     }
   }
   __syncthreads();

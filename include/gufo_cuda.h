@@ -469,7 +469,30 @@ int gufo_cuda_decoder_reset(gufo_cuda_decoder* decoder);
  * when the attention cache is full. */
 int gufo_cuda_decoder_step(gufo_cuda_decoder* decoder, int token,
                            float* host_logits);
-/* Device address of the last step's logits (vocab fp32). */
+/* NpuDecoder::Step(tokens, count, state, logits)
+ * (src/models/qwen35_2b/npu_decoder.hpp:57-65, npu_decoder.cpp:558-628): runs
+ * `count` (1 or 2) tokens from the current position in one pass, every weight
+ * read once for both; token t's logits land at t * vocab (host_logits may be
+ * NULL to leave them on the device). With want_logits == 0 the LM head is
+ * skipped (prompt passes) and host_logits must be NULL; the final residuals
+ * are kept either way (gufo_cuda_decoder_hidden_device). With two tokens the
+ * second stays a draft until gufo_cuda_decoder_resolve, which must come
+ * before the next step. Errors as gufo_cuda_decoder_step. */
+int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* decoder, const int* tokens,
+                                  int count, int want_logits,
+                                  float* host_logits);
+/* NpuDecoder::Resolve (npu_decoder.cpp:630-650) after a two-token step:
+ * keep_second != 0 keeps the draft (the DeltaNet draft states become the
+ * states), 0 rolls the decoder back to just after the first token (its conv
+ * windows, one position less; the draft's attention cache rows are overwritten
+ * by the next step). */
+int gufo_cuda_decoder_resolve(gufo_cuda_decoder* decoder, int keep_second);
+/* NpuDecoder::hidden(t) (npu_decoder.hpp:70-72): device address of the final
+ * residual (before output_norm, `hidden` fp32) of token t of the last step:
+ * the MTP head's input. Valid until the next step. */
+int gufo_cuda_decoder_hidden_device(gufo_cuda_decoder* decoder, int t,
+                                    const float** hidden);
+/* Device address of the last step's logits (vocab fp32 per token). */
 int gufo_cuda_decoder_logits_device(gufo_cuda_decoder* decoder,
                                     const float** device_logits);
 int gufo_cuda_decoder_position(const gufo_cuda_decoder* decoder);

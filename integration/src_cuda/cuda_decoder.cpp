@@ -100,6 +100,8 @@ Decoder::Decoder(const gguf::File& file, const CudaProjections& projections, int
     throw std::runtime_error(std::string("cuda: ") + gufo_cuda_last_error(projections.context()));
   }
   logits_.resize(static_cast<std::size_t>(c.vocab));
+  pair_logits_.resize(2 * logits_.size());
+  hidden_width_ = c.hidden;
 }
 
 Decoder::~Decoder() { gufo_cuda_decoder_destroy(decoder_); }
@@ -116,6 +118,42 @@ const std::vector<float>& Decoder::Step(int token) {
     throw std::runtime_error(std::string("cuda: ") + gufo_cuda_last_error(projections_.context()));
   }
   return logits_;
+}
+
+const float* Decoder::Step(const int* tokens, int count, bool logits) {
+  if (count < 1 || count > 2) {
+    throw std::invalid_argument("cuda decoder: 1 or 2 tokens per step");
+  }
+  const int status =
+      gufo_cuda_decoder_step_tokens(decoder_, tokens, count, logits ? 1 : 0, logits ? pair_logits_.data() : nullptr);
+  if (status == GUFO_CUDA_TOO_LARGE) {
+    throw std::length_error("cuda: the attention cache is full");
+  }
+  if (status != GUFO_CUDA_OK) {
+    const std::string text = gufo_cuda_last_error(projections_.context());
+    if (status == GUFO_CUDA_BAD_ARGUMENT && text.find("out of range") != std::string::npos) {
+      throw std::out_of_range(text);
+    }
+    throw std::runtime_error("cuda: " + text);
+  }
+  return logits ? pair_logits_.data() : nullptr;
+}
+
+void Decoder::Resolve(bool keep_second) {
+  if (gufo_cuda_decoder_resolve(decoder_, keep_second ? 1 : 0) != GUFO_CUDA_OK) {
+    throw std::logic_error(std::string("cuda: ") + gufo_cuda_last_error(projections_.context()));
+  }
+}
+
+const std::vector<float>& Decoder::hidden(int t) {
+  const float* device = nullptr;
+  hidden_.resize(static_cast<std::size_t>(hidden_width_));
+  if (gufo_cuda_decoder_hidden_device(decoder_, t, &device) != GUFO_CUDA_OK ||
+      gufo_cuda_download(projections_.context(), hidden_.data(), device, hidden_.size() * sizeof(float)) !=
+          GUFO_CUDA_OK) {
+    throw std::runtime_error(std::string("cuda: ") + gufo_cuda_last_error(projections_.context()));
+  }
+  return hidden_;
 }
 
 void Decoder::Reset() {

@@ -30,6 +30,9 @@ Decoder::Decoder(const gguf::File&, const CudaProjections& projections, int) : p
 }
 Decoder::~Decoder() = default;
 const std::vector<float>& Decoder::Step(int) { throw std::runtime_error("gufo-npu was built without CUDA"); }
+const float* Decoder::Step(const int*, int, bool) { throw std::runtime_error("gufo-npu was built without CUDA"); }
+void Decoder::Resolve(bool) { throw std::runtime_error("gufo-npu was built without CUDA"); }
+const std::vector<float>& Decoder::hidden(int) { throw std::runtime_error("gufo-npu was built without CUDA"); }
 void Decoder::Reset() { throw std::runtime_error("gufo-npu was built without CUDA"); }
 int Decoder::position() const { return 0; }
 

@@ -5,8 +5,11 @@
 // (integration/src_cuda/cuda_projections.cpp over libgufo_cuda.so) plugged in
 // behind the same Projections interface, and compares the logits of every
 // step; a third run takes the same tokens through the device-resident
-// cuda::Decoder (integration/src_cuda/cuda_decoder.cpp). Built by oracle/Makefile from the reference's sources where they lie;
-// the mixers, norms and sampling stay the reference's CPU code in both runs.
+// cuda::Decoder (integration/src_cuda/cuda_decoder.cpp), and a fourth walks them
+// in two-token steps whose drafts are kept or rolled back (Step(tokens, count) /
+// Resolve), every row against the reference's one-token logits. Built by
+// oracle/Makefile from the reference's sources where they lie; the mixers, norms
+// and sampling stay the reference's CPU code in the first two runs.
 //
 //   adapter_parity <model.gguf> <tokens>     exit 0 when every step agrees
 #include <cmath>
@@ -37,9 +40,13 @@ int main(int argc, char** argv) {
   auto sb = b.NewState();
   const int vocab = a.config().vocab;
   double worst = 0;
+  std::vector<int> tokens;
+  std::vector<std::vector<float>> wanted;
   for (int s = 0; s < steps; ++s) {
     const int token = (s * 7919 + 13) % vocab;
     const std::vector<float> want = a.Step(token, sa);
+    tokens.push_back(token);
+    wanted.push_back(want);
     const std::vector<float>& got = b.Step(token, sb);
     double num = 0, den = 0;
     int arg_want = 0, arg_got = 0;
@@ -71,6 +78,45 @@ int main(int argc, char** argv) {
       std::printf("FAIL\n");
       return 1;
     }
+  }
+  // Two-token steps: pairs alternately kept and rolled back (a rolled-back
+  // draft is a wrong token, so the next step must not see any trace of it).
+  gufo_npu::cuda::Decoder pairs(*file, gpu, steps + 8);
+  auto row_error = [&](const float* got, int s) {
+    double num = 0, den = 0;
+    for (int i = 0; i < vocab; ++i) {
+      num += (double(got[i]) - wanted[s][i]) * (double(got[i]) - wanted[s][i]);
+      den += double(wanted[s][i]) * wanted[s][i];
+    }
+    return std::sqrt(num / den);
+  };
+  bool keep = true;
+  for (int s = 0; s < steps;) {
+    if (s + 1 >= steps) {
+      const double err = row_error(pairs.Step(&tokens[s], 1), s);
+      std::printf("pair walk, step %d alone: rel-L2 %.3e\n", s, err);
+      worst = err > worst ? err : worst;
+      if (err > 2e-3) {
+        std::printf("FAIL\n");
+        return 1;
+      }
+      ++s;
+      continue;
+    }
+    const int pair[2] = {tokens[s], keep ? tokens[s + 1] : (tokens[s + 1] + 7) % vocab};
+    const float* both = pairs.Step(pair, 2);
+    const double first = row_error(both, s);
+    const double second = keep ? row_error(both + vocab, s + 1) : 0.0;
+    pairs.Resolve(keep);
+    std::printf("pair walk, steps %d+%d %s: rel-L2 %.3e %.3e\n", s, s + 1, keep ? "kept" : "rolled back", first,
+                second);
+    worst = std::fmax(worst, std::fmax(first, second));
+    s += keep ? 2 : 1;
+    if (first > 2e-3 || second > 2e-3 || pairs.position() != s) {
+      std::printf("FAIL\n");
+      return 1;
+    }
+    keep = !keep;
   }
   std::printf("PASS: %d steps, worst rel-L2 %.3e\n", steps, worst);
   return 0;

@@ -198,6 +198,21 @@ def test_moe_decoder_step_matches_reference_logits(ctx, golden, use_graph):
     dec.close()
 
 
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_moe_decoder_pair_steps_and_resolve(ctx, golden, use_graph):
+    """Two-token steps on the MoE model: both rows route on the device and run their experts in
+    one grouped launch; kept and rolled-back drafts against the reference's one-token logits."""
+    from tests.test_gpu_parity import check_pair_steps
+    cfg, tensors, proj = _moe_model(ctx)
+    dec = CudaDecoder(proj, tensors, max_positions=64, use_graph=use_graph)
+    g = golden("decoder")
+    tokens = [int(t) for t in g["decoder_moe_tokens"]]
+    for _ in range(3):
+        dec.Reset()
+        assert check_pair_steps(dec, cfg, tokens, g["decoder_moe_logits"]) < 1e-4
+    dec.close()
+
+
 def test_config4_shaped_experts(ctx, oracle):
     """Config-4 shapes (hidden 2048, expert FFN 512, Q4_K, top-8) on a bank of 32 experts: the
     grouped path against the oracle's fused row dots for two of the chosen experts."""

@@ -552,6 +552,75 @@ def test_decoder_step_matches_reference_logits(ctx, golden, use_graph):
     dec.close()
 
 
+def check_pair_steps(dec, cfg, tokens, want_logits):
+    """Walks `tokens` with two-token steps whose drafts are kept or rolled back
+    (NpuDecoder::Step / Resolve, src/models/qwen35_2b/npu_decoder.hpp:57-68); every row of
+    logits must be the one-token decoder's at that position (`want_logits`)."""
+    def check(row, i):
+        err = rel_l2(row, want_logits[i])
+        assert err <= STEP_TOL, (i, err)
+        assert int(np.argmax(row)) == int(np.argmax(want_logits[i]))
+        return err
+    worst = 0.0
+    wrong = lambda tok: (tok + 7) % cfg.vocab
+    # (0, 1) kept; (2, wrong) rolled back; (3, 4) kept; 5 alone; (6, wrong) rolled back; 7 alone.
+    both = dec.StepTokens(tokens[0:2])
+    assert both.shape == (2, cfg.vocab)
+    worst = max(worst, check(both[0], 0), check(both[1], 1))
+    with pytest.raises(Exception):
+        dec.Step(tokens[2])              # a pair awaits Resolve
+    dec.Resolve(True)
+    assert dec.position == 2
+    both = dec.StepTokens([tokens[2], wrong(tokens[3])])
+    worst = max(worst, check(both[0], 2))
+    dec.Resolve(False)
+    assert dec.position == 3
+    both = dec.StepTokens(tokens[3:5])
+    worst = max(worst, check(both[0], 3), check(both[1], 4))
+    dec.Resolve(True)
+    worst = max(worst, check(dec.Step(tokens[5]), 5))
+    both = dec.StepTokens([tokens[6], wrong(tokens[7])])
+    worst = max(worst, check(both[0], 6))
+    dec.Resolve(False)
+    worst = max(worst, check(dec.StepTokens([tokens[7]])[0], 7))
+    assert dec.position == 8
+    with pytest.raises(Exception):
+        dec.Resolve(True)                # nothing to resolve after a one-token step
+    return worst
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_decoder_pair_steps_and_resolve(ctx, golden, use_graph):
+    """Two-token steps with kept and rolled-back drafts against the committed logits of the
+    reference's Decoder::Step; three passes, so that the replayed graphs are covered."""
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    dec = CudaDecoder(CudaProjections(ctx, cfg, tensors), tensors, max_positions=64, use_graph=use_graph)
+    g = golden("decoder")
+    tokens = [int(t) for t in g["decoder_dense_tokens"]]
+    for _ in range(3):
+        dec.Reset()
+        assert check_pair_steps(dec, cfg, tokens, g["decoder_dense_logits"]) < 1e-4
+    # Prompt passes without logits, then the final residual and the next token's logits.
+    dec.Reset()
+    assert dec.StepTokens(tokens[0:2], logits=False) is None
+    dec.Resolve(True)
+    assert dec.StepTokens(tokens[2:3], logits=False) is None
+    hidden_quiet = dec.hidden(0)
+    assert rel_l2(dec.Step(tokens[3]), g["decoder_dense_logits"][3]) <= STEP_TOL
+    dec.Reset()
+    for tok in tokens[:3]:
+        dec.Step(tok)
+    assert rel_l2(hidden_quiet, dec.hidden(0)) <= 1e-4
+    pair = CudaDecoder(CudaProjections(ctx, cfg, tensors), tensors, max_positions=64, use_graph=False)
+    pair.StepTokens(tokens[0:2])
+    pair.Resolve(True)
+    pair.StepTokens(tokens[2:4])
+    assert rel_l2(pair.hidden(0), hidden_quiet) <= 1e-4
+    pair.close()
+    dec.close()
+
+
 def test_decoder_cache_capacity(ctx):
     cfg = synth.ModelConfig(**G.DENSE)
     tensors = synth.build_model(cfg, G.DENSE_SEED)
