@@ -75,6 +75,19 @@ __device__ __forceinline__ int ScaleOf(const uint4& sc) {
   return v;
 }
 
+// Word W (0..3) of a block's sixteen int8 scales.
+template <int W>
+__device__ __forceinline__ uint32_t ScaleWord(const uint4& sc) {
+  return W == 0 ? sc.x : (W == 1 ? sc.y : (W == 2 ? sc.z : sc.w));
+}
+
+// prmt with a selector whose nibbles may carry the sign-replicate bit.
+__device__ __forceinline__ int SignedByte(uint32_t w, uint32_t selector) {
+  int v;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(v) : "r"(w), "r"(0u), "r"(selector));
+  return v;
+}
+
 // Run K (0..3) of half H: 32 values, groups 8H + 2K and 8H + 2K + 1.
 template <int TOKENS, int H, int K>
 __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&hi)[2][2][4],
@@ -96,8 +109,6 @@ __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&h
     a[r] = (lo0 & 0x3C3C3C3Cu) | hi[r][0][K];
     a[2 + r] = (lo1 & 0x3C3C3C3Cu) | hi[r][1][K];
   }
-  const int s0g = ScaleOf<8 * H + 2 * K>(u.sc[0]), s1g = ScaleOf<8 * H + 2 * K + 1>(u.sc[0]);
-  const int s0h = ScaleOf<8 * H + 2 * K>(u.sc[1]), s1h = ScaleOf<8 * H + 2 * K + 1>(u.sc[1]);
   if constexpr (TOKENS == 1) {
     // One token fills three of the eight MMA columns, so one product serves both
     // groups of the run: columns 0..2 carry the planes for values 0..15 only,
@@ -107,8 +118,12 @@ __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&h
     const uint2 x = *reinterpret_cast<const uint2*>(at_first + 128 * H + 32 * K);
     int c[4];
     MmaS8S8(c, a, x.x, x.y);
-    const bool second = stride_second != 0;   // set for lanes t >= 2
-    const int sg = second ? s1g : s0g, sh = second ? s1h : s0h;
+    // The lane's group of the run is the first (t < 2) or the second; both
+    // scales sit in one word, so one byte permute with the sign-replicating
+    // selector (byte b to byte 0, its sign to bytes 1..3) extracts the lane's.
+    const uint32_t sel = (stride_second != 0 ? 0x9991u : 0x8880u) + ((K & 1) != 0 ? 0x2222u : 0u);
+    const int sg = SignedByte(ScaleWord<2 * H + (K >> 1)>(u.sc[0]), sel);
+    const int sh = SignedByte(ScaleWord<2 * H + (K >> 1)>(u.sc[1]), sel);
     sum[0][0] += sg * c[0];
     sum[0][1] += sg * c[1];
     sum[0][2] += sh * c[2];
@@ -117,6 +132,8 @@ __device__ __forceinline__ void MultiplyRun(const Q6KUnit& u, const uint32_t (&h
     (void)g;
     (void)stride_first;
   } else {
+  const int s0g = ScaleOf<8 * H + 2 * K>(u.sc[0]), s1g = ScaleOf<8 * H + 2 * K + 1>(u.sc[0]);
+  const int s0h = ScaleOf<8 * H + 2 * K>(u.sc[1]), s1h = ScaleOf<8 * H + 2 * K + 1>(u.sc[1]);
 #pragma unroll
   for (int nb = 0; nb < kNB; ++nb) {
     // Further column groups lie 8 planes on; the plane of zeros has no such
