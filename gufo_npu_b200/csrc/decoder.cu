@@ -29,6 +29,7 @@ constexpr int kAttnSplits = 8;      // position slices per KV head
 constexpr int kMaxGroup = 8;        // query heads per KV head
 constexpr int kMaxPerLane = 8;      // head_dim / 32
 constexpr int kStepTokens = 2;      // tokens of a pair step
+constexpr int kTokenSlots = 8;      // pinned token staging slots of a decoder
 
 __device__ __forceinline__ float SigmoidF(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float SiluF(float x) { return x * SigmoidF(x); }
@@ -492,7 +493,13 @@ struct gufo_cuda_decoder {
   int* chosen = nullptr;
   int* position_dev = nullptr;
   int* token_dev = nullptr;      // [kStepTokens]
-  int* token_pinned = nullptr;   // [kStepTokens] tokens, then the position (Resolve)
+  // Pinned staging for the token ids: a ring of slots, each reused only after
+  // the copy that read it has run (its event), so that steps enqueued without
+  // a wait in between never see one another's tokens. The last slot carries the
+  // position word Resolve uploads.
+  int* token_pinned = nullptr;   // [kTokenSlots + 1][kStepTokens]
+  cudaEvent_t token_read[gufo::kTokenSlots] = {};
+  unsigned token_slot = 0;
   int position = 0;
   int conv_cur = 0;              // which of a layer's conv windows is current
   int pending = 0;               // tokens of the last step that await Resolve (0 or 2)
@@ -1020,9 +1027,14 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
       (rc = gufo::Alloc(d, 4 * two, reinterpret_cast<void**>(&d->token_dev))) != GUFO_CUDA_OK) {
     return fail(rc);
   }
-  cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&d->token_pinned), 4 * (two + 1));
+  cudaError_t e = cudaMallocHost(reinterpret_cast<void**>(&d->token_pinned), 4 * two * (gufo::kTokenSlots + 1));
   if (e != cudaSuccess) {
     return fail(gufo::CudaFail(e, "cudaMallocHost"));
+  }
+  for (cudaEvent_t& read : d->token_read) {
+    if ((e = cudaEventCreateWithFlags(&read, cudaEventDisableTiming)) != cudaSuccess) {
+      return fail(gufo::CudaFail(e, "cudaEventCreate"));
+    }
   }
   *out = d;
   // Zero states (the lock is already held: reset's body inline).
@@ -1059,6 +1071,11 @@ int gufo_cuda_decoder_destroy(gufo_cuda_decoder* d) {
   }
   if (d->token_pinned != nullptr) {
     cudaFreeHost(d->token_pinned);
+  }
+  for (cudaEvent_t read : d->token_read) {
+    if (read != nullptr) {
+      cudaEventDestroy(read);
+    }
   }
   delete d;
   return GUFO_CUDA_OK;
@@ -1108,10 +1125,16 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
   gufo_cuda_ctx* ctx = d->ctx;
   std::lock_guard<std::mutex> lock(ctx->mu);
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
-  for (int t = 0; t < count; ++t) {
-    d->token_pinned[t] = tokens[t];
+  {
+    const unsigned slot = d->token_slot++ % gufo::kTokenSlots;
+    int* staged = d->token_pinned + slot * gufo::kStepTokens;
+    GUFO_CUDA_TRY(cudaEventSynchronize(d->token_read[slot]));   // returns at once for a slot never used
+    for (int t = 0; t < count; ++t) {
+      staged[t] = tokens[t];
+    }
+    GUFO_CUDA_TRY(cudaMemcpyAsync(d->token_dev, staged, 4 * count, cudaMemcpyHostToDevice, ctx->stream));
+    GUFO_CUDA_TRY(cudaEventRecord(d->token_read[slot], ctx->stream));
   }
-  GUFO_CUDA_TRY(cudaMemcpyAsync(d->token_dev, d->token_pinned, 4 * count, cudaMemcpyHostToDevice, ctx->stream));
   const int parity = d->conv_cur;
   const int pair = count - 1, with = want_logits != 0 ? 1 : 0;
   auto enqueue = [&]() { return gufo::EnqueueStep(d, parity, with != 0, count); };
@@ -1200,9 +1223,9 @@ int gufo_cuda_decoder_resolve(gufo_cuda_decoder* d, int keep_second) {
                                     cudaMemcpyDeviceToDevice, ctx->stream));
     }
     --d->position;
-    d->token_pinned[gufo::kStepTokens] = d->position;
-    GUFO_CUDA_TRY(cudaMemcpyAsync(d->position_dev, d->token_pinned + gufo::kStepTokens, 4, cudaMemcpyHostToDevice,
-                                  ctx->stream));
+    int* word = d->token_pinned + gufo::kTokenSlots * gufo::kStepTokens;
+    *word = d->position;
+    GUFO_CUDA_TRY(cudaMemcpyAsync(d->position_dev, word, 4, cudaMemcpyHostToDevice, ctx->stream));
     // The pinned word is read when the copy runs: wait, so that a later
     // Resolve cannot overwrite it first.
     GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));

@@ -2,24 +2,24 @@
 // mma_common.cuh). The product is the reference's fused Q6_K row dot
 // (gguf_dot::DotQ6_K, src/models/qwen35/gguf_dot.hpp:203-290):
 //   y_r = sum_blocks d * sum_g sc_g * ((q - 32) . x)_g        g = 16-value groups
-// computed as d * [ sum_g sc_g (q . x)_g  -  32 * sum_g sc_g (sum x)_g ]: the
-// unsigned 6-bit codes go to the MMA as they are, the -32 meets the fp32 group
-// sums of x that the staged image carries.
+// The codes go to the MMA as the signed bytes 4 * (q - 32), so no offset term
+// is left; the factor 1/4 sits in the staged image's column factors.
 //
 // Rows are read from the planar device arrangement (common.cuh): a slab of
 // eight blocks is one contiguous 1680-byte run per row, copied to shared memory
-// with 16-byte asynchronous copies by the whole thread block, three slabs in
-// flight; warp w multiplies block w of the slab. The pipeline, the persistent
+// with 16-byte asynchronous copies by the whole thread block, a ring of kStages
+// slabs in flight; warp w multiplies block w of the slab. The pipeline, the persistent
 // grid and the exchange of partial sums are those of the Q4_K kernel
 // (gemv_q4k_mma.cu).
 //
-// MMA operand layout (m16n8k32, A row-major u8, B column-major s8). A 32-value
+// MMA operand layout (m16n8k32, A row-major s8, B column-major s8). A 32-value
 // run (quarter k of a half) holds two scale groups: values 0..15 and 16..31.
 // Lane (g, t) loads bytes 8t..8t+7 of the run's nibble and high-bit planes, so
-// lanes t = 0, 1 carry the first group and t = 2, 3 the second. Each run is
-// multiplied twice, against B fragments in which the other group's lanes read
-// a plane of zeros; every product then holds one group's 16 dots and takes
-// that group's int8 scale.
+// lanes t = 0, 1 carry the first group and t = 2, 3 the second. With several
+// tokens each run is multiplied twice, against B fragments in which the other
+// group's lanes read a plane of zeros; every product then holds one group's 16
+// dots and takes that group's int8 scale. One token leaves room for both groups
+// in the eight columns of a single product (MultiplyRun).
 #include <cooperative_groups.h>
 
 #include "mma_common.cuh"

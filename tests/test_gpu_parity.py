@@ -621,6 +621,23 @@ def test_decoder_pair_steps_and_resolve(ctx, golden, use_graph):
     dec.close()
 
 
+def test_decoder_steps_enqueued_without_waits_keep_their_tokens(ctx, golden):
+    """Steps that leave their logits on the device return before the device has run them; each
+    must still see its own token id (the host side stages ids in slots it reuses only after
+    the copy that read them has run)."""
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    dec = CudaDecoder(CudaProjections(ctx, cfg, tensors), tensors, max_positions=64, use_graph=True)
+    g = golden("decoder")
+    tokens = [int(t) for t in g["decoder_dense_tokens"]]
+    for _ in range(4):
+        dec.Reset()
+        for tok in tokens[:7]:
+            dec.step_device(tok)
+        assert rel_l2(dec.Step(tokens[7]), g["decoder_dense_logits"][7]) <= STEP_TOL
+    dec.close()
+
+
 def test_decoder_cache_capacity(ctx):
     cfg = synth.ModelConfig(**G.DENSE)
     tensors = synth.build_model(cfg, G.DENSE_SEED)
