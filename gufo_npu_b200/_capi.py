@@ -59,6 +59,16 @@ class AttentionArgs(C.Structure):
                                           "queries", "partials", "ctx_out")]
 
 
+class FusedInput(C.Structure):
+    """gufo_cuda_fused_input."""
+    _fields_ = [("prologue", C.c_int), ("x", C.c_void_p), ("residual", C.c_void_p), ("delta", C.c_void_p),
+                ("norm_weight", C.c_void_p), ("rms_eps", C.c_float), ("residual_out", C.c_void_p),
+                ("scratch", C.c_void_p), ("advance", C.c_void_p)]
+
+
+PROLOGUE_PLAIN, PROLOGUE_RES_NORM, PROLOGUE_SWIGLU = 0, 1, 2
+
+
 class DecoderConfig(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("layers", "hidden", "ffn", "vocab")] + [("rms_eps", C.c_float)] + \
                [(n, C.c_int) for n in ("full_attention_interval", "heads", "kv_heads", "head_dim", "rope_dim")] + \
@@ -112,6 +122,8 @@ SIGNATURES = {
     "gufo_cuda_matmul": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "gufo_cuda_matmul_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.c_void_p, C.c_int,
                                           C.c_void_p]),
+    "gufo_cuda_matmul_fused_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.POINTER(FusedInput), C.c_int,
+                                                C.c_void_p]),
     "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                                      C.c_int, C.c_void_p]),
     "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,

@@ -194,6 +194,20 @@ class Context:
         self._check(self.lib.gufo_cuda_matmul_device(self.handle, parts_arr, nparts, C.c_void_p(_ptr(x)), tokens,
                                                      C.c_void_p(_ptr(y))))
 
+    def matmul_fused_device(self, parts_arr, nparts: int, tokens: int, y, *, x=None, residual=None, delta=None,
+                            norm_weight=None, rms_eps: float = 0.0, residual_out=None, scratch=None,
+                            advance=None, swiglu: bool = False) -> None:
+        """A product with its input step fused in (npu::Q4nxGemv's Prologue options,
+        src/npu/gemv.hpp:58-68): plain `x`; `residual` (+ `delta`) through RMSNorm; or SwiGLU of
+        [gate | up] rows in `x`."""
+        kind = _capi.PROLOGUE_RES_NORM if residual is not None else (
+            _capi.PROLOGUE_SWIGLU if swiglu else _capi.PROLOGUE_PLAIN)
+        p = lambda t: C.c_void_p(_ptr(t)) if t is not None else None
+        args = _capi.FusedInput(kind, p(x), p(residual), p(delta), p(norm_weight), rms_eps, p(residual_out),
+                                p(scratch), p(advance))
+        self._check(self.lib.gufo_cuda_matmul_fused_device(self.handle, parts_arr, nparts, C.byref(args), tokens,
+                                                           C.c_void_p(_ptr(y))))
+
     # -- routed experts -------------------------------------------------------
     def route_device(self, router, stride: int, tokens: int, experts: int, k: int, chosen, weights,
                      shared_scale=None) -> None:

@@ -594,10 +594,8 @@ struct Input {
 // One stage's product for `tokens` rows with its input fused into the GEMV
 // kernels where every part allows it; otherwise the input is materialised by the
 // small kernels first. `scratch` holds the materialised / normed rows.
-int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y,
-                 int tokens) {
-  gufo_cuda_ctx* ctx = d->ctx;
-  const gufo_cuda_decoder_config& c = d->c;
+int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const Input& in, float* scratch,
+                 float* y, int tokens) {
   const dim3 block(kSmallThreads);
   bool fused = !ctx->force_general && stage.nparts <= kFastMaxParts;
   int fast_parts = 0;
@@ -620,7 +618,7 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
       for (int t = 0; t < tokens; ++t) {
         GUFO_CUDA_TRY(LaunchOverlapped(AddNormKernel, dim3(1), block, 0, ctx->stream, 1, in.h_in + t * cols,
                                        in.h_out + t * cols, in.delta != nullptr ? in.delta + t * cols : nullptr,
-                                       in.norm_w, c.rms_eps, stage.cols, scratch + t * cols, in.advance));
+                                       in.norm_w, rms_eps, stage.cols, scratch + t * cols, in.advance));
       }
       ctx->launches.fetch_add(tokens);
       x = scratch;
@@ -649,7 +647,7 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
     args.h_in = in.h_in;
     args.delta = in.delta;
     args.norm_w = in.norm_w;
-    args.eps = c.rms_eps;
+    args.eps = rms_eps;
     args.h_out = in.h_out;
     args.normed_out = in.prologue == kPrologueResNorm ? scratch : nullptr;
     for (int p = 0; p < stage.nparts; ++p) {
@@ -685,7 +683,11 @@ int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, f
   return GUFO_CUDA_OK;
 }
 
-// Enqueues one step's kernels; `parity` picks the conv window that is current.
+int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y,
+                 int tokens) {
+  return FusedProduct(d->ctx, d->c.rms_eps, stage, in, scratch, y, tokens);
+}
+
 // Records an event that closes a stage of kind `kind` (timeline mode only).
 void Mark(gufo_cuda_decoder* d, int kind) {
   if (!d->timeline) {
@@ -819,6 +821,59 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) 
 using gufo::Fail;
 
 extern "C" {
+
+int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts, int nparts,
+                                  const gufo_cuda_fused_input* in, int tokens, float* y) {
+  if (ctx == nullptr || parts == nullptr || in == nullptr || y == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: null pointer");
+  }
+  if (tokens < 1) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: at least one token");
+  }
+  gufo::Input input{gufo::kProloguePlain};
+  switch (in->prologue) {
+    case GUFO_CUDA_PROLOGUE_PLAIN:
+    case GUFO_CUDA_PROLOGUE_SWIGLU:
+      if (in->x == nullptr || (in->prologue == GUFO_CUDA_PROLOGUE_SWIGLU && in->scratch == nullptr)) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: x (and, for SwiGLU, scratch) must be given");
+      }
+      input.prologue = in->prologue == GUFO_CUDA_PROLOGUE_PLAIN ? gufo::kProloguePlain : gufo::kPrologueSwiGlu;
+      input.x = in->x;
+      break;
+    case GUFO_CUDA_PROLOGUE_RES_NORM:
+      if (in->residual == nullptr || in->norm_weight == nullptr || in->residual_out == nullptr ||
+          in->scratch == nullptr || in->residual_out == in->residual) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                    "matmul_fused: residual, norm_weight, scratch and a residual_out apart from residual");
+      }
+      input.prologue = gufo::kPrologueResNorm;
+      input.h_in = in->residual;
+      input.delta = in->delta;
+      input.norm_w = in->norm_weight;
+      input.h_out = in->residual_out;
+      input.advance = in->advance;
+      break;
+    default:
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: unknown prologue");
+  }
+  const float* rows[] = {in->x, in->residual, in->delta, in->norm_weight, in->residual_out, in->scratch};
+  for (const float* p : rows) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: rows must be 16-byte aligned");
+    }
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::GemvArgs stage;
+  const int rc = gufo::BuildGemvArgs(ctx, parts, nparts, &stage);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (stage.cols % 4 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matmul_fused: cols must be a multiple of 4");
+  }
+  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, y, tokens);
+}
 
 int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config* config,
                              const gufo_cuda_decoder_weights* weights, gufo_cuda_decoder** out) {

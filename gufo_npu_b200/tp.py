@@ -121,6 +121,8 @@ class TpDecoder:
         width = max(l["in"][3] for l in self.layers)
         z = lambda n: torch.zeros(n, device=dev)
         self.h, self.normed, self.out = z(c.hidden), z(c.hidden), z(c.hidden)
+        self.h_next = z(c.hidden)
+        self._residual = (self.h, self.h_next)
         self.full_in, self.mixed = z(width), z(max(c.value_dim, c.heads * c.head_dim))
         self.ffn, self.act, self.logits = z(2 * c.ffn), z(c.ffn), z(c.vocab)
         self.local = z(max(max(max(l[k][2] for k in ("in", "out", "ffn_in", "ffn_down")) for l in self.layers),
@@ -138,30 +140,42 @@ class TpDecoder:
     def _check(self, status):
         _capi.check(self.lib, self.ctx.handle, status)
 
-    def _product(self, prod, x, y_full):
-        """Local rows of a stage into self.local, then all-gather into y_full."""
-        arr, n, local, total = prod
-        self.ctx.matmul_device(arr, n, x, 1, self.local)
+    def _gather(self, prod, y_full):
+        _, _, local, total = prod
         if self.world == 1:
             y_full[:total].copy_(self.local[:local])
         else:
             dist.all_gather_into_tensor(y_full[:total], self.local[:local])
 
-    def _add_norm(self, delta, weight, advance=False):
-        c = self.cfg
-        self._check(self.lib.gufo_cuda_add_rms_norm_device(
-            self.ctx.handle, self.h.data_ptr(), delta.data_ptr() if delta is not None else None,
-            weight.data_ptr(), c.rms_eps, c.hidden, self.normed.data_ptr(),
-            self.position_dev.data_ptr() if advance else None))
+    def _product(self, prod, x, y_full, swiglu=False):
+        """Local rows of a stage into self.local (x plain, or [gate | up] rows through SwiGLU
+        inside the product), then all-gather into y_full."""
+        arr, n, _, _ = prod
+        if swiglu:
+            self.ctx.matmul_fused_device(arr, n, 1, self.local, x=x, swiglu=True, scratch=self.act)
+        else:
+            self.ctx.matmul_device(arr, n, x, 1, self.local)
+        self._gather(prod, y_full)
+
+    def _norm_product(self, prod, delta, weight, y_full, advance=False):
+        """The residual add + RMSNorm inside the product's kernels (the residual stream
+        alternates between two buffers), then the all-gather."""
+        arr, n, _, _ = prod
+        src, dst = self.h, self.h_next
+        self.ctx.matmul_fused_device(arr, n, 1, self.local, residual=src, delta=delta, norm_weight=weight,
+                                     rms_eps=self.cfg.rms_eps, residual_out=dst, scratch=self.normed,
+                                     advance=self.position_dev if advance else None)
+        self.h, self.h_next = dst, src
+        self._gather(prod, y_full)
 
     def enqueue(self, parity: int) -> None:
         c = self.cfg
         lib, h = self.lib, self.ctx.handle
+        self.h, self.h_next = self._residual   # every step starts in the same buffer (graphs keep addresses)
         self._check(lib.gufo_cuda_embed_device(h, self.embed, self.token_dev.data_ptr(), self.h.data_ptr()))
         pending = None
         for il, l in enumerate(self.layers):
-            self._add_norm(pending, l["attn_norm"])
-            self._product(l["in"], self.normed, self.full_in)
+            self._norm_product(l["in"], pending, l["attn_norm"], self.full_in)
             if c.is_full_attention(il):
                 args = _capi.AttentionArgs(c.heads, c.kv_heads, c.head_dim, c.rope_dim, self.max_positions, c.rms_eps,
                                            self.position_dev.data_ptr(), self.full_in.data_ptr(),
@@ -174,13 +188,10 @@ class TpDecoder:
                     "in": self.full_in, "conv_in": l["conv"][parity], "conv_out": l["conv"][parity ^ 1],
                     "ssm": l["ssm"], "y": self.mixed}])
             self._product(l["out"], self.mixed, self.out)
-            self._add_norm(self.out, l["post_norm"])
-            self._product(l["ffn_in"], self.normed, self.ffn)
-            self._check(lib.gufo_cuda_swiglu_device(h, self.ffn.data_ptr(), c.ffn, self.act.data_ptr()))
-            self._product(l["ffn_down"], self.act, self.out)
+            self._norm_product(l["ffn_in"], self.out, l["post_norm"], self.ffn)
+            self._product(l["ffn_down"], self.ffn, self.out, swiglu=True)
             pending = self.out
-        self._add_norm(pending, self.output_norm, advance=True)
-        self._product(self.lm_head, self.normed, self.logits)
+        self._norm_product(self.lm_head, pending, self.output_norm, self.logits, advance=True)
 
     def step(self, token: int, stream, use_graph: bool = True) -> torch.Tensor:
         """Runs `token` at the current position on every rank; returns the full logits (device)."""

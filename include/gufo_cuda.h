@@ -163,6 +163,43 @@ int gufo_cuda_matmul_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
                             int nparts, const float* device_x, int tokens,
                             float* device_y);
 
+/* A product with its input step fused into the GEMV kernels, for chains of
+ * products that never leave the device: the options of the reference's NPU GEMV
+ * (npu::Q4nxGemv::Run with npu::Prologue / npu::Epilogue, src/npu/gemv.hpp:
+ * 58-68,134-152), which its NPU decoders chain per layer
+ * (src/models/qwen35_2b/npu_decoder.cpp:558-628).
+ *   PLAIN     x rows as they are (Prologue::kPlain).
+ *   RES_NORM  x = RMSNorm(residual + delta) * norm_weight; residual + delta
+ *             also goes to residual_out (Prologue::kResNorm: "H + D also goes to
+ *             the residual buffer"); the normed rows land in scratch.
+ *   SWIGLU    x[i] = silu(g[i]) * u[i] over rows [g | u] of 2 * cols values: the
+ *             previous product's Epilogue::kSwiGlu met at this product's input
+ *             (Prologue::kAct), so the stacked gate / up product stores plain rows.
+ * Rows of `tokens` tokens follow one another (cols apart; 2 * cols for SWIGLU
+ * inputs). All pointers are 16-byte aligned device pointers. Q4_K and Q6_K parts
+ * take the fused kernels when the rows fit their shared-memory image (up to
+ * eight tokens; fewer for wide rows); other parts, or more rows, read the
+ * materialised rows from scratch. */
+enum {
+  GUFO_CUDA_PROLOGUE_PLAIN = 0,
+  GUFO_CUDA_PROLOGUE_RES_NORM = 1,
+  GUFO_CUDA_PROLOGUE_SWIGLU = 2
+};
+typedef struct gufo_cuda_fused_input {
+  int prologue;
+  const float* x;            /* PLAIN: [tokens][cols]; SWIGLU: [tokens][2 * cols] */
+  const float* residual;     /* RES_NORM: H, [tokens][cols] */
+  const float* delta;        /* RES_NORM: D, [tokens][cols] (may be NULL) */
+  const float* norm_weight;  /* RES_NORM: [cols] */
+  float rms_eps;
+  float* residual_out;       /* RES_NORM: H + D, [tokens][cols]; not the same buffer as residual */
+  float* scratch;            /* RES_NORM, SWIGLU: [tokens][cols], the product's input rows */
+  int* advance;              /* RES_NORM: an int counter incremented by `tokens` (may be NULL) */
+} gufo_cuda_fused_input;
+int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
+                                  int nparts, const gufo_cuda_fused_input* input,
+                                  int tokens, float* device_y);
+
 /* The Q4_K product for callers that must not allocate device memory while
  * they run: code inside a region where cudaMalloc is off limits (a stream that
  * is being captured, a latency-critical loop) or a host that has handed the

@@ -176,6 +176,73 @@ def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
         ctx.matrix_free(m)
 
 
+@pytest.mark.parametrize("tokens", [1, 2, 3, 9])
+@pytest.mark.parametrize("cols", [768, 6144])
+def test_fused_products_match_the_separate_steps(ctx, oracle, tokens, cols):
+    """gufo_cuda_matmul_fused_device (the reference's npu::Prologue options, src/npu/gemv.hpp:58-68):
+    the residual add + RMSNorm and the SwiGLU done inside the product against numpy's, the product
+    against the oracle's fused row dots on those inputs. Q4_K and Q6_K parts with an F32 part
+    beside them; 9 tokens take the path that materialises the rows."""
+    from gufo_npu_b200._capi import GufoCudaError
+    dev = torch.device("cuda:0")
+    rows, eps = 80, 1e-6
+    raws = {"q4": Q.quantize(Q.GGML_Q4_K, torch.from_numpy(G.normal(70, rows, cols) * 0.02)).numpy(),
+            "q6": Q.quantize(Q.GGML_Q6_K, torch.from_numpy(G.normal(71, rows, cols) * 0.02)).numpy(),
+            "f32": (G.normal(72, 8, cols) * 0.05).astype(np.float32)}
+    types = {"q4": Q.GGML_Q4_K, "q6": Q.GGML_Q6_K, "f32": Q.GGML_F32}
+    nrows = {"q4": rows, "q6": rows, "f32": 8}
+    mats = {k: ctx.matrix_upload(types[k], raws[k], nrows[k], cols) for k in raws}
+    listing = [(mats[k], 0, nrows[k]) for k in ("q4", "q6", "f32")]
+    oracle_parts = [(raws[k].view(np.uint8) if k == "f32" else raws[k], types[k], 0, nrows[k])
+                    for k in ("q4", "q6", "f32")]
+    parts = Context._parts(listing)
+    total = sum(nrows.values())
+    up = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
+    y = torch.empty(tokens, total, device=dev)
+    scratch = torch.empty(tokens, cols, device=dev)
+    # Residual + delta through RMSNorm.
+    h, delta, w = G.normal(73, tokens, cols), G.normal(74, tokens, cols) * 0.3, G.normal(75, cols) * 0.2 + 1.0
+    h_out = torch.empty(tokens, cols, device=dev)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    ctx.matmul_fused_device(parts, len(listing), tokens, y, residual=up(h), delta=up(delta), norm_weight=up(w),
+                            rms_eps=eps, residual_out=h_out, scratch=scratch, advance=counter)
+    ctx.synchronize()
+    total_h = (h + delta).astype(np.float32)
+    normed = (total_h / np.sqrt((total_h.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + eps) * w).astype(np.float32)
+    assert np.array_equal(h_out.cpu().numpy(), total_h)
+    assert rel_l2(scratch.cpu().numpy(), normed) <= 1e-6
+    assert int(counter.item()) == tokens
+    assert rel_l2(y.cpu().numpy(), oracle.matmul(oracle_parts, cols, normed)) <= 1e-5
+    # Without a pending add the residual passes through.
+    ctx.matmul_fused_device(parts, len(listing), tokens, y, residual=up(h), norm_weight=up(w), rms_eps=eps,
+                            residual_out=h_out, scratch=scratch)
+    ctx.synchronize()
+    assert np.array_equal(h_out.cpu().numpy(), h.astype(np.float32))
+    # SwiGLU of [gate | up] rows (the F32 part sends the product down the materialising path).
+    gu = G.normal(76, tokens, 2 * cols)
+    act = (gu[:, :cols] / (1.0 + np.exp(-gu[:, :cols].astype(np.float64))) * gu[:, cols:]).astype(np.float32)
+    for picked, oparts in ((listing[:2], oracle_parts[:2]), (listing, oracle_parts)):
+        width = sum(p[2] for p in picked)
+        out = torch.empty(tokens, width, device=dev)
+        ctx.matmul_fused_device(Context._parts(picked), len(picked), tokens, out, x=up(gu), swiglu=True, scratch=scratch)
+        ctx.synchronize()
+        assert rel_l2(out.cpu().numpy(), oracle.matmul(oparts, cols, act)) <= 1e-5
+    # Plain rows: the same as the ordinary product.
+    x = G.normal(77, tokens, cols)
+    ctx.matmul_fused_device(parts, len(listing), tokens, y, x=up(x))
+    ctx.synchronize()
+    assert rel_l2(y.cpu().numpy(), ctx.matmul(listing, x, tokens, total)) <= 1e-6
+    # Refusals: residual_out on top of residual; a missing scratch.
+    same = up(h)
+    with pytest.raises(GufoCudaError):
+        ctx.matmul_fused_device(parts, len(listing), tokens, y, residual=same, norm_weight=up(w), rms_eps=eps,
+                                residual_out=same, scratch=scratch)
+    with pytest.raises(GufoCudaError):
+        ctx.matmul_fused_device(parts, len(listing), tokens, y, x=up(gu), swiglu=True)
+    for m in mats.values():
+        ctx.matrix_free(m)
+
+
 def test_empty_and_bad_products(ctx):
     from gufo_npu_b200._capi import GufoCudaError
     raw = Q.random_blocks(Q.GGML_Q4_K, 8, 256, seed=1).numpy()
