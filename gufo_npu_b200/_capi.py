@@ -67,6 +67,8 @@ class FusedInput(C.Structure):
 
 
 PROLOGUE_PLAIN, PROLOGUE_RES_NORM, PROLOGUE_SWIGLU = 0, 1, 2
+IPC_HANDLE_BYTES = 64
+PEER_HEADER_BYTES = 4096
 
 
 class DecoderConfig(C.Structure):
@@ -124,6 +126,12 @@ SIGNATURES = {
                                           C.c_void_p]),
     "gufo_cuda_matmul_fused_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.POINTER(FusedInput), C.c_int,
                                                 C.c_void_p]),
+    "gufo_cuda_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "gufo_cuda_peer_group_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p,
+                                              C.POINTER(C.c_void_p)]),
+    "gufo_cuda_peer_group_destroy": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_peer_allgather_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]),
+    "gufo_cuda_peer_group_status": (C.c_int, [C.c_void_p]),
     "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                                      C.c_int, C.c_void_p]),
     "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,

@@ -263,6 +263,66 @@ def _shape_error(name: str, shape, want) -> RuntimeError:
     return RuntimeError(f"qwen35: tensor {name} has shape {list(shape)}, expected {list(want)}")
 
 
+class _DeviceArray:
+    """A window of device memory for torch.as_tensor (the CUDA array interface)."""
+
+    def __init__(self, ptr: int, floats: int):
+        self.__cuda_array_interface__ = {"shape": (floats,), "typestr": "<f4", "data": (ptr, False), "version": 3,
+                                         "strides": None}
+
+
+class PeerGroup:
+    """The ranks of a row-split step sharing their output vectors over NVLink peer memory
+    (gufo_cuda_peer_group). Every rank constructs it with the same `arena_floats` and asks for
+    the same buffers in the same order, so that a vector sits at one offset on every rank.
+    `exchange(handle_bytes) -> [handle_bytes per rank]` is the host's all-gather of the IPC
+    handles (torch.distributed.all_gather_object, for one)."""
+
+    def __init__(self, ctx: Context, rank: int, world: int, arena_floats: int, exchange):
+        import torch
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.bytes = _capi.PEER_HEADER_BYTES + 4 * arena_floats
+        self.arena = ctx.malloc(self.bytes)
+        handle = (C.c_ubyte * _capi.IPC_HANDLE_BYTES)()
+        ctx._check(ctx.lib.gufo_cuda_ipc_export(ctx.handle, C.c_void_p(self.arena), handle))
+        handles = exchange(bytes(handle))
+        assert len(handles) == world and all(len(h) == _capi.IPC_HANDLE_BYTES for h in handles)
+        packed = (C.c_ubyte * (world * _capi.IPC_HANDLE_BYTES)).from_buffer_copy(b"".join(handles))
+        out = C.c_void_p()
+        ctx._check(ctx.lib.gufo_cuda_peer_group_create(ctx.handle, rank, world, C.c_void_p(self.arena), self.bytes,
+                                                       packed, C.byref(out)))
+        self.handle = out
+        self._next = _capi.PEER_HEADER_BYTES
+        self._torch = torch
+
+    def buffer(self, floats: int):
+        """The next `floats` values of the arena as a torch tensor (256-byte aligned)."""
+        offset = self._next
+        self._next = (offset + 4 * floats + 255) // 256 * 256
+        if self._next > self.bytes:
+            raise ValueError("peer arena exhausted")
+        view = self._torch.as_tensor(_DeviceArray(self.arena + offset, floats),
+                                     device=self._torch.device("cuda", self.ctx.device))
+        view.zero_()
+        return view
+
+    def offset_of(self, tensor) -> int:
+        return tensor.data_ptr() - self.arena
+
+    def allgather(self, local, full, slice_floats: int) -> None:
+        """Rank r's first `slice_floats` values of `local` to full[r * slice : (r + 1) * slice] on every rank."""
+        self.ctx._check(self.ctx.lib.gufo_cuda_peer_allgather_device(self.handle, C.c_void_p(_ptr(local)),
+                                                                     self.offset_of(full), slice_floats))
+
+    def status(self) -> None:
+        self.ctx._check(self.ctx.lib.gufo_cuda_peer_group_status(self.handle))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.ctx.lib.gufo_cuda_peer_group_destroy(self.handle)
+            self.handle = None
+
+
 class CudaProjections:
     """The matrix products of a Qwen3.5 forward pass on the device.
 

@@ -62,8 +62,11 @@ class TpDecoder:
     """One rank of the row-split decode step (dense models)."""
 
     def __init__(self, ctx, cfg: ModelConfig, tensors: Dict[str, Tensor], rank: int, world: int,
-                 max_positions: int = 4096):
+                 max_positions: int = 4096, collective: str = "peer"):
+        """`collective`: "peer" gathers with this library's kernel over NVLink peer memory
+        (gufo_cuda_peer_allgather_device), "nccl" with torch.distributed's all-gather."""
         self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
+        self.collective = collective if world > 1 else "none"
         self.lib = ctx.lib
         dev = torch.device("cuda", ctx.device)
         self.dev = dev
@@ -120,11 +123,27 @@ class TpDecoder:
         self.max_positions = max_positions
         width = max(l["in"][3] for l in self.layers)
         z = lambda n: torch.zeros(n, device=dev)
-        self.h, self.normed, self.out = z(c.hidden), z(c.hidden), z(c.hidden)
+        self.h, self.normed = z(c.hidden), z(c.hidden)
         self.h_next = z(c.hidden)
         self._residual = (self.h, self.h_next)
-        self.full_in, self.mixed = z(width), z(max(c.value_dim, c.heads * c.head_dim))
-        self.ffn, self.act, self.logits = z(2 * c.ffn), z(c.ffn), z(c.vocab)
+        self.mixed = z(max(c.value_dim, c.heads * c.head_dim))
+        self.act = z(c.ffn)
+        # The vectors every rank needs whole: in the peer arena when this library gathers them.
+        full_sizes = (width, c.hidden, 2 * c.ffn, c.vocab)
+        self.peers = None
+        if self.collective == "peer":
+            from .backend import PeerGroup
+
+            def exchange(handle):
+                handles = [None] * world
+                dist.all_gather_object(handles, handle)
+                return handles
+            self.peers = PeerGroup(ctx, rank, world, sum(n + 64 for n in full_sizes), exchange)
+            full = self.peers.buffer
+            dist.barrier()   # every rank's flags are zero before anyone gathers
+        else:
+            full = z
+        self.full_in, self.out, self.ffn, self.logits = (full(n) for n in full_sizes)
         self.local = z(max(max(max(l[k][2] for k in ("in", "out", "ffn_in", "ffn_down")) for l in self.layers),
                            self.lm_head[2]))
         self.queries = z(c.heads * c.head_dim)
@@ -144,6 +163,8 @@ class TpDecoder:
         _, _, local, total = prod
         if self.world == 1:
             y_full[:total].copy_(self.local[:local])
+        elif self.peers is not None:
+            self.peers.allgather(self.local, y_full, local)
         else:
             dist.all_gather_into_tensor(y_full[:total], self.local[:local])
 
@@ -233,7 +254,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64)
     del tensors
     rng = np.random.default_rng(7)
-    tokens = iter(rng.integers(0, cfg.vocab, size=4 * (steps + warmup) + 16).tolist())
+    tokens = iter(rng.integers(0, cfg.vocab, size=6 * (steps + warmup) + 16).tolist())
     host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
     for _ in range(warmup):
         dec.step(next(tokens), stream)
@@ -261,6 +282,15 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         host.copy_(logits, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     ms_e2e = timed(e2e_step)
+    if dec.peers is not None:
+        dec.peers.status()   # raises if a wait for a peer's flag ran out
+    # The same step with NCCL's all-gather in place of the peer-memory kernel, for comparison.
+    by_nccl = TpDecoder(ctx, cfg, synth.build_model(cfg, seed=1, device=f"cuda:{local}"), rank, world,
+                        max_positions=2 * (steps + warmup) + 64, collective="nccl")
+    for _ in range(warmup):
+        by_nccl.step(next(tokens), stream)
+    torch.cuda.synchronize()
+    ms_nccl = timed(lambda: by_nccl.step(next(tokens), stream))
     # For context beside the row-split number: the same GPUs as independent replicas, every rank
     # decoding its own sequence with the single-GPU resident decoder at the same time (no
     # collective on the data path). Timed the same way: barrier, device events, max over ranks.
@@ -280,7 +310,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
             "data": "synthetic",
             "config": {"workload": workload, "seed": 1, "parallelism": f"tp{world}: projections row-split, "
-                       f"{dec.gathers_per_step} NCCL all-gathers per step, mixers replicated",
+                       f"{dec.gathers_per_step} all-gathers per step by this library's kernel over NVLink peer "
+                       f"memory (CUDA IPC), mixers replicated; NCCL all-gathers instead: {ms_nccl:.3f} ms per step",
                        "l2": "weights exceed L2; no flush needed"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},
@@ -295,6 +326,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     # Captured graphs hold NCCL kernels: release them before the communicator goes away, and
     # leave without the collective teardown (it blocked here while graphs were alive).
     dec.graphs.clear()
+    by_nccl.graphs.clear()
     import sys
     sys.stdout.flush()
     sys.stderr.flush()

@@ -423,6 +423,39 @@ int gufo_cuda_moe_combine_device(gufo_cuda_ctx* ctx, const float* shared,
                                  const float* expert_out, int tokens, int k,
                                  int hidden, float* out);
 
+/* ---- row-split ranks: all-gather over NVLink peer memory ------------------- */
+
+/* For hosts that split a stage's rows over several GPUs (one process per GPU)
+ * and need every rank to see the whole output vector: each rank stores its
+ * slice straight into every rank's copy of the vector over NVLink and raises a
+ * flag there, one small kernel per gather on the context's stream (it can be
+ * captured in a CUDA graph). The reference has no counterpart (it runs on one
+ * accelerator); the products it follows are Projections::Apply's.
+ *
+ * Every rank allocates an arena of the same size with gufo_cuda_malloc, exports
+ * it (gufo_cuda_ipc_export), exchanges the 64-byte handles by its own means, and
+ * creates the group from all ranks' handles in rank order (its own entry is
+ * ignored). The first GUFO_CUDA_PEER_HEADER_BYTES of an arena belong to the
+ * group; full vectors live behind them at the same offset on every rank. All
+ * ranks must have created their group before any of them gathers. A flag that
+ * does not arrive within about four seconds ends the wait:
+ * gufo_cuda_peer_group_status then returns GUFO_CUDA_TIMEOUT. */
+#define GUFO_CUDA_IPC_HANDLE_BYTES 64
+#define GUFO_CUDA_PEER_HEADER_BYTES 4096
+typedef struct gufo_cuda_peer_group gufo_cuda_peer_group;
+int gufo_cuda_ipc_export(gufo_cuda_ctx* ctx, const void* device_ptr, void* handle);
+int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world,
+                                void* own_arena, size_t arena_bytes,
+                                const void* handles, gufo_cuda_peer_group** out);
+int gufo_cuda_peer_group_destroy(gufo_cuda_peer_group* group);
+/* Rank r's `slice_floats` values at local_src land at arena_offset (bytes) +
+ * r * slice_floats * 4 in every rank's arena; returns once enqueued. The kernel
+ * ends when the slices of all ranks have arrived in this rank's arena. */
+int gufo_cuda_peer_allgather_device(gufo_cuda_peer_group* group,
+                                    const float* local_src, size_t arena_offset,
+                                    size_t slice_floats);
+int gufo_cuda_peer_group_status(gufo_cuda_peer_group* group);
+
 /* ---- device-resident decode step ---------------------------------------- */
 
 /* Shape of a Qwen3.5-family model: the fields of qwen35::Config

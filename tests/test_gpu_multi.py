@@ -57,13 +57,21 @@ def _checks(rank, world, port, out):
         # Row-split decode step against the committed logits of the reference's Decoder::Step.
         cfg = synth.ModelConfig(**G.DENSE)
         tensors = synth.build_model(cfg, G.DENSE_SEED)
-        dec = TpDecoder(ctx, cfg, tensors, rank=rank, world=world, max_positions=32)
+        # Gathers by this library's kernel over NVLink peer memory, and by NCCL: the same rows
+        # travel either way, so the logits agree bit for bit; graphs replay from the third step.
+        dec = TpDecoder(ctx, cfg, tensors, rank=rank, world=world, max_positions=32, collective="peer")
+        by_nccl = TpDecoder(ctx, cfg, tensors, rank=rank, world=world, max_positions=32, collective="nccl")
         g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "decoder.npz"))
         for i, tok in enumerate(int(t) for t in g["decoder_dense_tokens"]):
             logits = dec.step(tok, stream).cpu().numpy()
             err = rel_l2(logits, g["decoder_dense_logits"][i])
             if err > STEP_TOL:
                 failures.append(("tp logits", i, err))
+            other = by_nccl.step(tok, stream).cpu().numpy()
+            if not np.array_equal(logits, other):
+                failures.append(("peer gather differs from NCCL's", i, rel_l2(logits, other)))
+        if dec.peers is not None:
+            dec.peers.status()   # raises if a wait for a peer's flag ran out
         # Expert parallelism against one device with every expert.
         mcfg = synth.ModelConfig(**G.MOE)
         mtensors = synth.build_model(mcfg, G.MOE_SEED)
