@@ -138,11 +138,20 @@ class TpDecoder:
                 handles = [None] * world
                 dist.all_gather_object(handles, handle)
                 return handles
-            self.peers = PeerGroup(ctx, rank, world, sum(n + 64 for n in full_sizes), exchange)
-            full = self.peers.buffer
-            dist.barrier()   # every rank's flags are zero before anyone gathers
-        else:
-            full = z
+            try:
+                self.peers = PeerGroup(ctx, rank, world, sum(n + 64 for n in full_sizes), exchange)
+            except Exception as e:   # noqa: BLE001 - e.g. a box whose GPUs cannot open each other's memory
+                print(f"rank {rank}: no peer-memory group ({e}); gathering with NCCL", flush=True)
+            # Every rank or none: the ranks agree before anyone gathers (the reduction is also the
+            # barrier after which all flags are zero).
+            ok = torch.tensor([1 if self.peers is not None else 0], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) == 0:
+                if self.peers is not None:
+                    self.peers.close()
+                self.peers = None
+                self.collective = "nccl"
+        full = self.peers.buffer if self.peers is not None else z
         self.full_in, self.out, self.ffn, self.logits = (full(n) for n in full_sizes)
         self.local = z(max(max(max(l[k][2] for k in ("in", "out", "ffn_in", "ffn_down")) for l in self.layers),
                            self.lm_head[2]))
@@ -310,8 +319,10 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
             "data": "synthetic",
             "config": {"workload": workload, "seed": 1, "parallelism": f"tp{world}: projections row-split, "
-                       f"{dec.gathers_per_step} all-gathers per step by this library's kernel over NVLink peer "
-                       f"memory (CUDA IPC), mixers replicated; NCCL all-gathers instead: {ms_nccl:.3f} ms per step",
+                       f"{dec.gathers_per_step} all-gathers per step by "
+                       + ("this library's kernel over NVLink peer memory (CUDA IPC)" if dec.peers is not None
+                          else "NCCL (no peer-memory group on this box)")
+                       + f", mixers replicated; NCCL all-gathers instead: {ms_nccl:.3f} ms per step",
                        "l2": "weights exceed L2; no flush needed"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},
