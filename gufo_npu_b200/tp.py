@@ -3,13 +3,14 @@
 Every output row of a projection is an independent dot product
 (src/models/qwen35/gguf_projections.cpp:241-243 in the reference), so a stage's stacked rows
 are cut into `world` equal runs; rank r computes run r with this backend's GEMV kernels and an
-NCCL all-gather over NVLink rebuilds the full vector on every rank. The mixers, norms and
+all-gather over NVLink rebuilds the full vector on every rank: this library's own kernel over
+peer memory (gufo_cuda_peer_allgather_device), or NCCL's. The mixers, norms and
 activations between the products run replicated (they need the full vectors and are a few
 percent of a step's bytes). The reference itself has no distributed execution; this module is
 new work on top of its operator interface.
 
-One process per GPU (torch.distributed, backend "nccl"); the step is captured once per conv
-parity into a CUDA graph, collectives included.
+One process per GPU (torch.distributed, backend "nccl", for the rendezvous and the comparison
+path); the step is captured once per conv parity into a CUDA graph, gathers included.
 """
 from __future__ import annotations
 
@@ -141,7 +142,8 @@ class TpDecoder:
             try:
                 self.peers = PeerGroup(ctx, rank, world, sum(n + 64 for n in full_sizes), exchange)
             except Exception as e:   # noqa: BLE001 - e.g. a box whose GPUs cannot open each other's memory
-                print(f"rank {rank}: no peer-memory group ({e}); gathering with NCCL", flush=True)
+                import sys
+                print(f"rank {rank}: no peer-memory group ({e}); gathering with NCCL", file=sys.stderr, flush=True)
             # Every rank or none: the ranks agree before anyone gathers (the reduction is also the
             # barrier after which all flags are zero).
             ok = torch.tensor([1 if self.peers is not None else 0], device=dev)
@@ -274,7 +276,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         try:
             dec.peers.status()
         except Exception as e:   # noqa: BLE001
-            print(f"rank {rank}: {e}", flush=True)
+            import sys
+            print(f"rank {rank}: {e}", file=sys.stderr, flush=True)
             healthy = 0
     agreed = torch.tensor([healthy], device=f"cuda:{local}")
     dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
