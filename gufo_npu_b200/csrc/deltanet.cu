@@ -65,7 +65,7 @@ struct DeltaShared {
   float v[kMaxHeadDim];
   float y[kMaxHeadDim];
   float gate[2];                              // decay, beta
-  float scratch[kDeltaThreads / 32];
+  float scratch[2 * (kDeltaThreads / 32)];
 };
 
 struct StateTile {
@@ -214,6 +214,24 @@ __device__ __forceinline__ float BlockSum(float v, DeltaShared& sh, int warps) {
   return total;
 }
 
+// Block-wide sums of two values per thread at once; results to every thread.
+__device__ __forceinline__ void BlockSum2(float& a, float& b, DeltaShared& sh, int warps) {
+  a = WarpSum(a);
+  b = WarpSum(b);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+    sh.scratch[2 * (threadIdx.x >> 5)] = a;
+    sh.scratch[2 * (threadIdx.x >> 5) + 1] = b;
+  }
+  __syncthreads();
+  a = 0.f;
+  b = 0.f;
+  for (int w = 0; w < warps; ++w) {
+    a += sh.scratch[2 * w];
+    b += sh.scratch[2 * w + 1];
+  }
+}
+
 // Mixer::Linear for one (sequence, value head). grid = (value_heads,
 // sequences), dk threads: thread t owns channel / column t of the head.
 __global__ void __launch_bounds__(kDeltaThreads)
@@ -235,18 +253,6 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const float* x = seq.in;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
   StateTile state_tile;
-  GridLaunchDependents();
-  if (args.early_state) {
-    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
-  }
-  GridDependencyWait();
-  if (!args.early_state) {
-    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
-  }
-  // What the epilogue needs, requested now so that it has arrived by then.
-  const float z = x[channels + head * dk + tid];
-  const float norm_w = args.ssm_norm[tid];
-
   // Causal depthwise conv + SiLU of channel ch; also advances that channel's
   // window when this block is the one that owns it. All loads of the three
   // channels are issued before the first store, so they overlap.
@@ -256,17 +262,26 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     float old[kMaxWindow];
     float w[kMaxWindow + 1];
   };
-  auto fetch = [&](int ch, Taps& taps) {
+  // The layer's weights never depend on the kernels before this one.
+  auto fetch_weights = [&](int ch, Taps& taps) {
     const float* kw = args.conv + static_cast<size_t>(ch) * kernel;
-    taps.cur = x[ch];
 #pragma unroll
     for (int t = 0; t < kMaxWindow; ++t) {
       if (t < window) {
-        taps.old[t] = seq.conv_in[static_cast<size_t>(t) * channels + ch];
         taps.w[t] = kw[t];
       }
     }
     taps.w[kMaxWindow] = kw[window];
+  };
+  // The window is state: written a step ago (early_state) or by the launch
+  // just before this one.
+  auto fetch_window = [&](int ch, Taps& taps) {
+#pragma unroll
+    for (int t = 0; t < kMaxWindow; ++t) {
+      if (t < window) {
+        taps.old[t] = seq.conv_in[static_cast<size_t>(t) * channels + ch];
+      }
+    }
   };
   auto conv = [&](int ch, const Taps& taps, bool owner) -> float {
     float acc = taps.w[kMaxWindow] * taps.cur;
@@ -286,22 +301,58 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   };
   // The window of the key head's q and k channels is advanced by the first
   // value head that reads the key head; every head advances its own v.
+  const int ch_q = kh * dk + tid, ch_k = key_dim + kh * dk + tid, ch_v = 2 * key_dim + head * dk + tid;
   Taps tq, tk, tv;
-  fetch(kh * dk + tid, tq);
-  fetch(key_dim + kh * dk + tid, tk);
-  fetch(2 * key_dim + head * dk + tid, tv);
+  // The first passes of the head's alpha and beta rows (weights as well).
+  constexpr int kGateAhead = 4;
+  const DeltaNetGateRows& g = args.gate_rows;
+  const bool gate_rows = g.alpha_w != nullptr;
+  const float4* wa = reinterpret_cast<const float4*>(g.alpha_w + static_cast<size_t>(head) * g.cols);
+  const float4* wb = reinterpret_cast<const float4*>(g.beta_w + static_cast<size_t>(head) * g.cols);
+  float4 wa_ahead[kGateAhead], wb_ahead[kGateAhead];
+  GridLaunchDependents();
+  if (args.early_state) {
+    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+    fetch_window(ch_q, tq);
+    fetch_window(ch_k, tk);
+    fetch_window(ch_v, tv);
+  }
+  fetch_weights(ch_q, tq);
+  fetch_weights(ch_k, tk);
+  fetch_weights(ch_v, tv);
+  if (gate_rows) {
+#pragma unroll
+    for (int j = 0; j < kGateAhead; ++j) {
+      const int i = tid + j * dk;
+      if (i < g.cols / 4) {
+        wa_ahead[j] = wa[i];
+        wb_ahead[j] = wb[i];
+      }
+    }
+  }
+  const float norm_w = args.ssm_norm[tid];
+  const float ssm_a = args.ssm_a[head], dt_bias = args.dt_bias[head];
+  GridDependencyWait();
+  if (!args.early_state) {
+    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+    fetch_window(ch_q, tq);
+    fetch_window(ch_k, tk);
+    fetch_window(ch_v, tv);
+  }
+  // What the epilogue needs, requested now so that it has arrived by then.
+  const float z = x[channels + head * dk + tid];
+  tq.cur = x[ch_q];
+  tk.cur = x[ch_k];
+  tv.cur = x[ch_v];
   float alpha, beta;
-  if (args.gate_rows.alpha_w != nullptr) {
+  if (gate_rows) {
     // The head's alpha and beta rows against the normed input, one float4 per
     // thread and pass (GgufProjections serves these F32 rows through its own
     // dot, src/models/qwen35/gguf_projections.cpp:162-170). With norm weights
     // the input is the residual stream and the RMS norm is applied on the way
     // (DeltaNetStep::Run, src/models/qwen35_2b/deltanet.cpp:358-392).
-    const DeltaNetGateRows& g = args.gate_rows;
     const float* gx = args.gate_x[blockIdx.y] != nullptr ? args.gate_x[blockIdx.y] : g.x;
     const float4* xa = reinterpret_cast<const float4*>(gx);
-    const float4* wa = reinterpret_cast<const float4*>(g.alpha_w + static_cast<size_t>(head) * g.cols);
-    const float4* wb = reinterpret_cast<const float4*>(g.beta_w + static_cast<size_t>(head) * g.cols);
     float inv = 1.0f;
     if (g.norm_w != nullptr) {
       float sq = 0.f;
@@ -312,34 +363,43 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
       inv = 1.0f / sqrtf(BlockSum(sq, sh, warps) / static_cast<float>(g.cols) + g.eps);
     }
     float pa = 0.f, pb = 0.f;
-    for (int i = tid; i < g.cols / 4; i += dk) {
+    auto pass = [&](int i, const float4& av, const float4& bv) {
       float4 xv = xa[i];
       if (g.norm_w != nullptr) {
         const float4 nw = reinterpret_cast<const float4*>(g.norm_w)[i];
         xv = make_float4(xv.x * inv * nw.x, xv.y * inv * nw.y, xv.z * inv * nw.z, xv.w * inv * nw.w);
       }
-      const float4 av = wa[i], bv = wb[i];
       pa += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
       pb += bv.x * xv.x + bv.y * xv.y + bv.z * xv.z + bv.w * xv.w;
+    };
+#pragma unroll
+    for (int j = 0; j < kGateAhead; ++j) {
+      const int i = tid + j * dk;
+      if (i < g.cols / 4) {
+        pass(i, wa_ahead[j], wb_ahead[j]);
+      }
     }
-    alpha = BlockSum(pa, sh, warps);
-    beta = BlockSum(pb, sh, warps);
+    for (int i = tid + kGateAhead * dk; i < g.cols / 4; i += dk) {
+      pass(i, wa[i], wb[i]);
+    }
+    BlockSum2(pa, pb, sh, warps);
+    alpha = pa;
+    beta = pb;
   } else {
     const float* gates = x + channels + value_dim;  // alpha | beta follow z
     alpha = gates[head];
     beta = gates[hv + head];
   }
-  const float ssm_a = args.ssm_a[head], dt_bias = args.dt_bias[head];
-  const float qv = conv(kh * dk + tid, tq, head < hk);
-  const float kv = conv(key_dim + kh * dk + tid, tk, head < hk);
-  sh.v[tid] = conv(2 * key_dim + head * dk + tid, tv, true);
+  const float qv = conv(ch_q, tq, head < hk);
+  const float kv = conv(ch_k, tk, head < hk);
+  sh.v[tid] = conv(ch_v, tv, true);
   if (tid == 0) {
     sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
     sh.gate[1] = Sigmoid(beta);
   }
   // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
-  const float qq = BlockSum(qv * qv, sh, warps);
-  const float kk = BlockSum(kv * kv, sh, warps);
+  float qq = qv * qv, kk = kv * kv;
+  BlockSum2(qq, kk, sh, warps);
   sh.q[tid] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
   sh.k[tid] = kv * (1.0f / sqrtf(kk + 1e-6f));
   __syncthreads();
