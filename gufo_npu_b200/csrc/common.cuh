@@ -177,8 +177,9 @@ int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 // Whether the image of `tokens` rows of `cols` values fits in shared memory.
 bool Q4KFastFits(int cols, int tokens);
 // One Mixer::Linear step per sequence; the caller holds ctx->mu.
-// `early_state`: the states and conv windows were not written by the kernels just before this
-// one in the stream, so their loads may run ahead of the dependency wait.
+// `early_state`: the states and conv windows were not written by the kernels
+// shortly before this one in the stream (several may be in flight at once), so
+// their loads may run ahead of the dependency wait.
 // The F32 alpha / beta rows of a DeltaNet layer's input product, for a step
 // that computes the two gates inside the mixer kernel instead of reading them
 // from the product's output: a = alpha_w[head] . x, b = beta_w[head] . x.

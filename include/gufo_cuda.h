@@ -79,9 +79,10 @@ const char* gufo_cuda_last_error(const gufo_cuda_ctx* ctx);
 /* Tuning and test switches, by name. "general_gemv" = 1 routes every product
  * through the general (non tensor-core) kernel; 0 (default) picks per part.
  * "deltanet_early_state" = 1 is the caller's promise that the DeltaNet states
- * and conv windows it passes were not written by the two kernels enqueued just
- * before the call (true when each is touched once per decode step): the kernels
- * then request them ahead of their dependency on the previous kernel.
+ * and conv windows it passes were not written by the kernels enqueued shortly
+ * before the call (true when each is touched once per decode step; kernels
+ * launch ahead of one another, so "shortly" is a handful of launches): the
+ * kernels then request them ahead of their dependency on the previous kernel.
  * "tc_gemm" = 1 (default) runs products of many token rows (32 for Q4_K, 48 for
  * Q6_K parts) on the tcgen05 GEMM, 0 keeps them on the 8-token passes of the
  * GEMV kernels, 2 sends every product of 16 or more rows to the GEMM.
