@@ -67,7 +67,9 @@ PeerAllGatherKernel(const __grid_constant__ PeerGatherArgs a) {
       dst[i] = a.src[i];
     }
   }
-  __threadfence_system();
+  // The barrier orders the block's stores before thread 0's release at system
+  // scope, which is cumulative: one fence for the block instead of one per thread
+  // and another for the flag.
   __syncthreads();
   if (threadIdx.x == 0) {
     StoreRelease(reinterpret_cast<unsigned*>(a.arena[peer]) + kFlagStride * a.rank, turn);
@@ -82,7 +84,6 @@ PeerAllGatherKernel(const __grid_constant__ PeerGatherArgs a) {
         break;
       }
     }
-    __threadfence_system();
     if (atomicAdd(header + kFinishedWord, 1u) == static_cast<unsigned>(a.world - 1)) {
       header[kFinishedWord] = 0;
       __threadfence();

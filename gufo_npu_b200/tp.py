@@ -264,7 +264,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     steps, warmup = args.steps, max(args.warmup, 3)
     dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64)
     rng = np.random.default_rng(7)
-    tokens = iter(rng.integers(0, cfg.vocab, size=8 * (steps + warmup) + 16).tolist())
+    tokens = iter(rng.integers(0, cfg.vocab, size=10 * (steps + warmup) + 16).tolist())
     host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
     for _ in range(warmup):
         dec.step(next(tokens), stream)
@@ -302,24 +302,38 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    launches0 = ctx.launch_count() + dec.replayed_kernels
-    ms_resident = timed(lambda: dec.step(next(tokens), stream))
-    launches = ctx.launch_count() + dec.replayed_kernels - launches0
+    def resident(d):
+        before = ctx.launch_count() + d.replayed_kernels
+        ms = timed(lambda: d.step(next(tokens), stream))
+        return ms, ctx.launch_count() + d.replayed_kernels - before
+
+    ms_resident, launches = resident(dec)
+    if dec.peers is not None:
+        dec.peers.status()   # raises if a wait for a peer's flag ran out
+    # The same step with NCCL's all-gather in place of the peer-memory kernel. The line's value
+    # is the faster of the two; `parallelism` names it and gives the other's time.
+    gathered_by = "this library's kernel over NVLink peer memory (CUDA IPC)" if dec.peers is not None else "NCCL"
+    other = ""
+    if dec.peers is not None:
+        by_nccl = TpDecoder(ctx, cfg, synth.build_model(cfg, seed=1, device=f"cuda:{local}"), rank, world,
+                            max_positions=2 * (steps + warmup) + 64, collective="nccl")
+        for _ in range(warmup):
+            by_nccl.step(next(tokens), stream)
+        torch.cuda.synchronize()
+        ms_nccl, launches_nccl = resident(by_nccl)
+        if ms_nccl < ms_resident:
+            other = f"; with the library's peer-memory gather kernel instead: {ms_resident:.3f} ms per step"
+            gathered_by = "NCCL"
+            dec, by_nccl = by_nccl, dec
+            ms_resident, launches = ms_nccl, launches_nccl
+        else:
+            other = f"; with NCCL's all-gather instead: {ms_nccl:.3f} ms per step"
 
     def e2e_step():
         logits = dec.step(next(tokens), stream)
         host.copy_(logits, non_blocking=True)
         torch.cuda.current_stream().synchronize()
     ms_e2e = timed(e2e_step)
-    if dec.peers is not None:
-        dec.peers.status()   # raises if a wait for a peer's flag ran out
-    # The same step with NCCL's all-gather in place of the peer-memory kernel, for comparison.
-    by_nccl = TpDecoder(ctx, cfg, synth.build_model(cfg, seed=1, device=f"cuda:{local}"), rank, world,
-                        max_positions=2 * (steps + warmup) + 64, collective="nccl")
-    for _ in range(warmup):
-        by_nccl.step(next(tokens), stream)
-    torch.cuda.synchronize()
-    ms_nccl = timed(lambda: by_nccl.step(next(tokens), stream))
     # For context beside the row-split number: the same GPUs as independent replicas, every rank
     # decoding its own sequence with the single-GPU resident decoder at the same time (no
     # collective on the data path). Timed the same way: barrier, device events, max over ranks.
@@ -339,10 +353,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
             "data": "synthetic",
             "config": {"workload": workload, "seed": 1, "parallelism": f"tp{world}: projections row-split, "
-                       f"{dec.gathers_per_step} all-gathers per step by "
-                       + ("this library's kernel over NVLink peer memory (CUDA IPC)" if dec.peers is not None
-                          else "NCCL (no peer-memory group on this box)")
-                       + f", mixers replicated; NCCL all-gathers instead: {ms_nccl:.3f} ms per step",
+                       f"{dec.gathers_per_step} all-gathers per step by {gathered_by}, mixers replicated{other}",
                        "l2": "weights exceed L2; no flush needed"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},
@@ -357,7 +368,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     # Captured graphs hold NCCL kernels: release them before the communicator goes away, and
     # leave without the collective teardown (it blocked here while graphs were alive).
     dec.graphs.clear()
-    by_nccl.graphs.clear()
+    if other:
+        by_nccl.graphs.clear()
     import sys
     sys.stdout.flush()
     sys.stderr.flush()
