@@ -12,6 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgufo_cuda.so")
 
 OK = 0
+STATUS_TIMEOUT = 6
 STATUS_NAMES = {1: "bad argument", 2: "shape", 3: "unsupported type", 4: "CUDA runtime",
                 5: "out of memory", 6: "timeout", 7: "too large"}
 
@@ -129,7 +130,11 @@ SIGNATURES = {
     "gufo_cuda_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "gufo_cuda_peer_group_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_void_p,
                                               C.POINTER(C.c_void_p)]),
+    "gufo_cuda_peer_group_create_local": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.c_size_t,
+                                                    C.POINTER(C.c_void_p)]),
     "gufo_cuda_peer_group_destroy": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_peer_group_set_limit": (C.c_int, [C.c_void_p, C.c_int64]),
+    "gufo_cuda_peer_group_reset": (C.c_int, [C.c_void_p]),
     "gufo_cuda_peer_allgather_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]),
     "gufo_cuda_peer_group_status": (C.c_int, [C.c_void_p]),
     "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,

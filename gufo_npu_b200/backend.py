@@ -301,10 +301,10 @@ class PeerGroup:
         self._next = (offset + 4 * floats + 255) // 256 * 256
         if self._next > self.bytes:
             raise ValueError("peer arena exhausted")
-        view = self._torch.as_tensor(_DeviceArray(self.arena + offset, floats),
+        # The arena was cleared when the group was created (before the ranks' barrier): clearing
+        # a view here could wipe a slice a faster peer has already stored.
+        return self._torch.as_tensor(_DeviceArray(self.arena + offset, floats),
                                      device=self._torch.device("cuda", self.ctx.device))
-        view.zero_()
-        return view
 
     def offset_of(self, tensor) -> int:
         return tensor.data_ptr() - self.arena

@@ -100,8 +100,10 @@ struct gufo_cuda_peer_group {
   int rank = 0;
   int world = 0;
   uint8_t* arena[gufo::kMaxPeers] = {};
+  bool opened[gufo::kMaxPeers] = {};   // mapped through CUDA IPC (closed at destroy)
   size_t arena_bytes = 0;
   long long limit = 0;
+  int khz = 0;
 };
 
 using gufo::Fail;
@@ -120,9 +122,14 @@ int gufo_cuda_ipc_export(gufo_cuda_ctx* ctx, const void* device_ptr, void* handl
   return GUFO_CUDA_OK;
 }
 
-int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world, void* own_arena, size_t arena_bytes,
-                                const void* handles, gufo_cuda_peer_group** out) {
-  if (ctx == nullptr || own_arena == nullptr || handles == nullptr || out == nullptr) {
+namespace {
+
+// Common part of the two ways to create a group: `handles` (IPC handles of all
+// ranks, another process each) or `arenas` (device pointers this process can
+// already reach: its own allocations, or peers' with peer access enabled).
+int CreatePeerGroup(gufo_cuda_ctx* ctx, int rank, int world, void* own_arena, size_t arena_bytes,
+                    const void* handles, void* const* arenas, gufo_cuda_peer_group** out) {
+  if (ctx == nullptr || own_arena == nullptr || (handles == nullptr && arenas == nullptr) || out == nullptr) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_create: null pointer");
   }
   *out = nullptr;
@@ -139,12 +146,22 @@ int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world, void* o
   g->rank = rank;
   g->world = world;
   g->arena_bytes = arena_bytes;
-  int khz = 0;
-  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device);
-  g->limit = static_cast<long long>(khz > 0 ? khz : 1000000) * 4000;   // about four seconds of SM clocks
+  cudaDeviceGetAttribute(&g->khz, cudaDevAttrClockRate, ctx->device);
+  if (g->khz <= 0) {
+    g->khz = 1000000;
+  }
+  g->limit = static_cast<long long>(g->khz) * 4000;   // about four seconds of SM clocks
   for (int r = 0; r < world; ++r) {
     if (r == rank) {
       g->arena[r] = static_cast<uint8_t*>(own_arena);
+      continue;
+    }
+    if (arenas != nullptr) {
+      if (arenas[r] == nullptr || (reinterpret_cast<uintptr_t>(arenas[r]) & 255) != 0) {
+        delete g;
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_create: every rank's arena must be given, 256-byte aligned");
+      }
+      g->arena[r] = static_cast<uint8_t*>(arenas[r]);
       continue;
     }
     cudaIpcMemHandle_t h;
@@ -153,7 +170,7 @@ int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world, void* o
     const cudaError_t e = cudaIpcOpenMemHandle(&opened, h, cudaIpcMemLazyEnablePeerAccess);
     if (e != cudaSuccess) {
       for (int q = 0; q < r; ++q) {
-        if (q != rank) {
+        if (g->opened[q]) {
           cudaIpcCloseMemHandle(g->arena[q]);
         }
       }
@@ -161,12 +178,56 @@ int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world, void* o
       return gufo::CudaFail(e, "cudaIpcOpenMemHandle");
     }
     g->arena[r] = static_cast<uint8_t*>(opened);
+    g->opened[r] = true;
   }
-  // Flags, counts and the error word start at zero on every rank; the caller
-  // lets all ranks pass a barrier before the first gather.
-  GUFO_CUDA_TRY(cudaMemsetAsync(own_arena, 0, GUFO_CUDA_PEER_HEADER_BYTES, ctx->stream));
+  // The whole arena starts at zero on every rank, flags, counts and the error
+  // word included, before this call returns: the caller lets all ranks pass a
+  // barrier between creating the group and the first gather, so no peer can
+  // store a slice into this arena before it has been cleared (clearing a vector
+  // later, once a faster rank may already have written its slice and raised its
+  // flag, would wipe the slice and keep the flag).
+  GUFO_CUDA_TRY(cudaMemsetAsync(own_arena, 0, arena_bytes, ctx->stream));
   GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
   *out = g;
+  return GUFO_CUDA_OK;
+}
+
+}  // namespace
+
+int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world, void* own_arena, size_t arena_bytes,
+                                const void* handles, gufo_cuda_peer_group** out) {
+  if (handles == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_create: null pointer");
+  }
+  return CreatePeerGroup(ctx, rank, world, own_arena, arena_bytes, handles, nullptr, out);
+}
+
+int gufo_cuda_peer_group_create_local(gufo_cuda_ctx* ctx, int rank, int world, void* const* arenas,
+                                      size_t arena_bytes, gufo_cuda_peer_group** out) {
+  if (arenas == nullptr || world < 1 || world > gufo::kMaxPeers || rank < 0 || rank >= world) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_create_local: arenas of 1 to 8 ranks, rank inside");
+  }
+  return CreatePeerGroup(ctx, rank, world, arenas[rank], arena_bytes, nullptr, arenas, out);
+}
+
+int gufo_cuda_peer_group_set_limit(gufo_cuda_peer_group* g, int64_t microseconds) {
+  if (g == nullptr || microseconds < 1 || microseconds > 60 * 1000000ll) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_set_limit: a group and 1 us to 60 s");
+  }
+  std::lock_guard<std::mutex> lock(g->ctx->mu);
+  g->limit = static_cast<long long>(g->khz) * microseconds / 1000;   // kHz * us / 1000 = cycles
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_peer_group_reset(gufo_cuda_peer_group* g) {
+  if (g == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_group_reset: null group");
+  }
+  gufo_cuda_ctx* ctx = g->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(cudaMemsetAsync(g->arena[g->rank], 0, GUFO_CUDA_PEER_HEADER_BYTES, ctx->stream));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
   return GUFO_CUDA_OK;
 }
 
@@ -177,7 +238,7 @@ int gufo_cuda_peer_group_destroy(gufo_cuda_peer_group* g) {
   cudaSetDevice(g->ctx->device);
   cudaStreamSynchronize(g->ctx->stream);
   for (int r = 0; r < g->world; ++r) {
-    if (r != g->rank && g->arena[r] != nullptr) {
+    if (g->opened[r]) {
       cudaIpcCloseMemHandle(g->arena[r]);
     }
   }

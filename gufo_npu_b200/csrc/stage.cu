@@ -127,6 +127,13 @@ extern "C" int gufo_cuda_matmul_q4k_static_device(gufo_cuda_ctx* ctx, const void
   if (reinterpret_cast<uintptr_t>(device_weights) % 16 != 0 || reinterpret_cast<uintptr_t>(device_x) % 16 != 0) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_q4k_static: weights and x must be 16-byte aligned");
   }
+  // Three byte planes per token: no row wider than this can fit, and the bound
+  // keeps the int arithmetic of the layout below in range.
+  if (cols > gufo::kStaticImageBytes / gufo::kLimbs) {
+    return Fail(GUFO_CUDA_TOO_LARGE, "matmul_q4k_static: rows of " + std::to_string(cols) +
+                                         " values cannot fit the built-in buffer of " +
+                                         std::to_string(gufo::kStaticImageBytes) + " bytes");
+  }
   gufo::StageArgs stage;
   stage.layout = gufo::MakeImageLayout(tokens, static_cast<int>(cols), 32);
   if (stage.layout.bytes > gufo::kStaticImageBytes || !gufo::Q4KFastFits(static_cast<int>(cols), tokens)) {

@@ -248,6 +248,24 @@ class TpDecoder:
         return self.logits
 
 
+PARITY_TOKENS = (11, 4242, 98765, 7)   # the first steps of every decoder in run_bench
+
+
+def first_logits(step, vocab: int) -> np.ndarray:
+    """Logits [len(PARITY_TOKENS), vocab] of a fresh decoder's first steps (`step(token)` returns
+    a host array or a device tensor)."""
+    rows = []
+    for tok in PARITY_TOKENS:
+        out = step(tok % vocab)
+        rows.append(out.detach().cpu().numpy().copy() if isinstance(out, torch.Tensor) else np.array(out, copy=True))
+    return np.stack(rows)
+
+
+def rel_l2(got: np.ndarray, want: np.ndarray) -> float:
+    got, want = got.astype(np.float64), want.astype(np.float64)
+    return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
+
+
 def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> None:
     """bench.py's N > 1 arm: launched by torchrun, one rank per GPU."""
     from . import synth
@@ -266,6 +284,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     rng = np.random.default_rng(7)
     tokens = iter(rng.integers(0, cfg.vocab, size=10 * (steps + warmup) + 16).tolist())
     host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
+    # Every decoder of this run starts with the same few tokens, whose logits are compared below.
+    parity_logits = {"row_split": first_logits(lambda t: dec.step(t, stream), cfg.vocab)}
     for _ in range(warmup):
         dec.step(next(tokens), stream)
     torch.cuda.synchronize()
@@ -284,6 +304,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     if int(agreed.item()) == 0:
         dec.graphs.clear()
         dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64, collective="nccl")
+        parity_logits["row_split"] = first_logits(lambda t: dec.step(t, stream), cfg.vocab)
         for _ in range(warmup):
             dec.step(next(tokens), stream)
         torch.cuda.synchronize()
@@ -317,6 +338,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     if dec.peers is not None:
         by_nccl = TpDecoder(ctx, cfg, synth.build_model(cfg, seed=1, device=f"cuda:{local}"), rank, world,
                             max_positions=2 * (steps + warmup) + 64, collective="nccl")
+        parity_logits["row_split_nccl"] = first_logits(lambda t: by_nccl.step(t, stream), cfg.vocab)
         for _ in range(warmup):
             by_nccl.step(next(tokens), stream)
         torch.cuda.synchronize()
@@ -342,10 +364,29 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     replica = CudaDecoder(CudaProjections(ctx, cfg, full), full, max_positions=2 * (steps + warmup) + 64,
                           use_graph=True)
     del full
+    parity_logits["one_gpu"] = first_logits(lambda t: replica.Step(t), cfg.vocab)
     for _ in range(warmup):
         replica.step_device(next(tokens))
     torch.cuda.synchronize()
     ms_replica = timed(lambda: replica.step_device(next(tokens)))
+    # The row-split decoders against the one-GPU decoder on the same tokens (every rank checks
+    # its own copy of the gathered logits; the worst over the ranks is reported), and the two
+    # gathers against each other, which must agree bit for bit.
+    worst = max(rel_l2(parity_logits["row_split"][i], parity_logits["one_gpu"][i]) for i in range(len(PARITY_TOKENS)))
+    same_argmax = all(int(np.argmax(parity_logits["row_split"][i])) == int(np.argmax(parity_logits["one_gpu"][i]))
+                      for i in range(len(PARITY_TOKENS)))
+    gathers_equal = 1
+    if "row_split_nccl" in parity_logits:
+        gathers_equal = int(np.array_equal(parity_logits["row_split"].view(np.uint32),
+                                           parity_logits["row_split_nccl"].view(np.uint32)))
+    check = torch.tensor([worst, 0.0 if same_argmax else 1.0, 0.0 if gathers_equal else 1.0], device=f"cuda:{local}")
+    dist.all_reduce(check, op=dist.ReduceOp.MAX)
+    worst, argmax_differs, gathers_differ = (float(v) for v in check.tolist())
+    parity = {"row_split_vs_one_gpu_logits_rel_l2": worst, "same_argmax": argmax_differs == 0.0,
+              "peer_and_nccl_gathers_bit_equal": (gathers_differ == 0.0) if "row_split_nccl" in parity_logits else None,
+              "tokens": len(PARITY_TOKENS), "tolerance": 2e-3}
+    if worst > 2e-3 or argmax_differs or gathers_differ:
+        raise SystemExit(f"row-split parity failed: {parity}")
     if rank == 0:
         print(json.dumps({
             "metric": metric, "value": 1e3 / ms_resident, "unit": unit, "n_gpus": world, "steps": steps,
@@ -361,6 +402,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "replicas": {"value": world * 1e3 / ms_replica, "unit": unit, "ms_per_step": ms_replica,
                          "note": "the same GPUs as independent sequences, one resident decoder per GPU, no "
                                  "collective; not the metric's row-split configuration"},
+            "parity": parity,
             "roofline": None, "cpu_baseline": None,
         }))
     dist.barrier()

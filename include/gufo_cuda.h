@@ -438,9 +438,19 @@ int gufo_cuda_moe_combine_device(gufo_cuda_ctx* ctx, const float* shared,
  * creates the group from all ranks' handles in rank order (its own entry is
  * ignored). The first GUFO_CUDA_PEER_HEADER_BYTES of an arena belong to the
  * group; full vectors live behind them at the same offset on every rank. All
- * ranks must have created their group before any of them gathers. A flag that
- * does not arrive within about four seconds ends the wait:
- * gufo_cuda_peer_group_status then returns GUFO_CUDA_TIMEOUT. */
+ * ranks must have created their group (which clears the whole arena) before any
+ * of them gathers: put a barrier of the host's own between the two. A flag that
+ * does not arrive within the limit (about four seconds unless
+ * gufo_cuda_peer_group_set_limit changed it) ends the wait:
+ * gufo_cuda_peer_group_status then returns GUFO_CUDA_TIMEOUT, and every later
+ * gather gives up at once, its output invalid, until every rank has called
+ * gufo_cuda_peer_group_reset (all ranks together, none of them gathering: it
+ * clears the flags, the gather count and the error word of the rank's arena).
+ *
+ * gufo_cuda_peer_group_create_local builds the same group from device pointers
+ * the process can already reach (`arenas[r]` for every rank r, its own
+ * included): for one process that drives several GPUs with peer access enabled,
+ * and for tests. */
 #define GUFO_CUDA_IPC_HANDLE_BYTES 64
 #define GUFO_CUDA_PEER_HEADER_BYTES 4096
 typedef struct gufo_cuda_peer_group gufo_cuda_peer_group;
@@ -448,7 +458,13 @@ int gufo_cuda_ipc_export(gufo_cuda_ctx* ctx, const void* device_ptr, void* handl
 int gufo_cuda_peer_group_create(gufo_cuda_ctx* ctx, int rank, int world,
                                 void* own_arena, size_t arena_bytes,
                                 const void* handles, gufo_cuda_peer_group** out);
+int gufo_cuda_peer_group_create_local(gufo_cuda_ctx* ctx, int rank, int world,
+                                      void* const* arenas, size_t arena_bytes,
+                                      gufo_cuda_peer_group** out);
 int gufo_cuda_peer_group_destroy(gufo_cuda_peer_group* group);
+/* How long a gather waits for a peer's flag, in microseconds of SM clocks. */
+int gufo_cuda_peer_group_set_limit(gufo_cuda_peer_group* group, int64_t microseconds);
+int gufo_cuda_peer_group_reset(gufo_cuda_peer_group* group);
 /* Rank r's `slice_floats` values at local_src land at arena_offset (bytes) +
  * r * slice_floats * 4 in every rank's arena; returns once enqueued. The kernel
  * ends when the slices of all ranks have arrived in this rank's arena. */

@@ -9,7 +9,7 @@ few small inputs) are stored. The quant/ directory beside this file holds the
 reference's own dequantization fixtures (tests/fixtures/quant in its tree),
 copied unchanged.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [name ...]
 """
 from __future__ import annotations
 
@@ -166,14 +166,44 @@ def decoder(ref: binding.RefLib) -> dict:
     return out
 
 
+# Positions whose logits decoder_long keeps: around the 128-position slices the reference's
+# attention cuts the cache into (decoder.cpp:326-333) and past a thousand positions.
+LONG_STEPS = 1100
+LONG_KEEP = (0, 7, 8, 63, 127, 128, 129, 255, 256, 511, 777, 1023, 1024, 1099)
+LONG_TOKEN_SEED = 31
+
+
+def long_tokens(vocab: int) -> np.ndarray:
+    return np.random.default_rng(LONG_TOKEN_SEED).integers(0, vocab, size=LONG_STEPS).astype(np.int32)
+
+
+def decoder_long(ref: binding.RefLib) -> dict:
+    """Decoder::Step logits of the dense model over 1100 positions, a few of them kept."""
+    cfg = synth.ModelConfig(**DENSE)
+    image = synth.to_gguf(cfg, synth.build_model(cfg, DENSE_SEED))
+    model = ref.open_model(image)
+    model.decoder_reset()
+    kept = []
+    for i, tok in enumerate(long_tokens(cfg.vocab)):
+        if i in LONG_KEEP:
+            kept.append(model.decoder_step(int(tok), cfg.vocab))
+        else:
+            model.decoder_step_discard(int(tok))
+    model.close()
+    return {"positions": np.array(LONG_KEEP, dtype=np.int32), "logits": np.stack(kept)}
+
+
 def main() -> int:
     binding.build()
     if not binding.RefLib.available():
         print("the reference tree is not mounted: cannot regenerate goldens")
         return 1
     ref = binding.RefLib()
+    only = set(sys.argv[1:])   # e.g. `make_golden.py decoder_long` regenerates that file alone
     for name, fn in (("dots", dots), ("projections", projections), ("deltanet", deltanet),
-                     ("routing", routing), ("decoder", decoder)):
+                     ("routing", routing), ("decoder", decoder), ("decoder_long", decoder_long)):
+        if only and name not in only:
+            continue
         arrays = fn(ref)
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)

@@ -134,3 +134,59 @@ def test_two_ranks_row_split_and_expert_parallel():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     _run(2)
+
+
+def test_peer_gather_wait_that_runs_out_is_reported_and_the_context_lives():
+    """A gather whose peer never raises its flag: a two-rank group on ONE device whose second
+    arena is a plain local allocation nobody writes to. With the limit set to two milliseconds
+    the kernel must return by itself, the group must report GUFO_CUDA_TIMEOUT, a later gather
+    must give up at once, and after a reset the one-rank part of the work and an ordinary
+    product must still run. No rank dies and no kernel traps: the wait simply runs out."""
+    import ctypes as C
+    import time
+
+    from gufo_npu_b200 import _capi
+    from gufo_npu_b200 import quantize as Q
+    from gufo_npu_b200._capi import GufoCudaError
+    from gufo_npu_b200.backend import Context
+    dev = torch.device("cuda:0")
+    ctx = Context(0)
+    lib = ctx.lib
+    floats = 1024
+    nbytes = _capi.PEER_HEADER_BYTES + 4 * 2 * floats
+    mine = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    silent = torch.zeros(nbytes, dtype=torch.uint8, device=dev)     # the "peer" that never answers
+    arenas = (C.c_void_p * 2)(mine.data_ptr(), silent.data_ptr())
+    group = C.c_void_p()
+    ctx._check(lib.gufo_cuda_peer_group_create_local(ctx.handle, 0, 2, arenas, nbytes, C.byref(group)))
+    ctx._check(lib.gufo_cuda_peer_group_set_limit(group, 2000))
+    src = torch.arange(floats, dtype=torch.float32, device=dev)
+    ctx._check(lib.gufo_cuda_peer_group_status(group))               # healthy before the first gather
+    t0 = time.perf_counter()
+    ctx._check(lib.gufo_cuda_peer_allgather_device(group, C.c_void_p(src.data_ptr()), _capi.PEER_HEADER_BYTES, floats))
+    ctx.synchronize()
+    first = time.perf_counter() - t0
+    assert first < 1.0, first                                        # two milliseconds, not four seconds
+    with pytest.raises(GufoCudaError) as e:
+        ctx._check(lib.gufo_cuda_peer_group_status(group))
+    assert e.value.status == _capi.STATUS_TIMEOUT
+    # The slice still reached both arenas (rank 0's half of the full vector).
+    at = _capi.PEER_HEADER_BYTES
+    for arena in (mine, silent):
+        got = arena[at:at + 4 * floats].view(torch.float32)
+        assert torch.equal(got, src)
+    # A later gather gives up at once: no second wait for the limit.
+    ctx._check(lib.gufo_cuda_peer_group_set_limit(group, 30 * 1000000))
+    t0 = time.perf_counter()
+    ctx._check(lib.gufo_cuda_peer_allgather_device(group, C.c_void_p(src.data_ptr()), _capi.PEER_HEADER_BYTES, floats))
+    ctx.synchronize()
+    assert time.perf_counter() - t0 < 1.0
+    # After a reset the group is healthy again, and the context still multiplies.
+    ctx._check(lib.gufo_cuda_peer_group_reset(group))
+    ctx._check(lib.gufo_cuda_peer_group_status(group))
+    raw = Q.random_blocks(Q.GGML_Q4_K, 64, 512, seed=5).numpy()
+    m = ctx.matrix_upload(Q.GGML_Q4_K, raw, 64, 512)
+    y = ctx.matmul([(m, 0, 64)], np.ones((1, 512), dtype=np.float32), 1, 64)
+    assert np.isfinite(y).all()
+    ctx._check(lib.gufo_cuda_peer_group_destroy(group))
+    ctx.close()

@@ -259,3 +259,28 @@ def test_live_reference_agrees_with_committed_goldens(reflib, golden):
         got = np.array([reflib.dot(t, rows[i], x[i]) for i in range(24)], dtype=np.float32)
         assert np.array_equal(bits(got), bits(g[f"dot_{name}_random_512"]))
     assert reflib.usable_cpus() >= 1
+
+
+def test_oracle_decoder_and_attention_match_reference_logits(oracle, golden):
+    """The Python restatement of Decoder::Step (oracle/decoder.py, with the attention of
+    oracle/attention.py) against the reference's committed logits: the 8-token run, and the
+    1100-position run up to position 256 (two of the reference's 128-position slices)."""
+    from oracle.decoder import OracleDecoder
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    g = golden("decoder")
+    dec = OracleDecoder(oracle, cfg, tensors, 8)
+    for i, tok in enumerate(int(t) for t in g["decoder_dense_tokens"]):
+        got = dec.step(tok)
+        want = g["decoder_dense_logits"][i]
+        err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+        assert err < 2e-5, (i, err)
+    long = golden("decoder_long")
+    keep = {int(p): i for i, p in enumerate(long["positions"])}
+    dec = OracleDecoder(oracle, cfg, tensors, 257)
+    for pos, tok in enumerate(G.long_tokens(cfg.vocab)[:257]):
+        got = dec.step(int(tok))
+        if pos in keep:
+            want = long["logits"][keep[pos]]
+            err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
+            assert err < 5e-5, (pos, err)
