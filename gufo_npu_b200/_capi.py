@@ -163,6 +163,9 @@ SIGNATURES = {
     "gufo_cuda_decoder_destroy": (C.c_int, [C.c_void_p]),
     "gufo_cuda_decoder_reset": (C.c_int, [C.c_void_p]),
     "gufo_cuda_decoder_step": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "gufo_cuda_decoder_status": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_decoder_step_profile": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int64),
+                                                 C.POINTER(C.c_double), C.POINTER(C.c_int)]),
     "gufo_cuda_decoder_step_tokens": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_void_p]),
     "gufo_cuda_decoder_resolve": (C.c_int, [C.c_void_p, C.c_int]),
     "gufo_cuda_decoder_hidden_device": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),

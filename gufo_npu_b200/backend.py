@@ -708,6 +708,26 @@ class CudaDecoder:
         self.ctx._check(self.ctx.lib.gufo_cuda_decoder_logits_device(self.handle, C.byref(out)))
         return int(out.value)
 
+    def status(self) -> None:
+        """Waits for the stream; raises GufoCudaError (timeout) if a wait inside the persistent
+        step kernel ran out since the last check."""
+        self.ctx._check(self.ctx.lib.gufo_cuda_decoder_status(self.handle))
+
+    def step_profile(self) -> List[dict]:
+        """Per operation of the last step run by the persistent kernel: stage name, bytes moved
+        and device microseconds; empty when the model runs on the launch chain."""
+        n = C.c_int()
+        lib = self.ctx.lib
+        self.ctx._check(lib.gufo_cuda_decoder_step_profile(self.handle, 0, None, None, None, C.byref(n)))
+        if n.value == 0:
+            return []
+        stages = (C.c_int * n.value)()
+        nbytes = (C.c_int64 * n.value)()
+        us = (C.c_double * n.value)()
+        self.ctx._check(lib.gufo_cuda_decoder_step_profile(self.handle, n.value, stages, nbytes, us, C.byref(n)))
+        return [{"stage": self.TIMELINE_KINDS[stages[i]], "bytes": int(nbytes[i]), "us": float(us[i])}
+                for i in range(n.value)]
+
     TIMELINE_KINDS = ("embed", "in", "deltanet", "attention", "out", "ffn_in", "ffn_down", "lm_head")
 
     def timeline(self, enable: bool) -> Dict[str, float]:

@@ -237,6 +237,16 @@ struct gufo_cuda_ctx {
   // The caller's promise that DeltaNet states passed to this context were not
   // written by the two kernels enqueued just before the call.
   bool early_state = false;
+  // One-token steps of a resident decoder run as one persistent kernel where
+  // the model allows it and this is set (option "step_kernel"). Off unless
+  // asked for: on B200 a grid-wide barrier costs as much as a programmatic
+  // kernel boundary, and the launch chain is the faster of the two.
+  bool step_kernel = false;
+  // How long a wait inside that kernel may take (option "step_wait_us").
+  int64_t step_wait_us = 2000000;
+  // Test hook (option "step_skip_arrival"): block 0 stays away from the grid
+  // barrier after this operation, so that the others' waits run out (-1: off).
+  int step_skip_arrival = -1;
 
   const gufo::Matrix* FindMatrix(int64_t id) const {
     auto it = matrices.find(id);

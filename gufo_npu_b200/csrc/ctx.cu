@@ -247,6 +247,21 @@ int gufo_cuda_ctx_set_option(gufo_cuda_ctx* ctx, const char* name, int value) {
     ctx->tc_gemm_all = value == 2;
     return GUFO_CUDA_OK;
   }
+  if (std::strcmp(name, "step_kernel") == 0) {
+    ctx->step_kernel = value != 0;
+    return GUFO_CUDA_OK;
+  }
+  if (std::strcmp(name, "step_wait_us") == 0) {
+    if (value < 1) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "set_option: step_wait_us takes microseconds, at least 1");
+    }
+    ctx->step_wait_us = value;
+    return GUFO_CUDA_OK;
+  }
+  if (std::strcmp(name, "step_skip_arrival") == 0) {
+    ctx->step_skip_arrival = value;
+    return GUFO_CUDA_OK;
+  }
   if (std::strcmp(name, "reuse_image") == 0) {
     ctx->reuse_image = value != 0;
     return GUFO_CUDA_OK;

@@ -18,16 +18,15 @@
 #include <cmath>
 #include <vector>
 
+#include "decode_device.cuh"
 #include "gemv.cuh"
 #include "moe.cuh"
+#include "step_kernel.cuh"
 
 namespace gufo {
 namespace {
 
-constexpr int kSmallThreads = 256;
-constexpr int kAttnSplits = 8;      // position slices per KV head
-constexpr int kMaxGroup = 8;        // query heads per KV head
-constexpr int kMaxPerLane = 8;      // head_dim / 32
+constexpr int kSmallThreads = kTeamThreads;
 constexpr int kStepTokens = 2;      // tokens of a pair step
 constexpr int kTokenSlots = 8;      // pinned token staging slots of a decoder
 
@@ -49,63 +48,12 @@ __device__ __forceinline__ float BlockSum256(float v, float* scratch) {
   return total;
 }
 
-// h = dequantized row *token of the embedding matrix (quant::Dequantize of one
-// row, src/models/qwen35/decoder.cpp:486-489). One thread block.
-struct EmbedArgs {
-  const uint8_t* data;
-  int type;
-  int row_bytes;
-  int cols;
-  const int* token;
-  float* h;
-};
-
+// The embedding row (body in decode_device.cuh). One thread block.
 __global__ void __launch_bounds__(kSmallThreads)
 EmbedKernel(const __grid_constant__ EmbedArgs a) {
   GridLaunchDependents();
   GridDependencyWait();
-  const uint8_t* row = a.data + static_cast<size_t>(*a.token) * a.row_bytes;
-  const int blocks = a.cols / kSuperBlock;
-  if (a.type == GUFO_CUDA_Q4_K) {
-    for (int item = threadIdx.x; item < blocks * 32; item += kSmallThreads) {
-      const int b = item >> 5, word = item & 31, p = word >> 3, c = word & 7;
-      const uint32_t* block = reinterpret_cast<const uint32_t*>(row + b * kQ4KBytes);
-      const uint32_t dd = block[0];
-      const float d = HalfBitsToFloat(static_cast<uint16_t>(dd & 0xFFFF));
-      const float dmin = HalfBitsToFloat(static_cast<uint16_t>(dd >> 16));
-      int sc_lo, m_lo, sc_hi, m_hi;
-      ScaleMinK4(2 * p, block[1], block[2], block[3], &sc_lo, &m_lo);
-      ScaleMinK4(2 * p + 1, block[1], block[2], block[3], &sc_hi, &m_hi);
-      const float d1 = __fmul_rn(d, static_cast<float>(sc_lo)), m1 = __fmul_rn(dmin, static_cast<float>(m_lo));
-      const float d2 = __fmul_rn(d, static_cast<float>(sc_hi)), m2 = __fmul_rn(dmin, static_cast<float>(m_hi));
-      const uint32_t q = block[4 + word];
-      float* out = a.h + b * kSuperBlock + 64 * p + 4 * c;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        out[i] = __fsub_rn(__fmul_rn(d1, static_cast<float>((q >> (8 * i)) & 0xF)), m1);
-        out[32 + i] = __fsub_rn(__fmul_rn(d2, static_cast<float>((q >> (8 * i + 4)) & 0xF)), m2);
-      }
-    }
-  } else if (a.type == GUFO_CUDA_Q6_K) {
-    for (int item = threadIdx.x; item < blocks * 64; item += kSmallThreads) {
-      const int b = item >> 6, half = (item >> 5) & 1, l = item & 31;
-      const Q6KBlock block = Q6KBlockAt(row, blocks, b);
-      const uint8_t* ql = block.ql + 64 * half;
-      const uint8_t* qh = block.qh + 32 * half;
-      const int8_t* sc = block.sc + 8 * half + (l >> 4);
-      const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(block.d));
-      const int x = ql[l], c = ql[l + 32], h = qh[l];
-      float* out = a.h + b * kSuperBlock + 128 * half + l;
-      out[0] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[0])), static_cast<float>(((x & 0xF) | ((h & 3) << 4)) - 32));
-      out[32] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[2])), static_cast<float>(((c & 0xF) | (((h >> 2) & 3) << 4)) - 32));
-      out[64] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[4])), static_cast<float>(((x >> 4) | (((h >> 4) & 3) << 4)) - 32));
-      out[96] = __fmul_rn(__fmul_rn(d, static_cast<float>(sc[6])), static_cast<float>(((c >> 4) | (((h >> 6) & 3) << 4)) - 32));
-    }
-  } else {
-    for (int i = threadIdx.x; i < a.cols; i += kSmallThreads) {
-      a.h[i] = reinterpret_cast<const float*>(row)[i];
-    }
-  }
+  EmbedBody(a, threadIdx.x);
 }
 
 // h = h_in + delta (delta when given; h may be h_in), then normed = RMS(h) * w (vec::RmsNorm,
@@ -150,225 +98,30 @@ SwiGluKernel(const float* __restrict__ ffn, int f, float* __restrict__ act) {
   }
 }
 
-struct AttnArgs {
-  int heads, kv_heads, head_dim, rope_dim, max_positions;
-  float rms_eps;
-  const int* position;
-  const float* in;          // [q and gate (2 heads hd, per head q | gate) | k | v]
-  const float* q_norm;
-  const float* k_norm;
-  const float* inv_freq;    // [rope_dim / 2]
-  __half* keys;             // [max_positions][kv_heads * hd]
-  __half* values;
-  float* queries;           // [heads][hd]
-  float* partials;          // [kv_heads][splits][group][hd + 2]
-  float* ctx;               // [heads][hd]
-  int offset = 0;           // the token sits at *position + offset
-};
-
-// q/k RMSNorm and RoPE; appends k and v to the cache in fp16
-// (decoder.cpp:280-323). Block h < heads: query head h; then one per KV head.
+// Decode attention (bodies in decode_device.cuh). Prep: block h < heads is
+// query head h, then one block per KV head. Slices: grid = (splits, kv_heads).
+// Merge: grid = heads.
 __global__ void __launch_bounds__(kSmallThreads)
 AttnPrepKernel(const __grid_constant__ AttnArgs a) {
-  __shared__ float scratch[kSmallThreads / 32];
-  __shared__ float vec[kMaxPerLane * 32];
+  __shared__ AttnScratch scratch;
   GridLaunchDependents();
   GridDependencyWait();
-  const int hd = a.head_dim;
-  const int half = a.rope_dim / 2;
-  const int pos = *a.position + a.offset;
-  const int head = blockIdx.x;
-  const bool is_query = head < a.heads;
-  const int kh = head - a.heads;
-  const float* x = is_query ? a.in + static_cast<size_t>(head) * 2 * hd
-                            : a.in + static_cast<size_t>(a.heads) * 2 * hd + kh * hd;
-  const float* w = is_query ? a.q_norm : a.k_norm;
-  const int e = threadIdx.x;
-  const float v = e < hd ? x[e] : 0.f;
-  const float total = BlockSum256(v * v, scratch);
-  const float inv = 1.0f / sqrtf(total / static_cast<float>(hd) + a.rms_eps);
-  if (e < hd) {
-    vec[e] = v * inv * w[e];
-  }
-  __syncthreads();
-  float out = e < hd ? vec[e] : 0.f;
-  if (e < 2 * half) {
-    const int i = e < half ? e : e - half;
-    const double angle = static_cast<double>(pos) * static_cast<double>(a.inv_freq[i]);
-    const float cs = static_cast<float>(cos(angle));
-    const float sn = static_cast<float>(sin(angle));
-    const float lo = vec[i], hi = vec[i + half];
-    out = e < half ? lo * cs - hi * sn : lo * sn + hi * cs;
-  }
-  if (e < hd) {
-    if (is_query) {
-      a.queries[head * hd + e] = out;
-    } else {
-      const size_t at = (static_cast<size_t>(pos) * a.kv_heads + kh) * hd + e;
-      a.keys[at] = __float2half_rn(out);
-      const float val = a.in[static_cast<size_t>(a.heads) * 2 * hd + a.kv_heads * hd + kh * hd + e];
-      a.values[at] = __float2half_rn(val);
-    }
-  }
+  AttnPrepBody(a, blockIdx.x, scratch, threadIdx.x, BlockSync());
 }
 
-// One slice of the cached positions for one KV head and the query heads that
-// share it: partial softmax (weighted values, max, sum) per query head
-// (the split-K jobs of decoder.cpp:326-381). grid = (splits, kv_heads).
 __global__ void __launch_bounds__(kSmallThreads)
 AttnSliceKernel(const __grid_constant__ AttnArgs a) {
-  __shared__ float q_sh[kMaxGroup][kMaxPerLane * 32];
-  __shared__ float merge_m[kSmallThreads / 32][kMaxGroup];
-  __shared__ float merge_l[kSmallThreads / 32][kMaxGroup];
-  __shared__ float merge_acc[kSmallThreads / 32][kMaxPerLane * 32];
+  __shared__ AttnScratch scratch;
   GridLaunchDependents();
   GridDependencyWait();
-  const int hd = a.head_dim;
-  const int per = hd / 32;
-  const int group = a.heads / a.kv_heads;
-  const int kh = blockIdx.y;
-  const int length = *a.position + a.offset + 1;
-  const int slice = (length + kAttnSplits - 1) / kAttnSplits;
-  const int begin = blockIdx.x * slice;
-  const int end = min(length, begin + slice);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float scale = 1.0f / sqrtf(static_cast<float>(hd));
-  for (int i = threadIdx.x; i < group * hd; i += kSmallThreads) {
-    q_sh[i / hd][i % hd] = a.queries[(kh * group) * hd + i];
-  }
-  __syncthreads();
-  float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][kMaxPerLane];
-#pragma unroll
-  for (int g = 0; g < kMaxGroup; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
-      acc[g][i] = 0.f;
-    }
-  }
-  const int kv = a.kv_heads * hd;
-  for (int j = begin + warp; j < end; j += kSmallThreads / 32) {
-    const __half* key = a.keys + static_cast<size_t>(j) * kv + kh * hd + lane * per;
-    const __half* val = a.values + static_cast<size_t>(j) * kv + kh * hd + lane * per;
-    float kf[kMaxPerLane], vf[kMaxPerLane];
-#pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
-      kf[i] = i < per ? __half2float(key[i]) : 0.f;
-      vf[i] = i < per ? __half2float(val[i]) : 0.f;
-    }
-#pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) {
-      if (g < group) {
-        float dot = 0.f;
-#pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-          if (i < per) {
-            dot = fmaf(q_sh[g][lane * per + i], kf[i], dot);
-          }
-        }
-        const float s = WarpSum(dot) * scale;
-        const float m_new = fmaxf(m[g], s);
-        const float keep = expf(m[g] - m_new);   // 0 on the first position
-        const float p = expf(s - m_new);
-        l[g] = l[g] * keep + p;
-#pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-          acc[g][i] = acc[g][i] * keep + p * vf[i];
-        }
-        m[g] = m_new;
-      }
-    }
-  }
-  // Merge the warps, one query head at a time.
-  for (int g = 0; g < group; ++g) {
-    float mg = -INFINITY, lg = 0.f, ag[kMaxPerLane];
-#pragma unroll
-    for (int gg = 0; gg < kMaxGroup; ++gg) {
-      if (gg == g) {
-        mg = m[gg];
-        lg = l[gg];
-#pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-          ag[i] = acc[gg][i];
-        }
-      }
-    }
-    __syncthreads();
-    if (lane == 0) {
-      merge_m[warp][0] = mg;
-    }
-    __syncthreads();
-    float top = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < kSmallThreads / 32; ++w) {
-      top = fmaxf(top, merge_m[w][0]);
-    }
-    const float wgt = mg == -INFINITY ? 0.f : expf(mg - top);
-    if (lane == 0) {
-      merge_l[warp][0] = lg * wgt;
-    }
-#pragma unroll
-    for (int i = 0; i < kMaxPerLane; ++i) {
-      if (i < per) {
-        merge_acc[warp][lane * per + i] = ag[i] * wgt;
-      }
-    }
-    __syncthreads();
-    float* out = a.partials + ((static_cast<size_t>(kh) * kAttnSplits + blockIdx.x) * group + g) * (hd + 2);
-    for (int e = threadIdx.x; e < hd; e += kSmallThreads) {
-      float total = 0.f;
-#pragma unroll
-      for (int w = 0; w < kSmallThreads / 32; ++w) {
-        total += merge_acc[w][e];
-      }
-      out[e] = total;
-    }
-    if (threadIdx.x == 0) {
-      float total = 0.f;
-#pragma unroll
-      for (int w = 0; w < kSmallThreads / 32; ++w) {
-        total += merge_l[w][0];
-      }
-      out[hd] = top;
-      out[hd + 1] = total;
-    }
-  }
+  AttnSliceBody(a, blockIdx.x, blockIdx.y, scratch, threadIdx.x, BlockSync());
 }
 
-// Merges the slices per query head and applies the output gate
-// (decoder.cpp:383-411). grid = heads.
 __global__ void __launch_bounds__(kSmallThreads)
 AttnMergeKernel(const __grid_constant__ AttnArgs a) {
   GridLaunchDependents();
   GridDependencyWait();
-  const int hd = a.head_dim;
-  const int group = a.heads / a.kv_heads;
-  const int qh = blockIdx.x;
-  const int kh = qh / group, g = qh % group;
-  auto slice = [&](int s) {
-    return a.partials + ((static_cast<size_t>(kh) * kAttnSplits + s) * group + g) * (hd + 2);
-  };
-  float top = -INFINITY;
-  for (int s = 0; s < kAttnSplits; ++s) {
-    top = fmaxf(top, slice(s)[hd]);
-  }
-  float total = 0.f;
-  float wgt[kAttnSplits];
-  for (int s = 0; s < kAttnSplits; ++s) {
-    const float ms = slice(s)[hd];
-    wgt[s] = ms == -INFINITY ? 0.f : expf(ms - top);
-    total += wgt[s] * slice(s)[hd + 1];
-  }
-  const float inv_total = 1.0f / total;
-  const float* gate = a.in + static_cast<size_t>(qh) * 2 * hd + hd;
-  for (int e = threadIdx.x; e < hd; e += kSmallThreads) {
-    float out = 0.f;
-    for (int s = 0; s < kAttnSplits; ++s) {
-      out += wgt[s] * slice(s)[e];
-    }
-    a.ctx[qh * hd + e] = out * (inv_total * SigmoidF(gate[e]));
-  }
+  AttnMergeBody(a, blockIdx.x, threadIdx.x);
 }
 
 template <typename T>
@@ -486,6 +239,7 @@ struct gufo_cuda_decoder {
   // Activations.
   float* h[2] = {nullptr, nullptr};   // the residual stream alternates between two buffers
   float *normed = nullptr, *in = nullptr, *mixed = nullptr, *out = nullptr;
+  float* mixed_raw = nullptr;   // DeltaNet outputs before the gated norm (the step kernel)
   float *ffn = nullptr, *act = nullptr, *logits = nullptr, *queries = nullptr, *partials = nullptr;
   // MoE scratch: router outputs, the routing, the experts' intermediate rows.
   float *router = nullptr, *route_weights = nullptr, *shared_scale = nullptr;
@@ -524,6 +278,28 @@ struct gufo_cuda_decoder {
   int64_t graph_kernels[2][2][2] = {};
   int eager_runs[2][2] = {};
   std::vector<void*> owned;   // every device allocation, for destroy
+
+  // The one-token step as one persistent kernel (step_kernel.cu), where the
+  // model allows it: the program of operations in device memory, two variants
+  // (with and without the LM head).
+  struct StepPlan {
+    bool ok = false;
+    int grid = 0;
+    int region_bytes = 0;
+    gufo::StepOp* ops[2] = {nullptr, nullptr};   // [with logits]
+    int nops[2] = {0, 0};
+    gufo::StepGemv* gemv = nullptr;
+    gufo::StepDelta* delta = nullptr;
+    gufo::AttnArgs* attn = nullptr;
+    unsigned* sync = nullptr;                    // arrivals, departures, error word
+    unsigned long long* stamps = nullptr;        // per-operation time stamps of the last launch
+    unsigned* error_pinned = nullptr;            // host copy of the error word
+    std::vector<int> op_stage[2];                // timeline kind of each operation
+    std::vector<int64_t> op_bytes[2];            // weight / state bytes each operation moves
+    int last_with = 0;
+    const float* final_h = nullptr;              // the final residual row of a step
+    std::string why_not;                         // why the model does not run on it
+  } plan;
 
   int in_width(const Layer& l) const { return l.in.total_rows; }
 };
@@ -815,6 +591,339 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) 
   return GUFO_CUDA_OK;
 }
 
+// Describes the one-token step of `d` as a program for the persistent kernel.
+// Leaves plan.ok false, with the reason, when the model needs something the
+// kernel does not do: the launch chain (EnqueueStep) then runs every step.
+int BuildStepPlan(gufo_cuda_decoder* d) {
+  auto& plan = d->plan;
+  gufo_cuda_ctx* ctx = d->ctx;
+  const gufo_cuda_decoder_config& c = d->c;
+  auto no = [&](const std::string& why) {
+    plan.why_not = why;
+    return GUFO_CUDA_OK;
+  };
+  if (c.experts > 0) {
+    return no("MoE layers run on the launch chain");
+  }
+  std::vector<StepGemv> gemv;
+  std::vector<StepDelta> delta;
+  std::vector<AttnArgs> attn;
+  struct HostOp {
+    StepOp op;
+    int stage;
+    int64_t bytes;
+  };
+  std::vector<HostOp> ops;
+  int region = StepScratchBytes();
+  int max_split = 1;
+  std::string problem;
+  // One product of the step. `split`: the consumer adds partial vectors, so a
+  // product over more than one slab of K may be cut into (tile, slab) items.
+  auto product = [&](const GemvArgs& stage, int rows_limit, bool split, float* y, int stage_kind) -> int {
+    StepGemv g{};
+    int64_t bytes = 0;
+    g.nparts = 0;
+    for (int p = 0; p < stage.nparts && rows_limit != 0; ++p) {
+      const GemvPart& part = stage.parts[p];
+      if (g.nparts == kFastMaxParts) {
+        problem = "a stage stacks more than four matrices";
+        return -1;
+      }
+      if (g.nparts == 0) {
+        g.type = part.type;
+        g.row_bytes = part.row_bytes;
+      }
+      if ((part.type != GUFO_CUDA_Q4_K && part.type != GUFO_CUDA_Q6_K) || part.type != g.type) {
+        problem = "a stage mixes block formats, or has rows that are neither Q4_K nor Q6_K";
+        return -1;
+      }
+      if ((reinterpret_cast<uintptr_t>(part.data) & 15) != 0 || part.row_bytes % 16 != 0) {
+        problem = "weight rows are not 16-byte aligned";
+        return -1;
+      }
+      g.parts[g.nparts++] = {part.data, part.rows, part.out_offset};
+      g.tiles += (part.rows + 15) / 16;
+      bytes += static_cast<int64_t>(part.rows) * RowBytes(part.type, stage.cols);
+    }
+    if (g.nparts == 0) {
+      g.type = GUFO_CUDA_Q4_K;   // a norm without a product (a step without logits)
+    }
+    g.cols = stage.cols;
+    if (g.cols % kSuperBlock != 0) {
+      problem = "a product's input is not a whole number of 256-value blocks";
+      return -1;
+    }
+    g.slabs_per_tile = (g.cols / kSuperBlock + 7) / 8;
+    g.split = split && g.slabs_per_tile > 1 ? 1 : 0;
+    g.y = y;
+    g.y_stride = stage.y_stride;
+    g.y_split_stride = c.hidden;
+    region = std::max(region, StepImageBytes(g.type, g.cols));
+    if (g.split) {
+      max_split = std::max(max_split, g.slabs_per_tile);
+    }
+    HostOp h{};
+    h.op.kind = kStepGemv;
+    h.op.items = g.split ? g.tiles * g.slabs_per_tile : g.tiles;
+    h.op.arg = static_cast<int>(gemv.size());
+    h.stage = stage_kind;
+    h.bytes = bytes;
+    ops.push_back(h);
+    gemv.push_back(g);
+    return static_cast<int>(gemv.size()) - 1;
+  };
+  auto res_norm = [&](StepGemv& g, const float* h_in, const float* pending, int pending_parts, const float* norm_w,
+                      float* h_out) {
+    g.prologue = kPrologueResNorm;
+    g.h_in = h_in;
+    g.delta = pending;
+    g.delta_parts = pending_parts;
+    g.delta_stride = c.hidden;
+    g.norm_w = norm_w;
+    g.eps = c.rms_eps;
+    g.h_out = h_out;
+    g.normed_out = d->normed;
+  };
+  // Every product that feeds a residual add writes its (partial) rows here.
+  float* out_parts = nullptr;   // allocated below, once max_split is known: patched in afterwards
+  {
+    HostOp h{};
+    h.op.kind = kStepEmbed;
+    h.op.items = 1;
+    h.stage = GUFO_CUDA_TIMELINE_EMBED;
+    ops.push_back(h);
+  }
+  if (d->embed.type != GUFO_CUDA_Q4_K && d->embed.type != GUFO_CUDA_Q6_K && d->embed.type != GUFO_CUDA_F32) {
+    return no("the embedding format runs on the launch chain");
+  }
+  int cur = 0;
+  bool have_pending = false;
+  int pending_parts = 1;
+  std::vector<int> out_users;    // gemv indices whose y is out_parts
+  std::vector<int> out_readers;  // gemv indices whose delta is out_parts
+  for (int il = 0; il < c.layers; ++il) {
+    auto& l = d->layers[il];
+    int gi = product(l.in, -1, false, d->in, GUFO_CUDA_TIMELINE_IN);
+    if (gi < 0) {
+      return no(problem);
+    }
+    res_norm(gemv[gi], d->h[cur], have_pending ? reinterpret_cast<const float*>(1) : nullptr, pending_parts,
+             l.attn_norm, d->h[cur ^ 1]);
+    if (have_pending) {
+      out_readers.push_back(gi);
+    }
+    cur ^= 1;
+    if (l.attention) {
+      AttnArgs a{c.heads, c.kv_heads, c.head_dim, c.rope_dim, c.max_positions, c.rms_eps, d->position_dev,
+                 d->in, l.q_norm, l.k_norm, d->inv_freq, l.keys, l.values, d->queries, d->partials, d->mixed, 0};
+      const int items[3] = {c.heads + c.kv_heads, kAttnSplits * c.kv_heads, c.heads};
+      const int kinds[3] = {kStepAttnPrep, kStepAttnSlice, kStepAttnMerge};
+      for (int k = 0; k < 3; ++k) {
+        HostOp h{};
+        h.op.kind = kinds[k];
+        h.op.items = items[k];
+        h.op.arg = static_cast<int>(attn.size());
+        h.stage = GUFO_CUDA_TIMELINE_ATTENTION;
+        ops.push_back(h);
+      }
+      attn.push_back(a);
+    } else {
+      const int dk = l.linear.head_dim;
+      if (l.gate_rows.alpha_w == nullptr) {
+        return no("ssm_alpha / ssm_beta are not F32 rows");
+      }
+      if (dk % 32 != 0 || dk > 128 || kSuperBlock % dk != 0 || c.hidden % 4 != 0) {
+        return no("the DeltaNet head width does not tile 256-value blocks");
+      }
+      StepDelta s{};
+      s.in = d->in;
+      s.gate_x = d->normed;
+      s.alpha_w = l.gate_rows.alpha_w;
+      s.beta_w = l.gate_rows.beta_w;
+      s.cols = c.hidden;
+      s.conv_w = l.linear.conv;
+      s.ssm_a = l.linear.ssm_a;
+      s.dt_bias = l.linear.dt_bias;
+      s.conv[0] = l.conv[0];
+      s.conv[1] = l.conv[1];
+      s.state = l.ssm;
+      s.y = d->mixed_raw;
+      s.key_heads = l.linear.key_heads;
+      s.value_heads = l.linear.value_heads;
+      s.head_dim = dk;
+      s.conv_kernel = l.linear.conv_kernel;
+      HostOp h{};
+      h.op.kind = kStepDelta;
+      h.op.items = s.value_heads * (dk / 32);
+      h.op.arg = static_cast<int>(delta.size());
+      h.stage = GUFO_CUDA_TIMELINE_DELTANET;
+      h.bytes = 2ll * s.value_heads * dk * dk * 4;
+      ops.push_back(h);
+      delta.push_back(s);
+    }
+    gi = product(l.out, -1, true, nullptr, GUFO_CUDA_TIMELINE_OUT);
+    if (gi < 0) {
+      return no(problem);
+    }
+    out_users.push_back(gi);
+    if (l.attention) {
+      gemv[gi].prologue = kProloguePlain;
+      gemv[gi].x = d->mixed;
+    } else {
+      const int64_t channels = static_cast<int64_t>(2 * l.linear.key_heads + l.linear.value_heads) * l.linear.head_dim;
+      gemv[gi].prologue = kPrologueGatedNorm;
+      gemv[gi].x = d->mixed_raw;
+      gemv[gi].z = d->in + channels;
+      gemv[gi].gate_w = l.linear.ssm_norm;
+      gemv[gi].gate_head_dim = l.linear.head_dim;
+      gemv[gi].eps = l.linear.rms_eps;
+    }
+    const int out_split = gemv[gi].split ? gemv[gi].slabs_per_tile : 1;
+    gi = product(l.ffn_in, -1, false, d->ffn, GUFO_CUDA_TIMELINE_FFN_IN);
+    if (gi < 0) {
+      return no(problem);
+    }
+    res_norm(gemv[gi], d->h[cur], reinterpret_cast<const float*>(1), out_split, l.post_norm, d->h[cur ^ 1]);
+    out_readers.push_back(gi);
+    cur ^= 1;
+    gi = product(l.ffn_down, -1, true, nullptr, GUFO_CUDA_TIMELINE_FFN_DOWN);
+    if (gi < 0) {
+      return no(problem);
+    }
+    out_users.push_back(gi);
+    gemv[gi].prologue = kPrologueSwiGlu;
+    gemv[gi].x = d->ffn;
+    have_pending = true;
+    pending_parts = gemv[gi].split ? gemv[gi].slabs_per_tile : 1;
+  }
+  // The tail: the LM head, or only the final norm.
+  const size_t body = ops.size();
+  std::vector<HostOp> tail[2];
+  for (int with = 0; with < 2; ++with) {
+    ops.resize(body);
+    const int gi = product(d->lm_head, with ? -1 : 0, false, d->logits, GUFO_CUDA_TIMELINE_LM_HEAD);
+    if (gi < 0) {
+      return no(problem);
+    }
+    res_norm(gemv[gi], d->h[cur], have_pending ? reinterpret_cast<const float*>(1) : nullptr, pending_parts,
+             d->output_norm, d->h[cur ^ 1]);
+    if (have_pending) {
+      out_readers.push_back(gi);
+    }
+    gemv[gi].advance = d->position_dev;
+    plan.final_h = d->h[cur ^ 1];
+    tail[with].push_back(ops.back());
+  }
+  ops.resize(body);
+  plan.region_bytes = (region + 127) / 128 * 128;
+  plan.grid = StepGridBlocks(ctx->device, plan.region_bytes);
+  if (plan.grid <= 0) {
+    return no("the device cannot hold the kernel's shared memory or has no cooperative launch");
+  }
+  int rc;
+  if ((rc = Alloc(d, static_cast<size_t>(max_split) * c.hidden * 4, reinterpret_cast<void**>(&out_parts))) != GUFO_CUDA_OK) {
+    return rc;
+  }
+  for (int gi : out_users) {
+    gemv[gi].y = out_parts;
+  }
+  for (int gi : out_readers) {
+    gemv[gi].delta = out_parts;
+  }
+  // Items are dealt to the grid's teams in one running round-robin over the
+  // whole step, so that a short operation does not always land on the same SMs.
+  const int teams = plan.grid * kStepTeams;
+  for (int with = 0; with < 2; ++with) {
+    std::vector<HostOp> all(ops.begin(), ops.end());
+    all.insert(all.end(), tail[with].begin(), tail[with].end());
+    std::vector<StepOp> dev;
+    int64_t rot = 0;
+    for (HostOp& h : all) {
+      h.op.rot = static_cast<int>(rot % teams);
+      rot += h.op.items;
+      dev.push_back(h.op);
+      plan.op_stage[with].push_back(h.stage);
+      plan.op_bytes[with].push_back(h.bytes);
+    }
+    plan.nops[with] = static_cast<int>(dev.size());
+    if ((rc = Alloc(d, dev.size() * sizeof(StepOp), reinterpret_cast<void**>(&plan.ops[with]))) != GUFO_CUDA_OK) {
+      return rc;
+    }
+    GUFO_CUDA_TRY(cudaMemcpyAsync(plan.ops[with], dev.data(), dev.size() * sizeof(StepOp), cudaMemcpyHostToDevice,
+                                  ctx->stream));
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  }
+  auto upload = [&](const void* host, size_t bytes, void** dev) -> int {
+    const int status = Alloc(d, bytes > 0 ? bytes : 16, dev);
+    if (status != GUFO_CUDA_OK) {
+      return status;
+    }
+    if (bytes > 0) {
+      GUFO_CUDA_TRY(cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+      GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    }
+    return GUFO_CUDA_OK;
+  };
+  if ((rc = upload(gemv.data(), gemv.size() * sizeof(StepGemv), reinterpret_cast<void**>(&plan.gemv))) != GUFO_CUDA_OK ||
+      (rc = upload(delta.data(), delta.size() * sizeof(StepDelta), reinterpret_cast<void**>(&plan.delta))) != GUFO_CUDA_OK ||
+      (rc = upload(attn.data(), attn.size() * sizeof(AttnArgs), reinterpret_cast<void**>(&plan.attn))) != GUFO_CUDA_OK ||
+      (rc = Alloc(d, 16, reinterpret_cast<void**>(&plan.sync))) != GUFO_CUDA_OK ||
+      (rc = Alloc(d, (std::max(plan.nops[0], plan.nops[1]) + 1) * 8, reinterpret_cast<void**>(&plan.stamps))) != GUFO_CUDA_OK) {
+    return rc;
+  }
+  GUFO_CUDA_TRY(cudaMemsetAsync(plan.sync, 0, 16, ctx->stream));
+  GUFO_CUDA_TRY(cudaMallocHost(reinterpret_cast<void**>(&plan.error_pinned), 4));
+  *plan.error_pinned = 0;
+  plan.ok = true;
+  return GUFO_CUDA_OK;
+}
+
+// Enqueues the one-token step as the persistent kernel.
+int EnqueueStepKernel(gufo_cuda_decoder* d, int parity, bool want_logits) {
+  auto& plan = d->plan;
+  gufo_cuda_ctx* ctx = d->ctx;
+  const int with = want_logits ? 1 : 0;
+  StepProgram p{};
+  p.ops = plan.ops[with];
+  p.nops = plan.nops[with];
+  p.gemv = plan.gemv;
+  p.delta = plan.delta;
+  p.attn = plan.attn;
+  p.embed = EmbedArgs{d->embed.data, d->embed.type, static_cast<int>(d->embed.row_bytes), d->c.hidden, d->token_dev,
+                      d->h[0]};
+  p.sync = plan.sync;
+  p.stamps = plan.stamps;
+  p.parity = parity;
+  p.region_bytes = plan.region_bytes;
+  int khz = 0;
+  cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device);
+  p.wait_limit = static_cast<long long>(khz > 0 ? khz : 1000000) * ctx->step_wait_us / 1000;
+  p.skip_arrival_at = ctx->step_skip_arrival;
+  plan.last_with = with;
+  d->final_h = plan.final_h;
+  return LaunchStep(ctx, p, plan.grid);
+}
+
+// After the stream has been synchronized: a wait of the persistent kernel that
+// ran out. Clears the error for the next step.
+int CheckStepKernel(gufo_cuda_decoder* d) {
+  auto& plan = d->plan;
+  if (!plan.ok) {
+    return GUFO_CUDA_OK;
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  GUFO_CUDA_TRY(cudaMemcpyAsync(plan.error_pinned, plan.sync + 2, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  const unsigned code = *plan.error_pinned;
+  if (code != 0) {
+    GUFO_CUDA_TRY(cudaMemsetAsync(plan.sync, 0, 16, ctx->stream));
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return Fail(GUFO_CUDA_TIMEOUT, "decoder step: a wait inside the step kernel ran out (code " +
+                                       std::to_string(code) + "); the outputs and states of that step are invalid");
+  }
+  return GUFO_CUDA_OK;
+}
+
 }  // namespace
 }  // namespace gufo
 
@@ -1061,7 +1170,8 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
     size_t n;
   } bufs[] = {{&d->h[0], two * c.hidden}, {&d->h[1], two * c.hidden},
               {&d->normed, two * c.hidden},
-              {&d->in, two * in_max}, {&d->mixed, two * mixed}, {&d->out, two * c.hidden},
+              {&d->in, two * in_max}, {&d->mixed, two * mixed}, {&d->mixed_raw, two * mixed},
+              {&d->out, two * c.hidden},
               {&d->ffn, two * 2 * c.ffn}, {&d->act, two * c.ffn},
               {&d->logits, two * c.vocab}, {&d->queries, static_cast<size_t>(attn_dim)},
               {&d->partials, static_cast<size_t>(c.kv_heads) * gufo::kAttnSplits * group * (c.head_dim + 2)},
@@ -1090,6 +1200,9 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
     if ((e = cudaEventCreateWithFlags(&read, cudaEventDisableTiming)) != cudaSuccess) {
       return fail(gufo::CudaFail(e, "cudaEventCreate"));
     }
+  }
+  if ((rc = gufo::BuildStepPlan(d)) != GUFO_CUDA_OK) {
+    return fail(rc);
   }
   *out = d;
   // Zero states (the lock is already held: reset's body inline).
@@ -1126,6 +1239,9 @@ int gufo_cuda_decoder_destroy(gufo_cuda_decoder* d) {
   }
   if (d->token_pinned != nullptr) {
     cudaFreeHost(d->token_pinned);
+  }
+  if (d->plan.error_pinned != nullptr) {
+    cudaFreeHost(d->plan.error_pinned);
   }
   for (cudaEvent_t read : d->token_read) {
     if (read != nullptr) {
@@ -1193,7 +1309,14 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
   const int parity = d->conv_cur;
   const int pair = count - 1, with = want_logits != 0 ? 1 : 0;
   auto enqueue = [&]() { return gufo::EnqueueStep(d, parity, with != 0, count); };
-  if (d->c.use_graph && d->eager_runs[pair][with] >= 2 && !d->timeline) {
+  // One token: the whole step as one persistent kernel, where the model allows it.
+  const bool kernel_step = count == 1 && d->plan.ok && ctx->step_kernel && !ctx->force_general && !d->timeline;
+  if (kernel_step) {
+    const int rc = gufo::EnqueueStepKernel(d, parity, with != 0);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+  } else if (d->c.use_graph && d->eager_runs[pair][with] >= 2 && !d->timeline) {
     cudaGraphExec_t& exec = d->graph[pair][parity][with];
     if (exec == nullptr) {
       cudaGraph_t graph = nullptr;
@@ -1245,7 +1368,54 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
   if (host_logits != nullptr) {
     GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(count) * d->c.vocab * 4,
                                   cudaMemcpyDeviceToHost, ctx->stream));
+    if (kernel_step) {
+      return gufo::CheckStepKernel(d);   // copies the error word down and waits for the stream
+    }
     GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  }
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_decoder_status(gufo_cuda_decoder* d) {
+  if (d == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_status: null decoder");
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return gufo::CheckStepKernel(d);
+}
+
+int gufo_cuda_decoder_step_profile(gufo_cuda_decoder* d, int capacity, int* stages, int64_t* bytes, double* us,
+                                   int* count) {
+  if (d == nullptr || count == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "decoder_step_profile: null pointer");
+  }
+  *count = 0;
+  const auto& plan = d->plan;
+  if (!plan.ok) {
+    return GUFO_CUDA_OK;   // the model runs on the launch chain: no operations to report
+  }
+  gufo_cuda_ctx* ctx = d->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  const int with = plan.last_with;
+  const int n = plan.nops[with];
+  std::vector<unsigned long long> stamps(n + 1);
+  GUFO_CUDA_TRY(cudaMemcpyAsync(stamps.data(), plan.stamps, (n + 1) * 8, cudaMemcpyDeviceToHost, ctx->stream));
+  GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  *count = n;
+  for (int i = 0; i < n && i < capacity; ++i) {
+    if (stages != nullptr) {
+      stages[i] = plan.op_stage[with][i];
+    }
+    if (bytes != nullptr) {
+      bytes[i] = plan.op_bytes[with][i];
+    }
+    if (us != nullptr) {
+      us[i] = static_cast<double>(stamps[i + 1] - stamps[i]) * 1e-3;
+    }
   }
   return GUFO_CUDA_OK;
 }

@@ -568,6 +568,33 @@ int gufo_cuda_decoder_step(gufo_cuda_decoder* decoder, int token,
 int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* decoder, const int* tokens,
                                   int count, int want_logits,
                                   float* host_logits);
+/* With the context option "step_kernel" = 1, one-token steps of a dense model
+ * whose stages hold one block format each (Q4_K or Q6_K; F32 alpha / beta rows)
+ * run as ONE persistent kernel, launched cooperatively with one thread block
+ * per SM, instead of a chain of launches: the reference's own NPU decoder
+ * submits a layer at a time for the same reason
+ * (src/models/qwen35_2b/npu_decoder.hpp:18-25). Other models and two-token
+ * steps take the launch chain regardless. The option is off unless set: on
+ * B200 a grid-wide barrier costs what a programmatic kernel boundary does and
+ * the chain is the faster of the two. Every wait inside the kernel is bounded (option "step_wait_us",
+ * two seconds unless set): a wait that runs out ends the kernel, and the step
+ * call that downloads the logits, or gufo_cuda_decoder_status, returns
+ * GUFO_CUDA_TIMEOUT once; the outputs and states of that step are invalid
+ * (gufo_cuda_decoder_reset starts over), the decoder and the context stay
+ * usable. gufo_cuda_decoder_status waits for the stream and reports such a
+ * failure of steps that left their logits on the device. */
+int gufo_cuda_decoder_status(gufo_cuda_decoder* decoder);
+/* The operations of the last step run by the persistent kernel, in order: the
+ * stage each belongs to (a GUFO_CUDA_TIMELINE_* kind, as
+ * gufo_cuda_decoder_timeline reports for the launch chain; the reference keeps
+ * the same split, NpuDecoder::Timeline, npu_decoder.hpp:121-154), the weight or
+ * state bytes it moves, and its device time in microseconds from block 0's
+ * clock stamps, barrier to barrier. Up to `capacity` entries are written
+ * (arrays may be NULL); *count receives the number of operations, 0 when the
+ * model runs on the launch chain. */
+int gufo_cuda_decoder_step_profile(gufo_cuda_decoder* decoder, int capacity,
+                                   int* stages, int64_t* bytes, double* us,
+                                   int* count);
 /* NpuDecoder::Resolve (npu_decoder.cpp:630-650) after a two-token step:
  * keep_second != 0 keeps the draft (the DeltaNet draft states become the
  * states), 0 rolls the decoder back to just after the first token (its conv

@@ -75,9 +75,12 @@ def test_lm_head_248320_rows_against_oracle_row_sample(ctx, oracle, cols, tokens
     dev = torch.device("cuda:0")
     gen = torch.Generator(device=dev).manual_seed(40 + cols)
     raw = Q.quantize(Q.GGML_Q6_K, torch.randn(rows, cols, device=dev, generator=gen) * 0.02)
-    m = ctx.matrix_from_device(Q.GGML_Q6_K, raw.data_ptr(), rows, cols)
     x = torch.randn(tokens, cols, device=dev, generator=gen)
     y = torch.empty(tokens, rows, device=dev)
+    # The context has its own stream: the inputs must be ready before it rearranges the Q6_K
+    # rows (matrix_from_device) and multiplies.
+    torch.cuda.synchronize()
+    m = ctx.matrix_from_device(Q.GGML_Q6_K, raw.data_ptr(), rows, cols)
     ctx.matmul_device(Context._parts([(m, 0, rows)]), 1, x, tokens, y)
     ctx.synchronize()
     got = y.cpu().numpy()
