@@ -375,9 +375,9 @@ def run_probe(which: str) -> None:
     torch.cuda.set_stream(stream)
     ctx = Context(0, stream.cuda_stream)
     gen = torch.Generator(device=dev).manual_seed(1)
-    if which in ("q4k", "q6k"):
-        t = Q.GGML_Q4_K if which == "q4k" else Q.GGML_Q6_K
-        rows, cols, copies = (6144, 2048, 24) if which == "q4k" else (131072, 2048, 1)
+    if which in ("q4k", "q6k", "q4k_big"):
+        t = Q.GGML_Q6_K if which == "q6k" else Q.GGML_Q4_K
+        rows, cols, copies = {"q4k": (6144, 2048, 24), "q6k": (131072, 2048, 1), "q4k_big": (262144, 2048, 1)}[which]
         raw = Q.quantize(t, torch.randn(rows, cols, device=dev, generator=gen) * 0.02)
         keep = [raw.clone() for _ in range(copies)]
         mats = [Context._parts([(ctx.matrix_from_device(t, r.data_ptr(), rows, cols), 0, rows)]) for r in keep]
@@ -527,7 +527,7 @@ def probe_moe(ctx, stream, dev, gen) -> None:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["q4k", "q6k", "deltanet", "gemm", "moe"],
+    ap.add_argument("--probe", default=None, choices=["q4k", "q4k_big", "q6k", "deltanet", "gemm", "moe"],
                     help="run a few launches of one kernel on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)

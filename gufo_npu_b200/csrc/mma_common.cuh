@@ -64,7 +64,7 @@ int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
 
 __device__ __forceinline__ void MmaU8S8(int (&d)[4], const uint32_t (&a)[4],
                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -74,7 +74,7 @@ __device__ __forceinline__ void MmaU8S8(int (&d)[4], const uint32_t (&a)[4],
 // The same with signed rows (A) as well.
 __device__ __forceinline__ void MmaS8S8(int (&d)[4], const uint32_t (&a)[4],
                                         uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 "
       "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
@@ -105,6 +105,36 @@ __device__ __forceinline__ uint32_t LoadStream4(const void* p) {
 __device__ __forceinline__ void PrefetchL2(const void* p, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
 }
+
+// ---- bulk copies completing on a shared-memory barrier ------------------------
+
+__device__ __forceinline__ uint32_t SharedAddress(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarArriveExpectTx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
+// `bytes` (a multiple of 16; both addresses 16-byte aligned) from global to this
+// block's shared memory; the barrier's pending byte count drops as they land.
+__device__ __forceinline__ void BulkCopy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// SM clock cycles a block waits for bytes it requested itself before giving the
+// slab up (about a second; a copy that has not landed by then never will).
+constexpr long long kLandLimit = 2000000000ll;
 
 // Copies `bytes` (a multiple of 16) from global to shared memory with 16-byte
 // asynchronous copies spread over the block, then waits and synchronizes.

@@ -1,7 +1,19 @@
 // The arithmetic of one Q4_K unit (16 rows x one 256-value block) on the int8
-// tensor-core path, shared by the GEMV kernel (gemv_q4k_mma.cu) and the
-// persistent decode-step kernel (step_kernel.cu). See gemv_q4k_mma.cu for the
-// operand layout and mma_common.cuh for the fixed-point image.
+// tensor-core path, shared by the GEMV kernel (gemv_mma.cu) and the persistent
+// decode-step kernel (step_kernel.cu); the fixed-point image of the activations
+// is described in mma_common.cuh. A unit is read from a slab in shared memory:
+// 16 rows of up to eight 144-byte blocks, rows padded by 32 bytes so that the
+// 64-bit fragment reads of the eight rows of a quarter-warp fall in distinct
+// banks.
+//
+// MMA operand layout (m16n8k32, A row-major u8, B column-major s8). Lane
+// (g = lane / 4, t = lane % 4) holds rows g and g + 8. The 32 bytes of a nibble
+// pair p carry sub-block 2p in the low and 2p + 1 in the high nibbles; lane t
+// loads bytes 8t..8t+7, so its two A words per row are values 8t..8t+3 and
+// 8t+4..8t+7 of the sub-block and the matching B words are the same eight
+// bytes of column g's plane: one 64-bit shared load, no permutation. High
+// nibbles are fed as 16 q (mask 0xF0), the factor 1/16 is folded into the
+// column scale.
 #pragma once
 
 #include "mma_common.cuh"
@@ -12,7 +24,6 @@ namespace q4k {
 constexpr int kSlabBlocks = 8;                              // blocks per slab = warps
 constexpr int kSlabRowBytes = kSlabBlocks * kQ4KBytes + 32;   // padded row in shared memory
 constexpr int kSlabBytes = 16 * kSlabRowBytes;
-constexpr int kStages = 3;
 
 struct Q4KUnit {
   uint4 head[2];   // rows g, g + 8: d|dmin, three scale words

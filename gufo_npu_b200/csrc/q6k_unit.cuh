@@ -1,7 +1,20 @@
 // The arithmetic of one Q6_K unit (16 rows x one 256-value block) on the int8
-// tensor-core path, shared by the GEMV kernel (gemv_q6k_mma.cu) and the
-// persistent decode-step kernel (step_kernel.cu). See gemv_q6k_mma.cu for the
-// operand layout and mma_common.cuh for the fixed-point image.
+// tensor-core path, shared by the GEMV kernel (gemv_mma.cu) and the persistent
+// decode-step kernel (step_kernel.cu); the fixed-point image of the activations
+// is described in mma_common.cuh. The codes go to the MMA as the signed bytes
+// 4 * (q - 32), so no offset term is left; the factor 1/4 sits in the staged
+// image's column factors. A unit is read from a slab in shared memory: 16 rows
+// of up to eight blocks in the planar device arrangement (common.cuh), one
+// contiguous run of up to 1680 bytes per row.
+//
+// MMA operand layout (m16n8k32, A row-major s8, B column-major s8). A 32-value
+// run (quarter k of a half) holds two scale groups: values 0..15 and 16..31.
+// Lane (g, t) loads bytes 8t..8t+7 of the run's nibble and high-bit planes, so
+// lanes t = 0, 1 carry the first group and t = 2, 3 the second. With several
+// tokens each run is multiplied twice, against B fragments in which the other
+// group's lanes read a plane of zeros; every product then holds one group's 16
+// dots and takes that group's int8 scale. One token leaves room for both groups
+// in the eight columns of a single product (MultiplyRun).
 #pragma once
 
 #include "mma_common.cuh"
@@ -13,7 +26,6 @@ constexpr int kSlabBlocks = kQ6KSlabBlocks;                    // blocks per sla
 constexpr int kSlabDataBytes = kSlabBlocks * kQ6KBytes;        // 1680
 constexpr int kSlabRowBytes = kSlabDataBytes + 16;             // 424 words: 8 mod 32
 constexpr int kSlabBytes = 16 * kSlabRowBytes;
-constexpr int kStages = 2;
 
 struct Q6KUnit {
   uint2 ql[2][2][2];   // [row][half][run parity]: bytes 8t..8t+7 of ql[32 * parity ..]

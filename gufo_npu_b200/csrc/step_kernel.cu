@@ -53,30 +53,8 @@ struct TeamSync {
   __device__ __forceinline__ void operator()() const { NamedSync(id, kTeamThreads); }
 };
 
-__device__ __forceinline__ uint32_t SharedAddr(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
 __device__ __forceinline__ void MbarArrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void MbarArriveExpectTx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ void BulkCopy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ unsigned LoadAcquireGpu(const unsigned* p) {
   unsigned v;
@@ -839,7 +817,7 @@ __device__ __noinline__ void Producer(const StepShared& sh, int gg0, int ng) {
       }
       any = true;
       const uint32_t bar = sh.full(team, slot);
-      const uint32_t dst = SharedAddr(sh.slot(team, slot));
+      const uint32_t dst = SharedAddress(sh.slot(team, slot));
       if (op.kind == kStepGemv) {
         const StepGemv& a = p.gemv[op.arg];
         const int spt = a.slabs_per_tile;
@@ -972,7 +950,7 @@ StepKernel(const __grid_constant__ StepProgram p) {
   sh.region = smem;
   sh.exchange = reinterpret_cast<float*>(smem + p.region_bytes);
   sh.ring = reinterpret_cast<uint8_t*>(sh.exchange) + kStepTeams * kStepExchange * kTeamWarps * 16 * TOKENS * 4;
-  sh.bars = SharedAddr(sh.ring + kStepTeams * kStepSlots * kStepSlotBytes);
+  sh.bars = SharedAddress(sh.ring + kStepTeams * kStepSlots * kStepSlotBytes);
   sh.abort = &abort_flag;
   sh.program = &p;
   const int warp = threadIdx.x >> 5;
