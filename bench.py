@@ -11,10 +11,12 @@ N(0, 0.02) values packed by this project's quantizers from a seed; nothing is do
 
 Prints ONE JSON line: decode-step tok/s with the state resident on the device (`value`), the
 same through the host-facing call with the token uploaded and the logits downloaded every step
-(`e2e`), the HBM roofline of the dominant kernel measured live (`roofline`), and the reference's
-own CPU decoder timed on the host cores (`cpu_baseline`). `--impl reference` times only the
-latter. With --gpus N > 1 (torchrun) the projections are row-split over N GPUs with an NCCL
-all-gather after each product.
+(`e2e`), the HBM roofline of the metric's kernel (the 6144 x 2048 Q4_K GEMV) measured live
+(`roofline`; other kernels under `roofline_more`), the logits' agreement with the reference on
+the same model and tokens (`parity`), and the reference's own CPU decoder timed on the host
+cores (`cpu_baseline`). `--impl reference` times only the latter. With --gpus N > 1 (torchrun)
+the projections are row-split over N GPUs with an all-gather after each product; the line then
+also carries the row-split verify batch and the expert-parallel MoE layer.
 """
 from __future__ import annotations
 
@@ -54,12 +56,8 @@ def weight_bytes(tensors) -> int:
 
 
 def measured_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            p = json.load(f)
-        return float(p["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+    from gufo_npu_b200.bench_support import measured_hbm_peak
+    return measured_hbm_peak()
 
 
 class ClockSampler:
@@ -129,9 +127,14 @@ def time_on_stream(fn, iters: int) -> float:
 
 # ---- reference arm / CPU baseline ---------------------------------------------
 
-def cpu_decode(tensors_host, cfg, steps: int, warmup: int, budget_s: float = 25.0):
+PARITY_TOKENS = (11, 4242, 98765, 7)   # the steps compared with the reference before the CPU timing
+
+
+def cpu_decode(tensors_host, cfg, steps: int, warmup: int, budget_s: float = 25.0, gpu_step=None):
     """Times the reference's own CPU decoder (Decoder::Step over GgufProjections, fp32) on the
-    host cores, where oracle/_ref was built; else this project's C restatement on a sample."""
+    host cores, where oracle/_ref was built; else this project's C restatement on a sample.
+    `gpu_step(token) -> logits`, when given, is run beside the reference's first steps and the
+    logits compared (the returned dict then carries "parity")."""
     from oracle import binding
     if binding.RefLib.available():
         ref = binding.RefLib()
@@ -139,6 +142,20 @@ def cpu_decode(tensors_host, cfg, steps: int, warmup: int, budget_s: float = 25.
         model = ref.open_model(image, precision_float=True)
         del image
         model.decoder_reset()
+        parity = None
+        if gpu_step is not None:
+            worst, same = 0.0, True
+            for tok in PARITY_TOKENS:
+                want = model.decoder_step(tok % cfg.vocab, cfg.vocab).astype(np.float64)
+                got = np.asarray(gpu_step(tok % cfg.vocab), dtype=np.float64)
+                worst = max(worst, float(np.linalg.norm(got - want) / np.linalg.norm(want)))
+                same = same and int(np.argmax(got)) == int(np.argmax(want))
+            parity = {"config2_logits_rel_l2": worst, "same_argmax": same, "tokens": len(PARITY_TOKENS),
+                      "tolerance": 2e-3, "against": "the reference's Decoder::Step over GgufProjections(kFloat), "
+                                                    "compiled from its sources, same model and tokens"}
+            if worst > 2e-3 or not same:
+                raise SystemExit(f"parity with the reference failed at the benchmarked configuration: {parity}")
+            model.decoder_reset()
         rng = np.random.default_rng(5)
         for _ in range(max(warmup, 1)):
             model.decoder_step_discard(int(rng.integers(0, cfg.vocab)))
@@ -150,14 +167,44 @@ def cpu_decode(tensors_host, cfg, steps: int, warmup: int, budget_s: float = 25.
             times.append(time.perf_counter() - t0)
             if time.perf_counter() - begin > budget_s:
                 break
+        # The reference's own kernels on two of the configurations, for the probes' rooflines:
+        # GgufProjections::MatMul over gate | up (2 x 6144 x 2048 Q4_K, rotating over the layers so
+        # that rows come from memory) and Mixer::Linear (16 heads of 128 x 128 state).
+        more = {}
+        x = rng.standard_normal(cfg.hidden).astype(np.float32)
+        t0 = time.perf_counter()
+        n = 0
+        while time.perf_counter() - t0 < 2.0:
+            model.apply("ffn_in", n % cfg.layers, x)
+            n += 1
+        us = (time.perf_counter() - t0) / n * 1e6
+        nbytes = 2 * cfg.ffn * Q.row_bytes(Q.GGML_Q4_K, cfg.hidden)
+        more["q4k_matmul_2x6144x2048"] = {"us": us, "GB/s": nbytes / us / 1e3}
+        linear_layers = [il for il in range(cfg.layers) if not cfg.is_full_attention(il)]
+        width = cfg.conv_channels + cfg.value_dim + 2 * cfg.linear_value_heads
+        conv = np.zeros((cfg.conv_kernel - 1) * cfg.conv_channels, dtype=np.float32)
+        ssm = (rng.standard_normal(cfg.linear_value_heads * cfg.linear_head_dim ** 2) * 0.1).astype(np.float32)
+        x_in = rng.standard_normal(width).astype(np.float32)
+        t0 = time.perf_counter()
+        n = 0
+        while time.perf_counter() - t0 < 1.0:
+            model.linear(linear_layers[n % len(linear_layers)], x_in, conv, ssm, cfg.value_dim)
+            n += 1
+        us = (time.perf_counter() - t0) / n * 1e6
+        more["deltanet_linear_16_heads_one_sequence"] = {"us": us, "GB/s": 2130048 / us / 1e3,
+                                                         "note": "the binding copies the 1 MiB state in and out per call"}
         model.close()
         ms = 1e3 * float(np.mean(times))
-        return {"value": 1e3 / ms, "unit": UNIT, "cores": ref.usable_cpus(), "kind": "reference",
-                "threads": f"{ref.projection_threads()} projection threads (HalfCpuWorkers + caller) and the mixers' pool, "
-                           f"the reference's defaults on {ref.usable_cpus()} usable CPUs",
-                "sample": f"{len(times)} whole decode steps of the same model through the reference's "
-                          f"Decoder::Step + GgufProjections(kFloat), compiled from its sources",
-                "ms_per_step": ms}
+        out = {"value": 1e3 / ms, "unit": UNIT, "cores": ref.usable_cpus(), "kind": "reference",
+               "threads": f"{ref.projection_threads()} projection threads (HalfCpuWorkers + caller) and the mixers' pool, "
+                          f"the reference's defaults on {ref.usable_cpus()} usable CPUs; the reference sizes its pools "
+                          f"itself (src/core/cpus.hpp:53-55) and offers no all-cores setting",
+               "sample": f"{len(times)} whole decode steps of the same model through the reference's "
+                         f"Decoder::Step + GgufProjections(kFloat), compiled from its sources",
+               "ms_per_step": ms, "kernels": more}
+        if parity is not None:
+            out["parity"] = parity
+        return out
     # Port: one layer's projections and 1/64 of the LM head through the single-threaded C
     # restatement, scaled to a step (the mixers' share is under 3 % of a step's bytes).
     oracle = binding.Oracle()
@@ -198,7 +245,7 @@ def run_reference(args):
     base = cpu_decode(host, cfg, steps=args.steps, warmup=args.warmup, budget_s=120.0)
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD, "seed": 1}, "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -222,7 +269,7 @@ def roofline_probes(ctx, proj, cfg, stream, peak):
         ctx.matmul_device(parts, 1, x, 1, y)
     ms = time_on_stream(lambda i: ctx.matmul_device(parts, 1, x, 1, y), 20)
     lm_bytes = cfg.vocab * Q.row_bytes(Q.GGML_Q6_K, cfg.hidden) + 4 * cfg.hidden + 4 * cfg.vocab
-    out["lm_head"] = {"kernel": "GemvQ6KMma (+ StageKernel)", "shape": f"{cfg.vocab}x{cfg.hidden} Q6_K, 1 token",
+    out["lm_head"] = {"kernel": "GemvMma<Q6_K, 1 token>", "shape": f"{cfg.vocab}x{cfg.hidden} Q6_K, 1 token",
                       "bytes": lm_bytes, "us": ms * 1e3, "achieved": lm_bytes / ms / 1e6,
                       "frac": lm_bytes / ms / 1e6 / peak}
     # 6144 x 2048 Q4_K: rotate over the 24 layers' gate matrices (170 MB > L2), graph-replayed.
@@ -238,9 +285,24 @@ def roofline_probes(ctx, proj, cfg, stream, peak):
     g.replay()
     ms = time_on_stream(lambda i: g.replay(), 20) / len(mats)
     b = cfg.ffn * Q.row_bytes(Q.GGML_Q4_K, cfg.hidden) + 4 * cfg.hidden + 4 * cfg.ffn
-    out["q4k_gemv"] = {"kernel": "GemvQ4KMma (+ StageKernel)", "shape": f"{cfg.ffn}x{cfg.hidden} Q4_K, 1 token",
+    out["q4k_gemv"] = {"kernel": "GemvMma<Q4_K, 1 token>", "shape": f"{cfg.ffn}x{cfg.hidden} Q4_K, 1 token",
                        "bytes": b, "us": ms * 1e3, "achieved": b / ms / 1e6, "frac": b / ms / 1e6 / peak,
                        "note": "24 distinct matrices per graph replay (170 MB, larger than L2)"}
+    # The same Q4_K kernel on a product large enough to run at its sustained rate (262144 x 2048,
+    # 302 MB): what the kernel streams once the per-launch ramp and tail are amortised.
+    big_rows = 262144
+    gen = torch.Generator(device=dev).manual_seed(9)
+    raw = Q.quantize(Q.GGML_Q4_K, torch.randn(big_rows, cfg.hidden, device=dev, generator=gen) * 0.02)
+    big = Context._parts([(ctx.matrix_from_device(Q.GGML_Q4_K, raw.data_ptr(), big_rows, cfg.hidden), 0, big_rows)])
+    yb = torch.empty(1, big_rows, device=dev)
+    for i in range(3):
+        ctx.matmul_device(big, 1, x, 1, yb)
+    ms = time_on_stream(lambda i: ctx.matmul_device(big, 1, x, 1, yb), 20)
+    b = big_rows * Q.row_bytes(Q.GGML_Q4_K, cfg.hidden) + 4 * cfg.hidden + 4 * big_rows
+    out["q4k_gemv_sustained"] = {"kernel": "GemvMma<Q4_K, 1 token>", "shape": f"{big_rows}x{cfg.hidden} Q4_K, 1 token",
+                                 "bytes": b, "us": ms * 1e3, "achieved": b / ms / 1e6, "frac": b / ms / 1e6 / peak}
+    torch.cuda.synchronize()
+    del raw, yb
     # DeltaNet step: 8 sequences x 16 heads x 128 x 128 fp32, 12 state sets (192 MB) rotated.
     hv, dk, nseq, sets = 16, 128, 8, 12
     st = torch.randn(sets, nseq, hv, dk, dk, device=dev) * 0.1
@@ -296,10 +358,10 @@ def run_ours(args):
     total_bytes = weight_bytes(tensors)
     ctx = Context(local, stream.cuda_stream)
     proj = CudaProjections(ctx, cfg, tensors)
-    dec = CudaDecoder(proj, tensors, max_positions=max(4096, 6 * (args.steps + args.warmup) + 64), use_graph=True)
+    dec = CudaDecoder(proj, tensors, max_positions=max(4096, 16 * (args.steps + args.warmup) + 256), use_graph=True)
     peak, peak_kind = measured_peaks()
     rng = np.random.default_rng(7)
-    tokens = rng.integers(0, cfg.vocab, size=6 * (args.steps + args.warmup) + 64).tolist()
+    tokens = rng.integers(0, cfg.vocab, size=16 * (args.steps + args.warmup) + 256).tolist()
     cursor = iter(tokens)
     logits_host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
 
@@ -307,14 +369,20 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         dec.step_device(next(cursor))
     torch.cuda.synchronize()
+    repeats = 5
     with ClockSampler(local) as clocks:
+        # K steps timed `repeats` times over (each between synchronizes, CUDA events on the
+        # launching stream); the median is reported, every repeat is listed.
         launches0 = ctx.launch_count()
-        ms_resident = time_on_stream(lambda i: dec.step_device(next(cursor)), args.steps)
-        launches = ctx.launch_count() - launches0
+        resident_ms = [time_on_stream(lambda i: dec.step_device(next(cursor)), args.steps) for _ in range(repeats)]
+        launches = (ctx.launch_count() - launches0) // repeats
+        ms_resident = float(np.median(resident_ms))
         # End to end: token id up (4 bytes, pinned), logits down (vocab fp32, pinned) every step.
         for _ in range(2):
             dec.Step(next(cursor), logits_host.numpy())
-        ms_e2e = time_on_stream(lambda i: dec.Step(next(cursor), logits_host.numpy()), args.steps)
+        e2e_ms = [time_on_stream(lambda i: dec.Step(next(cursor), logits_host.numpy()), args.steps)
+                  for _ in range(repeats)]
+        ms_e2e = float(np.median(e2e_ms))
         probes = roofline_probes(ctx, proj, cfg, stream, peak)
         # Two-token steps (a token and a draft, the weights read once for both), drafts kept
         # or rolled back: what speculative decoding pays per step on this path.
@@ -329,25 +397,37 @@ def run_ours(args):
     assert np.isfinite(logits_host.numpy()).all()
     host = {k: synth.Tensor(t.shape, t.ggml_type, t.data.cpu()) for k, t in tensors.items()}
     del tensors
-    base = cpu_decode(host, cfg, steps=200, warmup=2, budget_s=20.0)
-    lm = probes["lm_head"]
+    # The benchmarked decoder against the reference on the same first tokens, then the
+    # reference's own timing on the host cores.
+    dec.Reset()
+    base = cpu_decode(host, cfg, steps=200, warmup=2, budget_s=20.0, gpu_step=lambda tok: dec.Step(tok))
+    parity = base.pop("parity", None)
+    gemv = probes["q4k_gemv"]
     line = {
         "metric": METRIC, "value": 1e3 / ms_resident, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "weak",
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
         "data": "synthetic",
-        "config": {"workload": WORKLOAD, "seed": 1, "weight_bytes_per_step": total_bytes,
-                   "l2": "weights read per step (1.15 GB) exceed L2 (126 MB); no flush needed",
-                   "step_hbm_frac": total_bytes / (ms_resident * 1e-3) / 1e9 / peak,
-                   "launch": "CUDA graph per step parity, programmatic dependent launch"},
+        "config": {"workload": WORKLOAD, "seed": 1},
+        "notes": {"weight_bytes_per_step": total_bytes,
+                  "l2": "weights read per step (1.15 GB) exceed L2 (126 MB); no flush needed",
+                  "step_hbm_frac": total_bytes / (ms_resident * 1e-3) / 1e9 / peak,
+                  "launch": "CUDA graph per step parity, programmatic dependent launch",
+                  "timing": f"median of {repeats} repeats of {args.steps} steps",
+                  "ms_per_step_repeats": resident_ms, "e2e_ms_per_step_repeats": e2e_ms},
+        "parity": parity,
         "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                 "ms_per_step": ms_e2e},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "achieved": lm["achieved"], "peak": peak, "unit": "GB/s",
-                     "frac": lm["frac"], "traffic": LM_HEAD_TRAFFIC_BYTES_PER_ROW * cfg.vocab,
-                     "traffic_source": "ncu capture of the 131072-row case scaled by rows", "peak_kind": peak_kind, "kernel": lm["kernel"],
-                     "shape": lm["shape"], "bytes_per_launch": lm["bytes"], "us_per_launch": lm["us"]},
-        "roofline_more": {k: v for k, v in probes.items() if k != "lm_head"},
+        # The metric's kernel: the 6144 x 2048 Q4_K GEMV, one launch per product, 24 distinct
+        # matrices back to back. `traffic` is the DRAM traffic of one launch from an ncu capture of
+        # the same shape (read 7.09 MB + written 0.03 MB: the algorithmic bytes).
+        "roofline": {"bound": "hbm", "achieved": gemv["achieved"], "peak": peak, "unit": "GB/s",
+                     "frac": gemv["frac"], "traffic": Q4K_GEMV_TRAFFIC_BYTES,
+                     "traffic_source": "ncu capture of the same launch (bench.py --probe q4k)", "peak_kind": peak_kind,
+                     "kernel": gemv["kernel"], "shape": gemv["shape"], "bytes_per_launch": gemv["bytes"],
+                     "us_per_launch": gemv["us"], "note": gemv["note"]},
+        "roofline_more": {k: v for k, v in probes.items() if k != "q4k_gemv"},
         "pair_step": {"ms_kept": pair_ms[True], "ms_rolled_back": pair_ms[False],
                       "tok_s_all_kept": 2e3 / pair_ms[True], "tok_s_all_rolled_back": 1e3 / pair_ms[False],
                       "note": "NpuDecoder::Step(tokens, 2) + Resolve through gufo_cuda_decoder_step_tokens; "
@@ -358,11 +438,9 @@ def run_ours(args):
     print(json.dumps(line))
 
 
-# DRAM traffic of one LM-head launch: dram__bytes_read.sum + dram__bytes_write.sum of GemvQ6KMma
-# from one ncu capture of `bench.py --probe q6k` (131072 rows: 220.26 MB read, 4.04 MB written on
-# average), scaled by rows to the 248320-row launch (every row is read once, so traffic grows in
-# proportion). The summary with the command is profiles/gemv_q6k_mma_131072x2048.md.
-LM_HEAD_TRAFFIC_BYTES_PER_ROW = (220.26e6 + 4.04e6) / 131072
+# DRAM traffic of one 6144 x 2048 Q4_K GEMV launch: dram__bytes_read.sum + dram__bytes_write.sum
+# of the kernel from one ncu capture of `bench.py --probe q4k` (7.09 MB read, 0.03 MB written).
+Q4K_GEMV_TRAFFIC_BYTES = 7.09e6 + 0.03e6
 
 
 def run_probe(which: str) -> None:

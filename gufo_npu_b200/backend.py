@@ -346,9 +346,15 @@ class CudaProjections:
         attn_dim = c.heads * c.head_dim
         kv_dim = c.kv_heads * c.head_dim
         self.layers: List[dict] = []
-        for il in range(c.layers):
+        # The decoder layers, then the MTP layer (full attention) if the file has one
+        # (gguf_projections.cpp:114-125).
+        has_mtp = c.mtp_layers > 0 and f"blk.{c.layers}.nextn.eh_proj.weight" in tensors
+        for il in range(c.layers + (1 if has_mtp else 0)):
             p = f"blk.{il}."
             layer: dict = {}
+            if il >= c.layers:
+                self._check_shape(p + "nextn.eh_proj.weight", (2 * c.hidden, c.hidden))
+                layer[Stage.kMtpIn] = [self._all(p + "nextn.eh_proj.weight")]
             if c.is_moe:
                 self._check_shape(p + "ffn_gate_inp.weight", (c.hidden, c.experts))
                 self._check_shape(p + "ffn_gate_inp_shexp.weight", (c.hidden, 1))

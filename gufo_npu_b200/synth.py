@@ -44,6 +44,9 @@ class ModelConfig:
     expert_ffn: int = 0
     shared_expert_ffn: int = 0
     tied_embeddings: bool = True
+    # MTP (next-token prediction) layers stored after the decoder layers: blk.<layers> holds
+    # nextn.eh_proj and a full-attention layer (src/models/qwen35/config.cpp:25-26,74-78).
+    mtp_layers: int = 0
     # Types of the stored matrices.
     proj_type: int = Q.GGML_Q4_K
     down_type: int = Q.GGML_Q6_K
@@ -58,6 +61,8 @@ class ModelConfig:
         return self.shared_expert_ffn if self.is_moe else self.ffn
 
     def is_full_attention(self, layer: int) -> bool:
+        if layer >= self.layers:
+            return True   # the MTP layer (Config::IsFullAttention, config.hpp:52-54)
         return layer >= self.layers or (layer + 1) % self.full_attention_interval == 0
 
     @property
@@ -169,6 +174,30 @@ def build_model(cfg: ModelConfig, seed: int = 1, device: str = "cpu") -> Dict[st
             mat(p + "ffn_gate_exps.weight", c.hidden, c.expert_ffn, c.proj_type, c.experts)
             mat(p + "ffn_up_exps.weight", c.hidden, c.expert_ffn, c.proj_type, c.experts)
             mat(p + "ffn_down_exps.weight", c.expert_ffn, c.hidden, c.proj_type, c.experts)
+    if c.mtp_layers > 0:
+        # The MTP layer, drawn after everything else so that models without one keep their
+        # tensors: eh_proj over [embedding | hidden], its norms, a full-attention layer, an FFN.
+        p = f"blk.{c.layers}."
+        mat(p + "nextn.eh_proj.weight", 2 * c.hidden, c.hidden, c.proj_type)
+        for name in ("nextn.enorm.weight", "nextn.hnorm.weight", "nextn.shared_head_norm.weight",
+                     "attn_norm.weight", "post_attention_norm.weight"):
+            vec(p + name, 1.0 + rand(c.hidden, std=0.1))
+        mat(p + "attn_q.weight", c.hidden, 2 * attn_dim, c.proj_type)
+        mat(p + "attn_k.weight", c.hidden, kv_dim, c.proj_type)
+        mat(p + "attn_v.weight", c.hidden, kv_dim, c.proj_type)
+        mat(p + "attn_output.weight", attn_dim, c.hidden, c.proj_type)
+        vec(p + "attn_q_norm.weight", 1.0 + rand(c.head_dim, std=0.1))
+        vec(p + "attn_k_norm.weight", 1.0 + rand(c.head_dim, std=0.1))
+        suffix = "_shexp.weight" if c.is_moe else ".weight"
+        mat(p + "ffn_gate" + suffix, c.hidden, c.ffn_width, c.proj_type)
+        mat(p + "ffn_up" + suffix, c.hidden, c.ffn_width, c.proj_type)
+        mat(p + "ffn_down" + suffix, c.ffn_width, c.hidden, c.down_type)
+        if c.is_moe:
+            vec(p + "ffn_gate_inp.weight", rand(c.experts, c.hidden, std=0.05), (c.hidden, c.experts))
+            vec(p + "ffn_gate_inp_shexp.weight", rand(c.hidden, std=0.05), (c.hidden,))
+            mat(p + "ffn_gate_exps.weight", c.hidden, c.expert_ffn, c.proj_type, c.experts)
+            mat(p + "ffn_up_exps.weight", c.hidden, c.expert_ffn, c.proj_type, c.experts)
+            mat(p + "ffn_down_exps.weight", c.expert_ffn, c.hidden, c.proj_type, c.experts)
     return t
 
 
@@ -177,7 +206,7 @@ def metadata(cfg: ModelConfig) -> List[Tuple[str, object]]:
     a = cfg.architecture + "."
     keys: List[Tuple[str, object]] = [
         ("general.architecture", cfg.architecture),
-        (a + "block_count", cfg.layers),
+        (a + "block_count", cfg.layers + cfg.mtp_layers),
         (a + "embedding_length", cfg.hidden),
         (a + "attention.layer_norm_rms_epsilon", float(cfg.rms_eps)),
         (a + "full_attention_interval", cfg.full_attention_interval),
@@ -193,6 +222,8 @@ def metadata(cfg: ModelConfig) -> List[Tuple[str, object]]:
         (a + "ssm.time_step_rank", cfg.linear_value_heads),
         (a + "ssm.inner_size", cfg.value_dim),
     ]
+    if cfg.mtp_layers > 0:
+        keys.append((a + "nextn_predict_layers", cfg.mtp_layers))
     if cfg.is_moe:
         keys += [(a + "expert_count", cfg.experts), (a + "expert_used_count", cfg.experts_used),
                  (a + "expert_feed_forward_length", cfg.expert_ffn),

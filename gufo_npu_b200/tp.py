@@ -86,7 +86,11 @@ class TpDecoder:
             for i, (name, first, count) in enumerate(runs):
                 t = tensors[name]
                 rb = Q.row_bytes(t.ggml_type, t.cols)
-                view = t.data.to(dev)[first * rb:(first + count) * rb]
+                # A rank keeps its own rows only: a copy of the run, so that the whole tensor can
+                # be released once every stage has been cut.
+                view = t.data[first * rb:(first + count) * rb].to(dev)
+                if world > 1 and view.data_ptr() == t.data.data_ptr() + first * rb:
+                    view = view.clone()
                 self._keep.append(view)
                 arr[i] = _capi.Rows(ctx.matrix_from_device(t.ggml_type, view.data_ptr(), count, t.cols), 0, count)
             local = sum(count for _, _, count in runs)
@@ -387,6 +391,29 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
               "tokens": len(PARITY_TOKENS), "tolerance": 2e-3}
     if worst > 2e-3 or argmax_differs or gathers_differ:
         raise SystemExit(f"row-split parity failed: {parity}")
+    # The HBM roofline of the step's largest kernel on a rank: its run of the LM head's rows.
+    from .bench_support import measured_hbm_peak
+    peak, peak_kind = measured_hbm_peak()
+    head_arr, head_n, head_rows, _ = dec.lm_head
+    xh = torch.randn(1, cfg.hidden, device=f"cuda:{local}")
+    for _ in range(3):
+        ctx.matmul_device(head_arr, head_n, xh, 1, dec.local)
+    ms_head = timed(lambda: ctx.matmul_device(head_arr, head_n, xh, 1, dec.local))
+    head_bytes = head_rows * Q.row_bytes(Q.GGML_Q6_K, cfg.hidden) + 4 * cfg.hidden + 4 * head_rows
+    roofline = {"bound": "hbm", "achieved": head_bytes / ms_head / 1e6, "peak": peak, "unit": "GB/s",
+                "frac": head_bytes / ms_head / 1e6 / peak, "traffic": None, "peak_kind": peak_kind,
+                "kernel": "GemvMma<Q6_K, 1 token>", "shape": f"{head_rows}x{cfg.hidden} Q6_K: one rank's rows of the LM head",
+                "bytes_per_launch": head_bytes, "us_per_launch": ms_head * 1e3}
+    # The two other sharded paths: the row-split verify batch and the expert-parallel MoE layer.
+    dec.graphs.clear()
+    if other:
+        by_nccl.graphs.clear()
+    del replica
+    torch.cuda.empty_cache()
+    from . import mgpu_bench
+    sections = {}
+    for name, fn in (("verify_batch_row_split", mgpu_bench.verify_batch_tp), ("moe_layer_expert_parallel", mgpu_bench.moe_layer_ep)):
+        sections[name] = fn(ctx, rank, world, torch.device("cuda", local), max(steps // 2, 8), peak)
     if rank == 0:
         print(json.dumps({
             "metric": metric, "value": 1e3 / ms_resident, "unit": unit, "n_gpus": world, "steps": steps,
@@ -403,7 +430,9 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
                          "note": "the same GPUs as independent sequences, one resident decoder per GPU, no "
                                  "collective; not the metric's row-split configuration"},
             "parity": parity,
-            "roofline": None, "cpu_baseline": None,
+            "roofline": roofline, "cpu_baseline": None,
+            "verify_batch_row_split": sections["verify_batch_row_split"],
+            "moe_layer_expert_parallel": sections["moe_layer_expert_parallel"],
         }))
     dist.barrier()
     torch.cuda.synchronize()

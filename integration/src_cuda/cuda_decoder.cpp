@@ -108,14 +108,21 @@ Decoder::~Decoder() { gufo_cuda_decoder_destroy(decoder_); }
 
 const std::vector<float>& Decoder::Step(int token) {
   const int status = gufo_cuda_decoder_step(decoder_, token, logits_.data());
-  if (status == GUFO_CUDA_BAD_ARGUMENT) {
-    throw std::out_of_range("qwen35: token id out of range");
-  }
   if (status == GUFO_CUDA_TOO_LARGE) {
     throw std::length_error("cuda: the attention cache is full");
   }
   if (status != GUFO_CUDA_OK) {
-    throw std::runtime_error(std::string("cuda: ") + gufo_cuda_last_error(projections_.context()));
+    // A bad argument is a token id out of range (Decoder::Step's std::out_of_range,
+    // src/models/qwen35/decoder.cpp:483-485) only when the message says so; a step
+    // that awaits Resolve is a misuse of the interface.
+    const std::string text = gufo_cuda_last_error(projections_.context());
+    if (status == GUFO_CUDA_BAD_ARGUMENT) {
+      if (text.find("out of range") != std::string::npos) {
+        throw std::out_of_range(text);
+      }
+      throw std::logic_error("cuda: " + text);
+    }
+    throw std::runtime_error("cuda: " + text);
   }
   return logits_;
 }
@@ -131,8 +138,11 @@ const float* Decoder::Step(const int* tokens, int count, bool logits) {
   }
   if (status != GUFO_CUDA_OK) {
     const std::string text = gufo_cuda_last_error(projections_.context());
-    if (status == GUFO_CUDA_BAD_ARGUMENT && text.find("out of range") != std::string::npos) {
-      throw std::out_of_range(text);
+    if (status == GUFO_CUDA_BAD_ARGUMENT) {
+      if (text.find("out of range") != std::string::npos) {
+        throw std::out_of_range(text);
+      }
+      throw std::logic_error("cuda: " + text);
     }
     throw std::runtime_error("cuda: " + text);
   }

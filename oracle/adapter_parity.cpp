@@ -22,6 +22,7 @@
 #include "cuda/cuda_projections.hpp"
 #include "models/qwen35/decoder.hpp"
 #include "models/qwen35/gguf_projections.hpp"
+#include "models/qwen35/reference.hpp"
 
 int main(int argc, char** argv) {
   if (argc != 3) {
@@ -117,6 +118,36 @@ int main(int argc, char** argv) {
       return 1;
     }
     keep = !keep;
+  }
+  // A file with an MTP layer: Stage::kMtpIn and the MTP layer's own stages at
+  // layer index `layers`, adapter against GgufProjections on the same rows.
+  if (qwen35::HasMtpLayer(*file, a.config())) {
+    const qwen35::Config& c = a.config();
+    const qwen35::Stage stages[] = {qwen35::Stage::kMtpIn, qwen35::Stage::kAttentionIn, qwen35::Stage::kMixerOut,
+                                    qwen35::Stage::kFfnIn, qwen35::Stage::kFfnDown};
+    for (const qwen35::Stage stage : stages) {
+      const int in = qwen35::StageInputs(c, stage, c.layers);
+      const int out = qwen35::StageOutputs(c, stage, c.layers);
+      std::vector<float> x(static_cast<std::size_t>(2) * in), want(static_cast<std::size_t>(2) * out),
+          got(static_cast<std::size_t>(2) * out);
+      for (std::size_t i = 0; i < x.size(); ++i) {
+        x[i] = std::sin(0.37 * static_cast<double>(i) + static_cast<int>(stage));
+      }
+      cpu.Apply(stage, c.layers, x.data(), 2, want.data());
+      gpu.Apply(stage, c.layers, x.data(), 2, got.data());
+      double num = 0, den = 0;
+      for (std::size_t i = 0; i < want.size(); ++i) {
+        num += (double(got[i]) - want[i]) * (double(got[i]) - want[i]);
+        den += double(want[i]) * want[i];
+      }
+      const double err = std::sqrt(num / den);
+      std::printf("MTP layer, stage %d: rel-L2 %.3e\n", static_cast<int>(stage), err);
+      worst = err > worst ? err : worst;
+      if (err > 1e-3) {
+        std::printf("FAIL\n");
+        return 1;
+      }
+    }
   }
   std::printf("PASS: %d steps, worst rel-L2 %.3e\n", steps, worst);
   return 0;

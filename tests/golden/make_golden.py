@@ -166,6 +166,27 @@ def decoder(ref: binding.RefLib) -> dict:
     return out
 
 
+MTP_SEED = 13
+
+
+def projections_mtp(ref: binding.RefLib) -> dict:
+    """GgufProjections on a dense model with an MTP layer: Stage::kMtpIn (nextn.eh_proj over
+    [embedding | hidden]) and the MTP layer's own attention and FFN stages at layer index
+    `layers` (gguf_projections.cpp:114-125,205-207)."""
+    out = {}
+    cfg = synth.ModelConfig(**DENSE, mtp_layers=1)
+    image = synth.to_gguf(cfg, synth.build_model(cfg, MTP_SEED))
+    il = cfg.layers
+    for prec, flt in (("f32", True), ("f64", False)):
+        model = ref.open_model(image, precision_float=flt)
+        for stage in ("mtp_in", "attention_in", "mixer_out", "ffn_in", "ffn_down"):
+            for tokens in (1, 3):
+                x = normal(8000 + tokens, tokens, model.stage_inputs(stage, il))
+                out[f"{prec}_{stage}_{tokens}"] = model.apply(stage, il, x)
+        model.close()
+    return out
+
+
 # Positions whose logits decoder_long keeps: around the 128-position slices the reference's
 # attention cuts the cache into (decoder.cpp:326-333) and past a thousand positions.
 LONG_STEPS = 1100
@@ -201,7 +222,8 @@ def main() -> int:
     ref = binding.RefLib()
     only = set(sys.argv[1:])   # e.g. `make_golden.py decoder_long` regenerates that file alone
     for name, fn in (("dots", dots), ("projections", projections), ("deltanet", deltanet),
-                     ("routing", routing), ("decoder", decoder), ("decoder_long", decoder_long)):
+                     ("routing", routing), ("decoder", decoder), ("decoder_long", decoder_long),
+                     ("projections_mtp", projections_mtp)):
         if only and name not in only:
             continue
         arrays = fn(ref)

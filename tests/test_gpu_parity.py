@@ -307,6 +307,33 @@ def test_projections_match_reference_outputs(ctx, golden, tag, kwargs, seed):
             proj.ApplyExpert(Stage.kExpertIn, 0, 0, np.zeros(cfg.hidden, dtype=np.float32), 1)
 
 
+def test_mtp_layer_projections_match_reference_outputs(ctx, golden):
+    """A model with an MTP layer: Stage.kMtpIn (nextn.eh_proj over [embedding | hidden]) and the
+    MTP layer's attention and FFN stages at layer index `layers`, against the committed outputs
+    of the reference's GgufProjections (gguf_projections.cpp:114-125,205-207)."""
+    cfg = synth.ModelConfig(**G.DENSE, mtp_layers=1)
+    tensors = synth.build_model(cfg, G.MTP_SEED)
+    proj = CudaProjections(ctx, cfg, tensors)
+    g = golden("projections_mtp")
+    il = cfg.layers
+    names = {Stage.kMtpIn: "mtp_in", Stage.kAttentionIn: "attention_in", Stage.kMixerOut: "mixer_out",
+             Stage.kFfnIn: "ffn_in", Stage.kFfnDown: "ffn_down"}
+    assert stage_inputs(cfg, Stage.kMtpIn, il) == 2 * cfg.hidden
+    for stage, name in names.items():
+        for tokens in (1, 3):
+            x = G.normal(8000 + tokens, tokens, stage_inputs(cfg, stage, il))
+            got = proj.Apply(stage, il, x, tokens)
+            for prec in ("f32", "f64"):
+                err = rel_l2(got, g[f"{prec}_{name}_{tokens}"])
+                assert err <= 1e-5, (stage, tokens, prec, err)
+    # The decoder layers have no such stage; a model without the layer has no such layer.
+    with pytest.raises(LookupError):
+        proj.Apply(Stage.kMtpIn, 0, np.zeros(2 * cfg.hidden, dtype=np.float32), 1)
+    plain = CudaProjections(ctx, synth.ModelConfig(**G.DENSE), synth.build_model(synth.ModelConfig(**G.DENSE), G.DENSE_SEED))
+    with pytest.raises(IndexError):
+        plain.Apply(Stage.kMtpIn, il, np.zeros(2 * cfg.hidden, dtype=np.float32), 1)
+
+
 def test_projection_shape_check_at_construction(ctx):
     cfg = synth.ModelConfig(**G.DENSE)
     tensors = synth.build_model(cfg, G.DENSE_SEED)
@@ -737,7 +764,8 @@ def test_row_split_decoder_single_rank_matches_reference_logits(golden):
     c.close()
 
 
-@pytest.mark.parametrize("tag,kwargs,seed", [("dense", G.DENSE, G.DENSE_SEED), ("moe", G.MOE, G.MOE_SEED)])
+@pytest.mark.parametrize("tag,kwargs,seed", [("dense", G.DENSE, G.DENSE_SEED), ("moe", G.MOE, G.MOE_SEED),
+                                             ("mtp", dict(G.DENSE, mtp_layers=1), G.MTP_SEED)])
 def test_reference_decoder_with_cuda_adapter(tmp_path, tag, kwargs, seed):
     """Drop-in at step level: the reference's own Decoder::Step (its mixers, norms, routing)
     with the C++ adapter over this library plugged in behind qwen35::Projections, against the

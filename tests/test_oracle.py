@@ -284,3 +284,25 @@ def test_oracle_decoder_and_attention_match_reference_logits(oracle, golden):
             want = long["logits"][keep[pos]]
             err = np.linalg.norm(got.astype(np.float64) - want) / np.linalg.norm(want)
             assert err < 5e-5, (pos, err)
+
+
+def test_oracle_mtp_layer_projections_match_reference(oracle, golden):
+    """Stage::kMtpIn and the MTP layer's stages: the oracle's fused dots over the same rows the
+    reference stacks (gguf_projections.cpp:114-125), bit for bit in fp32."""
+    cfg = synth.ModelConfig(**G.DENSE, mtp_layers=1)
+    tensors = synth.build_model(cfg, G.MTP_SEED)
+    g = golden("projections_mtp")
+    p = f"blk.{cfg.layers}."
+    stages = {"mtp_in": ["nextn.eh_proj.weight"], "attention_in": ["attn_q.weight", "attn_k.weight", "attn_v.weight"],
+              "mixer_out": ["attn_output.weight"], "ffn_in": ["ffn_gate.weight", "ffn_up.weight"],
+              "ffn_down": ["ffn_down.weight"]}
+    for name, parts in stages.items():
+        rows = [(tensors[p + n].data.numpy().reshape(tensors[p + n].rows, -1), tensors[p + n].ggml_type, 0,
+                 tensors[p + n].rows) for n in parts]
+        cols = tensors[p + parts[0]].cols
+        for tokens in (1, 3):
+            x = G.normal(8000 + tokens, tokens, cols)
+            got = oracle.matmul(rows, cols, x)
+            assert np.array_equal(bits(got), bits(g[f"f32_{name}_{tokens}"])), (name, tokens)
+            exact = oracle.matmul(rows, cols, x, exact=True)
+            assert np.array_equal(bits(exact), bits(g[f"f64_{name}_{tokens}"])), (name, tokens)
