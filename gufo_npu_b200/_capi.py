@@ -137,6 +137,9 @@ SIGNATURES = {
     "gufo_cuda_peer_group_reset": (C.c_int, [C.c_void_p]),
     "gufo_cuda_peer_allgather_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t]),
     "gufo_cuda_peer_group_status": (C.c_int, [C.c_void_p]),
+    "gufo_cuda_matmul_gather_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.POINTER(FusedInput), C.c_size_t,
+                                                 C.c_int, C.c_int]),
+    "gufo_cuda_peer_wait_device": (C.c_int, [C.c_void_p, C.c_int]),
     "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                                      C.c_int, C.c_void_p]),
     "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,

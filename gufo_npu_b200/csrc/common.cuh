@@ -99,6 +99,26 @@ enum FastPrologue {
 };
 
 constexpr int kFastMaxParts = 4;
+constexpr int kMaxPeers = 8;
+
+// Row-split ranks (peer.cu). A product with `world` > 0 stores its rows into
+// every rank's copy of the full vector and, when its last thread block is
+// done, raises this rank's flag of the vector's slot in every rank's arena.
+struct PeerOut {
+  int world;
+  int rank;
+  int slot;
+  float* y[kMaxPeers];          // where this rank's rows start in rank p's arena
+  unsigned* header[kMaxPeers];  // the arenas' headers (flags, counters)
+};
+// A kernel whose input is such a vector waits (bounded) until every rank's
+// flag of the slot has reached the turn this rank's own product announced.
+struct PeerWait {
+  const unsigned* header;       // this rank's arena header; null: no wait
+  int world;
+  int slot;
+  long long limit;              // clock cycles
+};
 
 struct FastPart {
   const uint8_t* w;   // first row
@@ -142,6 +162,8 @@ struct FastGemvArgs {
   // the multiplies and leaves only the data movement.
   int variant;
   int y_group_stride;     // floats between the groups' outputs
+  PeerOut peer_out;       // world == 0: an ordinary product
+  PeerWait peer_wait;
 };
 
 // A single-part launch against a staged image.

@@ -21,6 +21,7 @@
 #include "decode_device.cuh"
 #include "gemv.cuh"
 #include "moe.cuh"
+#include "peer.cuh"
 #include "step_kernel.cuh"
 
 namespace gufo {
@@ -371,7 +372,7 @@ struct Input {
 // kernels where every part allows it; otherwise the input is materialised by the
 // small kernels first. `scratch` holds the materialised / normed rows.
 int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const Input& in, float* scratch,
-                 float* y, int tokens) {
+                 float* y, int tokens, const PeerOut* peer_out = nullptr, const PeerWait* peer_wait = nullptr) {
   const dim3 block(kSmallThreads);
   bool fused = !ctx->force_general && stage.nparts <= kFastMaxParts;
   int fast_parts = 0;
@@ -388,6 +389,18 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
     }
   }
   const size_t cols = static_cast<size_t>(stage.cols);
+  if (peer_out != nullptr || peer_wait != nullptr) {
+    // A product that gathers by itself is one launch of the tensor-core kernel.
+    bool one_type = true;
+    for (int p = 1; p < stage.nparts; ++p) {
+      one_type = one_type && stage.parts[p].type == stage.parts[0].type;
+    }
+    if (!fused || fast_parts != stage.nparts || !one_type) {
+      return Fail(GUFO_CUDA_UNSUPPORTED_TYPE,
+                  "matmul_gather: the stage must be up to four Q4_K or Q6_K parts of one format that fit the "
+                  "tensor-core GEMV");
+    }
+  }
   if (!fused || fast_parts == 0) {
     const float* x = in.x;
     if (in.prologue == kPrologueResNorm) {
@@ -439,6 +452,12 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
     }
     args.advance = first ? in.advance : nullptr;
     first = false;
+    if (peer_out != nullptr) {
+      args.peer_out = *peer_out;
+    }
+    if (peer_wait != nullptr) {
+      args.peer_wait = *peer_wait;
+    }
     GUFO_STEP_TRY(type == GUFO_CUDA_Q4_K ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args));
   }
   // Rows of other formats (the F32 alpha / beta rows) read the rows block 0 wrote.
@@ -982,6 +1001,81 @@ int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* part
     return Fail(GUFO_CUDA_SHAPE, "matmul_fused: cols must be a multiple of 4");
   }
   return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, y, tokens);
+}
+
+int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* g, const gufo_cuda_rows* parts, int nparts,
+                                   const gufo_cuda_fused_input* in, size_t arena_offset, int slot, int wait_slot) {
+  if (g == nullptr || parts == nullptr || in == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: null pointer");
+  }
+  if (slot < 0 || slot >= gufo::kPeerSlots || wait_slot >= gufo::kPeerSlots) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: slots are 0 to 7 (wait_slot < 0: no wait)");
+  }
+  gufo::Input input{gufo::kProloguePlain};
+  switch (in->prologue) {
+    case GUFO_CUDA_PROLOGUE_PLAIN:
+    case GUFO_CUDA_PROLOGUE_SWIGLU:
+      if (in->x == nullptr) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: x must be given");
+      }
+      input.prologue = in->prologue == GUFO_CUDA_PROLOGUE_PLAIN ? gufo::kProloguePlain : gufo::kPrologueSwiGlu;
+      input.x = in->x;
+      break;
+    case GUFO_CUDA_PROLOGUE_RES_NORM:
+      if (in->residual == nullptr || in->norm_weight == nullptr || in->residual_out == nullptr ||
+          in->scratch == nullptr || in->residual_out == in->residual) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                    "matmul_gather: residual, norm_weight, scratch and a residual_out apart from residual");
+      }
+      input.prologue = gufo::kPrologueResNorm;
+      input.h_in = in->residual;
+      input.delta = in->delta;
+      input.norm_w = in->norm_weight;
+      input.h_out = in->residual_out;
+      input.advance = in->advance;
+      break;
+    default:
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: unknown prologue");
+  }
+  const float* rows[] = {in->x, in->residual, in->delta, in->norm_weight, in->residual_out, in->scratch};
+  for (const float* p : rows) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: rows must be 16-byte aligned");
+    }
+  }
+  gufo_cuda_ctx* ctx = g->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::GemvArgs stage;
+  const int rc = gufo::BuildGemvArgs(ctx, parts, nparts, &stage);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (stage.cols % 4 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matmul_gather: cols must be a multiple of 4");
+  }
+  const size_t local = static_cast<size_t>(stage.total_rows);
+  if (arena_offset < GUFO_CUDA_PEER_HEADER_BYTES || arena_offset % 16 != 0 ||
+      arena_offset + local * 4 * g->world > g->arena_bytes) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: the full vector must lie inside the arena, 16-byte aligned");
+  }
+  gufo::PeerOut out{};
+  out.world = g->world;
+  out.rank = g->rank;
+  out.slot = slot;
+  for (int p = 0; p < g->world; ++p) {
+    out.y[p] = reinterpret_cast<float*>(g->arena[p] + arena_offset) + static_cast<size_t>(g->rank) * local;
+    out.header[p] = reinterpret_cast<unsigned*>(g->arena[p]);
+  }
+  gufo::PeerWait wait{};
+  if (wait_slot >= 0) {
+    wait.header = reinterpret_cast<const unsigned*>(g->arena[g->rank]);
+    wait.world = g->world;
+    wait.slot = wait_slot;
+    wait.limit = g->limit;
+  }
+  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, out.y[g->rank], 1, &out,
+                            wait_slot >= 0 ? &wait : nullptr);
 }
 
 int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config* config,

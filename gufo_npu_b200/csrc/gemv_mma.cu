@@ -32,6 +32,7 @@
 
 #include <type_traits>
 
+#include "peer.cuh"
 #include "q4k_unit.cuh"
 #include "q6k_unit.cuh"
 
@@ -198,6 +199,8 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   GridLaunchDependents();
   // The weights above never depend on earlier kernels; the image and y do.
   GridDependencyWait();
+  // Row-split ranks: the input vector may still be on its way from the peers.
+  PeerWaitBlock(a.peer_wait);
   if (a.prologue == kPrologueImage) {
     const uint32_t base = SharedAddress(smem);
     for (int at = threadIdx.x * 16; at < l.bytes; at += kFastThreads * 16) {
@@ -242,8 +245,17 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     const int k = o % TOKENS;
     const int row = local * 16 + o / TOKENS;
     if (row < a.parts[part].rows) {
-      a.y[static_cast<size_t>(group) * a.y_group_stride + static_cast<size_t>(k) * a.y_stride +
-          a.parts[part].y_offset + row] = total;
+      const size_t at = static_cast<size_t>(group) * a.y_group_stride + static_cast<size_t>(k) * a.y_stride +
+                        a.parts[part].y_offset + row;
+      if (a.peer_out.world > 0) {
+        // Row-split ranks: this rank's rows go straight into every rank's copy
+        // of the full vector (plain stores over NVLink for the peers).
+        for (int p = 0; p < a.peer_out.world; ++p) {
+          a.peer_out.y[p][at] = total;
+        }
+      } else {
+        a.y[at] = total;
+      }
     }
   };
   // Every thread of the block (of the cluster's blocks) comes here.
@@ -396,6 +408,9 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   if (my_tiles > 0) {
     __syncthreads();
     gather(my_tiles - 1);
+  }
+  if (a.peer_out.world > 0) {
+    PeerSignal(a.peer_out);
   }
 }
 

@@ -14,16 +14,11 @@
 // kernel returns.
 #include <cstring>
 
-#include "common.cuh"
+#include "peer.cuh"
 
 namespace gufo {
 namespace {
 
-constexpr int kMaxPeers = 8;
-constexpr int kFlagStride = 16;        // words between two peers' flags
-constexpr int kCountWord = 256;        // gathers completed by this rank
-constexpr int kFinishedWord = 257;     // blocks of the running gather that are done
-constexpr int kErrorWord = 258;
 constexpr int kPeerThreads = 256;
 
 struct PeerGatherArgs {
@@ -35,15 +30,6 @@ struct PeerGatherArgs {
   unsigned slice;        // floats per rank
   long long limit;       // clock cycles a flag may take
 };
-
-__device__ __forceinline__ void StoreRelease(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned LoadAcquire(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 // Block b serves peer b: it stores this rank's slice into b's arena, raises this
 // rank's flag there, then waits for b's flag here.
@@ -72,13 +58,13 @@ PeerAllGatherKernel(const __grid_constant__ PeerGatherArgs a) {
   // and another for the flag.
   __syncthreads();
   if (threadIdx.x == 0) {
-    StoreRelease(reinterpret_cast<unsigned*>(a.arena[peer]) + kFlagStride * a.rank, turn);
+    StoreReleaseSys(reinterpret_cast<unsigned*>(a.arena[peer]) + kFlagStride * a.rank, turn);
     const unsigned* mine = header + kFlagStride * peer;
     // After a first failure the later gathers of the step give up at once.
     const long long limit = *reinterpret_cast<volatile unsigned*>(header + kErrorWord) != 0 ? 0 : a.limit;
     const long long start = clock64();
     // Flags only grow; the difference copes with the counter wrapping.
-    while (static_cast<int>(LoadAcquire(mine) - turn) < 0) {
+    while (static_cast<int>(LoadAcquireSys(mine) - turn) < 0) {
       if (clock64() - start > limit) {
         atomicExch(header + kErrorWord, 1u);
         break;
@@ -92,19 +78,26 @@ PeerAllGatherKernel(const __grid_constant__ PeerGatherArgs a) {
   }
 }
 
-}  // namespace
-}  // namespace gufo
+// Waits for a slot's rows on behalf of kernels that do not wait themselves.
+__global__ void __launch_bounds__(32)
+PeerWaitKernel(const __grid_constant__ PeerWait w) {
+  GridLaunchDependents();
+  GridDependencyWait();
+  PeerWaitBlock(w);
+}
 
-struct gufo_cuda_peer_group {
-  gufo_cuda_ctx* ctx = nullptr;
-  int rank = 0;
-  int world = 0;
-  uint8_t* arena[gufo::kMaxPeers] = {};
-  bool opened[gufo::kMaxPeers] = {};   // mapped through CUDA IPC (closed at destroy)
-  size_t arena_bytes = 0;
-  long long limit = 0;
-  int khz = 0;
-};
+}  // namespace
+
+PeerWait MakePeerWait(const gufo_cuda_peer_group* g, int slot) {
+  PeerWait w{};
+  w.header = reinterpret_cast<const unsigned*>(g->arena[g->rank]);
+  w.world = g->world;
+  w.slot = slot;
+  w.limit = g->limit;
+  return w;
+}
+
+}  // namespace gufo
 
 using gufo::Fail;
 
@@ -271,6 +264,19 @@ int gufo_cuda_peer_allgather_device(gufo_cuda_peer_group* g, const float* local_
   a.limit = g->limit;
   GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::PeerAllGatherKernel, dim3(g->world), dim3(gufo::kPeerThreads), 0,
                                        ctx->stream, 1, a));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+int gufo_cuda_peer_wait_device(gufo_cuda_peer_group* g, int slot) {
+  if (g == nullptr || slot < 0 || slot >= gufo::kPeerSlots) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "peer_wait: a group and a slot below 8");
+  }
+  gufo_cuda_ctx* ctx = g->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::PeerWaitKernel, dim3(1), dim3(32), 0, ctx->stream, 1,
+                                       gufo::MakePeerWait(g, slot)));
   ctx->launches.fetch_add(1);
   return GUFO_CUDA_OK;
 }

@@ -24,17 +24,31 @@ from .backend import Context, CudaMoe, CudaProjections
 
 
 def _timed(fn, steps: int, device) -> float:
-    """Milliseconds per call: barrier, CUDA events on the current stream, max over the ranks."""
-    dist.barrier()
+    """Milliseconds per call of `fn`: `steps` calls captured into one CUDA graph (kernels, torch
+    ops and NCCL collectives alike, so that the host's launch pace does not enter), replayed
+    between a barrier and synchronizes, CUDA events on the current stream, the median of five
+    replays, then the maximum over the ranks."""
+    fn()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=torch.cuda.current_stream()):
+        for _ in range(steps):
+            fn()
+    graph.replay()
     torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
+    times = []
+    for _ in range(5):
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / steps)
+    ms = torch.tensor([float(np.median(times))], device=device)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    del graph
     return float(ms.item())
 
 

@@ -45,15 +45,19 @@ def shard_rows(parts: Sequence[Tuple[str, int]], rank: int, world: int) -> List[
     return out
 
 
-def stage_tensors(cfg: ModelConfig, il: int) -> Dict[str, List[str]]:
+def stage_tensors(cfg: ModelConfig, il: int, gates_in_mixer: bool = False) -> Dict[str, List[str]]:
     """GGUF tensor names stacked per stage of layer `il`, in the reference's order
-    (src/models/qwen35/gguf_projections.cpp:139-171)."""
+    (src/models/qwen35/gguf_projections.cpp:139-171). With `gates_in_mixer` the DeltaNet input
+    stage stops after [qkv | z]: the F32 alpha / beta rows are multiplied inside the mixer's
+    kernel (as the reference's fused step does, src/models/qwen35_2b/deltanet.cpp:358-392)."""
     p = f"blk.{il}."
     if cfg.is_full_attention(il):
         first = [p + "attn_q.weight", p + "attn_k.weight", p + "attn_v.weight"]
         out = [p + "attn_output.weight"]
     else:
-        first = [p + "attn_qkv.weight", p + "attn_gate.weight", p + "ssm_alpha.weight", p + "ssm_beta.weight"]
+        first = [p + "attn_qkv.weight", p + "attn_gate.weight"]
+        if not gates_in_mixer:
+            first += [p + "ssm_alpha.weight", p + "ssm_beta.weight"]
         out = [p + "ssm_out.weight"]
     return {"in": first, "out": out, "ffn_in": [p + "ffn_gate.weight", p + "ffn_up.weight"],
             "ffn_down": [p + "ffn_down.weight"]}
@@ -64,10 +68,13 @@ class TpDecoder:
 
     def __init__(self, ctx, cfg: ModelConfig, tensors: Dict[str, Tensor], rank: int, world: int,
                  max_positions: int = 4096, collective: str = "peer"):
-        """`collective`: "peer" gathers with this library's kernel over NVLink peer memory
-        (gufo_cuda_peer_allgather_device), "nccl" with torch.distributed's all-gather."""
+        """`collective`: "fused" lets every product store its rows into the peers' copies of
+        the full vector itself (gufo_cuda_matmul_gather_device: product and gather in one
+        kernel); "peer" gathers with a separate kernel over NVLink peer memory
+        (gufo_cuda_peer_allgather_device); "nccl" with torch.distributed's all-gather."""
         self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
         self.collective = collective if world > 1 else "none"
+        self.fused = self.collective == "fused"
         self.lib = ctx.lib
         dev = torch.device("cuda", ctx.device)
         self.dev = dev
@@ -98,7 +105,7 @@ class TpDecoder:
 
         self.layers = []
         for il in range(c.layers):
-            names = stage_tensors(c, il)
+            names = stage_tensors(c, il, gates_in_mixer=self.fused)
             layer = {k: product(v) for k, v in names.items()}
             p = f"blk.{il}."
             layer["attn_norm"] = f32(p + "attn_norm.weight")
@@ -114,6 +121,11 @@ class TpDecoder:
                     c.linear_key_heads, c.linear_value_heads, c.linear_head_dim, c.conv_kernel, c.rms_eps,
                     *(tensors[p + n].data.cpu().numpy().view(np.float32) for n in
                       ("ssm_conv1d.weight", "ssm_a", "ssm_dt.bias", "ssm_norm.weight")))
+                if self.fused:
+                    # The whole F32 alpha / beta rows on every rank: the mixer multiplies them.
+                    layer["gates"] = tuple(
+                        ctx.matrix_upload(tensors[p + n].ggml_type, tensors[p + n].data.cpu().numpy(), tensors[p + n].rows,
+                                          tensors[p + n].cols) for n in ("ssm_alpha.weight", "ssm_beta.weight"))
                 layer["conv"] = [torch.zeros((c.conv_kernel - 1) * c.conv_channels, device=dev) for _ in range(2)]
                 layer["ssm"] = torch.zeros(c.linear_value_heads * c.linear_head_dim ** 2, device=dev)
             self.layers.append(layer)
@@ -136,7 +148,7 @@ class TpDecoder:
         # The vectors every rank needs whole: in the peer arena when this library gathers them.
         full_sizes = (width, c.hidden, 2 * c.ffn, c.vocab)
         self.peers = None
-        if self.collective == "peer":
+        if self.collective in ("peer", "fused"):
             from .backend import PeerGroup
 
             def exchange(handle):
@@ -156,6 +168,8 @@ class TpDecoder:
                 if self.peers is not None:
                     self.peers.close()
                 self.peers = None
+                if self.fused:
+                    raise RuntimeError("the fused gather needs the peers' arenas; use collective=\"nccl\"")
                 self.collective = "nccl"
         full = self.peers.buffer if self.peers is not None else z
         self.full_in, self.out, self.ffn, self.logits = (full(n) for n in full_sizes)
@@ -229,21 +243,78 @@ class TpDecoder:
             pending = self.out
         self._norm_product(self.lm_head, pending, self.output_norm, self.logits, advance=True)
 
+    def _gather_product(self, prod, full, slot: int, wait_slot: int, *, x=None, residual=None, delta=None,
+                        norm_weight=None, swiglu: bool = False, advance: bool = False) -> None:
+        """A stage's local rows by the kernel that also stores them into every rank's `full`
+        vector and raises the slot's flag; `wait_slot` >= 0: its input is the vector of that slot."""
+        arr, n, _, _ = prod
+        kind = _capi.PROLOGUE_RES_NORM if residual is not None else (
+            _capi.PROLOGUE_SWIGLU if swiglu else _capi.PROLOGUE_PLAIN)
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+        dst = None
+        if residual is not None:
+            dst = self.h_next
+        args = _capi.FusedInput(kind, p(x), p(residual), p(delta), p(norm_weight), self.cfg.rms_eps, p(dst),
+                                p(self.normed if residual is not None else self.act),
+                                p(self.position_dev) if advance else None)
+        self._check(self.lib.gufo_cuda_matmul_gather_device(self.peers.handle, arr, n, C.byref(args),
+                                                            self.peers.offset_of(full), slot, wait_slot))
+        if residual is not None:
+            self.h, self.h_next = self.h_next, self.h
+
+    def enqueue_fused(self, parity: int) -> None:
+        """The step with every product gathering by itself. Vector slots: 0 the mixers' input,
+        1 the projections' output (twice per layer), 2 the FFN rows, 3 the logits."""
+        c = self.cfg
+        lib, h = self.lib, self.ctx.handle
+        self.h, self.h_next = self._residual
+        self._check(lib.gufo_cuda_embed_device(h, self.embed, self.token_dev.data_ptr(), self.h.data_ptr()))
+        pending, pending_slot = None, -1
+        for il, l in enumerate(self.layers):
+            self._gather_product(l["in"], self.full_in, 0, pending_slot, residual=self.h, delta=pending,
+                                 norm_weight=l["attn_norm"])
+            self._check(lib.gufo_cuda_peer_wait_device(self.peers.handle, 0))
+            if c.is_full_attention(il):
+                args = _capi.AttentionArgs(c.heads, c.kv_heads, c.head_dim, c.rope_dim, self.max_positions, c.rms_eps,
+                                           self.position_dev.data_ptr(), self.full_in.data_ptr(),
+                                           l["q_norm"].data_ptr(), l["k_norm"].data_ptr(), self.inv_freq.data_ptr(),
+                                           l["keys"].data_ptr(), l["values"].data_ptr(), self.queries.data_ptr(),
+                                           self.partials.data_ptr(), self.mixed.data_ptr())
+                self._check(lib.gufo_cuda_attention_device(h, C.byref(args)))
+            else:
+                # The gates from the residual stream (the product's norm wrote it to self.h).
+                seq = _capi.DeltaNetStepSeq(1, self.full_in.data_ptr(), 0, self.h.data_ptr(), 0,
+                                            l["conv"][parity].data_ptr(), l["conv"][parity ^ 1].data_ptr(), None,
+                                            l["ssm"].data_ptr(), None, self.mixed.data_ptr(), 0)
+                alpha, beta = l["gates"]
+                self._check(lib.gufo_cuda_deltanet_step_device(h, l["linear"], alpha, beta,
+                                                               C.c_void_p(l["attn_norm"].data_ptr()), c.rms_eps,
+                                                               C.byref(seq), 1))
+            self._gather_product(l["out"], self.out, 1, -1, x=self.mixed)
+            self._gather_product(l["ffn_in"], self.ffn, 2, 1, residual=self.h, delta=self.out,
+                                 norm_weight=l["post_norm"])
+            self._gather_product(l["ffn_down"], self.out, 1, 2, x=self.ffn, swiglu=True)
+            pending, pending_slot = self.out, 1
+        self._gather_product(self.lm_head, self.logits, 3, pending_slot, residual=self.h, delta=pending,
+                             norm_weight=self.output_norm, advance=True)
+        self._check(lib.gufo_cuda_peer_wait_device(self.peers.handle, 3))
+
     def step(self, token: int, stream, use_graph: bool = True) -> torch.Tensor:
         """Runs `token` at the current position on every rank; returns the full logits (device)."""
         if self.position >= self.max_positions:
             raise RuntimeError("the attention cache is full")
         self.token_dev.fill_(token)
         parity = self.position & 1
+        enqueue = self.enqueue_fused if self.fused else self.enqueue
         if not use_graph or self.position < 2:
-            self.enqueue(parity)
+            enqueue(parity)
         else:
             if parity not in self.graphs:
                 g = torch.cuda.CUDAGraph()
                 torch.cuda.synchronize()
                 before = self.ctx.launch_count()
                 with torch.cuda.graph(g, stream=stream):
-                    self.enqueue(parity)
+                    enqueue(parity)
                 self.kernels_per_step = self.ctx.launch_count() - before
                 self.graphs[parity] = g
             self.graphs[parity].replay()
@@ -284,35 +355,10 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     tensors = synth.build_model(cfg, seed=1, device=f"cuda:{local}")
     ctx = Context(local, stream.cuda_stream)
     steps, warmup = args.steps, max(args.warmup, 3)
-    dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64)
     rng = np.random.default_rng(7)
-    tokens = iter(rng.integers(0, cfg.vocab, size=10 * (steps + warmup) + 16).tolist())
+    tokens = iter(rng.integers(0, cfg.vocab, size=40 * (steps + warmup) + 64).tolist())
     host = torch.empty(cfg.vocab, dtype=torch.float32).pin_memory()
-    # Every decoder of this run starts with the same few tokens, whose logits are compared below.
-    parity_logits = {"row_split": first_logits(lambda t: dec.step(t, stream), cfg.vocab)}
-    for _ in range(warmup):
-        dec.step(next(tokens), stream)
-    torch.cuda.synchronize()
-    # A wait for a peer's flag that ran out on any rank during the warm-up: all ranks go over to
-    # NCCL's all-gather for the measurement, and the line says so.
-    healthy = 1
-    if dec.peers is not None:
-        try:
-            dec.peers.status()
-        except Exception as e:   # noqa: BLE001
-            import sys
-            print(f"rank {rank}: {e}", file=sys.stderr, flush=True)
-            healthy = 0
-    agreed = torch.tensor([healthy], device=f"cuda:{local}")
-    dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
-    if int(agreed.item()) == 0:
-        dec.graphs.clear()
-        dec = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=2 * (steps + warmup) + 64, collective="nccl")
-        parity_logits["row_split"] = first_logits(lambda t: dec.step(t, stream), cfg.vocab)
-        for _ in range(warmup):
-            dec.step(next(tokens), stream)
-        torch.cuda.synchronize()
-    del tensors
+    positions = 8 * (steps + warmup) + 64
 
     def timed(fn):
         dist.barrier()
@@ -327,33 +373,61 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    def resident(d):
-        before = ctx.launch_count() + d.replayed_kernels
-        ms = timed(lambda: d.step(next(tokens), stream))
-        return ms, ctx.launch_count() + d.replayed_kernels - before
-
-    ms_resident, launches = resident(dec)
-    if dec.peers is not None:
-        dec.peers.status()   # raises if a wait for a peer's flag ran out
-    # The same step with NCCL's all-gather in place of the peer-memory kernel. The line's value
-    # is the faster of the two; `parallelism` names it and gives the other's time.
-    gathered_by = "this library's kernel over NVLink peer memory (CUDA IPC)" if dec.peers is not None else "NCCL"
-    other = ""
-    if dec.peers is not None:
-        by_nccl = TpDecoder(ctx, cfg, synth.build_model(cfg, seed=1, device=f"cuda:{local}"), rank, world,
-                            max_positions=2 * (steps + warmup) + 64, collective="nccl")
-        parity_logits["row_split_nccl"] = first_logits(lambda t: by_nccl.step(t, stream), cfg.vocab)
+    # The three ways to rebuild the full vectors: every product storing its rows into the peers'
+    # arenas itself, a separate gather kernel over peer memory, NCCL's all-gather. Each decoder
+    # starts with the same few tokens (their logits are compared below), warms up, and is timed;
+    # the line's value is the fastest, `parallelism` names it and gives the others' times.
+    how = {"fused": "every product stores its rows into the peers' copies itself (one kernel per stage, "
+                    "NVLink peer stores, flags)",
+           "peer": "a gather kernel of this library over NVLink peer memory after every product",
+           "nccl": "NCCL's all-gather after every product"}
+    parity_logits, measured, decoders = {}, {}, {}
+    for name in ("fused", "peer", "nccl"):
+        ok = 1
+        d = None
+        try:
+            d = TpDecoder(ctx, cfg, tensors, rank, world, max_positions=positions, collective=name)
+            if d.collective != name:
+                ok = 0   # the peers' arenas could not be opened: this decoder fell back to NCCL
+        except Exception as e:   # noqa: BLE001
+            import sys
+            print(f"rank {rank}: no {name} decoder ({e})", file=sys.stderr, flush=True)
+            ok = 0
+        agreed = torch.tensor([ok], device=f"cuda:{local}")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            del d
+            continue
+        parity_logits[name] = first_logits(lambda t, d=d: d.step(t, stream), cfg.vocab)
         for _ in range(warmup):
-            by_nccl.step(next(tokens), stream)
+            d.step(next(tokens), stream)
         torch.cuda.synchronize()
-        ms_nccl, launches_nccl = resident(by_nccl)
-        if ms_nccl < ms_resident:
-            other = f"; with the library's peer-memory gather kernel instead: {ms_resident:.3f} ms per step"
-            gathered_by = "NCCL"
-            dec, by_nccl = by_nccl, dec
-            ms_resident, launches = ms_nccl, launches_nccl
-        else:
-            other = f"; with NCCL's all-gather instead: {ms_nccl:.3f} ms per step"
+        healthy = 1
+        if d.peers is not None:
+            try:
+                d.peers.status()
+            except Exception as e:   # noqa: BLE001 - a wait for a peer's flag ran out
+                import sys
+                print(f"rank {rank}: {name}: {e}", file=sys.stderr, flush=True)
+                healthy = 0
+        agreed = torch.tensor([healthy], device=f"cuda:{local}")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            d.graphs.clear()
+            continue
+        before = ctx.launch_count() + d.replayed_kernels
+        ms = timed(lambda d=d: d.step(next(tokens), stream))
+        measured[name] = (ms, ctx.launch_count() + d.replayed_kernels - before)
+        decoders[name] = d
+        if d.peers is not None:
+            d.peers.status()
+    del tensors
+    best = min(measured, key=lambda k: measured[k][0])
+    dec = decoders[best]
+    ms_resident, launches = measured[best]
+    gathered_by = how[best]
+    other = "; ".join(f"{how[k]}: {measured[k][0]:.3f} ms per step" for k in measured if k != best)
+    other = f"; measured beside it: {other}" if other else ""
 
     def e2e_step():
         logits = dec.step(next(tokens), stream)
@@ -376,18 +450,19 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     # The row-split decoders against the one-GPU decoder on the same tokens (every rank checks
     # its own copy of the gathered logits; the worst over the ranks is reported), and the two
     # gathers against each other, which must agree bit for bit.
-    worst = max(rel_l2(parity_logits["row_split"][i], parity_logits["one_gpu"][i]) for i in range(len(PARITY_TOKENS)))
-    same_argmax = all(int(np.argmax(parity_logits["row_split"][i])) == int(np.argmax(parity_logits["one_gpu"][i]))
-                      for i in range(len(PARITY_TOKENS)))
+    one = parity_logits.pop("one_gpu")
+    worst = max(rel_l2(rows[i], one[i]) for rows in parity_logits.values() for i in range(len(PARITY_TOKENS)))
+    same_argmax = all(int(np.argmax(rows[i])) == int(np.argmax(one[i]))
+                      for rows in parity_logits.values() for i in range(len(PARITY_TOKENS)))
     gathers_equal = 1
-    if "row_split_nccl" in parity_logits:
-        gathers_equal = int(np.array_equal(parity_logits["row_split"].view(np.uint32),
-                                           parity_logits["row_split_nccl"].view(np.uint32)))
+    if "peer" in parity_logits and "nccl" in parity_logits:
+        gathers_equal = int(np.array_equal(parity_logits["peer"].view(np.uint32), parity_logits["nccl"].view(np.uint32)))
     check = torch.tensor([worst, 0.0 if same_argmax else 1.0, 0.0 if gathers_equal else 1.0], device=f"cuda:{local}")
     dist.all_reduce(check, op=dist.ReduceOp.MAX)
     worst, argmax_differs, gathers_differ = (float(v) for v in check.tolist())
     parity = {"row_split_vs_one_gpu_logits_rel_l2": worst, "same_argmax": argmax_differs == 0.0,
-              "peer_and_nccl_gathers_bit_equal": (gathers_differ == 0.0) if "row_split_nccl" in parity_logits else None,
+              "decoders_compared": sorted(parity_logits),
+              "peer_and_nccl_gathers_bit_equal": (gathers_differ == 0.0) if "peer" in parity_logits and "nccl" in parity_logits else None,
               "tokens": len(PARITY_TOKENS), "tolerance": 2e-3}
     if worst > 2e-3 or argmax_differs or gathers_differ:
         raise SystemExit(f"row-split parity failed: {parity}")
@@ -405,9 +480,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
                 "kernel": "GemvMma<Q6_K, 1 token>", "shape": f"{head_rows}x{cfg.hidden} Q6_K: one rank's rows of the LM head",
                 "bytes_per_launch": head_bytes, "us_per_launch": ms_head * 1e3}
     # The two other sharded paths: the row-split verify batch and the expert-parallel MoE layer.
-    dec.graphs.clear()
-    if other:
-        by_nccl.graphs.clear()
+    for d in decoders.values():
+        d.graphs.clear()
     del replica
     torch.cuda.empty_cache()
     from . import mgpu_bench
@@ -420,9 +494,10 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "warmup": warmup, "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
             "data": "synthetic",
-            "config": {"workload": workload, "seed": 1, "parallelism": f"tp{world}: projections row-split, "
-                       f"{dec.gathers_per_step} all-gathers per step by {gathered_by}, mixers replicated{other}",
-                       "l2": "weights exceed L2; no flush needed"},
+            "config": {"workload": workload, "seed": 1},
+            "notes": {"parallelism": f"tp{world}: projections row-split, {dec.gathers_per_step} gathers per step: "
+                                     f"{gathered_by}; mixers replicated{other}",
+                      "l2": "weights exceed L2; no flush needed"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},
             "gpu_launches": int(launches),
@@ -438,9 +513,8 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     torch.cuda.synchronize()
     # Captured graphs hold NCCL kernels: release them before the communicator goes away, and
     # leave without the collective teardown (it blocked here while graphs were alive).
-    dec.graphs.clear()
-    if other:
-        by_nccl.graphs.clear()
+    for d in decoders.values():
+        d.graphs.clear()
     import sys
     sys.stdout.flush()
     sys.stderr.flush()

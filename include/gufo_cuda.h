@@ -472,6 +472,25 @@ int gufo_cuda_peer_allgather_device(gufo_cuda_peer_group* group,
                                     const float* local_src, size_t arena_offset,
                                     size_t slice_floats);
 int gufo_cuda_peer_group_status(gufo_cuda_peer_group* group);
+/* The product and the gather in one kernel: a one-token product with a fused
+ * input (gufo_cuda_matmul_fused_device; up to four Q4_K or Q6_K parts of one
+ * block format) whose thread blocks store this rank's rows straight into every
+ * rank's copy of the full vector (arena_offset bytes into each arena, rank r's
+ * rows at r * rows * 4 behind it: plain peer stores over NVLink) and whose last
+ * thread block raises this rank's flag of `slot` (0..7, one per vector that can
+ * be in flight) in every arena. No rank waits inside this kernel. A kernel that
+ * reads the full vector must first wait for the slot: pass `wait_slot` to the
+ * next gufo_cuda_matmul_gather_device whose input it is (the wait then sits in
+ * that kernel's prologue), or enqueue gufo_cuda_peer_wait_device (a one-block
+ * kernel that waits) ahead of other readers. wait_slot < 0: the input is local.
+ * A slot's vector may be rewritten once every rank has launched a later gather
+ * of another slot (a rank raises a flag only after all its earlier kernels,
+ * readers included, have finished). Waits are bounded and report through
+ * gufo_cuda_peer_group_status as above. The reference has no counterpart. */
+int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* group, const gufo_cuda_rows* parts,
+                                   int nparts, const gufo_cuda_fused_input* input,
+                                   size_t arena_offset, int slot, int wait_slot);
+int gufo_cuda_peer_wait_device(gufo_cuda_peer_group* group, int slot);
 
 /* ---- device-resident decode step ---------------------------------------- */
 

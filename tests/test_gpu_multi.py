@@ -72,6 +72,17 @@ def _checks(rank, world, port, out):
                 failures.append(("peer gather differs from NCCL's", i, rel_l2(logits, other)))
         if dec.peers is not None:
             dec.peers.status()   # raises if a wait for a peer's flag ran out
+        if world > 1:
+            # Product and gather in one kernel: every stage stores its rows into the peers'
+            # arenas itself; the gates of the DeltaNet layers are computed in the mixer, so the
+            # logits agree with the reference's within the step tolerance, not bit for bit.
+            fused = TpDecoder(ctx, cfg, tensors, rank=rank, world=world, max_positions=32, collective="fused")
+            for i, tok in enumerate(int(t) for t in g["decoder_dense_tokens"]):
+                logits = fused.step(tok, stream).cpu().numpy()
+                err = rel_l2(logits, g["decoder_dense_logits"][i])
+                if err > STEP_TOL:
+                    failures.append(("fused tp logits", i, err))
+            fused.peers.status()
         # Expert parallelism against one device with every expert.
         mcfg = synth.ModelConfig(**G.MOE)
         mtensors = synth.build_model(mcfg, G.MOE_SEED)
@@ -189,4 +200,74 @@ def test_peer_gather_wait_that_runs_out_is_reported_and_the_context_lives():
     y = ctx.matmul([(m, 0, 64)], np.ones((1, 512), dtype=np.float32), 1, 64)
     assert np.isfinite(y).all()
     ctx._check(lib.gufo_cuda_peer_group_destroy(group))
+    ctx.close()
+
+
+def test_product_that_gathers_by_itself_on_one_device():
+    """gufo_cuda_matmul_gather_device with both ranks of a two-rank group on ONE device and one
+    stream (two local arenas): each rank's product stores its rows into both arenas and raises
+    its flags; the waits, enqueued after both products, find the flags set. Both arenas must
+    then hold the whole product, equal to the ordinary entry point's, over several turns (a
+    residual + norm input, a plain one, a SwiGLU one)."""
+    import ctypes as C
+
+    from gufo_npu_b200 import _capi
+    from gufo_npu_b200 import quantize as Q
+    from gufo_npu_b200.backend import Context
+    dev = torch.device("cuda:0")
+    ctx = Context(0)
+    lib = ctx.lib
+    rows, cols = 96, 512          # per rank: 48 rows
+    local = rows // 2
+    raw = Q.random_blocks(Q.GGML_Q4_K, rows, cols, seed=8).to(dev)
+    torch.cuda.synchronize()
+    whole = Context._parts([(ctx.matrix_from_device(Q.GGML_Q4_K, raw.data_ptr(), rows, cols), 0, rows)])
+    rb = Q.row_bytes(Q.GGML_Q4_K, cols)
+    halves = [Context._parts([(ctx.matrix_from_device(Q.GGML_Q4_K, raw.data_ptr() + r * local * rb, local, cols), 0,
+                               local)]) for r in range(2)]
+    nbytes = _capi.PEER_HEADER_BYTES + 4 * rows
+    arenas_t = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
+    arenas = (C.c_void_p * 2)(*(a.data_ptr() for a in arenas_t))
+    groups = []
+    for r in range(2):
+        group = C.c_void_p()
+        ctx._check(lib.gufo_cuda_peer_group_create_local(ctx.handle, r, 2, arenas, nbytes, C.byref(group)))
+        groups.append(group)
+    gen = torch.Generator(device=dev).manual_seed(9)
+    for turn in range(5):
+        kind = turn % 3
+        want = torch.empty(1, rows, device=dev)
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+        if kind == 0:     # residual + delta through RMSNorm
+            h = torch.randn(cols, device=dev, generator=gen)
+            delta = torch.randn(cols, device=dev, generator=gen)
+            w = 1.0 + 0.1 * torch.randn(cols, device=dev, generator=gen)
+            x_full = (h + delta) * torch.rsqrt(((h + delta) ** 2).mean() + 1e-6) * w
+            h_out = [torch.empty(cols, device=dev) for _ in range(2)]
+            scratch = [torch.empty(cols, device=dev) for _ in range(2)]
+            inputs = [_capi.FusedInput(_capi.PROLOGUE_RES_NORM, None, p(h), p(delta), p(w), 1e-6, p(h_out[r]),
+                                       p(scratch[r]), None) for r in range(2)]
+        elif kind == 1:   # plain rows
+            x_full = torch.randn(cols, device=dev, generator=gen)
+            inputs = [_capi.FusedInput(_capi.PROLOGUE_PLAIN, p(x_full), None, None, None, 0.0, None, None, None)] * 2
+        else:             # SwiGLU of [gate | up]
+            gate_up = torch.randn(2 * cols, device=dev, generator=gen)
+            x_full = torch.nn.functional.silu(gate_up[:cols]) * gate_up[cols:]
+            inputs = [_capi.FusedInput(_capi.PROLOGUE_SWIGLU, p(gate_up), None, None, None, 0.0, None, None, None)] * 2
+        torch.cuda.synchronize()
+        ctx.matmul_device(whole, 1, x_full.reshape(1, cols).contiguous(), 1, want)
+        for r in range(2):
+            ctx._check(lib.gufo_cuda_matmul_gather_device(groups[r], halves[r], 1, C.byref(inputs[r]),
+                                                          _capi.PEER_HEADER_BYTES, 0, -1))
+        for r in range(2):
+            ctx._check(lib.gufo_cuda_peer_wait_device(groups[r], 0))
+        ctx.synchronize()
+        for r in range(2):
+            ctx._check(lib.gufo_cuda_peer_group_status(groups[r]))
+            got = arenas_t[r][_capi.PEER_HEADER_BYTES:].view(torch.float32)
+            assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-5, (turn, r)
+        if kind == 0:
+            assert torch.allclose(h_out[0], h + delta)
+    for group in groups:
+        ctx._check(lib.gufo_cuda_peer_group_destroy(group))
     ctx.close()
