@@ -11,6 +11,7 @@
 #include <string>
 #include <utility>
 #include <unordered_map>
+#include <vector>
 
 #include "gufo_cuda.h"
 
@@ -246,6 +247,9 @@ struct gufo_cuda_ctx {
   // images, the partial sums of split products.
   uint8_t* tc_scratch = nullptr;
   size_t tc_scratch_bytes = 0;
+  // Scratch blocks that were outgrown: a CUDA graph captured earlier may still
+  // hold their addresses, so they stay allocated until the context goes.
+  std::vector<void*> retired;
   // Products of 16 or more token rows run on the tcgen05 GEMM (option "tc_gemm").
   bool tc_gemm = true;
   bool tc_gemm_all = false;   // option value 2: from 16 rows on, whatever is faster
@@ -275,6 +279,10 @@ struct gufo_cuda_ctx {
     return it == matrices.end() ? nullptr : &it->second;
   }
   int Reserve(float** buffer, size_t* have, size_t want);
+  // Grows a device scratch block to `want` bytes (at least `floor`) without
+  // freeing the old one and without waiting for the stream; refuses while the
+  // stream is being captured (a capture cannot allocate). ctx->mu is held.
+  int GrowScratch(uint8_t** block, size_t* have, size_t want, size_t floor, const char* what);
 };
 
 #define GUFO_CUDA_TRY(expr)                                 \

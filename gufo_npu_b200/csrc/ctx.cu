@@ -183,6 +183,27 @@ int gufo_cuda_ctx_create(int device, void* stream, gufo_cuda_ctx** out) {
   return GUFO_CUDA_OK;
 }
 
+int gufo_cuda_ctx::GrowScratch(uint8_t** block, size_t* have, size_t want, size_t floor, const char* what) {
+  if (*have >= want) {
+    return GUFO_CUDA_OK;
+  }
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &capturing) == cudaSuccess && capturing != cudaStreamCaptureStatusNone) {
+    return gufo::Fail(GUFO_CUDA_BAD_ARGUMENT,
+                      std::string(what) + ": the context's scratch must grow for this product, which a stream "
+                                          "capture cannot do; run the product once before capturing");
+  }
+  const size_t grown = want < floor ? floor : want;
+  uint8_t* fresh = nullptr;
+  GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&fresh), grown));
+  if (*block != nullptr) {
+    retired.push_back(*block);   // a graph captured earlier may still use it
+  }
+  *block = fresh;
+  *have = grown;
+  return GUFO_CUDA_OK;
+}
+
 int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx) {
   if (ctx == nullptr) {
     return GUFO_CUDA_OK;
@@ -204,6 +225,9 @@ int gufo_cuda_ctx_destroy(gufo_cuda_ctx* ctx) {
   cudaFree(ctx->stage_y);
   cudaFree(ctx->image);
   cudaFree(ctx->tc_scratch);
+  for (void* block : ctx->retired) {
+    cudaFree(block);
+  }
   if (ctx->own_stream) {
     cudaStreamDestroy(ctx->stream);
   }

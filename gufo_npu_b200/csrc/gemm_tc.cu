@@ -750,15 +750,13 @@ int ReserveTc(gufo_cuda_ctx* ctx, size_t bytes) {
   if (ctx->tc_scratch_bytes >= bytes) {
     return GUFO_CUDA_OK;
   }
-  if (ctx->tc_scratch != nullptr) {
-    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    GUFO_CUDA_TRY(cudaFree(ctx->tc_scratch));
-    ctx->tc_scratch = nullptr;
-    ctx->tc_scratch_bytes = 0;
+  // An outgrown block is kept (a captured graph may hold it); its error word
+  // is not carried over: a failure is read from the current block.
+  const int rc = ctx->GrowScratch(&ctx->tc_scratch, &ctx->tc_scratch_bytes, bytes, 1u << 20, "tcgen05 gemm");
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
   }
-  GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&ctx->tc_scratch), bytes));
   GUFO_CUDA_TRY(cudaMemsetAsync(ctx->tc_scratch, 0, 256, ctx->stream));
-  ctx->tc_scratch_bytes = bytes;
   return GUFO_CUDA_OK;
 }
 

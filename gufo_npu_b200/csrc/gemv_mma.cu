@@ -187,8 +187,15 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
       ++req_n;
     }
   };
+  // One token: a warp reads its fragments ahead of the block's barrier, so the
+  // slot is free for the slab kStages on as soon as the barrier has passed.
+  // More tokens hold too many registers for that to pay (the two-token step ran
+  // 7 % slower with it): the barrier comes first and frees the slot of the slab
+  // before, for the slab kStages - 1 on.
+  constexpr bool kEarly = TOKENS == 1;
+  constexpr int kAhead = kEarly ? kStages : kStages - 1;
 #pragma unroll
-  for (int q = 0; q < kStages; ++q) {
+  for (int q = 0; q < kAhead; ++q) {
     if (q < my_slabs) {
       if (warp == q) {
         issue(q, req_n, rank + req_s * ks);
@@ -302,6 +309,24 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     const bool mine = warp < nblk && a.variant != 1;
     const uint8_t* data = ring + (q % kStages) * S::kBytes;
     typename std::conditional<kQ4, q4k::Q4KUnit, q6k::Q6KUnit>::type unit;
+    // The block's barrier: behind it a ring slot is free (every warp is done with
+    // its slab: read into registers, or multiplied) and the row sums of the tile
+    // before are in the exchange buffer. Warp q % 8 requests the next slab.
+    auto meet = [&]() {
+      __syncthreads();
+      if (q + kAhead < my_slabs) {
+        if (warp == (q & 7)) {
+          issue(q + kAhead, req_n, rank + req_s * ks);
+        }
+        advance();
+      }
+      if (s == 0 && n > 0) {
+        gather(n - 1);
+      }
+    };
+    if constexpr (!kEarly) {
+      meet();
+    }
     if (mine) {
       if constexpr (kQ4) {
         q4k::LoadUnit(unit, data, warp, g, t);
@@ -309,17 +334,8 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
         q6k::LoadUnit(unit, data, warp, nblk, g, t);
       }
     }
-    // Every warp holds its fragments of slab q: the slot takes the slab kStages
-    // further on, and the row sums of the tile before are in the exchange buffer.
-    __syncthreads();
-    if (q + kStages < my_slabs) {
-      if (warp == (q & 7)) {
-        issue(q + kStages, req_n, rank + req_s * ks);
-      }
-      advance();
-    }
-    if (s == 0 && n > 0) {
-      gather(n - 1);
+    if constexpr (kEarly) {
+      meet();
     }
     if (mine) {
       if constexpr (kQ4) {

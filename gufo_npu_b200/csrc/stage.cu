@@ -55,16 +55,9 @@ int StageActivations(gufo_cuda_ctx* ctx, const float* x, int tokens, int cols,
   StageArgs args;
   args.layout = MakeImageLayout(tokens, cols, group);
   const size_t need = static_cast<size_t>(args.layout.bytes);
-  if (ctx->image_bytes < need) {
-    if (ctx->image != nullptr) {
-      GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-      GUFO_CUDA_TRY(cudaFree(ctx->image));
-      ctx->image = nullptr;
-      ctx->image_bytes = 0;
-    }
-    const size_t grown = need < (256u << 10) ? (256u << 10) : need;
-    GUFO_CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&ctx->image), grown));
-    ctx->image_bytes = grown;
+  const int grow = ctx->GrowScratch(&ctx->image, &ctx->image_bytes, need, 256u << 10, "staging");
+  if (grow != GUFO_CUDA_OK) {
+    return grow;
   }
   if (ctx->reuse_image) {
     *image = ctx->image;

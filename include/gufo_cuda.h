@@ -157,7 +157,14 @@ typedef struct gufo_cuda_rows {
  *   y[t] = [W_0 x[t] | W_1 x[t] | ...]  for t in [0, tokens)
  * x is `tokens` rows of `cols` fp32 (all parts share cols), y is `tokens` rows
  * of sum(parts[p].rows) fp32. Each output is one row dot, so results do not
- * depend on how rows are stacked or how many tokens come together. */
+ * depend on how rows are stacked or how many tokens come together.
+ * The _device forms only enqueue on the context's stream. Products of two or
+ * more tokens stage their input in scratch memory the context owns; the first
+ * product of a larger shape makes it grow (a cudaMalloc, no wait, the outgrown
+ * block is kept until gufo_cuda_ctx_destroy so that CUDA graphs captured
+ * earlier stay valid). A stream capture cannot allocate: while the stream is
+ * being captured such a product returns GUFO_CUDA_BAD_ARGUMENT instead, so run
+ * every shape once before capturing it. */
 int gufo_cuda_matmul(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
                      int nparts, const float* host_x, int tokens, float* host_y);
 int gufo_cuda_matmul_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
