@@ -14,7 +14,7 @@ namespace gufo {
 
 constexpr int kTeamThreads = 256;
 constexpr int kTeamWarps = kTeamThreads / 32;
-constexpr int kAttnSplits = 8;      // position slices per KV head
+constexpr int kAttnSplits = 32;     // position slices per KV head
 constexpr int kMaxGroup = 8;        // query heads per KV head
 constexpr int kMaxPerLane = 8;      // head_dim / 32
 
@@ -196,6 +196,10 @@ __device__ __forceinline__ void LoadHalves(const __half* p, int per, float (&out
   }
 }
 
+// Where element e of a query sits in AttnScratch::q: lane e / per reads its
+// elements at i * 32 + lane, one bank per lane.
+__device__ __forceinline__ int QuerySlot(int e, int per) { return (e % per) * 32 + e / per; }
+
 // One slice of the cached positions for one KV head and the query heads that
 // share it: partial softmax (weighted values, max, sum) per query head (the
 // split-K jobs of decoder.cpp:326-381).
@@ -212,7 +216,7 @@ __device__ __forceinline__ void AttnSliceBody(const AttnArgs& a, int split, int 
   const int warp = tid >> 5, lane = tid & 31;
   const float scale = 1.0f / sqrtf(static_cast<float>(hd));
   for (int i = tid; i < group * hd; i += kTeamThreads) {
-    s.q[i / hd][i % hd] = __ldcg(a.queries + (kh * group) * hd + i);
+    s.q[i / hd][QuerySlot(i % hd, per)] = __ldcg(a.queries + (kh * group) * hd + i);
   }
   sync();
   float m[kMaxGroup], l[kMaxGroup], acc[kMaxGroup][kMaxPerLane];
@@ -226,32 +230,42 @@ __device__ __forceinline__ void AttnSliceBody(const AttnArgs& a, int split, int 
     }
   }
   const int kv = a.kv_heads * hd;
-  for (int j = begin + warp; j < end; j += kTeamWarps) {
-    const __half* key = a.keys + static_cast<size_t>(j) * kv + kh * hd + lane * per;
-    const __half* val = a.values + static_cast<size_t>(j) * kv + kh * hd + lane * per;
-    float kf[kMaxPerLane], vf[kMaxPerLane];
-    LoadHalves(key, per, kf);
-    LoadHalves(val, per, vf);
+  // Two positions per pass, their four loads in flight together.
+  for (int j0 = begin + 2 * warp; j0 < end; j0 += 2 * kTeamWarps) {
+    float kf[2][kMaxPerLane], vf[2][kMaxPerLane];
 #pragma unroll
-    for (int g = 0; g < kMaxGroup; ++g) {
-      if (g < group) {
-        float dot = 0.f;
+    for (int u = 0; u < 2; ++u) {
+      const int j = min(j0 + u, end - 1);
+      const __half* key = a.keys + static_cast<size_t>(j) * kv + kh * hd + lane * per;
+      const __half* val = a.values + static_cast<size_t>(j) * kv + kh * hd + lane * per;
+      LoadHalves(key, per, kf[u]);
+      LoadHalves(val, per, vf[u]);
+    }
 #pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-          if (i < per) {
-            dot = fmaf(s.q[g][lane * per + i], kf[i], dot);
+    for (int u = 0; u < 2; ++u) {
+      if (j0 + u < end) {
+#pragma unroll
+        for (int g = 0; g < kMaxGroup; ++g) {
+          if (g < group) {
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMaxPerLane; ++i) {
+              if (i < per) {
+                dot = fmaf(s.q[g][i * 32 + lane], kf[u][i], dot);
+              }
+            }
+            const float sc = WarpSum(dot) * scale;
+            const float m_new = fmaxf(m[g], sc);
+            const float keep = expf(m[g] - m_new);   // 0 on the first position
+            const float p = expf(sc - m_new);
+            l[g] = l[g] * keep + p;
+#pragma unroll
+            for (int i = 0; i < kMaxPerLane; ++i) {
+              acc[g][i] = acc[g][i] * keep + p * vf[u][i];
+            }
+            m[g] = m_new;
           }
         }
-        const float sc = WarpSum(dot) * scale;
-        const float m_new = fmaxf(m[g], sc);
-        const float keep = expf(m[g] - m_new);   // 0 on the first position
-        const float p = expf(sc - m_new);
-        l[g] = l[g] * keep + p;
-#pragma unroll
-        for (int i = 0; i < kMaxPerLane; ++i) {
-          acc[g][i] = acc[g][i] * keep + p * vf[i];
-        }
-        m[g] = m_new;
       }
     }
   }
@@ -313,33 +327,48 @@ __device__ __forceinline__ void AttnSliceBody(const AttnArgs& a, int split, int 
 }
 
 // Merges the slices of query head `qh` and applies the output gate
-// (decoder.cpp:383-411).
+// (decoder.cpp:383-411). Two rounds of loads: the slices' maxima and sums, a
+// lane each, then every thread's kAttnSplits values per output at once.
 __device__ __forceinline__ void AttnMergeBody(const AttnArgs& a, int qh, int tid) {
+  static_assert(kAttnSplits == 32, "a warp holds the slices, a lane each");
   const int hd = a.head_dim;
   const int group = a.heads / a.kv_heads;
   const int kh = qh / group, g = qh % group;
+  const int lane = tid & 31;
   auto slice = [&](int s) {
     return a.partials + ((static_cast<size_t>(kh) * kAttnSplits + s) * group + g) * (hd + 2);
   };
-  float top = -INFINITY;
-  for (int s = 0; s < kAttnSplits; ++s) {
-    top = fmaxf(top, __ldcg(slice(s) + hd));
+  // Every warp works the weights out for itself (no shared memory, no barrier).
+  const float m = __ldcg(slice(lane) + hd);
+  const float l = __ldcg(slice(lane) + hd + 1);
+  float top = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    top = fmaxf(top, __shfl_xor_sync(0xFFFFFFFFu, top, o));
   }
-  float total = 0.f;
+  const float mine = m == -INFINITY ? 0.f : expf(m - top);
+  float total = 0.f;   // in slice order
   float wgt[kAttnSplits];
+#pragma unroll
   for (int s = 0; s < kAttnSplits; ++s) {
-    const float ms = __ldcg(slice(s) + hd);
-    wgt[s] = ms == -INFINITY ? 0.f : expf(ms - top);
-    total += wgt[s] * __ldcg(slice(s) + hd + 1);
+    wgt[s] = __shfl_sync(0xFFFFFFFFu, mine, s);
+    total += __shfl_sync(0xFFFFFFFFu, mine * l, s);
   }
   const float inv_total = 1.0f / total;
   const float* gate = a.in + static_cast<size_t>(qh) * 2 * hd + hd;
   for (int e = tid; e < hd; e += kTeamThreads) {
-    float out = 0.f;
+    float part[kAttnSplits];
+#pragma unroll
     for (int s = 0; s < kAttnSplits; ++s) {
-      out += wgt[s] * __ldcg(slice(s) + e);
+      part[s] = __ldcg(slice(s) + e);
     }
-    a.ctx[qh * hd + e] = out * (inv_total * SigmoidDev(__ldcg(gate + e)));
+    const float gv = __ldcg(gate + e);
+    float out = 0.f;
+#pragma unroll
+    for (int s = 0; s < kAttnSplits; ++s) {
+      out += wgt[s] * part[s];
+    }
+    a.ctx[qh * hd + e] = out * (inv_total * SigmoidDev(gv));
   }
 }
 

@@ -176,7 +176,7 @@ class TpDecoder:
         self.local = z(max(max(max(l[k][2] for k in ("in", "out", "ffn_in", "ffn_down")) for l in self.layers),
                            self.lm_head[2]))
         self.queries = z(c.heads * c.head_dim)
-        self.partials = z(c.kv_heads * 8 * (c.heads // c.kv_heads) * (c.head_dim + 2))
+        self.partials = z(c.kv_heads * 32 * (c.heads // c.kv_heads) * (c.head_dim + 2))
         self.position_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.token_dev = torch.zeros(1, dtype=torch.int32, device=dev)
         self.position = 0

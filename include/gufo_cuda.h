@@ -374,7 +374,7 @@ typedef struct gufo_cuda_attention_args {
   void* keys;            /* fp16 [max_positions][kv_heads * head_dim] */
   void* values;
   float* queries;        /* scratch [heads][head_dim] */
-  float* partials;       /* scratch [kv_heads][8][heads / kv_heads][head_dim + 2] */
+  float* partials;       /* scratch [kv_heads][32][heads / kv_heads][head_dim + 2] */
   float* ctx_out;
 } gufo_cuda_attention_args;
 

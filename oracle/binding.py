@@ -21,8 +21,14 @@ _u8p = C.POINTER(C.c_uint8)
 _i32p = C.POINTER(C.c_int)
 
 
-def build(reference: str = "/root/reference") -> None:
-    """Runs oracle/Makefile (the restatement, and _ref when the reference tree exists)."""
+def build(reference: str | None = None) -> None:
+    """Runs oracle/Makefile (the restatement, and _ref when the reference tree exists).
+    `reference` is the reference checkout; by default the environment's GUFO_REFERENCE,
+    else a directory named "reference" beside this repository (neither: only the
+    restatement is built)."""
+    if reference is None:
+        beside = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+        reference = os.environ.get("GUFO_REFERENCE") or (beside if os.path.isdir(beside) else "")
     subprocess.run(["make", "-C", HERE, f"REFERENCE={reference}"], check=True,
                    stdout=subprocess.DEVNULL)
 

@@ -143,7 +143,7 @@ def test_attention_device_matches_cpu_restatement(ctx, heads, kv_heads, head_dim
     keys, values = t(keys_h.copy()), t(values_h.copy())
     qn, kn, fr = t(q_norm), t(k_norm), t(inv_freq)
     queries = torch.empty(heads * head_dim, device=dev)
-    partials = torch.empty(kv_heads * 8 * (heads // kv_heads) * (head_dim + 2), device=dev)
+    partials = torch.empty(kv_heads * 32 * (heads // kv_heads) * (head_dim + 2), device=dev)
     out = torch.empty(heads * head_dim, device=dev)
     position = torch.zeros(1, dtype=torch.int32, device=dev)
     for pos in (0, 1, 6, 7, 8, 9, 130, 1000, 1536):
