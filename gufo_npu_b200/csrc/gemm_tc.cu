@@ -19,9 +19,11 @@
 //     (cp.async.bulk) each: the activations were converted once per product into
 //     fp16 tile images that already carry the shared-memory swizzle;
 //   - sixteen dequant warps, two threads per weight row: w = d*sc*q - dmin*m
-//     (DequantQ4_K, src/core/quant.cpp:33-59) or w = d*sc*(q - 32) (DequantQ6_K,
-//     :98-125) in fp32, rounded once to fp16 and stored in the
-//     128-byte-swizzled K-major layout the MMA reads;
+//     (DequantQ4_K, src/core/quant.cpp:33-59) in packed fp16 arithmetic (two
+//     weights per instruction, as d*sc*(q - 8) + (8*d*sc - dmin*m)) or
+//     w = d*sc*(q - 32) (DequantQ6_K, :98-125) in fp32 rounded once to fp16,
+//     stored in the 128-byte-swizzled K-major layout the MMA reads; all sixteen
+//     warps work on one tile at a time, in the order the MMA consumes them;
 //   - one thread issues tcgen05.mma (kind::f16, M = 128, N = 256, K = 16, four
 //     per tile) and tcgen05.commit hands the tile buffers back;
 //   - four epilogue warps read the accumulator with tcgen05.ld (lane = token,
@@ -248,37 +250,40 @@ __device__ __forceinline__ void TmemLoad16(uint32_t taddr, float (&v)[16]) {
   }
 }
 
-// Nibble I (bits 4I .. 4I + 3, I <= 4) of `w` as a float: the nibble is masked
-// in place under the exponent whose mantissa bit 4I is worth 1, which reads as
-// 2^(23 - 4I) + code; subtracting the power of two leaves the code exactly.
-// One logic instruction and one add instead of a byte permute (half rate here).
-template <int I>
-__device__ __forceinline__ float Nibble(uint32_t w) {
-  static_assert(I >= 0 && I <= 4, "the nibble must sit below the exponent");
-  constexpr uint32_t kExponent = static_cast<uint32_t>(127 + 23 - 4 * I) << 23;
-  return __uint_as_float((w & (0xFu << (4 * I))) | kExponent) - __uint_as_float(kExponent);
+// Within every four consecutive values of K the tiles hold them in the order
+// (0, 2, 1, 3): a Q4_K word yields the nibbles of its bytes 0 and 2 together (and
+// 1 and 3), so this order lets a pair leave the arithmetic as it arrives. The
+// activation tiles (StageHalfKernel) and the Q6_K tiles follow the same order;
+// a contraction does not care how K is numbered.
+//
+// Eight weights from two words of a sub-block pair's nibble bytes, in packed
+// fp16 arithmetic. A nibble is masked in place under an fp16
+// exponent whose mantissa bit there is worth 1 (1024 + code for bits 0-3,
+// 64 + code for bits 4-7: one logic instruction for two codes); subtracting the
+// power of two plus 8 leaves code - 8 exactly, and one fused multiply-add per
+// pair gives w = scale * (code - 8) + (8 * scale - offset). Centring the code
+// keeps both terms of the size of w itself, so rounding the scale and the
+// constant to fp16 costs about what rounding w does; scale * code - offset
+// loses three more bits to cancellation (measured relative L2 of a product:
+// 7e-4 that way, 3.8e-4 centred, 2e-4 with fp32 arithmetic rounded once).
+__device__ __forceinline__ uint32_t HalfPairFma(uint32_t biased, uint32_t bias, uint32_t scale, uint32_t constant) {
+  const __half2 code = __hsub2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&bias));
+  const __half2 w = __hfma2(code, *reinterpret_cast<const __half2*>(&scale), *reinterpret_cast<const __half2*>(&constant));
+  return *reinterpret_cast<const uint32_t*>(&w);
 }
 
-// The sixteen weights in two words of a sub-block pair's nibble bytes: the low
-// nibbles of the eight bytes (sub-block 2t) and the high nibbles (sub-block
-// 2t + 1), each as four fp16 pairs in byte order: w = scale * code - offset in
-// fp32, rounded once.
-__device__ __forceinline__ void SixteenWeights(uint32_t w0, uint32_t w1, float a_lo, float b_lo, float a_hi,
-                                               float b_hi, uint4* low, uint4* high) {
-  // Nibbles 5 to 7 of a word are nibbles 2 to 4 of the word shifted down by 12.
-  const uint32_t s0 = w0 >> 12, s1 = w1 >> 12;
-  auto pack = [](float x, float y) {
-    const __half2 h = __floats2half2_rn(x, y);
-    return *reinterpret_cast<const uint32_t*>(&h);
-  };
-  low->x = pack(fmaf(Nibble<0>(w0), a_lo, -b_lo), fmaf(Nibble<2>(w0), a_lo, -b_lo));
-  low->y = pack(fmaf(Nibble<4>(w0), a_lo, -b_lo), fmaf(Nibble<3>(s0), a_lo, -b_lo));
-  low->z = pack(fmaf(Nibble<0>(w1), a_lo, -b_lo), fmaf(Nibble<2>(w1), a_lo, -b_lo));
-  low->w = pack(fmaf(Nibble<4>(w1), a_lo, -b_lo), fmaf(Nibble<3>(s1), a_lo, -b_lo));
-  high->x = pack(fmaf(Nibble<1>(w0), a_hi, -b_hi), fmaf(Nibble<3>(w0), a_hi, -b_hi));
-  high->y = pack(fmaf(Nibble<2>(s0), a_hi, -b_hi), fmaf(Nibble<4>(s0), a_hi, -b_hi));
-  high->z = pack(fmaf(Nibble<1>(w1), a_hi, -b_hi), fmaf(Nibble<3>(w1), a_hi, -b_hi));
-  high->w = pack(fmaf(Nibble<2>(s1), a_hi, -b_hi), fmaf(Nibble<4>(s1), a_hi, -b_hi));
+// HIGH = false: the low nibbles of the eight bytes of w0 and w1 (eight values of
+// sub-block 2t); HIGH = true: the high nibbles (of sub-block 2t + 1).
+template <bool HIGH>
+__device__ __forceinline__ uint4 EightWeights(uint32_t w0, uint32_t w1, uint32_t scale, uint32_t constant) {
+  constexpr uint32_t kMask = HIGH ? 0x00F000F0u : 0x000F000Fu;
+  constexpr uint32_t kOne = HIGH ? 0x54005400u : 0x64006400u;    // 64 or 1024 as fp16 pairs
+  constexpr uint32_t kBias = HIGH ? 0x54805480u : 0x64086408u;   // 72 or 1032
+  const uint32_t s0 = w0 >> 8, s1 = w1 >> 8;
+  return make_uint4(HalfPairFma((w0 & kMask) | kOne, kBias, scale, constant),    // bytes 0 and 2
+                    HalfPairFma((s0 & kMask) | kOne, kBias, scale, constant),    // bytes 1 and 3
+                    HalfPairFma((w1 & kMask) | kOne, kBias, scale, constant),
+                    HalfPairFma((s1 & kMask) | kOne, kBias, scale, constant));
 }
 
 // Byte I of `w` (a code below 64) minus 32 as a float, exactly: bytes 0 to 2
@@ -294,17 +299,18 @@ __device__ __forceinline__ float CodeMinus32(uint32_t w) {
 }
 
 // Eight Q6_K weights from the codes in the bytes of two words, as four fp16
-// pairs in byte order: w = scale * (code - 32), rounded once.
+// pairs: w = scale * (code - 32) in fp32, rounded once.
 __device__ __forceinline__ uint4 EightCodes(uint32_t w0, uint32_t w1, float scale) {
   const uint32_t s0 = w0 >> 16, s1 = w1 >> 16;
   auto pack = [](float x, float y) {
     const __half2 h = __floats2half2_rn(x, y);
     return *reinterpret_cast<const uint32_t*>(&h);
   };
-  return make_uint4(pack(CodeMinus32<0>(w0) * scale, CodeMinus32<1>(w0) * scale),
-                    pack(CodeMinus32<0>(s0) * scale, CodeMinus32<1>(s0) * scale),
-                    pack(CodeMinus32<0>(w1) * scale, CodeMinus32<1>(w1) * scale),
-                    pack(CodeMinus32<0>(s1) * scale, CodeMinus32<1>(s1) * scale));
+  // Bytes (0, 2) and (1, 3) of each word: the tiles' order of K.
+  return make_uint4(pack(CodeMinus32<0>(w0) * scale, CodeMinus32<0>(s0) * scale),
+                    pack(CodeMinus32<1>(w0) * scale, CodeMinus32<1>(s0) * scale),
+                    pack(CodeMinus32<0>(w1) * scale, CodeMinus32<0>(s1) * scale),
+                    pack(CodeMinus32<1>(w1) * scale, CodeMinus32<1>(s1) * scale));
 }
 
 // Where unit `u` of a launch works: its part, weight rows and K range.
@@ -372,7 +378,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
       MbarInit(raw_empty(s), kDequantThreads / 32);
     }
     for (int s = 0; s < kWStages; ++s) {
-      MbarInit(w_full(s), kTileRows / 32);
+      MbarInit(w_full(s), kDequantThreads / 32);
       MbarInit(w_empty(s), 1);
     }
     for (int s = 0; s < kXStages; ++s) {
@@ -549,9 +555,10 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
       }
     }
   } else if (warp < kDequantThreads / 32) {
-    // ---- dequant: threads r and r + 256 own weight row r of the tile; the
-    // first takes sub-block pairs 0 and 1 of every block, the second 2 and 3.
-    // Tile g = 4 * block + pair of the thread block's stream lands in buffer g % 3.
+    // ---- dequant: threads r and r + 256 own weight row r; all sixteen warps
+    // work on the same tile, in the order the MMA consumes them (the first
+    // thread takes the first half of each tile row, the second the other).
+    // Tile g = 4 * block + t of the thread block's stream lands in buffer g % stages.
     const int r = threadIdx.x & (kTileRows - 1);
     const int half = threadIdx.x / kTileRows;
     int i = 0;   // blocks done so far
@@ -567,16 +574,21 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
           const float d = HalfBitsToFloat(static_cast<uint16_t>(head.x & 0xFFFF));
           const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head.x >> 16));
   #pragma unroll
-          for (int tt = 0; tt < 2; ++tt) {
-            const int t = 2 * half + tt;
+          for (int t = 0; t < 4; ++t) {
             const int g = 4 * i + t;
             const int ws = g % kWStages;
             const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
-            int sc_lo, m_lo, sc_hi, m_hi;
-            ScaleMinK4(2 * t, head.y, head.z, head.w, &sc_lo, &m_lo);
-            ScaleMinK4(2 * t + 1, head.y, head.z, head.w, &sc_hi, &m_hi);
-            const float a_lo = d * static_cast<float>(sc_lo), a_hi = d * static_cast<float>(sc_hi);
-            const float b_lo = dmin * static_cast<float>(m_lo), b_hi = dmin * static_cast<float>(m_hi);
+            // This thread's sub-block of the pair: its scale and the constant
+            // 8 * scale - offset, each doubled into an fp16 pair.
+            int sc, m;
+            ScaleMinK4(2 * t + half, head.y, head.z, head.w, &sc, &m);
+            auto pair = [](float v) {
+              const __half2 h = __float2half2_rn(v);
+              return *reinterpret_cast<const uint32_t*>(&h);
+            };
+            const float scale = d * static_cast<float>(sc);
+            const uint32_t scale2 = pair(scale);
+            const uint32_t constant2 = pair(fmaf(8.0f, scale, -dmin * static_cast<float>(m)));
             const uint4 q0 = *reinterpret_cast<const uint4*>(block + 16 + 32 * t);
             const uint4 q1 = *reinterpret_cast<const uint4*>(block + 32 + 32 * t);
             const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
@@ -585,10 +597,9 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
   #pragma unroll
             for (int c = 0; c < 4; ++c) {
               // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
-              uint4 low, high;
-              SixteenWeights(words[2 * c], words[2 * c + 1], a_lo, b_lo, a_hi, b_hi, &low, &high);
-              *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) = low;
-              *reinterpret_cast<uint4*>(tile_row + (((4 + c) ^ (r & 7)) << 4)) = high;
+              const uint4 eight = half == 0 ? EightWeights<false>(words[2 * c], words[2 * c + 1], scale2, constant2)
+                                            : EightWeights<true>(words[2 * c], words[2 * c + 1], scale2, constant2);
+              *reinterpret_cast<uint4*>(tile_row + (((4 * half + c) ^ (r & 7)) << 4)) = eight;
             }
             // Make the generic-proxy stores visible to the tensor core's reads; one
             // lane then arrives for the warp.
@@ -599,56 +610,55 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
             }
           }
         } else {
-          // Thread (row r, half n) turns the 128 values of its half of the block
-          // into tiles 2n (low nibbles) and 2n + 1 (high nibbles): w = d * sc *
-          // (code - 32), code = nibble | two bits of qh << 4 (DequantQ6_K,
-          // src/core/quant.cpp:98-125).
+          // Tile t of the block holds values 64t .. 64t + 63: half n = t / 2 of
+          // the block, the low (t even) or high nibbles of its 64 ql bytes, two
+          // bits of its 32 qh bytes: w = d * sc * (code - 32), code = nibble |
+          // two bits of qh << 4 (DequantQ6_K, src/core/quant.cpp:98-125). This
+          // thread takes chunks 4 * half .. 4 * half + 3 of every tile: ql bytes
+          // 32 * half .. + 31 of the tile's half.
           const uint8_t* block = smem + Smem::kRaw + s * kRawBytes + r * Q::kRowBytes;
-          const uint4 l0 = *reinterpret_cast<const uint4*>(block + 64 * half);
-          const uint4 l1 = *reinterpret_cast<const uint4*>(block + 64 * half + 16);
-          const uint4 l2 = *reinterpret_cast<const uint4*>(block + 64 * half + 32);
-          const uint4 l3 = *reinterpret_cast<const uint4*>(block + 64 * half + 48);
-          const uint4 h0 = *reinterpret_cast<const uint4*>(block + 128 + 32 * half);
-          const uint4 h1 = *reinterpret_cast<const uint4*>(block + 128 + 32 * half + 16);
-          const uint2 sc8 = *reinterpret_cast<const uint2*>(block + 192 + 8 * half);
           const float d = HalfBitsToFloat(*reinterpret_cast<const uint16_t*>(
               block + 208 + 2 * ((unit.first_block + b) % kQ6KSlabBlocks)));
-          const uint32_t ql[16] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w,
-                                   l2.x, l2.y, l2.z, l2.w, l3.x, l3.y, l3.z, l3.w};
-          const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-          // Scale of 16-value group i of this half (int8).
-          auto scale = [&](int i) {
-            const uint32_t word = i < 4 ? sc8.x : sc8.y;
-            return d * static_cast<float>(static_cast<int>(word << (24 - 8 * (i & 3))) >> 24);
-          };
 #pragma unroll
-          for (int tt = 0; tt < 2; ++tt) {
-            const int t = 2 * half + tt;
-            const int g = 4 * i + t;
-            const int ws = g % kWStages;
-            const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
-            BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
-            uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
+          for (int n = 0; n < 2; ++n) {
+            const uint4 l0 = *reinterpret_cast<const uint4*>(block + 64 * n + 32 * half);
+            const uint4 l1 = *reinterpret_cast<const uint4*>(block + 64 * n + 32 * half + 16);
+            const uint4 h0 = *reinterpret_cast<const uint4*>(block + 128 + 32 * n);
+            const uint4 h1 = *reinterpret_cast<const uint4*>(block + 128 + 32 * n + 16);
+            const uint2 sc8 = *reinterpret_cast<const uint2*>(block + 192 + 8 * n);
+            const uint32_t ql[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            const uint32_t qh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            // Scale of 16-value group j of this half of the block (int8).
+            auto scale = [&](int j) {
+              const uint32_t word = j < 4 ? sc8.x : sc8.y;
+              return d * static_cast<float>(static_cast<int>(word << (24 - 8 * (j & 3))) >> 24);
+            };
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              // Chunk c < 4: values 8c .. 8c + 7 from ql bytes 8c .., chunk c >= 4: from ql
-              // bytes 32 + 8(c - 4) ..; both take their two high bits from qh bytes
-              // 8(c & 3) .., at bit 2 * (2 tt + (c >> 2)).
-              const int k = c & 3;
-              const int shift = 2 * (2 * tt + (c >> 2));   // where the two bits sit in qh
-              const uint32_t q0 = ql[(c >> 2) * 8 + 2 * k], q1 = ql[(c >> 2) * 8 + 2 * k + 1];
-              const uint32_t n0 = tt == 0 ? (q0 & 0x0F0F0F0Fu) : ((q0 >> 4) & 0x0F0F0F0Fu);
-              const uint32_t n1 = tt == 0 ? (q1 & 0x0F0F0F0Fu) : ((q1 >> 4) & 0x0F0F0F0Fu);
-              const uint32_t b0 = shift <= 4 ? (qh[2 * k] << (4 - shift)) : (qh[2 * k] >> (shift - 4));
-              const uint32_t b1 = shift <= 4 ? (qh[2 * k + 1] << (4 - shift)) : (qh[2 * k + 1] >> (shift - 4));
-              const float sc = scale(4 * tt + 2 * (c >> 2) + (k >> 1));
-              *reinterpret_cast<uint4*>(tile_row + ((c ^ (r & 7)) << 4)) =
-                  EightCodes(n0 | (b0 & 0x30303030u), n1 | (b1 & 0x30303030u), sc);
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-              MbarArrive(w_full(ws));
+            for (int tt = 0; tt < 2; ++tt) {
+              const int g = 4 * i + 2 * n + tt;
+              const int ws = g % kWStages;
+              const uint32_t w_phase = static_cast<uint32_t>(g / kWStages) & 1u;
+              BoundedWait(w_empty(ws), w_phase ^ 1u, abort_flag, a.error, 5);
+              uint8_t* tile_row = smem + Smem::kW + ws * kWTileBytes + r * 128;
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                // Chunk 4 * half + k: values from ql bytes 32 * half + 8k .., their two
+                // high bits from qh bytes 8k .. at bit 2 * (2 tt + half).
+                const int shift = 2 * (2 * tt + half);
+                const uint32_t q0 = ql[2 * k], q1 = ql[2 * k + 1];
+                const uint32_t n0 = tt == 0 ? (q0 & 0x0F0F0F0Fu) : ((q0 >> 4) & 0x0F0F0F0Fu);
+                const uint32_t n1 = tt == 0 ? (q1 & 0x0F0F0F0Fu) : ((q1 >> 4) & 0x0F0F0F0Fu);
+                const uint32_t b0 = shift <= 4 ? (qh[2 * k] << (4 - shift)) : (qh[2 * k] >> (shift - 4));
+                const uint32_t b1 = shift <= 4 ? (qh[2 * k + 1] << (4 - shift)) : (qh[2 * k + 1] >> (shift - 4));
+                const float sc = scale(4 * tt + 2 * half + (k >> 1));
+                *reinterpret_cast<uint4*>(tile_row + (((4 * half + k) ^ (r & 7)) << 4)) =
+                    EightCodes(n0 | (b0 & 0x30303030u), n1 | (b1 & 0x30303030u), sc);
+              }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                MbarArrive(w_full(ws));
+              }
             }
           }
         }
@@ -717,8 +727,9 @@ StageHalfKernel(const float* __restrict__ x, int tokens, int cols, int npad, uin
     if (n < tokens) {
       const float4 v0 = *reinterpret_cast<const float4*>(x + static_cast<size_t>(n) * cols + k);
       const float4 v1 = *reinterpret_cast<const float4*>(x + static_cast<size_t>(n) * cols + k + 4);
-      const __half2 h0 = __floats2half2_rn(v0.x * up, v0.y * up), h1 = __floats2half2_rn(v0.z * up, v0.w * up);
-      const __half2 h2 = __floats2half2_rn(v1.x * up, v1.y * up), h3 = __floats2half2_rn(v1.z * up, v1.w * up);
+      // Values (0, 2, 1, 3) of every four: the order of K the weight tiles use.
+      const __half2 h0 = __floats2half2_rn(v0.x * up, v0.z * up), h1 = __floats2half2_rn(v0.y * up, v0.w * up);
+      const __half2 h2 = __floats2half2_rn(v1.x * up, v1.z * up), h3 = __floats2half2_rn(v1.y * up, v1.w * up);
       packed = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
                           *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
     }

@@ -8,11 +8,12 @@
 namespace gufo {
 
 // Fewest token rows that take this path; below, the GEMV kernels re-read the
-// weights once per 8 tokens and are faster (measured on 2 x 9728 x 2560 Q4_K:
-// 9 us per pass against 37 us here; on 248320 x 2560 Q6_K: 130 us per pass
-// against 680 us).
-constexpr int kTcMinTokens = 32;       // Q4_K parts
-constexpr int kTcMinTokensQ6K = 48;    // Q6_K parts
+// weights once per 8 tokens and are faster. Measured: 2 x 9728 x 2560 Q4_K costs
+// 27 us per 8-token pass against 31 us here whatever the rows (so from a second
+// pass on this path wins, and the third is where it is taken); 248320 x 2560
+// Q6_K 330 us per pass against 670 us here (from a third pass on).
+constexpr int kTcMinTokens = 17;       // Q4_K parts
+constexpr int kTcMinTokensQ6K = 17;    // Q6_K parts
 constexpr int kTcMaxTokens = 128;   // token rows per pass (the MMA's N)
 
 // Whether a product of `tokens` rows against parts of `type` runs on this path.

@@ -83,9 +83,10 @@ const char* gufo_cuda_last_error(const gufo_cuda_ctx* ctx);
  * before the call (true when each is touched once per decode step; kernels
  * launch ahead of one another, so "shortly" is a handful of launches): the
  * kernels then request them ahead of their dependency on the previous kernel.
- * "tc_gemm" = 1 (default) runs products of many token rows (32 for Q4_K, 48 for
- * Q6_K parts) on the tcgen05 GEMM, 0 keeps them on the 8-token passes of the
- * GEMV kernels, 2 sends every product of 16 or more rows to the GEMM.
+ * "tc_gemm" = 1 (default) runs products of 17 or more token rows (where the
+ * GEMV kernels would need a third pass over the weights) on the tcgen05 GEMM,
+ * 0 keeps them on the 8-token passes of the GEMV kernels, 2 sends every
+ * product of 16 or more rows to the GEMM.
  * "gemv_variant" = 1 is a timing aid: the tensor-core GEMV kernels skip their
  * multiplies and only move the weights (outputs are then meaningless).
  * "reuse_image" = 1 is a timing aid: products skip the staging of x and

@@ -164,7 +164,7 @@ def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
     hence the wider bound from 16 tokens on. Both are far inside the 1e-3 bound."""
     rows, cols = 96, 768
     x = G.normal(50 + tokens, tokens, cols)
-    exact_tol, same_tol = (1e-5, 1e-6) if tokens < 16 else (4e-4, 4e-4)
+    exact_tol, same_tol = (1e-5, 1e-6) if tokens < 16 else (5e-4, 5e-4)
     for name, t in TYPES.items():
         raw = Q.quantize(t, torch.from_numpy(G.normal(60, rows, cols) * 0.02)).numpy()
         m = ctx.matrix_upload(t, raw, rows, cols)
