@@ -421,7 +421,7 @@ def run_ours(args):
         "gpu_launches": int(launches),
         # The metric's kernel: the 6144 x 2048 Q4_K GEMV, one launch per product, 24 distinct
         # matrices back to back. `traffic` is the DRAM traffic of one launch from an ncu capture of
-        # the same shape (read 7.09 MB + written 0.03 MB: the algorithmic bytes).
+        # the same shape (the algorithmic bytes plus 0.6 %).
         "roofline": {"bound": "hbm", "achieved": gemv["achieved"], "peak": peak, "unit": "GB/s",
                      "frac": gemv["frac"], "traffic": Q4K_GEMV_TRAFFIC_BYTES,
                      "traffic_source": "ncu capture of the same launch (bench.py --probe q4k)", "peak_kind": peak_kind,
@@ -439,13 +439,14 @@ def run_ours(args):
 
 
 # DRAM traffic of one 6144 x 2048 Q4_K GEMV launch: dram__bytes_read.sum + dram__bytes_write.sum
-# of the kernel from one ncu capture of `bench.py --probe q4k` (7.09 MB read, 0.03 MB written).
-Q4K_GEMV_TRAFFIC_BYTES = 7.09e6 + 0.03e6
+# of the kernel from one ncu capture of `bench.py --probe q4k` (7 152 128 B read, none written:
+# the 24 KB of outputs are still in L2 when the kernel ends).
+Q4K_GEMV_TRAFFIC_BYTES = 7152128
 
 
 def run_probe(which: str) -> None:
     """A handful of launches of one kernel family on a small case (a few hundred MB on the
-    device, inputs larger than L2): the program `ncu` captures for the summaries in profiles/."""
+    device, inputs larger than L2): the program that `ncu` is pointed at."""
     from gufo_npu_b200 import _capi
     from gufo_npu_b200.backend import Context
     dev = torch.device("cuda:0")
@@ -463,6 +464,17 @@ def run_probe(which: str) -> None:
         y = torch.empty(1, rows, device=dev)
         for i in range(8):
             ctx.matmul_device(mats[i % copies], 1, x, 1, y)
+    elif which == "step_kernel":
+        # The config-2 decode step as one cooperative kernel (context option "step_kernel").
+        from gufo_npu_b200.backend import CudaDecoder, CudaProjections
+        ctx.set_option("step_kernel", 1)
+        cfg = model_config()
+        tensors = synth.build_model(cfg, seed=1, device=str(dev))
+        dec = CudaDecoder(CudaProjections(ctx, cfg, tensors), tensors, max_positions=64, use_graph=False)
+        for t in range(6):
+            dec.step_device(t + 1)
+        torch.cuda.synchronize()
+        dec.status()
     elif which == "gemm":
         return probe_gemm(ctx, stream, dev, gen)
     elif which == "moe":
@@ -605,7 +617,7 @@ def probe_moe(ctx, stream, dev, gen) -> None:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--probe", default=None, choices=["q4k", "q4k_big", "q6k", "deltanet", "gemm", "moe"],
+    ap.add_argument("--probe", default=None, choices=["q4k", "q4k_big", "q6k", "deltanet", "gemm", "moe", "step_kernel"],
                     help="run a few launches of one kernel on a small case (for ncu) and exit")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
