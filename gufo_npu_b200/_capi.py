@@ -64,7 +64,7 @@ class FusedInput(C.Structure):
     """gufo_cuda_fused_input."""
     _fields_ = [("prologue", C.c_int), ("x", C.c_void_p), ("residual", C.c_void_p), ("delta", C.c_void_p),
                 ("norm_weight", C.c_void_p), ("rms_eps", C.c_float), ("residual_out", C.c_void_p),
-                ("scratch", C.c_void_p), ("advance", C.c_void_p)]
+                ("scratch", C.c_void_p), ("advance", C.c_void_p), ("delta_parts", C.c_int), ("delta_stride", C.c_int)]
 
 
 PROLOGUE_PLAIN, PROLOGUE_RES_NORM, PROLOGUE_SWIGLU = 0, 1, 2
@@ -140,6 +140,8 @@ SIGNATURES = {
     "gufo_cuda_matmul_gather_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.POINTER(FusedInput), C.c_size_t,
                                                  C.c_int, C.c_int]),
     "gufo_cuda_peer_wait_device": (C.c_int, [C.c_void_p, C.c_int]),
+    "gufo_cuda_matmul_wait_device": (C.c_int, [C.c_void_p, C.POINTER(Rows), C.c_int, C.POINTER(FusedInput), C.c_int,
+                                               C.c_void_p]),
     "gufo_cuda_matmul_q4k_static_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
                                                      C.c_int, C.c_void_p]),
     "gufo_cuda_delta_rule_device": (C.c_int, [C.c_void_p, C.POINTER(DeltaSeq), C.c_int, C.c_int, C.c_int,

@@ -142,6 +142,8 @@ struct FastGemvArgs {
   const float* x;        // kProloguePlain: [tokens][cols]; kPrologueSwiGlu: [tokens][2 * cols]
   const float* h_in;     // kPrologueResNorm: the residual stream [tokens][cols] ...
   const float* delta;    //   ... plus this, [tokens][cols] (may be null)
+  int delta_parts;       //   ... and delta_parts - 1 more such vectors, delta_stride floats apart,
+  int delta_stride;      //   added in order (0 or 1: the one vector; one token only otherwise)
   const float* norm_w;
   float eps;
   float* h_out;          //   h_in + delta, written by block 0 (must not alias h_in)

@@ -363,6 +363,8 @@ struct Input {
   const float* x = nullptr;        // plain: the rows; SwiGLU: [gate | up] rows
   const float* h_in = nullptr;     // residual + norm
   const float* delta = nullptr;
+  int delta_parts = 1;             // vectors to add, delta_stride floats apart
+  int delta_stride = 0;
   const float* norm_w = nullptr;
   float* h_out = nullptr;
   int* advance = nullptr;
@@ -401,6 +403,11 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
                   "tensor-core GEMV");
     }
   }
+  if (in.delta_parts > 1 && (!fused || fast_parts != stage.nparts || tokens != 1)) {
+    return Fail(GUFO_CUDA_UNSUPPORTED_TYPE,
+                "fused product: several vectors are added to the residual only by the tensor-core GEMV (Q4_K or "
+                "Q6_K parts that fit it, one token)");
+  }
   if (!fused || fast_parts == 0) {
     const float* x = in.x;
     if (in.prologue == kPrologueResNorm) {
@@ -435,6 +442,8 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
     args.x = in.x;
     args.h_in = in.h_in;
     args.delta = in.delta;
+    args.delta_parts = in.delta_parts;
+    args.delta_stride = in.delta_stride;
     args.norm_w = in.norm_w;
     args.eps = rms_eps;
     args.h_out = in.h_out;
@@ -977,6 +986,12 @@ int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* part
       input.prologue = gufo::kPrologueResNorm;
       input.h_in = in->residual;
       input.delta = in->delta;
+      if (in->delta_parts < 0 || (in->delta_parts > 1 && (in->delta == nullptr || in->delta_stride % 4 != 0))) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                    "matmul_fused: delta_parts vectors need delta and a delta_stride that is a multiple of 4");
+      }
+      input.delta_parts = in->delta_parts > 1 ? in->delta_parts : 1;
+      input.delta_stride = in->delta_stride;
       input.norm_w = in->norm_weight;
       input.h_out = in->residual_out;
       input.advance = in->advance;
@@ -1003,6 +1018,58 @@ int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* part
   return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, y, tokens);
 }
 
+// The fused input of the peer-group products, checked.
+static int PeerProductInput(const gufo_cuda_fused_input* in, const char* who, gufo::Input* input) {
+  *input = gufo::Input{gufo::kProloguePlain};
+  switch (in->prologue) {
+    case GUFO_CUDA_PROLOGUE_PLAIN:
+    case GUFO_CUDA_PROLOGUE_SWIGLU:
+      if (in->x == nullptr) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string(who) + ": x must be given");
+      }
+      input->prologue = in->prologue == GUFO_CUDA_PROLOGUE_PLAIN ? gufo::kProloguePlain : gufo::kPrologueSwiGlu;
+      input->x = in->x;
+      break;
+    case GUFO_CUDA_PROLOGUE_RES_NORM:
+      if (in->residual == nullptr || in->norm_weight == nullptr || in->residual_out == nullptr ||
+          in->scratch == nullptr || in->residual_out == in->residual) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                    std::string(who) + ": residual, norm_weight, scratch and a residual_out apart from residual");
+      }
+      if (in->delta_parts < 0 || (in->delta_parts > 1 && (in->delta == nullptr || in->delta_stride % 4 != 0))) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT,
+                    std::string(who) + ": delta_parts vectors need delta and a delta_stride that is a multiple of 4");
+      }
+      input->prologue = gufo::kPrologueResNorm;
+      input->h_in = in->residual;
+      input->delta = in->delta;
+      input->delta_parts = in->delta_parts > 1 ? in->delta_parts : 1;
+      input->delta_stride = in->delta_stride;
+      input->norm_w = in->norm_weight;
+      input->h_out = in->residual_out;
+      input->advance = in->advance;
+      break;
+    default:
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string(who) + ": unknown prologue");
+  }
+  const float* rows[] = {in->x, in->residual, in->delta, in->norm_weight, in->residual_out, in->scratch};
+  for (const float* p : rows) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, std::string(who) + ": rows must be 16-byte aligned");
+    }
+  }
+  return GUFO_CUDA_OK;
+}
+
+static gufo::PeerWait WaitOn(const gufo_cuda_peer_group* g, int wait_slot) {
+  gufo::PeerWait wait{};
+  wait.header = reinterpret_cast<const unsigned*>(g->arena[g->rank]);
+  wait.world = g->world;
+  wait.slot = wait_slot;
+  wait.limit = g->limit;
+  return wait;
+}
+
 int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* g, const gufo_cuda_rows* parts, int nparts,
                                    const gufo_cuda_fused_input* in, size_t arena_offset, int slot, int wait_slot) {
   if (g == nullptr || parts == nullptr || in == nullptr) {
@@ -1012,42 +1079,15 @@ int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* g, const gufo_cuda_rows
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: slots are 0 to 7 (wait_slot < 0: no wait)");
   }
   gufo::Input input{gufo::kProloguePlain};
-  switch (in->prologue) {
-    case GUFO_CUDA_PROLOGUE_PLAIN:
-    case GUFO_CUDA_PROLOGUE_SWIGLU:
-      if (in->x == nullptr) {
-        return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: x must be given");
-      }
-      input.prologue = in->prologue == GUFO_CUDA_PROLOGUE_PLAIN ? gufo::kProloguePlain : gufo::kPrologueSwiGlu;
-      input.x = in->x;
-      break;
-    case GUFO_CUDA_PROLOGUE_RES_NORM:
-      if (in->residual == nullptr || in->norm_weight == nullptr || in->residual_out == nullptr ||
-          in->scratch == nullptr || in->residual_out == in->residual) {
-        return Fail(GUFO_CUDA_BAD_ARGUMENT,
-                    "matmul_gather: residual, norm_weight, scratch and a residual_out apart from residual");
-      }
-      input.prologue = gufo::kPrologueResNorm;
-      input.h_in = in->residual;
-      input.delta = in->delta;
-      input.norm_w = in->norm_weight;
-      input.h_out = in->residual_out;
-      input.advance = in->advance;
-      break;
-    default:
-      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: unknown prologue");
-  }
-  const float* rows[] = {in->x, in->residual, in->delta, in->norm_weight, in->residual_out, in->scratch};
-  for (const float* p : rows) {
-    if ((reinterpret_cast<uintptr_t>(p) & 15) != 0) {
-      return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: rows must be 16-byte aligned");
-    }
+  int rc = PeerProductInput(in, "matmul_gather", &input);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
   }
   gufo_cuda_ctx* ctx = g->ctx;
   std::lock_guard<std::mutex> lock(ctx->mu);
   GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
   gufo::GemvArgs stage;
-  const int rc = gufo::BuildGemvArgs(ctx, parts, nparts, &stage);
+  rc = gufo::BuildGemvArgs(ctx, parts, nparts, &stage);
   if (rc != GUFO_CUDA_OK) {
     return rc;
   }
@@ -1067,15 +1107,37 @@ int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* g, const gufo_cuda_rows
     out.y[p] = reinterpret_cast<float*>(g->arena[p] + arena_offset) + static_cast<size_t>(g->rank) * local;
     out.header[p] = reinterpret_cast<unsigned*>(g->arena[p]);
   }
-  gufo::PeerWait wait{};
-  if (wait_slot >= 0) {
-    wait.header = reinterpret_cast<const unsigned*>(g->arena[g->rank]);
-    wait.world = g->world;
-    wait.slot = wait_slot;
-    wait.limit = g->limit;
-  }
+  const gufo::PeerWait wait = WaitOn(g, wait_slot);
   return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, out.y[g->rank], 1, &out,
                             wait_slot >= 0 ? &wait : nullptr);
+}
+
+int gufo_cuda_matmul_wait_device(gufo_cuda_peer_group* g, const gufo_cuda_rows* parts, int nparts,
+                                 const gufo_cuda_fused_input* in, int wait_slot, float* device_y) {
+  if (g == nullptr || parts == nullptr || in == nullptr || device_y == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_wait: null pointer");
+  }
+  if (wait_slot < 0 || wait_slot >= gufo::kPeerSlots || (reinterpret_cast<uintptr_t>(device_y) & 15) != 0) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_wait: wait_slot is 0 to 7 and y 16-byte aligned");
+  }
+  gufo::Input input{gufo::kProloguePlain};
+  int rc = PeerProductInput(in, "matmul_wait", &input);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  gufo_cuda_ctx* ctx = g->ctx;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::GemvArgs stage;
+  rc = gufo::BuildGemvArgs(ctx, parts, nparts, &stage);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (stage.cols % 4 != 0) {
+    return Fail(GUFO_CUDA_SHAPE, "matmul_wait: cols must be a multiple of 4");
+  }
+  const gufo::PeerWait wait = WaitOn(g, wait_slot);
+  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, device_y, 1, nullptr, &wait);
 }
 
 int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config* config,

@@ -266,11 +266,15 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
       auto residual = [&](int at, float (&v)[8]) {
         load8(a.h_in + row + at, v);
         if (a.delta != nullptr) {
-          float d[8];
-          load8(a.delta + row + at, d);
+          // Partial sums of several ranks are added in rank order.
+          const int parts = a.delta_parts > 1 ? a.delta_parts : 1;
+          for (int p = 0; p < parts; ++p) {
+            float d[8];
+            load8(a.delta + static_cast<size_t>(p) * a.delta_stride + row + at, d);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            v[i] += d[i];
+            for (int i = 0; i < 8; ++i) {
+              v[i] += d[i];
+            }
           }
         }
       };

@@ -9,6 +9,14 @@ activations between the products run replicated (they need the full vectors and 
 percent of a step's bytes). The reference itself has no distributed execution; this module is
 new work on top of its operator interface.
 
+With collective="split" the ranks divide a layer the other way round: each rank owns a share
+of the heads (its rows of the input projection, its slice of the mixer, the matching columns
+of the output projection) and a share of the FFN width (its gate / up rows, the matching
+columns of the down projection). The two column-split products leave partial sums of the whole
+output vector; every rank stores its partial into all ranks' arenas and the next product adds
+them to the residual in rank order. That is two exchanges per layer instead of four gathers,
+and a rank never multiplies, convolves or updates another rank's heads.
+
 One process per GPU (torch.distributed, backend "nccl", for the rendezvous and the comparison
 path); the step is captured once per conv parity into a CUDA graph, gathers included.
 """
@@ -45,6 +53,35 @@ def shard_rows(parts: Sequence[Tuple[str, int]], rank: int, world: int) -> List[
     return out
 
 
+def split_plan(cfg: ModelConfig, rank: int, world: int) -> Dict[str, object]:
+    """What rank `rank` of `world` owns when the ranks split heads and FFN width: counts and
+    first indices. Raises ValueError when the model does not divide that way (column slices must
+    be whole 256-value blocks; every rank needs whole heads)."""
+    c = cfg
+    if c.is_moe:
+        raise ValueError("the head split covers dense models")
+    if c.heads % world or c.linear_value_heads % world or c.linear_key_heads % world or c.ffn % world:
+        raise ValueError("heads and FFN width must divide over the ranks")
+    if c.linear_value_heads != c.linear_key_heads:
+        raise ValueError("the head split takes DeltaNet layers with as many key heads as value heads")
+    heads = c.heads // world
+    # A KV head is owned by the ranks whose query heads share it: whole KV heads per rank while
+    # there are enough of them, one (replicated over neighbouring ranks) afterwards.
+    if c.kv_heads % world == 0:
+        kv_heads, kv_first = c.kv_heads // world, rank * (c.kv_heads // world)
+    elif world % c.kv_heads == 0:
+        kv_heads, kv_first = 1, rank // (world // c.kv_heads)
+    else:
+        raise ValueError("KV heads and ranks must divide one another")
+    linear = c.linear_value_heads // world
+    plan = {"heads": heads, "head_first": rank * heads, "kv_heads": kv_heads, "kv_first": kv_first,
+            "linear_heads": linear, "linear_first": rank * linear, "ffn": c.ffn // world, "ffn_first": rank * (c.ffn // world)}
+    for cols in (heads * c.head_dim, linear * c.linear_head_dim, plan["ffn"]):
+        if cols % 256:
+            raise ValueError("a rank's columns of the output and down projections must be whole 256-value blocks")
+    return plan
+
+
 def stage_tensors(cfg: ModelConfig, il: int, gates_in_mixer: bool = False) -> Dict[str, List[str]]:
     """GGUF tensor names stacked per stage of layer `il`, in the reference's order
     (src/models/qwen35/gguf_projections.cpp:139-171). With `gates_in_mixer` the DeltaNet input
@@ -73,13 +110,26 @@ class TpDecoder:
         kernel); "peer" gathers with a separate kernel over NVLink peer memory
         (gufo_cuda_peer_allgather_device); "nccl" with torch.distributed's all-gather."""
         self.ctx, self.cfg, self.rank, self.world = ctx, cfg, rank, world
-        self.collective = collective if world > 1 else "none"
+        self.collective = collective if world > 1 or collective == "split" else "none"
         self.fused = self.collective == "fused"
+        self.split = self.collective == "split"
         self.lib = ctx.lib
         dev = torch.device("cuda", ctx.device)
         self.dev = dev
         self._keep = []
         c = cfg
+        self.position_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.token_dev = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.position = 0
+        self.graphs = {}
+        self.kernels_per_step = 0
+        self.replayed_kernels = 0      # this backend's kernels launched through graph replays
+        self.max_positions = max_positions
+        self.inv_freq = torch.tensor([1.0 / (float(c.rope_theta) ** (2.0 * i / c.rope_dim))
+                                      for i in range(c.rope_dim // 2)], dtype=torch.float64).float().to(dev)
+        if self.split:
+            self._init_split(tensors)
+            return
 
         def f32(name):
             t = tensors[name].data.to(dev).view(torch.float32).contiguous()
@@ -135,9 +185,6 @@ class TpDecoder:
         self._embed_data = embed.data.to(dev)
         self.embed = ctx.matrix_from_device(embed.ggml_type, self._embed_data.data_ptr(), embed.rows, embed.cols)
         self.output_norm = f32("output_norm.weight")
-        self.inv_freq = torch.tensor([1.0 / (float(c.rope_theta) ** (2.0 * i / c.rope_dim))
-                                      for i in range(c.rope_dim // 2)], dtype=torch.float64).float().to(dev)
-        self.max_positions = max_positions
         width = max(l["in"][3] for l in self.layers)
         z = lambda n: torch.zeros(n, device=dev)
         self.h, self.normed = z(c.hidden), z(c.hidden)
@@ -177,13 +224,181 @@ class TpDecoder:
                            self.lm_head[2]))
         self.queries = z(c.heads * c.head_dim)
         self.partials = z(c.kv_heads * 32 * (c.heads // c.kv_heads) * (c.head_dim + 2))
-        self.position_dev = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.token_dev = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.position = 0
-        self.graphs = {}
-        self.kernels_per_step = 0
-        self.replayed_kernels = 0      # this backend's kernels launched through graph replays
         self.gathers_per_step = 4 * c.layers + 1
+
+    def _init_split(self, tensors: Dict[str, Tensor]) -> None:
+        """The rank's share of every layer for collective="split" (see the module text)."""
+        ctx, c, rank, world, dev = self.ctx, self.cfg, self.rank, self.world, self.dev
+        plan = split_plan(c, rank, world)
+        self.plan = plan
+
+        def f32(name):
+            t = tensors[name].data.to(dev).view(torch.float32).contiguous()
+            self._keep.append(t)
+            return t
+
+        def rows_of(name, first, count):
+            """Rows [first, first + count) of a tensor as a matrix of their own."""
+            t = tensors[name]
+            rb = Q.row_bytes(t.ggml_type, t.cols)
+            view = t.data[first * rb:(first + count) * rb].to(dev).clone()
+            self._keep.append(view)
+            return _capi.Rows(ctx.matrix_from_device(t.ggml_type, view.data_ptr(), count, t.cols), 0, count)
+
+        def cols_of(name, first, count):
+            """Columns [first, first + count) (whole 256-value blocks) of every row."""
+            t = tensors[name]
+            bb = Q.row_bytes(t.ggml_type, 256)
+            blocks = t.cols // 256
+            view = t.data.to(dev).view(t.rows, blocks, bb)[:, first // 256:(first + count) // 256, :].contiguous().view(-1)
+            self._keep.append(view)
+            return _capi.Rows(ctx.matrix_from_device(t.ggml_type, view.data_ptr(), t.rows, count), 0, t.rows)
+
+        def stack(*rows):
+            arr = (_capi.Rows * len(rows))(*rows)
+            local = sum(int(r.rows) for r in rows)
+            return arr, len(rows), local, local * world
+
+        hd, dk = c.head_dim, c.linear_head_dim
+        nh, h0 = plan["heads"], plan["head_first"]
+        nkv, kv0 = plan["kv_heads"], plan["kv_first"]
+        nl, l0 = plan["linear_heads"], plan["linear_first"]
+        nf, f0 = plan["ffn"], plan["ffn_first"]
+        key_dim = c.linear_key_heads * dk
+        self.layers = []
+        for il in range(c.layers):
+            p = f"blk.{il}."
+            layer = {"attn_norm": f32(p + "attn_norm.weight"), "post_norm": f32(p + "post_attention_norm.weight")}
+            if c.is_full_attention(il):
+                layer["in"] = stack(rows_of(p + "attn_q.weight", h0 * 2 * hd, nh * 2 * hd),
+                                    rows_of(p + "attn_k.weight", kv0 * hd, nkv * hd),
+                                    rows_of(p + "attn_v.weight", kv0 * hd, nkv * hd))
+                layer["out"] = stack(cols_of(p + "attn_output.weight", h0 * hd, nh * hd))
+                layer["q_norm"] = f32(p + "attn_q_norm.weight")
+                layer["k_norm"] = f32(p + "attn_k_norm.weight")
+                layer["keys"] = torch.zeros(self.max_positions, nkv * hd, dtype=torch.float16, device=dev)
+                layer["values"] = torch.zeros(self.max_positions, nkv * hd, dtype=torch.float16, device=dev)
+            else:
+                # [q | k | v | z] of the rank's heads, as a smaller layer of its own.
+                layer["in"] = stack(rows_of(p + "attn_qkv.weight", l0 * dk, nl * dk),
+                                    rows_of(p + "attn_qkv.weight", key_dim + l0 * dk, nl * dk),
+                                    rows_of(p + "attn_qkv.weight", 2 * key_dim + l0 * dk, nl * dk),
+                                    rows_of(p + "attn_gate.weight", l0 * dk, nl * dk))
+                layer["out"] = stack(cols_of(p + "ssm_out.weight", l0 * dk, nl * dk))
+                conv = tensors[p + "ssm_conv1d.weight"].data.cpu().numpy().view(np.float32).reshape(-1, c.conv_kernel)
+                mine = np.concatenate([conv[l0 * dk:(l0 + nl) * dk], conv[key_dim + l0 * dk:key_dim + (l0 + nl) * dk],
+                                       conv[2 * key_dim + l0 * dk:2 * key_dim + (l0 + nl) * dk]])
+                small = lambda n: tensors[p + n].data.cpu().numpy().view(np.float32)
+                layer["linear"] = ctx.deltanet_layer_create(
+                    nl, nl, dk, c.conv_kernel, c.rms_eps, np.ascontiguousarray(mine).reshape(-1),
+                    np.ascontiguousarray(small("ssm_a")[l0:l0 + nl]), np.ascontiguousarray(small("ssm_dt.bias")[l0:l0 + nl]),
+                    small("ssm_norm.weight"))
+                layer["gates"] = tuple(
+                    ctx.matrix_upload(Q.GGML_F32, np.ascontiguousarray(
+                        small(n).reshape(c.linear_value_heads, c.hidden)[l0:l0 + nl]).view(np.uint8).reshape(-1), nl, c.hidden)
+                    for n in ("ssm_alpha.weight", "ssm_beta.weight"))
+                layer["conv"] = [torch.zeros((c.conv_kernel - 1) * 3 * nl * dk, device=dev) for _ in range(2)]
+                layer["ssm"] = torch.zeros(nl * dk * dk, device=dev)
+            layer["ffn_in"] = stack(rows_of(p + "ffn_gate.weight", f0, nf), rows_of(p + "ffn_up.weight", f0, nf))
+            layer["ffn_down"] = stack(cols_of(p + "ffn_down.weight", f0, nf))
+            self.layers.append(layer)
+        head = "token_embd.weight" if c.tied_embeddings else "output.weight"
+        if c.vocab % world:
+            raise ValueError("the LM head's rows must divide over the ranks")
+        self.lm_head = stack(rows_of(head, rank * (c.vocab // world), c.vocab // world))
+        embed = tensors["token_embd.weight"]
+        self._embed_data = embed.data.to(dev)
+        self.embed = ctx.matrix_from_device(embed.ggml_type, self._embed_data.data_ptr(), embed.rows, embed.cols)
+        self.output_norm = f32("output_norm.weight")
+        z = lambda n: torch.zeros(n, device=dev)
+        self.h, self.h_next, self.normed = z(c.hidden), z(c.hidden), z(c.hidden)
+        self._residual = (self.h, self.h_next)
+        self.local_in = z(max(l["in"][2] for l in self.layers))
+        self.mixed = z(max(nh * hd, nl * dk))
+        self.ffn_rows = z(2 * nf)
+        self.act = z(nf)
+        self.local = z(self.lm_head[2])
+        self.queries = z(nh * hd)
+        self.partials = z(nkv * 32 * (nh // nkv) * (hd + 2))
+        from .backend import PeerGroup
+
+        def exchange(handle):
+            handles = [None] * world
+            if world > 1:
+                dist.all_gather_object(handles, handle)
+            else:
+                handles[0] = handle
+            return handles
+        sizes = (world * c.hidden, world * c.hidden, c.vocab)
+        self.peers = PeerGroup(ctx, rank, world, sum(n + 64 for n in sizes), exchange)
+        if world > 1:
+            ok = torch.tensor([1], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # every arena is open and zeroed before anyone stores
+        # The partial sums of the output and of the down projection, [world][hidden] each, and the logits.
+        self.part_out, self.part_down, self.logits = (self.peers.buffer(n) for n in sizes)
+        self.gathers_per_step = 2 * c.layers + 1
+
+    def _split_product(self, prod, *, x=None, swiglu=False, residual=None, delta=None, norm_weight=None,
+                       wait_slot: int = -1, store=None, slot: int = -1, local=None, advance: bool = False) -> None:
+        """One product of the head-split step. `store` (an arena vector) and `slot`: the rows go
+        to every rank's copy, this rank's at rank * rows; else they stay in `local`, and the
+        input's `wait_slot` is awaited. `delta`: the [world][hidden] partial sums to add."""
+        arr, n, *_ = prod
+        kind = _capi.PROLOGUE_RES_NORM if residual is not None else (
+            _capi.PROLOGUE_SWIGLU if swiglu else _capi.PROLOGUE_PLAIN)
+        p = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+        dst = self.h_next if residual is not None else None
+        args = _capi.FusedInput(kind, p(x), p(residual), p(delta), p(norm_weight), self.cfg.rms_eps, p(dst),
+                                p(self.normed if residual is not None else self.act),
+                                p(self.position_dev) if advance else None,
+                                self.world if delta is not None else 0, self.cfg.hidden)
+        if store is not None:
+            self._check(self.lib.gufo_cuda_matmul_gather_device(self.peers.handle, arr, n, C.byref(args),
+                                                                self.peers.offset_of(store), slot, wait_slot))
+        elif wait_slot >= 0:
+            self._check(self.lib.gufo_cuda_matmul_wait_device(self.peers.handle, arr, n, C.byref(args), wait_slot,
+                                                              C.c_void_p(local.data_ptr())))
+        else:
+            self._check(self.lib.gufo_cuda_matmul_fused_device(self.ctx.handle, arr, n, C.byref(args), 1,
+                                                               C.c_void_p(local.data_ptr())))
+        if residual is not None:
+            self.h, self.h_next = self.h_next, self.h
+
+    def enqueue_split(self, parity: int) -> None:
+        """The head-split step. Slot 1: the output projections' partial sums, slot 2: the down
+        projections', slot 3: the logits."""
+        c, plan = self.cfg, self.plan
+        lib, h = self.lib, self.ctx.handle
+        self.h, self.h_next = self._residual
+        self._check(lib.gufo_cuda_embed_device(h, self.embed, self.token_dev.data_ptr(), self.h.data_ptr()))
+        pending, pending_slot = None, -1
+        for il, l in enumerate(self.layers):
+            self._split_product(l["in"], residual=self.h, delta=pending, norm_weight=l["attn_norm"],
+                                wait_slot=pending_slot, local=self.local_in)
+            if c.is_full_attention(il):
+                args = _capi.AttentionArgs(plan["heads"], plan["kv_heads"], c.head_dim, c.rope_dim, self.max_positions,
+                                           c.rms_eps, self.position_dev.data_ptr(), self.local_in.data_ptr(),
+                                           l["q_norm"].data_ptr(), l["k_norm"].data_ptr(), self.inv_freq.data_ptr(),
+                                           l["keys"].data_ptr(), l["values"].data_ptr(), self.queries.data_ptr(),
+                                           self.partials.data_ptr(), self.mixed.data_ptr())
+                self._check(lib.gufo_cuda_attention_device(h, C.byref(args)))
+            else:
+                # The gates from the residual stream (the product's norm wrote it to self.h).
+                seq = _capi.DeltaNetStepSeq(1, self.local_in.data_ptr(), 0, self.h.data_ptr(), 0,
+                                            l["conv"][parity].data_ptr(), l["conv"][parity ^ 1].data_ptr(), None,
+                                            l["ssm"].data_ptr(), None, self.mixed.data_ptr(), 0)
+                alpha, beta = l["gates"]
+                self._check(lib.gufo_cuda_deltanet_step_device(h, l["linear"], alpha, beta,
+                                                               C.c_void_p(l["attn_norm"].data_ptr()), c.rms_eps,
+                                                               C.byref(seq), 1))
+            self._split_product(l["out"], x=self.mixed, store=self.part_out, slot=1)
+            self._split_product(l["ffn_in"], residual=self.h, delta=self.part_out, norm_weight=l["post_norm"],
+                                wait_slot=1, local=self.ffn_rows)
+            self._split_product(l["ffn_down"], x=self.ffn_rows, swiglu=True, store=self.part_down, slot=2)
+            pending, pending_slot = self.part_down, 2
+        self._split_product(self.lm_head, residual=self.h, delta=pending, norm_weight=self.output_norm,
+                            wait_slot=pending_slot, store=self.logits, slot=3, advance=True)
+        self._check(lib.gufo_cuda_peer_wait_device(self.peers.handle, 3))
 
     def _check(self, status):
         _capi.check(self.lib, self.ctx.handle, status)
@@ -305,7 +520,7 @@ class TpDecoder:
             raise RuntimeError("the attention cache is full")
         self.token_dev.fill_(token)
         parity = self.position & 1
-        enqueue = self.enqueue_fused if self.fused else self.enqueue
+        enqueue = self.enqueue_split if self.split else (self.enqueue_fused if self.fused else self.enqueue)
         if not use_graph or self.position < 2:
             enqueue(parity)
         else:
@@ -349,6 +564,10 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
+    # The line this arm prints is the only thing on stdout: NCCL's version banner (it goes to
+    # stdout at NCCL_DEBUG=VERSION) is kept out of it.
+    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
@@ -373,16 +592,21 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    # The three ways to rebuild the full vectors: every product storing its rows into the peers'
-    # arenas itself, a separate gather kernel over peer memory, NCCL's all-gather. Each decoder
+    # The ways to run the step over the ranks: heads and FFN width split (partial sums exchanged
+    # twice per layer), or rows split with the full vectors rebuilt by every product storing its
+    # rows into the peers' arenas itself, by a separate gather kernel, by NCCL. Each decoder
     # starts with the same few tokens (their logits are compared below), warms up, and is timed;
     # the line's value is the fastest, `parallelism` names it and gives the others' times.
-    how = {"fused": "every product stores its rows into the peers' copies itself (one kernel per stage, "
+    how = {"split": "heads and FFN width split over the ranks: a rank multiplies its heads' input rows, runs its "
+                    "slice of the mixer, and the column-split output and down products store partial sums into "
+                    "every rank's arena (NVLink peer stores, flags) that the next product adds to the residual: "
+                    "two exchanges per layer",
+           "fused": "every product stores its rows into the peers' copies itself (one kernel per stage, "
                     "NVLink peer stores, flags)",
            "peer": "a gather kernel of this library over NVLink peer memory after every product",
            "nccl": "NCCL's all-gather after every product"}
     parity_logits, measured, decoders = {}, {}, {}
-    for name in ("fused", "peer", "nccl"):
+    for name in ("split", "fused", "peer", "nccl"):
         ok = 1
         d = None
         try:
@@ -495,8 +719,10 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
             "data": "synthetic",
             "config": {"workload": workload, "seed": 1},
-            "notes": {"parallelism": f"tp{world}: projections row-split, {dec.gathers_per_step} gathers per step: "
-                                     f"{gathered_by}; mixers replicated{other}",
+            "notes": {"parallelism": (f"tp{world}: {gathered_by} ({dec.gathers_per_step} exchanges per step){other}"
+                                      if best == "split" else
+                                      f"tp{world}: projections row-split, {dec.gathers_per_step} gathers per step: "
+                                      f"{gathered_by}; mixers replicated{other}"),
                       "l2": "weights exceed L2; no flush needed"},
             "e2e": {"value": 1e3 / ms_e2e, "unit": unit, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
                     "ms_per_step": ms_e2e},

@@ -204,6 +204,10 @@ typedef struct gufo_cuda_fused_input {
   float* residual_out;       /* RES_NORM: H + D, [tokens][cols]; not the same buffer as residual */
   float* scratch;            /* RES_NORM, SWIGLU: [tokens][cols], the product's input rows */
   int* advance;              /* RES_NORM: an int counter incremented by `tokens` (may be NULL) */
+  int delta_parts;           /* RES_NORM: D is the sum, in order, of this many vectors starting at   */
+  int delta_stride;          /*   delta, delta_stride floats apart (0 or 1: delta alone). More than  */
+                             /*   one: partial sums of ranks that split a product over its columns;  */
+                             /*   one token, Q4_K / Q6_K parts on the tensor-core GEMV only.        */
 } gufo_cuda_fused_input;
 int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
                                   int nparts, const gufo_cuda_fused_input* input,
@@ -499,6 +503,19 @@ int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* group, const gufo_cuda_
                                    int nparts, const gufo_cuda_fused_input* input,
                                    size_t arena_offset, int slot, int wait_slot);
 int gufo_cuda_peer_wait_device(gufo_cuda_peer_group* group, int slot);
+/* The same one-token fused product with its rows kept local (device_y, this
+ * rank's memory) and the bounded wait for `wait_slot` in its prologue: the
+ * consumer of vectors that the ranks' earlier products stored into the arenas.
+ * With ranks that split the heads of a layer and the columns of its output and
+ * down projections, every rank's gufo_cuda_matmul_gather_device product stores
+ * its partial sums (all rows, its share of the columns) as rank r's run of a
+ * [world][rows] vector, and the next product adds them to the residual in rank
+ * order (gufo_cuda_fused_input.delta_parts = world, delta_stride = rows): two
+ * exchanges per layer instead of four gathers, and no rank multiplies another
+ * rank's heads. The reference has no counterpart. */
+int gufo_cuda_matmul_wait_device(gufo_cuda_peer_group* group, const gufo_cuda_rows* parts,
+                                 int nparts, const gufo_cuda_fused_input* input,
+                                 int wait_slot, float* device_y);
 
 /* ---- device-resident decode step ---------------------------------------- */
 

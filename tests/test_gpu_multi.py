@@ -16,6 +16,9 @@ from tests.golden import make_golden as G
 pytestmark = pytest.mark.gpu
 
 STEP_TOL = 2e-3
+# A dense model whose heads and FFN width divide over two ranks in whole 256-value blocks.
+SPLIT_MODEL = dict(layers=4, hidden=256, ffn=512, vocab=512, full_attention_interval=4, heads=2, kv_heads=1,
+                   head_dim=256, rope_dim=64, linear_key_heads=4, linear_value_heads=4, linear_head_dim=128)
 
 
 def rel_l2(got, want):
@@ -83,6 +86,20 @@ def _checks(rank, world, port, out):
                 if err > STEP_TOL:
                     failures.append(("fused tp logits", i, err))
             fused.peers.status()
+        # Heads and FFN width split over the ranks (partial sums added by the next product):
+        # against the one-GPU resident decoder on a model whose slices are whole blocks.
+        from gufo_npu_b200.backend import CudaDecoder
+        scfg = synth.ModelConfig(**SPLIT_MODEL)
+        stensors = synth.build_model(scfg, 31)
+        split = TpDecoder(ctx, scfg, stensors, rank=rank, world=world, max_positions=32, collective="split")
+        one = CudaDecoder(CudaProjections(ctx, scfg, stensors), stensors, max_positions=32, use_graph=False)
+        for i, tok in enumerate((5, 77, 300, 12, 501, 9, 250, 64)):
+            logits = split.step(tok, stream).cpu().numpy()
+            want = one.Step(tok)
+            err = rel_l2(logits, want)
+            if err > 1e-4 or int(np.argmax(logits)) != int(np.argmax(want)):
+                failures.append(("head-split logits", i, err))
+        split.peers.status()
         # Expert parallelism against one device with every expert.
         mcfg = synth.ModelConfig(**G.MOE)
         mtensors = synth.build_model(mcfg, G.MOE_SEED)
