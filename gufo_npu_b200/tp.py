@@ -564,10 +564,12 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
-    # The line this arm prints is the only thing on stdout: NCCL's version banner (it goes to
-    # stdout at NCCL_DEBUG=VERSION) is kept out of it.
-    if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # The line this arm prints is the only thing on stdout: whatever the libraries write there
+    # (NCCL's version banner, for one) goes to stderr, the line itself to the saved descriptor.
+    import sys
+    sys.stdout.flush()
+    line_out = os.dup(1)
+    os.dup2(2, 1)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
@@ -713,7 +715,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
     for name, fn in (("verify_batch_row_split", mgpu_bench.verify_batch_tp), ("moe_layer_expert_parallel", mgpu_bench.moe_layer_ep)):
         sections[name] = fn(ctx, rank, world, torch.device("cuda", local), max(steps // 2, 8), peak)
     if rank == 0:
-        print(json.dumps({
+        os.write(line_out, (json.dumps({
             "metric": metric, "value": 1e3 / ms_resident, "unit": unit, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms_resident, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (int8 tensor-core code dots, 24-bit fixed-point activations)",
@@ -734,7 +736,7 @@ def run_bench(args, cfg: ModelConfig, metric: str, unit: str, workload: str) -> 
             "roofline": roofline, "cpu_baseline": None,
             "verify_batch_row_split": sections["verify_batch_row_split"],
             "moe_layer_expert_parallel": sections["moe_layer_expert_parallel"],
-        }))
+        }) + "\n").encode())
     dist.barrier()
     torch.cuda.synchronize()
     # Captured graphs hold NCCL kernels: release them before the communicator goes away, and
