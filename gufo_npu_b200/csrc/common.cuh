@@ -100,6 +100,7 @@ enum FastPrologue {
 };
 
 constexpr int kFastMaxParts = 4;
+constexpr int kEpilogueSwiGlu = 1;
 constexpr int kMaxPeers = 8;
 
 // Row-split ranks (peer.cu). A product with `world` > 0 stores its rows into
@@ -165,6 +166,12 @@ struct FastGemvArgs {
   // the multiplies and leaves only the data movement.
   int variant;
   int y_group_stride;     // floats between the groups' outputs
+  // kEpilogueSwiGlu: the two parts are the gate and up rows of an FFN (equal row
+  // counts, whole tiles); every block multiplies tile t of both and stores
+  // act[t] = silu(gate[t]) * up[t] as rows/part outputs per token, y_stride
+  // apart (npu::Epilogue::kSwiGlu, src/npu/gemv.hpp:64-68). The launcher gives
+  // every tile pair a block of its own.
+  int epilogue;
   PeerOut peer_out;       // world == 0: an ordinary product
   PeerWait peer_wait;
 };
@@ -201,6 +208,7 @@ namespace gufo {
 int LaunchGemvQ4KFast(gufo_cuda_ctx* ctx, const FastGemvArgs& args);
 // Whether the image of `tokens` rows of `cols` values fits in shared memory.
 bool Q4KFastFits(int cols, int tokens);
+bool FastSwiGluPairsFit(const gufo_cuda_ctx* ctx, int type, int cols, int tokens, int pairs);
 // One Mixer::Linear step per sequence; the caller holds ctx->mu.
 // `early_state`: the states and conv windows were not written by the kernels
 // shortly before this one in the stream (several may be in flight at once), so

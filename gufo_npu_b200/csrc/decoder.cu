@@ -373,9 +373,39 @@ struct Input {
 // One stage's product for `tokens` rows with its input fused into the GEMV
 // kernels where every part allows it; otherwise the input is materialised by the
 // small kernels first. `scratch` holds the materialised / normed rows.
+// With `activate` set, `stage` is the stacked gate and up rows of an FFN and y
+// receives act = silu(gate) * up ([tokens][rows / 2]) instead of the rows
+// themselves, from the product's own epilogue (the reference's
+// Epilogue::kSwiGlu, src/npu/gemv.hpp:64-68); the caller has asked
+// SwiGluInProduct first.
 int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const Input& in, float* scratch,
-                 float* y, int tokens, const PeerOut* peer_out = nullptr, const PeerWait* peer_wait = nullptr) {
+                 float* y, int tokens, const PeerOut* peer_out = nullptr, const PeerWait* peer_wait = nullptr,
+                 bool activate = false) {
   const dim3 block(kSmallThreads);
+  if (activate) {
+    FastGemvArgs args{};
+    args.cols = stage.cols;
+    args.y = y;
+    args.y_stride = static_cast<int>(stage.total_rows / 2);
+    args.tokens = tokens;
+    args.prologue = in.prologue;
+    args.x = in.x;
+    args.h_in = in.h_in;
+    args.delta = in.delta;
+    args.delta_parts = in.delta_parts;
+    args.delta_stride = in.delta_stride;
+    args.norm_w = in.norm_w;
+    args.eps = rms_eps;
+    args.h_out = in.h_out;
+    args.normed_out = in.prologue == kPrologueResNorm ? scratch : nullptr;
+    args.advance = in.advance;
+    args.epilogue = kEpilogueSwiGlu;
+    args.row_bytes = stage.parts[0].row_bytes;
+    for (int p = 0; p < 2; ++p) {
+      args.parts[args.nparts++] = {stage.parts[p].data, stage.parts[p].rows, stage.parts[p].out_offset};
+    }
+    return stage.parts[0].type == GUFO_CUDA_Q4_K ? LaunchGemvQ4KFast(ctx, args) : LaunchGemvQ6KFast(ctx, args);
+  }
   bool fused = !ctx->force_general && stage.nparts <= kFastMaxParts;
   int fast_parts = 0;
   for (int p = 0; p < stage.nparts; ++p) {
@@ -488,8 +518,17 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
 }
 
 int FusedProduct(gufo_cuda_decoder* d, const GemvArgs& stage, const Input& in, float* scratch, float* y,
-                 int tokens) {
-  return FusedProduct(d->ctx, d->c.rms_eps, stage, in, scratch, y, tokens);
+                 int tokens, bool activate = false) {
+  return FusedProduct(d->ctx, d->c.rms_eps, stage, in, scratch, y, tokens, nullptr, nullptr, activate);
+}
+
+// Whether the gate / up product `stage` can leave silu(gate) * up by itself for
+// `tokens` rows: two parts of one tensor-core format with equal whole tiles, and
+// a resident thread block for every tile pair.
+bool SwiGluInProduct(const gufo_cuda_ctx* ctx, const GemvArgs& stage, int tokens) {
+  return !ctx->force_general && stage.nparts == 2 && stage.parts[0].rows == stage.parts[1].rows &&
+         stage.parts[0].rows % 16 == 0 && stage.parts[0].type == stage.parts[1].type &&
+         FastSwiGluPairsFit(ctx, stage.parts[0].type, stage.cols, tokens, static_cast<int>(stage.parts[0].rows / 16));
 }
 
 // Records an event that closes a stage of kind `kind` (timeline mode only).
@@ -574,12 +613,16 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) 
     norm2.delta = d->out;
     norm2.norm_w = l.post_norm;
     norm2.h_out = d->h[cur ^ 1];
-    GUFO_STEP_TRY(FusedProduct(d, l.ffn_in, norm2, d->normed, d->ffn, tokens));
+    // Where it can, the gate / up product leaves silu(gate) * up (its kernel's
+    // epilogue) and the down product starts from plain rows; else the
+    // activation is the down product's fused input.
+    const bool activate = SwiGluInProduct(ctx, l.ffn_in, tokens);
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_in, norm2, d->normed, activate ? d->act : d->ffn, tokens, activate));
     Mark(d, GUFO_CUDA_TIMELINE_FFN_IN);
     cur ^= 1;
-    Input swiglu{kPrologueSwiGlu};
-    swiglu.x = d->ffn;
-    GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, swiglu, d->act, d->out, tokens));
+    Input down_in{activate ? kProloguePlain : kPrologueSwiGlu};
+    down_in.x = activate ? d->act : d->ffn;
+    GUFO_STEP_TRY(FusedProduct(d, l.ffn_down, down_in, activate ? d->normed : d->act, d->out, tokens));
     if (c.experts > 0) {
       // Decoder::MoeFfn (decoder.cpp:535-557): d->out holds the shared
       // expert's output, d->normed the layer's normed input.

@@ -203,6 +203,8 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
       advance();
     }
   }
+  float norm_ahead[8];
+  LoadNormAhead(a, norm_ahead);
   GridLaunchDependents();
   // The weights above never depend on earlier kernels; the image and y do.
   GridDependencyWait();
@@ -219,7 +221,7 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   } else {
     FillImage<TOKENS>(a, l, smem, S::kExtra,
                       a.x + static_cast<size_t>(group / (a.x_group_div > 1 ? a.x_group_div : 1)) * a.x_group_stride,
-                      rank, ks, 8);
+                      rank, ks, 8, norm_ahead);
   }
 
   float out[kNB][4];
@@ -253,7 +255,7 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     const int row = local * 16 + o / TOKENS;
     if (row < a.parts[part].rows) {
       const size_t at = static_cast<size_t>(group) * a.y_group_stride + static_cast<size_t>(k) * a.y_stride +
-                        a.parts[part].y_offset + row;
+                        (a.epilogue == kEpilogueSwiGlu ? 0 : a.parts[part].y_offset) + row;
       if (a.peer_out.world > 0) {
         // Row-split ranks: this rank's rows go straight into every rank's copy
         // of the full vector (plain stores over NVLink for the peers).
@@ -265,12 +267,22 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
       }
     }
   };
-  // Every thread of the block (of the cluster's blocks) comes here.
+  // Every thread of the block (of the cluster's blocks) comes here. With the
+  // SwiGLU epilogue a block's tiles alternate gate, up: the gate's sum waits in
+  // a register for the up tile's.
+  float held_gate = 0.f;
   auto gather = [&](int n) {
     const int o = threadIdx.x;
     if (ks == 1) {
       if (o < kTileFloats) {
-        store(n, o, total_of(n % kExchange, o));
+        const float total = total_of(n % kExchange, o);
+        if (a.epilogue != kEpilogueSwiGlu) {
+          store(n, o, total);
+        } else if ((n & 1) == 0) {
+          held_gate = total;
+        } else {
+          store(n, o, SiluFast(held_gate) * total);
+        }
       }
       return;
     }
@@ -430,17 +442,43 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   }
 }
 
+// Lets the kernel use all the shared memory a block may have (once per device).
+template <int TYPE, int TOKENS, int PER_SM>
+int Configure(const gufo_cuda_ctx* ctx) {
+  static bool configured[16] = {};
+  if (!configured[ctx->device & 15]) {
+    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemvMma<TYPE, TOKENS, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kFastMaxShared));
+    configured[ctx->device & 15] = true;
+  }
+  return GUFO_CUDA_OK;
+}
+
+// One token needs few enough registers for three resident blocks per SM.
+template <int TOKENS>
+constexpr int PerSm() { return TOKENS == 1 ? 3 : 2; }
+
+// Whether `pairs` (gate tile, up tile) pairs each get a resident block.
+template <int TYPE, int TOKENS>
+bool PairsFit(const gufo_cuda_ctx* ctx, int cols, int pairs) {
+  const size_t smem = SharedBytes<TYPE, TOKENS>(cols);
+  if (smem > static_cast<size_t>(kFastMaxShared) || Configure<TYPE, TOKENS, PerSm<TOKENS>()>(ctx) != GUFO_CUDA_OK) {
+    return false;
+  }
+  return pairs <= ResidentBlocks(GemvMma<TYPE, TOKENS, PerSm<TOKENS>()>, ctx->device, kFastThreads, smem, 1);
+}
+
 template <int TYPE, int TOKENS, int PER_SM>
 int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   const size_t smem = SharedBytes<TYPE, TOKENS>(args.cols);
   if (smem > static_cast<size_t>(kFastMaxShared)) {
     return GUFO_CUDA_TOO_LARGE;
   }
-  static bool configured[16] = {};
-  if (!configured[ctx->device & 15]) {
-    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemvMma<TYPE, TOKENS, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kFastMaxShared));
-    configured[ctx->device & 15] = true;
+  {
+    const int rc = Configure<TYPE, TOKENS, PER_SM>(ctx);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
   }
   int row_tiles = 0;
   for (int p = 0; p < args.nparts; ++p) {
@@ -459,6 +497,17 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
     }
     launch.ksplit = 1;
     grid = row_tiles * args.groups;   // one block per tile
+  } else if (args.epilogue == kEpilogueSwiGlu) {
+    // One block per (gate tile, up tile) pair: block t takes tiles t and t + grid.
+    if (args.nparts != 2 || args.parts[0].rows != args.parts[1].rows || args.parts[0].rows % 16 != 0 ||
+        args.peer_out.world > 0) {
+      return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: the SwiGLU epilogue takes two parts of equal whole tiles");
+    }
+    launch.ksplit = 1;
+    grid = row_tiles / 2;
+    if (grid > ResidentBlocks(GemvMma<TYPE, TOKENS, PER_SM>, ctx->device, kFastThreads, smem, 1)) {
+      return GUFO_CUDA_TOO_LARGE;   // more tile pairs than resident blocks: the caller activates by itself
+    }
   } else {
     // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
     PlanFastGrid(GemvMma<TYPE, TOKENS, PER_SM>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit,
@@ -472,8 +521,7 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
 
 template <int TYPE, int TOKENS>
 int Launch(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
-  // One token needs few enough registers for three resident blocks per SM.
-  return LaunchVariant<TYPE, TOKENS, (TOKENS == 1 ? 3 : 2)>(ctx, args);
+  return LaunchVariant<TYPE, TOKENS, PerSm<TOKENS>()>(ctx, args);
 }
 
 template <int TYPE>
@@ -506,7 +554,29 @@ int LaunchTokens(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
   }
 }
 
+template <int TYPE>
+bool PairsFitTokens(const gufo_cuda_ctx* ctx, int cols, int tokens, int pairs) {
+  switch (tokens) {
+    case 1: return PairsFit<TYPE, 1>(ctx, cols, pairs);
+    case 2: return PairsFit<TYPE, 2>(ctx, cols, pairs);
+    case 3: return PairsFit<TYPE, 3>(ctx, cols, pairs);
+    case 4: return PairsFit<TYPE, 4>(ctx, cols, pairs);
+    case 5: return PairsFit<TYPE, 5>(ctx, cols, pairs);
+    case 6: return PairsFit<TYPE, 6>(ctx, cols, pairs);
+    case 7: return PairsFit<TYPE, 7>(ctx, cols, pairs);
+    case 8: return PairsFit<TYPE, 8>(ctx, cols, pairs);
+    default: return false;
+  }
+}
+
 }  // namespace
+
+// Whether a launch with the SwiGLU epilogue can give each of `pairs` tile pairs
+// (rows of one part / 16) a resident thread block.
+bool FastSwiGluPairsFit(const gufo_cuda_ctx* ctx, int type, int cols, int tokens, int pairs) {
+  return type == GUFO_CUDA_Q4_K ? PairsFitTokens<GUFO_CUDA_Q4_K>(ctx, cols, tokens, pairs)
+                                : type == GUFO_CUDA_Q6_K && PairsFitTokens<GUFO_CUDA_Q6_K>(ctx, cols, tokens, pairs);
+}
 
 // Whether `tokens` rows of `cols` values fit the shared-memory image.
 bool Q4KFastFits(int cols, int tokens) { return Fits<GUFO_CUDA_Q4_K>(cols, tokens); }

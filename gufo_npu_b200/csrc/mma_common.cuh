@@ -220,10 +220,29 @@ __device__ __forceinline__ float SiluFast(float x) { return x * (1.0f / (1.0f + 
 // `ks`, slabs of `slab_blocks` blocks dealt round-robin) converts only the
 // blocks of its own slabs; the others are never read. Ends with a
 // __syncthreads. kFastThreads threads.
+// The norm weights of the calling warp's first block (values 8 * lane .. + 7 of
+// block `warp`), for FillImage: they never depend on an earlier kernel, so a
+// kernel asks for them before it waits for its predecessor (a layer's norm
+// vector is read once per step: the load goes all the way to HBM, about as long
+// as the whole conversion takes).
+__device__ __forceinline__ void LoadNormAhead(const FastGemvArgs& a, float (&w)[8]) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    w[i] = 0.f;
+  }
+  if (a.prologue == kPrologueResNorm && warp < a.cols / kSuperBlock) {
+    const float4 v0 = *reinterpret_cast<const float4*>(a.norm_w + warp * kSuperBlock + lane * 8);
+    const float4 v1 = *reinterpret_cast<const float4*>(a.norm_w + warp * kSuperBlock + lane * 8 + 4);
+    w[0] = v0.x, w[1] = v0.y, w[2] = v0.z, w[3] = v0.w;
+    w[4] = v1.x, w[5] = v1.y, w[6] = v1.z, w[7] = v1.w;
+  }
+}
+
 template <int TOKENS>
 __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayout& l,
                                           uint8_t* image, float extra, const float* x,
-                                          int rank, int ks, int slab_blocks) {
+                                          int rank, int ks, int slab_blocks, const float (&keep_w)[8]) {
   __shared__ float reduce[kFastWarps];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -253,13 +272,8 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     // pending add (src/models/qwen35/decoder.cpp:493,504-508). The first pass
     // sums the squares; the second reads the same values again (they sit in
     // L2, and the warp's first block is still in registers).
-    // The norm weights of the warp's first block never depend on an earlier
-    // kernel: their load rides with the first pass instead of following the
-    // barrier.
-    float keep_w[8] = {};
-    if (warp < blocks) {
-      load8(a.norm_w + warp * kSuperBlock + lane * 8, keep_w);
-    }
+    // keep_w: the norm weights of the warp's first block, requested by the
+    // caller ahead of its dependency wait (LoadNormAhead).
 #pragma unroll 1
     for (int tok = 0; tok < TOKENS; ++tok) {
       const size_t row = static_cast<size_t>(tok) * n;
@@ -342,25 +356,61 @@ __device__ __forceinline__ void FillImage(const FastGemvArgs& a, const ImageLayo
     }
   } else {
     const size_t stride = a.prologue == kPrologueSwiGlu ? 2 * static_cast<size_t>(n) : static_cast<size_t>(n);
-#pragma unroll 1
-    for (int tok = 0; tok < TOKENS; ++tok) {
-      const float* xt = x + tok * stride;
-      for (int b = warp; b < blocks; b += kFastWarps) {
-        if (!mine(b)) {
-          continue;
-        }
-        const int at = b * kSuperBlock + lane * 8;
-        float v[8];
-        load8(xt + at, v);
-        if (a.prologue == kPrologueSwiGlu) {
-          float up[8];
-          load8(xt + n + at, up);
+    const bool act = a.prologue == kPrologueSwiGlu;
+    if constexpr (TOKENS == 1) {
+      // A warp's blocks in batches of kBatch: all loads of a batch are in flight
+      // before the first value is used (one round trip per batch, not per
+      // block; a 6144-value input is three blocks per warp).
+      constexpr int kBatch = 3;
+      for (int b0 = warp; b0 < blocks; b0 += kBatch * kFastWarps) {
+        float v[kBatch][8], up[kBatch][8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            v[i] = SiluFast(v[i]) * up[i];
+        for (int j = 0; j < kBatch; ++j) {
+          const int b = b0 + j * kFastWarps;
+          if (b < blocks && mine(b)) {
+            const int at = b * kSuperBlock + lane * 8;
+            load8(x + at, v[j]);
+            if (act) {
+              load8(x + n + at, up[j]);
+            }
           }
         }
-        StageBlock(v, lane, tok, b, l, image, extra);
+#pragma unroll
+        for (int j = 0; j < kBatch; ++j) {
+          const int b = b0 + j * kFastWarps;
+          if (b < blocks && mine(b)) {
+            if (act) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                v[j][i] = SiluFast(v[j][i]) * up[j][i];
+              }
+            }
+            StageBlock(v[j], lane, 0, b, l, image, extra);
+          }
+        }
+      }
+    } else {
+      // More tokens hold more registers elsewhere in the kernel: block by block.
+#pragma unroll 1
+      for (int tok = 0; tok < TOKENS; ++tok) {
+        const float* xt = x + tok * stride;
+        for (int b = warp; b < blocks; b += kFastWarps) {
+          if (!mine(b)) {
+            continue;
+          }
+          const int at = b * kSuperBlock + lane * 8;
+          float v[8];
+          load8(xt + at, v);
+          if (act) {
+            float up[8];
+            load8(xt + n + at, up);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              v[i] = SiluFast(v[i]) * up[i];
+            }
+          }
+          StageBlock(v, lane, tok, b, l, image, extra);
+        }
       }
     }
   }
