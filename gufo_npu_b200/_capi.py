@@ -13,6 +13,7 @@ LIB_PATH = os.path.join(HERE, "libgufo_cuda.so")
 
 OK = 0
 STATUS_TIMEOUT = 6
+STATUS_UNSUPPORTED_TYPE = 3
 STATUS_NAMES = {1: "bad argument", 2: "shape", 3: "unsupported type", 4: "CUDA runtime",
                 5: "out of memory", 6: "timeout", 7: "too large"}
 
@@ -64,10 +65,12 @@ class FusedInput(C.Structure):
     """gufo_cuda_fused_input."""
     _fields_ = [("prologue", C.c_int), ("x", C.c_void_p), ("residual", C.c_void_p), ("delta", C.c_void_p),
                 ("norm_weight", C.c_void_p), ("rms_eps", C.c_float), ("residual_out", C.c_void_p),
-                ("scratch", C.c_void_p), ("advance", C.c_void_p), ("delta_parts", C.c_int), ("delta_stride", C.c_int)]
+                ("scratch", C.c_void_p), ("advance", C.c_void_p), ("delta_parts", C.c_int), ("delta_stride", C.c_int),
+                ("epilogue", C.c_int)]
 
 
 PROLOGUE_PLAIN, PROLOGUE_RES_NORM, PROLOGUE_SWIGLU = 0, 1, 2
+EPILOGUE_NONE, EPILOGUE_SWIGLU = 0, 1
 IPC_HANDLE_BYTES = 64
 PEER_HEADER_BYTES = 4096
 

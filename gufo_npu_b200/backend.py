@@ -196,15 +196,19 @@ class Context:
 
     def matmul_fused_device(self, parts_arr, nparts: int, tokens: int, y, *, x=None, residual=None, delta=None,
                             norm_weight=None, rms_eps: float = 0.0, residual_out=None, scratch=None,
-                            advance=None, swiglu: bool = False) -> None:
+                            advance=None, swiglu: bool = False, delta_parts: int = 0, delta_stride: int = 0,
+                            activate: bool = False) -> None:
         """A product with its input step fused in (npu::Q4nxGemv's Prologue options,
-        src/npu/gemv.hpp:58-68): plain `x`; `residual` (+ `delta`) through RMSNorm; or SwiGLU of
-        [gate | up] rows in `x`."""
+        src/npu/gemv.hpp:58-68): plain `x`; `residual` (+ `delta`, or the sum of `delta_parts`
+        vectors `delta_stride` floats apart) through RMSNorm; or SwiGLU of [gate | up] rows in
+        `x`. `activate`: the parts are gate and up rows and y receives silu(gate) * up
+        (Epilogue::kSwiGlu); raises GufoCudaError (unsupported type) where the kernel cannot."""
         kind = _capi.PROLOGUE_RES_NORM if residual is not None else (
             _capi.PROLOGUE_SWIGLU if swiglu else _capi.PROLOGUE_PLAIN)
         p = lambda t: C.c_void_p(_ptr(t)) if t is not None else None
         args = _capi.FusedInput(kind, p(x), p(residual), p(delta), p(norm_weight), rms_eps, p(residual_out),
-                                p(scratch), p(advance))
+                                p(scratch), p(advance), delta_parts, delta_stride,
+                                _capi.EPILOGUE_SWIGLU if activate else _capi.EPILOGUE_NONE)
         self._check(self.lib.gufo_cuda_matmul_fused_device(self.handle, parts_arr, nparts, C.byref(args), tokens,
                                                            C.c_void_p(_ptr(y))))
 

@@ -400,6 +400,9 @@ int FusedProduct(gufo_cuda_ctx* ctx, float rms_eps, const GemvArgs& stage, const
     args.normed_out = in.prologue == kPrologueResNorm ? scratch : nullptr;
     args.advance = in.advance;
     args.epilogue = kEpilogueSwiGlu;
+    if (peer_wait != nullptr) {
+      args.peer_wait = *peer_wait;
+    }
     args.row_bytes = stage.parts[0].row_bytes;
     for (int p = 0; p < 2; ++p) {
       args.parts[args.nparts++] = {stage.parts[p].data, stage.parts[p].rows, stage.parts[p].out_offset};
@@ -1058,7 +1061,16 @@ int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* part
   if (stage.cols % 4 != 0) {
     return Fail(GUFO_CUDA_SHAPE, "matmul_fused: cols must be a multiple of 4");
   }
-  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, y, tokens);
+  bool activate = false;
+  if (in->epilogue == GUFO_CUDA_EPILOGUE_SWIGLU) {
+    if (!gufo::SwiGluInProduct(ctx, stage, tokens)) {
+      return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "matmul_fused: this product cannot activate its own rows");
+    }
+    activate = true;
+  } else if (in->epilogue != GUFO_CUDA_EPILOGUE_NONE) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_fused: unknown epilogue");
+  }
+  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, y, tokens, nullptr, nullptr, activate);
 }
 
 // The fused input of the peer-group products, checked.
@@ -1121,6 +1133,9 @@ int gufo_cuda_matmul_gather_device(gufo_cuda_peer_group* g, const gufo_cuda_rows
   if (slot < 0 || slot >= gufo::kPeerSlots || wait_slot >= gufo::kPeerSlots) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: slots are 0 to 7 (wait_slot < 0: no wait)");
   }
+  if (in->epilogue != GUFO_CUDA_EPILOGUE_NONE) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_gather: rows that travel to the peers are stored as they are");
+  }
   gufo::Input input{gufo::kProloguePlain};
   int rc = PeerProductInput(in, "matmul_gather", &input);
   if (rc != GUFO_CUDA_OK) {
@@ -1179,8 +1194,17 @@ int gufo_cuda_matmul_wait_device(gufo_cuda_peer_group* g, const gufo_cuda_rows* 
   if (stage.cols % 4 != 0) {
     return Fail(GUFO_CUDA_SHAPE, "matmul_wait: cols must be a multiple of 4");
   }
+  bool activate = false;
+  if (in->epilogue == GUFO_CUDA_EPILOGUE_SWIGLU) {
+    if (!gufo::SwiGluInProduct(ctx, stage, 1)) {
+      return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "matmul_wait: this product cannot activate its own rows");
+    }
+    activate = true;
+  } else if (in->epilogue != GUFO_CUDA_EPILOGUE_NONE) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "matmul_wait: unknown epilogue");
+  }
   const gufo::PeerWait wait = WaitOn(g, wait_slot);
-  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, device_y, 1, nullptr, &wait);
+  return gufo::FusedProduct(ctx, in->rms_eps, stage, input, in->scratch, device_y, 1, nullptr, &wait, activate);
 }
 
 int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config* config,

@@ -309,7 +309,7 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const bool gate_rows = g.alpha_w != nullptr;
   const float4* wa = reinterpret_cast<const float4*>(g.alpha_w + static_cast<size_t>(head) * g.cols);
   const float4* wb = reinterpret_cast<const float4*>(g.beta_w + static_cast<size_t>(head) * g.cols);
-  float4 wa_ahead[kGateAhead], wb_ahead[kGateAhead];
+  float4 wa_ahead[kGateAhead], wb_ahead[kGateAhead], nw_ahead[kGateAhead];
   GridLaunchDependents();
   if (args.early_state) {
     LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
@@ -327,6 +327,9 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
       if (i < g.cols / 4) {
         wa_ahead[j] = wa[i];
         wb_ahead[j] = wb[i];
+        if (g.norm_w != nullptr) {
+          nw_ahead[j] = reinterpret_cast<const float4*>(g.norm_w)[i];
+        }
       }
     }
   }
@@ -353,34 +356,46 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     // (DeltaNetStep::Run, src/models/qwen35_2b/deltanet.cpp:358-392).
     const float* gx = args.gate_x[blockIdx.y] != nullptr ? args.gate_x[blockIdx.y] : g.x;
     const float4* xa = reinterpret_cast<const float4*>(gx);
+    // The input's first passes stay in registers between the norm's sum of
+    // squares and the dot products (one round trip to L2 for them, not two).
+    float4 x_ahead[kGateAhead];
+#pragma unroll
+    for (int j = 0; j < kGateAhead; ++j) {
+      const int i = tid + j * dk;
+      x_ahead[j] = i < g.cols / 4 ? xa[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float inv = 1.0f;
     if (g.norm_w != nullptr) {
       float sq = 0.f;
-      for (int i = tid; i < g.cols / 4; i += dk) {
+#pragma unroll
+      for (int j = 0; j < kGateAhead; ++j) {
+        const float4 xv = x_ahead[j];
+        sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+      }
+      for (int i = tid + kGateAhead * dk; i < g.cols / 4; i += dk) {
         const float4 xv = xa[i];
         sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
       }
       inv = 1.0f / sqrtf(BlockSum(sq, sh, warps) / static_cast<float>(g.cols) + g.eps);
     }
     float pa = 0.f, pb = 0.f;
-    auto pass = [&](int i, const float4& av, const float4& bv) {
-      float4 xv = xa[i];
+    auto pass = [&](float4 xv, const float4& nw, const float4& av, const float4& bv) {
       if (g.norm_w != nullptr) {
-        const float4 nw = reinterpret_cast<const float4*>(g.norm_w)[i];
         xv = make_float4(xv.x * inv * nw.x, xv.y * inv * nw.y, xv.z * inv * nw.z, xv.w * inv * nw.w);
       }
       pa += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
       pb += bv.x * xv.x + bv.y * xv.y + bv.z * xv.z + bv.w * xv.w;
     };
+    const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f);
 #pragma unroll
     for (int j = 0; j < kGateAhead; ++j) {
       const int i = tid + j * dk;
       if (i < g.cols / 4) {
-        pass(i, wa_ahead[j], wb_ahead[j]);
+        pass(x_ahead[j], g.norm_w != nullptr ? nw_ahead[j] : one4, wa_ahead[j], wb_ahead[j]);
       }
     }
     for (int i = tid + kGateAhead * dk; i < g.cols / 4; i += dk) {
-      pass(i, wa[i], wb[i]);
+      pass(xa[i], g.norm_w != nullptr ? reinterpret_cast<const float4*>(g.norm_w)[i] : one4, wa[i], wb[i]);
     }
     BlockSum2(pa, pb, sh, warps);
     alpha = pa;

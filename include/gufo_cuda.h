@@ -208,7 +208,15 @@ typedef struct gufo_cuda_fused_input {
   int delta_stride;          /*   delta, delta_stride floats apart (0 or 1: delta alone). More than  */
                              /*   one: partial sums of ranks that split a product over its columns;  */
                              /*   one token, Q4_K / Q6_K parts on the tensor-core GEMV only.        */
+  int epilogue;              /* GUFO_CUDA_EPILOGUE_SWIGLU: the parts are an FFN's gate and up rows    */
+                             /*   (two parts, equal whole 16-row tiles, one of Q4_K / Q6_K) and y    */
+                             /*   receives silu(gate) * up, [tokens][rows / 2], from the product's   */
+                             /*   own kernel (npu::Epilogue::kSwiGlu, src/npu/gemv.hpp:64-68). Where  */
+                             /*   the kernel cannot (more tile pairs than resident thread blocks,    */
+                             /*   other formats) the call returns GUFO_CUDA_UNSUPPORTED_TYPE and      */
+                             /*   enqueues nothing: ask for plain rows and a SWIGLU input instead.   */
 } gufo_cuda_fused_input;
+enum { GUFO_CUDA_EPILOGUE_NONE = 0, GUFO_CUDA_EPILOGUE_SWIGLU = 1 };
 int gufo_cuda_matmul_fused_device(gufo_cuda_ctx* ctx, const gufo_cuda_rows* parts,
                                   int nparts, const gufo_cuda_fused_input* input,
                                   int tokens, float* device_y);

@@ -156,6 +156,58 @@ def test_activation_extremes(ctx, oracle):
         ctx.matrix_free(m)
 
 
+@pytest.mark.parametrize("ggml_type", [Q.GGML_Q4_K, Q.GGML_Q6_K])
+@pytest.mark.parametrize("tokens,cols,rows", [(1, 768, 96), (2, 768, 96), (1, 2048, 3072), (1, 512, 16)])
+def test_gate_up_product_activates_its_own_rows(request, ctx, oracle, ggml_type, tokens, cols, rows):
+    """gufo_cuda_fused_input.epilogue = SWIGLU (the reference's npu::Epilogue::kSwiGlu,
+    src/npu/gemv.hpp:64-68): the stacked gate and up rows multiplied by one launch that stores
+    silu(gate) * up, against the activation of the oracle's rows; with a fused residual + norm
+    input whose pending add is the sum of three vectors (delta_parts)."""
+    dev = torch.device("cuda:0")
+    eps = 1e-6
+    gate = Q.quantize(ggml_type, torch.from_numpy(G.normal(170, rows, cols) * 0.05)).numpy()
+    up_w = Q.quantize(ggml_type, torch.from_numpy(G.normal(171, rows, cols) * 0.05)).numpy()
+    mg, mu = ctx.matrix_upload(ggml_type, gate, rows, cols), ctx.matrix_upload(ggml_type, up_w, rows, cols)
+    parts = Context._parts([(mg, 0, rows), (mu, 0, rows)])
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
+    x = G.normal(172, tokens, cols)
+    want_rows = oracle.matmul([(gate, ggml_type, 0, rows), (up_w, ggml_type, 0, rows)], cols, x)
+    g, u = want_rows[:, :rows].astype(np.float64), want_rows[:, rows:].astype(np.float64)
+    want = g / (1.0 + np.exp(-g)) * u
+    act = torch.empty(tokens, rows, device=dev)
+    from gufo_npu_b200._capi import GufoCudaError
+    if "general" in request.node.name:
+        # The general kernel has no such epilogue: refused, nothing enqueued.
+        with pytest.raises(GufoCudaError):
+            ctx.matmul_fused_device(parts, 2, tokens, act, x=t(x), activate=True)
+        ctx.matrix_free(mg)
+        ctx.matrix_free(mu)
+        return
+    ctx.matmul_fused_device(parts, 2, tokens, act, x=t(x), activate=True)
+    ctx.synchronize()
+    assert rel_l2(act.cpu().numpy(), want) <= 1e-5
+    if tokens == 1:
+        # Residual plus three partial vectors through the norm, then the activating product.
+        h, w = G.normal(173, 1, cols), G.normal(174, cols) * 0.2 + 1.0
+        partials = G.normal(175, 3, cols) * 0.3
+        total = (h[0] + partials[0] + partials[1] + partials[2]).astype(np.float32)
+        normed = (total / np.sqrt((total.astype(np.float64) ** 2).mean() + eps) * w).astype(np.float32)
+        h_out, scratch = torch.empty(1, cols, device=dev), torch.empty(1, cols, device=dev)
+        ctx.matmul_fused_device(parts, 2, 1, act, residual=t(h), delta=t(partials), delta_parts=3, delta_stride=cols,
+                                norm_weight=t(w), rms_eps=eps, residual_out=h_out, scratch=scratch, activate=True)
+        ctx.synchronize()
+        assert np.array_equal(h_out.cpu().numpy()[0], ((h[0] + partials[0]) + partials[1]) + partials[2])
+        rows2 = oracle.matmul([(gate, ggml_type, 0, rows), (up_w, ggml_type, 0, rows)], cols, normed[None, :])
+        g, u = rows2[:, :rows].astype(np.float64), rows2[:, rows:].astype(np.float64)
+        assert rel_l2(act.cpu().numpy()[:1], g / (1.0 + np.exp(-g)) * u) <= 1e-5
+    # Parts that are not whole tiles are refused and nothing runs.
+    odd = Context._parts([(mg, 0, rows - 8), (mu, 0, rows - 8)])
+    with pytest.raises(GufoCudaError):
+        ctx.matmul_fused_device(odd, 2, tokens, act, x=t(x), activate=True)
+    ctx.matrix_free(mg)
+    ctx.matrix_free(mu)
+
+
 @pytest.mark.parametrize("tokens", [1, 2, 3, 4, 7, 8, 9, 19])
 def test_small_m_tokens_do_not_change_rows(ctx, oracle, tokens):
     """Results do not depend on how many tokens come together
