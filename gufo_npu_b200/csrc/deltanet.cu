@@ -65,7 +65,7 @@ struct DeltaShared {
   float v[kMaxHeadDim];
   float y[kMaxHeadDim];
   float gate[2];                              // decay, beta
-  float scratch[2 * (kDeltaThreads / 32)];
+  float scratch[2 * (2 * kDeltaThreads / 32)];
 };
 
 struct StateTile {
@@ -155,6 +155,95 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
   }
 }
 
+// The same for a warp that owns 16 columns (the decode step's kernel, whose
+// blocks have twice as many warps): a lane holds rows rg, rg + 8, ... (rg =
+// lane / 4) of four adjacent columns (4 * (lane % 4)).
+constexpr int kNarrowCols = 16;
+constexpr int kNarrowRowGroups = 8;
+constexpr int kNarrowRowsPerLane = kMaxHeadDim / kNarrowRowGroups;   // 16
+
+struct NarrowTile {
+  float4 s[kNarrowRowsPerLane];
+};
+
+__device__ __forceinline__ void LoadNarrowTile(NarrowTile& tile, const float* __restrict__ src, int dk,
+                                               int tile_index) {
+  const int lane = threadIdx.x & 31;
+  const int col = tile_index * kNarrowCols + 4 * (lane & 3);
+  const int ig = lane >> 2;
+  const int rows = dk / kNarrowRowGroups;
+#pragma unroll
+  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
+    if (r < rows) {
+      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kNarrowRowGroups + ig) * dk + col);
+    }
+  }
+}
+
+__device__ __forceinline__ float4 NarrowColumnSum(float4 v) {
+#pragma unroll
+  for (int o = 4; o <= 16; o <<= 1) {
+    v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, o);
+    v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, o);
+    v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, o);
+    v.w += __shfl_xor_sync(0xFFFFFFFFu, v.w, o);
+  }
+  return v;
+}
+
+// DeltaTile's arithmetic on a 16-column tile.
+__device__ __forceinline__ void NarrowDeltaTile(NarrowTile& tile, float* __restrict__ dst, int dk,
+                                                int tile_index, DeltaShared& sh) {
+  const int lane = threadIdx.x & 31;
+  const int col = tile_index * kNarrowCols + 4 * (lane & 3);
+  const int ig = lane >> 2;
+  const int rows = dk / kNarrowRowGroups;
+  const float decay = sh.gate[0];
+  const float beta = sh.gate[1];
+  float4 (&s)[kNarrowRowsPerLane] = tile.s;
+  float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
+    if (r < rows) {
+      const float ki = sh.k[r * kNarrowRowGroups + ig] * decay;
+      u.x = fmaf(s[r].x, ki, u.x);
+      u.y = fmaf(s[r].y, ki, u.y);
+      u.z = fmaf(s[r].z, ki, u.z);
+      u.w = fmaf(s[r].w, ki, u.w);
+    }
+  }
+  u = NarrowColumnSum(u);
+  const float4 v = *reinterpret_cast<const float4*>(&sh.v[col]);
+  float4 delta;
+  delta.x = beta * (v.x - u.x);
+  delta.y = beta * (v.y - u.y);
+  delta.z = beta * (v.z - u.z);
+  delta.w = beta * (v.w - u.w);
+  float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
+    if (r < rows) {
+      const int i = r * kNarrowRowGroups + ig;
+      const float ki = sh.k[i];
+      const float qi = sh.q[i];
+      float4 n;
+      n.x = fmaf(s[r].x, decay, ki * delta.x);
+      n.y = fmaf(s[r].y, decay, ki * delta.y);
+      n.z = fmaf(s[r].z, decay, ki * delta.z);
+      n.w = fmaf(s[r].w, decay, ki * delta.w);
+      *reinterpret_cast<float4*>(dst + static_cast<size_t>(i) * dk + col) = n;
+      y.x = fmaf(n.x, qi, y.x);
+      y.y = fmaf(n.y, qi, y.y);
+      y.z = fmaf(n.z, qi, y.z);
+      y.w = fmaf(n.w, qi, y.w);
+    }
+  }
+  y = NarrowColumnSum(y);
+  if (ig == 0) {
+    *reinterpret_cast<float4*>(&sh.y[col]) = y;
+  }
+}
+
 // Gates given: one warp per thread block, grid = (dk / 32, value_heads,
 // sequences). The tiles of a head need nothing from one another here, and
 // several small blocks per SM let one tile's stores overlap another's loads.
@@ -233,8 +322,12 @@ __device__ __forceinline__ void BlockSum2(float& a, float& b, DeltaShared& sh, i
 }
 
 // Mixer::Linear for one (sequence, value head). grid = (value_heads,
-// sequences), dk threads: thread t owns channel / column t of the head.
-__global__ void __launch_bounds__(kDeltaThreads)
+// sequences), 2 * dk threads: thread t < dk owns channel t of the head's q and k
+// and output t of the epilogue, thread dk + t channel t of v; warp w owns columns
+// 16 w .. 16 w + 15 of the state. (With dk threads and 32 columns per warp the
+// kernel spent 6.5 us per layer of the decode step on four warps' worth of
+// dependent instructions.)
+__global__ void __launch_bounds__(2 * kDeltaThreads)
 DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   __shared__ __align__(16) DeltaShared sh;
   const gufo_cuda_linear_seq& seq = args.seq[blockIdx.y];
@@ -242,7 +335,8 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const int hk = args.key_heads;
   const int hv = args.value_heads;
   const int dk = args.head_dim;
-  const int warps = dk / 32;
+  const int threads = 2 * dk;
+  const int warps = threads / 32;
   const int key_dim = hk * dk;
   const int value_dim = hv * dk;
   const int channels = 2 * key_dim + value_dim;
@@ -250,11 +344,13 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const int window = kernel - 1;
   const int kh = head % hk;
   const int tid = threadIdx.x;
+  const bool lower = tid < dk;        // q and k channels, the epilogue
+  const int ch = lower ? tid : tid - dk;
   const float* x = seq.in;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
-  StateTile state_tile;
-  // Causal depthwise conv + SiLU of channel ch; also advances that channel's
-  // window when this block is the one that owns it. All loads of the three
+  NarrowTile state_tile;
+  // Causal depthwise conv + SiLU of a channel; also advances that channel's
+  // window when this block is the one that owns it. All loads of a thread's
   // channels are issued before the first store, so they overlap.
   constexpr int kMaxWindow = 7;
   struct Taps {
@@ -263,8 +359,8 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     float w[kMaxWindow + 1];
   };
   // The layer's weights never depend on the kernels before this one.
-  auto fetch_weights = [&](int ch, Taps& taps) {
-    const float* kw = args.conv + static_cast<size_t>(ch) * kernel;
+  auto fetch_weights = [&](int c, Taps& taps) {
+    const float* kw = args.conv + static_cast<size_t>(c) * kernel;
 #pragma unroll
     for (int t = 0; t < kMaxWindow; ++t) {
       if (t < window) {
@@ -275,36 +371,38 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   };
   // The window is state: written a step ago (early_state) or by the launch
   // just before this one.
-  auto fetch_window = [&](int ch, Taps& taps) {
+  auto fetch_window = [&](int c, Taps& taps) {
 #pragma unroll
     for (int t = 0; t < kMaxWindow; ++t) {
       if (t < window) {
-        taps.old[t] = seq.conv_in[static_cast<size_t>(t) * channels + ch];
+        taps.old[t] = seq.conv_in[static_cast<size_t>(t) * channels + c];
       }
     }
   };
-  auto conv = [&](int ch, const Taps& taps, bool owner) -> float {
+  auto conv = [&](int c, const Taps& taps, bool owner) -> float {
     float acc = taps.w[kMaxWindow] * taps.cur;
 #pragma unroll
     for (int t = 0; t < kMaxWindow; ++t) {
       if (t < window) {
         acc = fmaf(taps.w[t], taps.old[t], acc);
         if (owner && t > 0) {
-          seq.conv_out[static_cast<size_t>(t - 1) * channels + ch] = taps.old[t];
+          seq.conv_out[static_cast<size_t>(t - 1) * channels + c] = taps.old[t];
         }
       }
     }
     if (owner) {
-      seq.conv_out[static_cast<size_t>(window - 1) * channels + ch] = taps.cur;
+      seq.conv_out[static_cast<size_t>(window - 1) * channels + c] = taps.cur;
     }
     return Silu(acc);
   };
   // The window of the key head's q and k channels is advanced by the first
   // value head that reads the key head; every head advances its own v.
-  const int ch_q = kh * dk + tid, ch_k = key_dim + kh * dk + tid, ch_v = 2 * key_dim + head * dk + tid;
-  Taps tq, tk, tv;
+  // A lower thread convolves q (ta) and k (tb) of its channel, an upper one v (ta).
+  const int ch_a = lower ? kh * dk + ch : 2 * key_dim + head * dk + ch;
+  const int ch_b = key_dim + kh * dk + ch;
+  Taps ta, tb;
   // The first passes of the head's alpha and beta rows (weights as well).
-  constexpr int kGateAhead = 4;
+  constexpr int kGateAhead = 2;
   const DeltaNetGateRows& g = args.gate_rows;
   const bool gate_rows = g.alpha_w != nullptr;
   const float4* wa = reinterpret_cast<const float4*>(g.alpha_w + static_cast<size_t>(head) * g.cols);
@@ -312,18 +410,20 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   float4 wa_ahead[kGateAhead], wb_ahead[kGateAhead], nw_ahead[kGateAhead];
   GridLaunchDependents();
   if (args.early_state) {
-    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
-    fetch_window(ch_q, tq);
-    fetch_window(ch_k, tk);
-    fetch_window(ch_v, tv);
+    LoadNarrowTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+    fetch_window(ch_a, ta);
+    if (lower) {
+      fetch_window(ch_b, tb);
+    }
   }
-  fetch_weights(ch_q, tq);
-  fetch_weights(ch_k, tk);
-  fetch_weights(ch_v, tv);
+  fetch_weights(ch_a, ta);
+  if (lower) {
+    fetch_weights(ch_b, tb);
+  }
   if (gate_rows) {
 #pragma unroll
     for (int j = 0; j < kGateAhead; ++j) {
-      const int i = tid + j * dk;
+      const int i = tid + j * threads;
       if (i < g.cols / 4) {
         wa_ahead[j] = wa[i];
         wb_ahead[j] = wb[i];
@@ -333,20 +433,22 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
       }
     }
   }
-  const float norm_w = args.ssm_norm[tid];
+  const float norm_w = lower ? args.ssm_norm[ch] : 0.f;
   const float ssm_a = args.ssm_a[head], dt_bias = args.dt_bias[head];
   GridDependencyWait();
   if (!args.early_state) {
-    LoadTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
-    fetch_window(ch_q, tq);
-    fetch_window(ch_k, tk);
-    fetch_window(ch_v, tv);
+    LoadNarrowTile(state_tile, seq.ssm + state_at, dk, tid >> 5);
+    fetch_window(ch_a, ta);
+    if (lower) {
+      fetch_window(ch_b, tb);
+    }
   }
   // What the epilogue needs, requested now so that it has arrived by then.
-  const float z = x[channels + head * dk + tid];
-  tq.cur = x[ch_q];
-  tk.cur = x[ch_k];
-  tv.cur = x[ch_v];
+  const float z = lower ? x[channels + head * dk + ch] : 0.f;
+  ta.cur = x[ch_a];
+  if (lower) {
+    tb.cur = x[ch_b];
+  }
   float alpha, beta;
   if (gate_rows) {
     // The head's alpha and beta rows against the normed input, one float4 per
@@ -361,7 +463,7 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     float4 x_ahead[kGateAhead];
 #pragma unroll
     for (int j = 0; j < kGateAhead; ++j) {
-      const int i = tid + j * dk;
+      const int i = tid + j * threads;
       x_ahead[j] = i < g.cols / 4 ? xa[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float inv = 1.0f;
@@ -372,7 +474,7 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
         const float4 xv = x_ahead[j];
         sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
       }
-      for (int i = tid + kGateAhead * dk; i < g.cols / 4; i += dk) {
+      for (int i = tid + kGateAhead * threads; i < g.cols / 4; i += threads) {
         const float4 xv = xa[i];
         sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
       }
@@ -389,12 +491,12 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     const float4 one4 = make_float4(1.f, 1.f, 1.f, 1.f);
 #pragma unroll
     for (int j = 0; j < kGateAhead; ++j) {
-      const int i = tid + j * dk;
+      const int i = tid + j * threads;
       if (i < g.cols / 4) {
         pass(x_ahead[j], g.norm_w != nullptr ? nw_ahead[j] : one4, wa_ahead[j], wb_ahead[j]);
       }
     }
-    for (int i = tid + kGateAhead * dk; i < g.cols / 4; i += dk) {
+    for (int i = tid + kGateAhead * threads; i < g.cols / 4; i += threads) {
       pass(xa[i], g.norm_w != nullptr ? reinterpret_cast<const float4*>(g.norm_w)[i] : one4, wa[i], wb[i]);
     }
     BlockSum2(pa, pb, sh, warps);
@@ -405,28 +507,40 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     alpha = gates[head];
     beta = gates[hv + head];
   }
-  const float qv = conv(ch_q, tq, head < hk);
-  const float kv = conv(ch_k, tk, head < hk);
-  sh.v[tid] = conv(ch_v, tv, true);
-  if (tid == 0) {
+  // The two gates by two threads of the upper half, while the lower half convolves.
+  if (tid == dk) {
     sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
+  }
+  if (tid == (dk >= 64 ? dk + 32 : dk)) {
     sh.gate[1] = Sigmoid(beta);
   }
+  float qq = 0.f, kk = 0.f, qv = 0.f, kv = 0.f;
+  if (lower) {
+    qv = conv(ch_a, ta, head < hk);
+    kv = conv(ch_b, tb, head < hk);
+    qq = qv * qv;
+    kk = kv * kv;
+  } else {
+    sh.v[ch] = conv(ch_a, ta, true);
+  }
   // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
-  float qq = qv * qv, kk = kv * kv;
   BlockSum2(qq, kk, sh, warps);
-  sh.q[tid] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
-  sh.k[tid] = kv * (1.0f / sqrtf(kk + 1e-6f));
+  if (lower) {
+    sh.q[ch] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
+    sh.k[ch] = kv * (1.0f / sqrtf(kk + 1e-6f));
+  }
   __syncthreads();
 
   float* dst = (seq.ssm_out != nullptr ? seq.ssm_out : seq.ssm) + state_at;
-  DeltaTile(state_tile, dst, dk, tid >> 5, sh);
-  __syncwarp();
+  NarrowDeltaTile(state_tile, dst, dk, tid >> 5, sh);
   // Gated RMSNorm over the head's dk outputs: RMS(o) * w * silu(z).
-  const float o = sh.y[tid];
+  __syncthreads();
+  const float o = lower ? sh.y[ch] : 0.f;
   const float total = BlockSum(o * o, sh, warps);
-  const float inv = 1.0f / sqrtf(total / static_cast<float>(dk) + args.rms_eps);
-  seq.y[head * dk + tid] = o * inv * norm_w * Silu(z);
+  if (lower) {
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(dk) + args.rms_eps);
+    seq.y[head * dk + ch] = o * inv * norm_w * Silu(z);
+  }
 }
 
 int CheckHeads(int key_heads, int value_heads, int head_dim) {
@@ -698,7 +812,7 @@ int EnqueueDeltaNetLinear(gufo_cuda_ctx* ctx, const DeltaNetLayer& l,
       args.gate_rows.xs = nullptr;
     }
     GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaNetLinearKernel, dim3(l.value_heads, n),
-                                         dim3(l.head_dim), 0, ctx->stream, 1, args));
+                                         dim3(2 * l.head_dim), 0, ctx->stream, 1, args));
     ctx->launches.fetch_add(1);
   }
   return GUFO_CUDA_OK;
