@@ -23,11 +23,8 @@
 
 namespace gufo {
 
-constexpr int kTileCols = 32;
 constexpr int kMaxHeadDim = 128;
 constexpr int kDeltaThreads = kMaxHeadDim;            // one thread per column
-constexpr int kRowGroups = 4;                         // lanes / 8
-constexpr int kMaxRowsPerLane = kMaxHeadDim / kRowGroups;  // 32
 constexpr int kMaxSeqs = 16;                          // descriptors per launch
 
 struct DeltaRuleArgs {
@@ -68,29 +65,38 @@ struct DeltaShared {
   float scratch[2 * (2 * kDeltaThreads / 32)];
 };
 
-struct StateTile {
-  float4 s[kMaxRowsPerLane];
+// A warp's tile of COLS (8 or 16) adjacent columns of a head's state: a lane
+// holds rows ig, ig + 32 / G, ... (ig = lane / G, G = COLS / 4) of four adjacent
+// columns (4 * (lane % G)). Narrow tiles mean many warps per head.
+template <int COLS>
+struct NarrowTile {
+  static constexpr int kGroups = COLS / 4;                 // lanes across the columns
+  static constexpr int kRowGroups = 32 / kGroups;
+  static constexpr int kRowsPerLane = kMaxHeadDim / kRowGroups;
+  float4 s[kRowsPerLane];
 };
 
-// Issues this lane's loads of its warp's column tile.
-__device__ __forceinline__ void LoadTile(StateTile& tile, const float* __restrict__ src, int dk,
-                                         int tile_index) {
+template <int COLS>
+__device__ __forceinline__ void LoadNarrowTile(NarrowTile<COLS>& tile, const float* __restrict__ src, int dk,
+                                               int tile_index) {
+  using T = NarrowTile<COLS>;
   const int lane = threadIdx.x & 31;
-  const int col = tile_index * kTileCols + 4 * (lane & 7);
-  const int ig = lane >> 3;
-  const int rows = dk / kRowGroups;
+  const int col = tile_index * COLS + 4 * (lane % T::kGroups);
+  const int ig = lane / T::kGroups;
+  const int rows = dk / T::kRowGroups;
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerLane; ++r) {
+  for (int r = 0; r < T::kRowsPerLane; ++r) {
     if (r < rows) {
-      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kRowGroups + ig) * dk + col);
+      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * T::kRowGroups + ig) * dk + col);
     }
   }
 }
 
-// Sum over the warp's four row groups; every lane gets its columns' totals.
-__device__ __forceinline__ float4 ColumnSum(float4 v) {
+// Sum over the warp's row groups; every lane gets its columns' totals.
+template <int COLS>
+__device__ __forceinline__ float4 NarrowColumnSum(float4 v) {
 #pragma unroll
-  for (int o = 8; o <= 16; o <<= 1) {
+  for (int o = NarrowTile<COLS>::kGroups; o <= 16; o <<= 1) {
     v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, o);
     v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, o);
     v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, o);
@@ -101,28 +107,30 @@ __device__ __forceinline__ float4 ColumnSum(float4 v) {
 
 // The delta rule on this warp's column tile. sh.q, sh.k, sh.v and sh.gate are
 // ready. Writes S' to dst and the tile's outputs to sh.y (no barrier).
-__device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ dst, int dk,
-                                          int tile_index, DeltaShared& sh) {
+template <int COLS>
+__device__ __forceinline__ void NarrowDeltaTile(NarrowTile<COLS>& tile, float* __restrict__ dst, int dk,
+                                                int tile_index, DeltaShared& sh) {
+  using T = NarrowTile<COLS>;
   const int lane = threadIdx.x & 31;
-  const int col = tile_index * kTileCols + 4 * (lane & 7);
-  const int ig = lane >> 3;
-  const int rows = dk / kRowGroups;
+  const int col = tile_index * COLS + 4 * (lane % T::kGroups);
+  const int ig = lane / T::kGroups;
+  const int rows = dk / T::kRowGroups;
   const float decay = sh.gate[0];
   const float beta = sh.gate[1];
-  float4 (&s)[kMaxRowsPerLane] = tile.s;
+  float4 (&s)[T::kRowsPerLane] = tile.s;
   // Pass 1: u_j = sum_i S_ij * (k_i * decay).
   float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerLane; ++r) {
+  for (int r = 0; r < T::kRowsPerLane; ++r) {
     if (r < rows) {
-      const float ki = sh.k[r * kRowGroups + ig] * decay;
+      const float ki = sh.k[r * T::kRowGroups + ig] * decay;
       u.x = fmaf(s[r].x, ki, u.x);
       u.y = fmaf(s[r].y, ki, u.y);
       u.z = fmaf(s[r].z, ki, u.z);
       u.w = fmaf(s[r].w, ki, u.w);
     }
   }
-  u = ColumnSum(u);
+  u = NarrowColumnSum<COLS>(u);
   const float4 v = *reinterpret_cast<const float4*>(&sh.v[col]);
   float4 delta;
   delta.x = beta * (v.x - u.x);
@@ -132,9 +140,9 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
   // Pass 2: S'_ij = S_ij * decay + k_i * delta_j; y_j = sum_i S'_ij * q_i.
   float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-  for (int r = 0; r < kMaxRowsPerLane; ++r) {
+  for (int r = 0; r < T::kRowsPerLane; ++r) {
     if (r < rows) {
-      const int i = r * kRowGroups + ig;
+      const int i = r * T::kRowGroups + ig;
       const float ki = sh.k[i];
       const float qi = sh.q[i];
       float4 n;
@@ -149,104 +157,19 @@ __device__ __forceinline__ void DeltaTile(StateTile& tile, float* __restrict__ d
       y.w = fmaf(n.w, qi, y.w);
     }
   }
-  y = ColumnSum(y);
+  y = NarrowColumnSum<COLS>(y);
   if (ig == 0) {
     *reinterpret_cast<float4*>(&sh.y[col]) = y;
   }
 }
 
-// The same for a warp that owns 16 columns (the decode step's kernel, whose
-// blocks have twice as many warps): a lane holds rows rg, rg + 8, ... (rg =
-// lane / 4) of four adjacent columns (4 * (lane % 4)).
-constexpr int kNarrowCols = 16;
-constexpr int kNarrowRowGroups = 8;
-constexpr int kNarrowRowsPerLane = kMaxHeadDim / kNarrowRowGroups;   // 16
+constexpr int kStepCols = 16;   // columns per warp in the decode step's kernel
+constexpr int kRuleCols = 16;   // and in the stand-alone delta rule (8: 4.9 us for config 3, 16: 4.1, 32: 4.6)
 
-struct NarrowTile {
-  float4 s[kNarrowRowsPerLane];
-};
-
-__device__ __forceinline__ void LoadNarrowTile(NarrowTile& tile, const float* __restrict__ src, int dk,
-                                               int tile_index) {
-  const int lane = threadIdx.x & 31;
-  const int col = tile_index * kNarrowCols + 4 * (lane & 3);
-  const int ig = lane >> 2;
-  const int rows = dk / kNarrowRowGroups;
-#pragma unroll
-  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
-    if (r < rows) {
-      tile.s[r] = *reinterpret_cast<const float4*>(src + static_cast<size_t>(r * kNarrowRowGroups + ig) * dk + col);
-    }
-  }
-}
-
-__device__ __forceinline__ float4 NarrowColumnSum(float4 v) {
-#pragma unroll
-  for (int o = 4; o <= 16; o <<= 1) {
-    v.x += __shfl_xor_sync(0xFFFFFFFFu, v.x, o);
-    v.y += __shfl_xor_sync(0xFFFFFFFFu, v.y, o);
-    v.z += __shfl_xor_sync(0xFFFFFFFFu, v.z, o);
-    v.w += __shfl_xor_sync(0xFFFFFFFFu, v.w, o);
-  }
-  return v;
-}
-
-// DeltaTile's arithmetic on a 16-column tile.
-__device__ __forceinline__ void NarrowDeltaTile(NarrowTile& tile, float* __restrict__ dst, int dk,
-                                                int tile_index, DeltaShared& sh) {
-  const int lane = threadIdx.x & 31;
-  const int col = tile_index * kNarrowCols + 4 * (lane & 3);
-  const int ig = lane >> 2;
-  const int rows = dk / kNarrowRowGroups;
-  const float decay = sh.gate[0];
-  const float beta = sh.gate[1];
-  float4 (&s)[kNarrowRowsPerLane] = tile.s;
-  float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
-    if (r < rows) {
-      const float ki = sh.k[r * kNarrowRowGroups + ig] * decay;
-      u.x = fmaf(s[r].x, ki, u.x);
-      u.y = fmaf(s[r].y, ki, u.y);
-      u.z = fmaf(s[r].z, ki, u.z);
-      u.w = fmaf(s[r].w, ki, u.w);
-    }
-  }
-  u = NarrowColumnSum(u);
-  const float4 v = *reinterpret_cast<const float4*>(&sh.v[col]);
-  float4 delta;
-  delta.x = beta * (v.x - u.x);
-  delta.y = beta * (v.y - u.y);
-  delta.z = beta * (v.z - u.z);
-  delta.w = beta * (v.w - u.w);
-  float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-  for (int r = 0; r < kNarrowRowsPerLane; ++r) {
-    if (r < rows) {
-      const int i = r * kNarrowRowGroups + ig;
-      const float ki = sh.k[i];
-      const float qi = sh.q[i];
-      float4 n;
-      n.x = fmaf(s[r].x, decay, ki * delta.x);
-      n.y = fmaf(s[r].y, decay, ki * delta.y);
-      n.z = fmaf(s[r].z, decay, ki * delta.z);
-      n.w = fmaf(s[r].w, decay, ki * delta.w);
-      *reinterpret_cast<float4*>(dst + static_cast<size_t>(i) * dk + col) = n;
-      y.x = fmaf(n.x, qi, y.x);
-      y.y = fmaf(n.y, qi, y.y);
-      y.z = fmaf(n.z, qi, y.z);
-      y.w = fmaf(n.w, qi, y.w);
-    }
-  }
-  y = NarrowColumnSum(y);
-  if (ig == 0) {
-    *reinterpret_cast<float4*>(&sh.y[col]) = y;
-  }
-}
-
-// Gates given: one warp per thread block, grid = (dk / 32, value_heads,
+// Gates given: one warp per thread block, grid = (dk / 16, value_heads,
 // sequences). The tiles of a head need nothing from one another here, and
-// several small blocks per SM let one tile's stores overlap another's loads.
+// many small blocks per SM let one tile's stores overlap another's loads
+// (16-column tiles: 1024 warps for eight sequences of sixteen heads).
 __global__ void __launch_bounds__(32)
 DeltaRuleKernel(const __grid_constant__ DeltaRuleArgs args) {
   __shared__ __align__(16) DeltaShared sh;
@@ -257,29 +180,33 @@ DeltaRuleKernel(const __grid_constant__ DeltaRuleArgs args) {
   const int kh = head % args.key_heads;
   const int lane = threadIdx.x;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
-  StateTile state;
+  NarrowTile<kRuleCols> state;
   GridLaunchDependents();
   if (args.early_state) {
-    LoadTile(state, seq.state + state_at, dk, tile);
+    LoadNarrowTile(state, seq.state + state_at, dk, tile);
   }
   GridDependencyWait();
   if (!args.early_state) {
-    LoadTile(state, seq.state + state_at, dk, tile);
+    LoadNarrowTile(state, seq.state + state_at, dk, tile);
   }
   for (int i = lane; i < dk; i += 32) {
     sh.q[i] = seq.q[kh * dk + i];
     sh.k[i] = seq.k[kh * dk + i];
   }
-  sh.v[tile * kTileCols + lane] = seq.v[head * dk + tile * kTileCols + lane];
+  if (lane < kRuleCols) {
+    sh.v[tile * kRuleCols + lane] = seq.v[head * dk + tile * kRuleCols + lane];
+  }
   if (lane == 0) {
     sh.gate[0] = seq.decay[head];
     sh.gate[1] = seq.beta[head];
   }
   __syncwarp();
   float* dst = (seq.state_out != nullptr ? seq.state_out : seq.state) + state_at;
-  DeltaTile(state, dst, dk, tile, sh);
+  NarrowDeltaTile(state, dst, dk, tile, sh);
   __syncwarp();
-  seq.y[head * dk + tile * kTileCols + lane] = sh.y[tile * kTileCols + lane];
+  if (lane < kRuleCols) {
+    seq.y[head * dk + tile * kRuleCols + lane] = sh.y[tile * kRuleCols + lane];
+  }
 }
 
 __device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -348,7 +275,7 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   const int ch = lower ? tid : tid - dk;
   const float* x = seq.in;
   const size_t state_at = static_cast<size_t>(head) * dk * dk;
-  NarrowTile state_tile;
+  NarrowTile<kStepCols> state_tile;
   // Causal depthwise conv + SiLU of a channel; also advances that channel's
   // window when this block is the one that owns it. All loads of a thread's
   // channels are issued before the first store, so they overlap.
@@ -547,7 +474,7 @@ int CheckHeads(int key_heads, int value_heads, int head_dim) {
   if (key_heads <= 0 || value_heads <= 0 || value_heads % key_heads != 0) {
     return Fail(GUFO_CUDA_SHAPE, "deltanet: value heads must tile the key heads");
   }
-  if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % kTileCols != 0) {
+  if (head_dim <= 0 || head_dim > kMaxHeadDim || head_dim % 32 != 0) {
     return Fail(GUFO_CUDA_SHAPE,
                 "deltanet: unsupported head dim " + std::to_string(head_dim) +
                     " (multiples of 32 up to 128)");
@@ -594,7 +521,7 @@ int gufo_cuda_delta_rule_device(gufo_cuda_ctx* ctx,
     args.value_heads = value_heads;
     args.head_dim = head_dim;
     args.early_state = ctx->early_state ? 1 : 0;
-    const dim3 grid(head_dim / gufo::kTileCols, value_heads, n);
+    const dim3 grid(head_dim / gufo::kRuleCols, value_heads, n);
     GUFO_CUDA_TRY(gufo::LaunchOverlapped(gufo::DeltaRuleKernel, grid, dim3(32), 0,
                                          ctx->stream, 1, args));
     ctx->launches.fetch_add(1);
