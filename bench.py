@@ -275,19 +275,26 @@ def roofline_probes(ctx, proj, cfg, stream, peak):
     # 6144 x 2048 Q4_K: rotate over the 24 layers' gate matrices (170 MB > L2), graph-replayed.
     mats = [Context._parts([proj.layers[il][3][0]]) for il in range(cfg.layers)]   # Stage.kFfnIn, gate
     yg = torch.empty(1, cfg.ffn, device=dev)
-    g = torch.cuda.CUDAGraph()
-    for m in mats[:3]:
-        ctx.matmul_device(m, 1, x, 1, yg)
-    torch.cuda.synchronize()
-    with torch.cuda.graph(g, stream=stream):
-        for m in mats:
-            ctx.matmul_device(m, 1, x, 1, yg)
-    g.replay()
-    ms = time_on_stream(lambda i: g.replay(), 20) / len(mats)
+    # One launch per product, as the decode step runs it: the kernel converts x by itself
+    # (gufo_cuda_matmul_fused_device, plain input). Beside it the two-launch form of
+    # gufo_cuda_matmul_device (a staging kernel, then the GEMV against the staged image).
+    def replay_us(enqueue):
+        g = torch.cuda.CUDAGraph()
+        for m in mats[:3]:
+            enqueue(m)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            for m in mats:
+                enqueue(m)
+        g.replay()
+        return time_on_stream(lambda i: g.replay(), 20) / len(mats)
+    ms = replay_us(lambda m: ctx.matmul_fused_device(m, 1, 1, yg, x=x))
+    ms_staged = replay_us(lambda m: ctx.matmul_device(m, 1, x, 1, yg))
     b = cfg.ffn * Q.row_bytes(Q.GGML_Q4_K, cfg.hidden) + 4 * cfg.hidden + 4 * cfg.ffn
     out["q4k_gemv"] = {"kernel": "GemvMma<Q4_K, 1 token>", "shape": f"{cfg.ffn}x{cfg.hidden} Q4_K, 1 token",
                        "bytes": b, "us": ms * 1e3, "achieved": b / ms / 1e6, "frac": b / ms / 1e6 / peak,
-                       "note": "24 distinct matrices per graph replay (170 MB, larger than L2)"}
+                       "note": "24 distinct matrices per graph replay (170 MB, larger than L2), one launch per "
+                               f"product; with x staged by a kernel of its own first: {ms_staged * 1e3:.2f} us"}
     # The same Q4_K kernel on a product large enough to run at its sustained rate (262144 x 2048,
     # 302 MB): what the kernel streams once the per-launch ramp and tail are amortised.
     big_rows = 262144
@@ -463,7 +470,7 @@ def run_probe(which: str) -> None:
         x = torch.randn(1, cols, device=dev, generator=gen)
         y = torch.empty(1, rows, device=dev)
         for i in range(8):
-            ctx.matmul_device(mats[i % copies], 1, x, 1, y)
+            ctx.matmul_fused_device(mats[i % copies], 1, 1, y, x=x)   # one launch per product
     elif which == "step_kernel":
         # The config-2 decode step as one cooperative kernel (context option "step_kernel").
         from gufo_npu_b200.backend import CudaDecoder, CudaProjections
