@@ -368,7 +368,16 @@ SwiGluGroups(const float* __restrict__ x, int n, int x_stride, int x_div, const 
 
 }  // namespace
 
-int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, float* scratch) {
+// Whether a grouped gate / up product can leave silu(gate) * up by itself (two
+// Q4_K parts of equal whole tiles on the tensor-core kernel).
+bool GroupedSwiGluInProduct(const gufo_cuda_ctx* ctx, const GemvArgs& base) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(base.x) & 15) == 0 && base.x_group_stride % 4 == 0;
+  return !ctx->force_general && aligned && Q4KFastFits(base.cols, 1) && base.nparts == 2 &&
+         base.parts[0].type == GUFO_CUDA_Q4_K && base.parts[1].type == GUFO_CUDA_Q4_K &&
+         base.parts[0].rows == base.parts[1].rows && base.parts[0].rows % 16 == 0;
+}
+
+int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, float* scratch, bool activate) {
   if (base.group_ids == nullptr || base.groups <= 0 ||
       (prologue != kProloguePlain && prologue != kPrologueSwiGlu)) {
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "grouped product: ids, groups and a plain or SwiGLU input");
@@ -390,6 +399,12 @@ int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& base, int prologue, fl
   args.x_group_stride = base.x_group_stride;
   args.x_group_div = base.x_group_div;
   args.y_group_stride = base.y_group_stride;
+  if (activate) {
+    if (!GroupedSwiGluInProduct(ctx, base)) {
+      return Fail(GUFO_CUDA_UNSUPPORTED_TYPE, "grouped product: these parts cannot activate their own rows");
+    }
+    args.epilogue = kEpilogueSwiGlu;
+  }
   for (int p = 0; p < base.nparts; ++p) {
     const GemvPart& part = base.parts[p];
     if (fast4 && part.type == GUFO_CUDA_Q4_K) {

@@ -38,7 +38,11 @@ struct GemvArgs {
 // input; `prologue` is kProloguePlain (x fp32) or kPrologueSwiGlu (x = [gate |
 // up] per group; `scratch` then holds groups * cols activated values for parts
 // the tensor-core kernel does not run). Fill the group fields of `args`.
-int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& args, int prologue, float* scratch);
+int LaunchGemvGrouped(gufo_cuda_ctx* ctx, const GemvArgs& args, int prologue, float* scratch,
+                      bool activate = false);
+// Whether that product can store silu(gate) * up of its two parts by itself
+// (`activate`: y then holds rows / 2 values per group).
+bool GroupedSwiGluInProduct(const gufo_cuda_ctx* ctx, const GemvArgs& args);
 
 // Enqueues y = [W_0 x | W_1 x | ...] for `tokens` rows; x and y on the device.
 // The caller holds ctx->mu.

@@ -125,9 +125,12 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   // matrix of each part, the input and the output.
   int group = 0;
   size_t matrix = 0;
+  // Grouped launches give a block one tile of its group, or (SwiGLU epilogue) one
+  // gate tile and the up tile of the same rows.
+  const int units_per_group = a.epilogue == kEpilogueSwiGlu ? tiles_per_group / 2 : tiles_per_group;
   if (grouped) {
     GridDependencyWait();   // the ids come from an earlier kernel
-    group = slot / tiles_per_group;
+    group = slot / units_per_group;
     const int id = a.group_ids[group];
     if (id < 0) {
       return;
@@ -135,7 +138,8 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     matrix = static_cast<size_t>(id);
   }
   auto locate = [&](int n, int* part, int* local) {
-    LocateTile(a, grouped ? slot - group * tiles_per_group : slot + n * stride, part, local);
+    LocateTile(a, grouped ? slot - group * units_per_group + (n & 1) * units_per_group : slot + n * stride, part,
+               local);
   };
   if (threadIdx.x == 0) {
 #pragma unroll
@@ -497,6 +501,12 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
     }
     launch.ksplit = 1;
     grid = row_tiles * args.groups;   // one block per tile
+    if (args.epilogue == kEpilogueSwiGlu) {
+      if (args.nparts != 2 || args.parts[0].rows != args.parts[1].rows || args.parts[0].rows % 16 != 0) {
+        return Fail(GUFO_CUDA_BAD_ARGUMENT, "fast gemv: the SwiGLU epilogue takes two parts of equal whole tiles");
+      }
+      grid /= 2;                      // one block per (gate tile, up tile) pair
+    }
   } else if (args.epilogue == kEpilogueSwiGlu) {
     // One block per (gate tile, up tile) pair: block t takes tiles t and t + grid.
     if (args.nparts != 2 || args.parts[0].rows != args.parts[1].rows || args.parts[0].rows % 16 != 0 ||

@@ -211,17 +211,30 @@ int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids,
   in.x_group_stride = x_stride;
   in.x_group_div = pairs_per_input > 1 ? pairs_per_input : 1;
   in.y_group_stride = 2 * bank.expert_ffn;
+  GemvArgs down = bank.down;
+  down.y = y;
+  down.group_ids = ids;
+  down.groups = pairs;
+  down.y_group_stride = bank.hidden;
+  if (act != nullptr && GroupedSwiGluInProduct(ctx, in)) {
+    // A block multiplies a gate tile and the up tile of the same rows and stores
+    // silu(gate) * up; the down product starts from plain rows.
+    in.y = act;
+    in.y_group_stride = bank.expert_ffn;
+    const int rc = LaunchGemvGrouped(ctx, in, kProloguePlain, nullptr, true);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+    down.x = act;
+    down.x_group_stride = bank.expert_ffn;
+    return LaunchGemvGrouped(ctx, down, kProloguePlain, nullptr);
+  }
   int rc = LaunchGemvGrouped(ctx, in, kProloguePlain, nullptr);
   if (rc != GUFO_CUDA_OK) {
     return rc;
   }
-  GemvArgs down = bank.down;
   down.x = ffn;
-  down.y = y;
-  down.group_ids = ids;
-  down.groups = pairs;
   down.x_group_stride = 2 * bank.expert_ffn;
-  down.y_group_stride = bank.hidden;
   return LaunchGemvGrouped(ctx, down, kPrologueSwiGlu, act);
 }
 

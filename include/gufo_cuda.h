@@ -429,7 +429,9 @@ typedef struct gufo_cuda_expert_bank {
  * they do not hold). x_p = x + (p / pairs_per_input) * x_stride: a batch of
  * tokens with k slots each passes x_stride = hidden and pairs_per_input = k;
  * x_stride 0 shares one input. Scratch: ffn [pairs][2 * expert_ffn], act
- * [pairs][expert_ffn]. */
+ * [pairs][expert_ffn]; which of the two holds intermediate values afterwards
+ * depends on the kernels taken (Q4_K banks activate inside the gate / up
+ * launch and leave ffn untouched). */
 int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx,
                                 const gufo_cuda_expert_bank* bank,
                                 const int* ids, int pairs, const float* x,
