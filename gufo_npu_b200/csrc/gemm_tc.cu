@@ -10,7 +10,7 @@
 // per 64 columns. The tokens sit on the MMA's M (the tensor core spends M cycles
 // per instruction whatever N is, measured here: 128 x 32 x 16 took as long as
 // 128 x 128 x 16), the weight rows fill its N = 256.
-//   - two loader warps copy one block of each of the 256 rows per stage (Q4_K:
+//   - six loader warps copy one block of each of the 256 rows per stage (Q4_K:
 //     its 144 bytes; Q6_K: 208 bytes from the three planes of the device
 //     arrangement plus the slab's d values) with 16-byte cp.async whose
 //     completion arrives on an mbarrier (tiled TMA boxes this narrow, 144 B wide,
@@ -21,7 +21,7 @@
 //   - sixteen dequant warps, two threads per weight row: w = d*sc*q - dmin*m
 //     (DequantQ4_K, src/core/quant.cpp:33-59) in packed fp16 arithmetic (two
 //     weights per instruction, as d*sc*(q - 8) + (8*d*sc - dmin*m)) or
-//     w = d*sc*(q - 32) (DequantQ6_K, :98-125) in fp32 rounded once to fp16,
+//     w = d*sc*(q - 32) (DequantQ6_K, :98-125), likewise two per instruction,
 //     stored in the 128-byte-swizzled K-major layout the MMA reads; all sixteen
 //     warps work on one tile at a time, in the order the MMA consumes them;
 //   - one thread issues tcgen05.mma (kind::f16, M = 128, N = 256, K = 16, four
@@ -73,6 +73,7 @@ template <>
 struct Quant<GUFO_CUDA_Q4_K> {
   static constexpr int kRowBytes = kQ4KBytes;   // shared memory per row and block
   static constexpr int kWStages = 3, kXStages = 3, kRawStages = 2;
+  static constexpr int kLoaders = 3;            // loader warps at work (of kLoaderWarps)
   // Chunk `chunk` of block `block` of a row: the GGUF bytes as they are.
   __device__ static const uint8_t* Source(const uint8_t* row, int blocks, int block, int chunk) {
     (void)blocks;
@@ -85,6 +86,7 @@ struct Quant<GUFO_CUDA_Q6_K> {
   // ql 128 | qh 64 | scales 16 | the 16 bytes that hold the slab's d values.
   static constexpr int kRowBytes = 224;
   static constexpr int kWStages = 2, kXStages = 2, kRawStages = 2;
+  static constexpr int kLoaders = 6;
   // The planar device arrangement (Q6KBlockAt): a slab of n blocks stores
   // ql n x 128 | qh n x 64 | scales n x 16 | d n x 2.
   __device__ static const uint8_t* Source(const uint8_t* row, int blocks, int block, int chunk) {
@@ -109,7 +111,11 @@ constexpr int kDequantThreads = 2 * kTileRows;         // two threads per weight
 constexpr int kEpilogueWarp = kDequantThreads / 32;    // four epilogue warps, one per lane quarter
 constexpr int kEpilogueWarps = 4;
 constexpr int kLoaderWarp = kEpilogueWarp + kEpilogueWarps;   // and the next: weight loaders
-constexpr int kMmaWarp = kLoaderWarp + 2;
+// Up to six of them (Quant<TYPE>::kLoaders at work): with two, in-kernel cycle
+// counters showed the loaders issuing copies 70 % (Q4_K) and 98 % (Q6_K) of the
+// time while every other role waited.
+constexpr int kLoaderWarps = 6;
+constexpr int kMmaWarp = kLoaderWarp + kLoaderWarps;
 constexpr int kTileLoaderWarp = kMmaWarp + 1;
 constexpr int kTcThreads = (kTileLoaderWarp + 1) * 32;
 constexpr int kTmemColumns = 512;                      // two accumulators of 256 columns
@@ -286,31 +292,21 @@ __device__ __forceinline__ uint4 EightWeights(uint32_t w0, uint32_t w1, uint32_t
                     HalfPairFma((s1 & kMask) | kOne, kBias, scale, constant));
 }
 
-// Byte I of `w` (a code below 64) minus 32 as a float, exactly: bytes 0 to 2
-// are masked in place under the exponent whose mantissa bit 8I is worth 1
-// (2^(23 - 8I) + code) and the power of two and the 32 are subtracted together;
-// byte 3 is read as byte 1 of the word shifted down by 16.
-template <int I>
-__device__ __forceinline__ float CodeMinus32(uint32_t w) {
-  static_assert(I >= 0 && I <= 2, "the byte must sit below the exponent");
-  constexpr uint32_t kExponent = static_cast<uint32_t>(127 + 23 - 8 * I) << 23;
-  constexpr float kBias = static_cast<float>(1u << (23 - 8 * I)) + 32.0f;
-  return __uint_as_float((w & (0x3Fu << (8 * I))) | kExponent) - kBias;
-}
-
 // Eight Q6_K weights from the codes in the bytes of two words, as four fp16
-// pairs: w = scale * (code - 32) in fp32, rounded once.
+// pairs, in packed fp16 arithmetic: the codes of bytes 0 and 2 (and 1 and 3) are
+// masked in place under the fp16 exponent of 1024, 1024 + 32 is subtracted
+// exactly, and one multiply per pair applies the group's scale, itself rounded
+// to fp16: w = scale * (code - 32).
 __device__ __forceinline__ uint4 EightCodes(uint32_t w0, uint32_t w1, float scale) {
-  const uint32_t s0 = w0 >> 16, s1 = w1 >> 16;
-  auto pack = [](float x, float y) {
-    const __half2 h = __floats2half2_rn(x, y);
-    return *reinterpret_cast<const uint32_t*>(&h);
+  constexpr uint32_t kMask = 0x003F003Fu, kOne = 0x64006400u, kBias = 0x64206420u;   // 1024, 1056
+  const __half2 s2 = __float2half2_rn(scale);
+  auto two = [&](uint32_t w) {
+    const uint32_t biased = (w & kMask) | kOne;
+    const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&kBias)), s2);
+    return *reinterpret_cast<const uint32_t*>(&v);
   };
   // Bytes (0, 2) and (1, 3) of each word: the tiles' order of K.
-  return make_uint4(pack(CodeMinus32<0>(w0) * scale, CodeMinus32<0>(s0) * scale),
-                    pack(CodeMinus32<1>(w0) * scale, CodeMinus32<1>(s0) * scale),
-                    pack(CodeMinus32<0>(w1) * scale, CodeMinus32<0>(s1) * scale),
-                    pack(CodeMinus32<1>(w1) * scale, CodeMinus32<1>(s1) * scale));
+  return make_uint4(two(w0), two(w0 >> 8), two(w1), two(w1 >> 8));
 }
 
 // Where unit `u` of a launch works: its part, weight rows and K range.
@@ -374,7 +370,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kRawStages; ++s) {
-      MbarInit(raw_full(s), 64);
+      MbarInit(raw_full(s), 32 * Q::kLoaders);
       MbarInit(raw_empty(s), kDequantThreads / 32);
     }
     for (int s = 0; s < kWStages; ++s) {
@@ -409,10 +405,10 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
   // Every role walks the same units, blockIdx.x, blockIdx.x + gridDim.x, ...;
   // the stage counters run on across units, so the pipeline never drains
   // between them.
-  if (warp == kLoaderWarp || warp == kLoaderWarp + 1) {
+  if (warp >= kLoaderWarp && warp < kLoaderWarp + Q::kLoaders) {
     // ---- weight loaders: the 16-byte chunks of one block of every row (Q4_K: 9
     // per row, one 144-byte run; Q6_K: 14 per row from its four planes), split
-    // between the two warps; consecutive lanes take consecutive chunks ----------
+    // between the loader warps; consecutive lanes take consecutive chunks -------
     const int which = warp - kLoaderWarp;
     constexpr int kChunksPerRow = Q::kRowBytes / 16;
     constexpr int kChunks = kTileRows * kChunksPerRow;
@@ -426,7 +422,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
         BoundedWait(raw_empty(s), phase ^ 1u, abort_flag, a.error, 1);
         const uint32_t to = base + Smem::kRaw + s * kRawBytes;
 #pragma unroll 6
-        for (int c = which * 32 + lane; c < kChunks; c += 64) {
+        for (int c = which * 32 + lane; c < kChunks; c += 32 * Q::kLoaders) {
           const int r = c / kChunksPerRow;
           const int chunk = c - r * kChunksPerRow;
           // Rows past the end repeat the last row; their sums are never stored.
