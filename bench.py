@@ -424,7 +424,11 @@ def run_ours(args):
                   "ms_per_step_repeats": resident_ms, "e2e_ms_per_step_repeats": e2e_ms},
         "parity": parity,
         "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab * 4,
-                "ms_per_step": ms_e2e},
+                "ms_per_step": ms_e2e,
+                "note": "gufo_cuda_decoder_step per token: the id is copied up, the step runs, the logits land in the "
+                        "caller's pinned buffer (written there over PCIe by the LM head's own stores while it "
+                        "runs; a pageable buffer gets a copy after the step) and the call returns after a "
+                        "stream synchronize"},
         "gpu_launches": int(launches),
         # The metric's kernel: the 6144 x 2048 Q4_K GEMV, one launch per product, 24 distinct
         # matrices back to back. `traffic` is the DRAM traffic of one launch from an ncu capture of

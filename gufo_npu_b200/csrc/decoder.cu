@@ -275,8 +275,16 @@ struct gufo_cuda_decoder {
   // One graph per (tokens - 1, current conv window, with logits); each kind of
   // step runs eagerly twice first (that sizes staging buffers and sets kernel
   // attributes, which a capture cannot).
-  cudaGraphExec_t graph[2][2][2] = {};
-  int64_t graph_kernels[2][2][2] = {};
+  // The last index: 0 no logits, 1 logits on the device, 2 logits on the device
+  // and mirrored into `host_mirror` by the LM head's own stores.
+  cudaGraphExec_t graph[2][2][3] = {};
+  int64_t graph_kernels[2][2][3] = {};
+  // A pinned, device-visible host buffer the caller reads logits from: the LM
+  // head writes its rows there as well (posted writes over PCIe while the
+  // kernel runs), so no copy follows the step. Null: logits are copied down.
+  float* host_mirror = nullptr;        // device-side address
+  const float* host_mirror_for = nullptr;   // the host pointer it belongs to
+  bool mirror_ok = false;              // the LM head is one tensor-core launch
   int eager_runs[2][2] = {};
   std::vector<void*> owned;   // every device allocation, for destroy
 
@@ -556,7 +564,7 @@ void Mark(gufo_cuda_decoder* d, int kind) {
 // second token's go to ssm_spec and the other conv window (DeltaNetStep::Run,
 // src/models/qwen35_2b/deltanet.hpp:35-44). Token t's rows sit at t * width in
 // every activation buffer.
-int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) {
+int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens, bool mirror = false) {
   gufo_cuda_ctx* ctx = d->ctx;
   const gufo_cuda_decoder_config& c = d->c;
   cudaStream_t st = ctx->stream;
@@ -650,7 +658,17 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens) 
   last.h_out = d->h[cur ^ 1];
   last.advance = d->position_dev;
   d->final_h = last.h_out;
-  if (want_logits) {
+  if (want_logits && mirror) {
+    // The logits go to the device buffer and, by the same stores, to the
+    // caller's pinned host buffer.
+    PeerOut both{};
+    both.world = 2;
+    both.rank = 0;
+    both.slot = -1;
+    both.y[0] = d->logits;
+    both.y[1] = d->host_mirror;
+    GUFO_STEP_TRY(FusedProduct(ctx, c.rms_eps, d->lm_head, last, d->normed, d->logits, tokens, &both, nullptr));
+  } else if (want_logits) {
     GUFO_STEP_TRY(FusedProduct(d, d->lm_head, last, d->normed, d->logits, tokens));
   } else {
     // A prompt pass whose logits nobody reads: only the final residuals.
@@ -1252,6 +1270,11 @@ int gufo_cuda_decoder_create(gufo_cuda_ctx* ctx, const gufo_cuda_decoder_config*
     if ((rc = gufo::Stack(ctx, &head, &rows, 1, c.hidden, "the LM head", &d->lm_head)) != GUFO_CUDA_OK) {
       return fail(rc);
     }
+    // One launch of the tensor-core GEMV: its stores can mirror the logits into host memory.
+    const int type = d->lm_head.parts[0].type;
+    d->mirror_ok = d->lm_head.nparts == 1 &&
+                   ((type == GUFO_CUDA_Q4_K && gufo::Q4KFastFits(c.hidden, 1)) ||
+                    (type == GUFO_CUDA_Q6_K && gufo::Q6KFastFits(c.hidden, 1)));
   }
   if ((rc = gufo::UploadVec(d, weights->output_norm, c.hidden, &d->output_norm, "output_norm")) != GUFO_CUDA_OK) {
     return fail(rc);
@@ -1530,8 +1553,37 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
     GUFO_CUDA_TRY(cudaEventRecord(d->token_read[slot], ctx->stream));
   }
   const int parity = d->conv_cur;
-  const int pair = count - 1, with = want_logits != 0 ? 1 : 0;
-  auto enqueue = [&]() { return gufo::EnqueueStep(d, parity, with != 0, count); };
+  const int pair = count - 1;
+  int with = want_logits != 0 ? 1 : 0;
+  // One token into a pinned host buffer that the device can address: the LM
+  // head mirrors its rows there and no copy follows.
+  if (host_logits != nullptr && count == 1 && d->mirror_ok && d->c.use_graph && !d->timeline && !ctx->force_general &&
+      !ctx->step_kernel && d->eager_runs[pair][1] >= 2) {
+    if (host_logits != d->host_mirror_for) {
+      cudaPointerAttributes attr{};
+      float* device_side = nullptr;
+      if (cudaPointerGetAttributes(&attr, host_logits) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+          attr.devicePointer != nullptr && (reinterpret_cast<uintptr_t>(attr.devicePointer) & 15) == 0) {
+        device_side = static_cast<float*>(attr.devicePointer);
+      } else {
+        cudaGetLastError();   // pageable memory is not an error here
+      }
+      // The graphs of the old buffer hold its address.
+      for (int w = 0; w < 2; ++w) {
+        if (d->graph[0][w][2] != nullptr) {
+          cudaGraphExecDestroy(d->graph[0][w][2]);
+          d->graph[0][w][2] = nullptr;
+        }
+      }
+      d->host_mirror = device_side;
+      d->host_mirror_for = host_logits;
+    }
+    if (d->host_mirror != nullptr) {
+      with = 2;
+    }
+  }
+  const int ran = with == 2 ? 1 : with;   // which count of eager runs the step belongs to
+  auto enqueue = [&]() { return gufo::EnqueueStep(d, parity, with != 0, count, with == 2); };
   // One token: the whole step as one persistent kernel, where the model allows it.
   const bool kernel_step = count == 1 && d->plan.ok && ctx->step_kernel && !ctx->force_general && !d->timeline;
   if (kernel_step) {
@@ -1539,7 +1591,7 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
     if (rc != GUFO_CUDA_OK) {
       return rc;
     }
-  } else if (d->c.use_graph && d->eager_runs[pair][with] >= 2 && !d->timeline) {
+  } else if (d->c.use_graph && d->eager_runs[pair][ran] >= 2 && !d->timeline) {
     cudaGraphExec_t& exec = d->graph[pair][parity][with];
     if (exec == nullptr) {
       cudaGraph_t graph = nullptr;
@@ -1569,7 +1621,7 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
     if (rc != GUFO_CUDA_OK) {
       return rc;
     }
-    ++d->eager_runs[pair][with];
+    ++d->eager_runs[pair][ran];
   }
   d->position += count;
   d->conv_cur ^= 1;
@@ -1588,7 +1640,10 @@ int gufo_cuda_decoder_step_tokens(gufo_cuda_decoder* d, const int* tokens, int c
     d->mark_kind.clear();
     ++d->timeline_steps;
   }
-  if (host_logits != nullptr) {
+  if (host_logits != nullptr && with == 2) {
+    // The LM head wrote the caller's buffer itself; the step's end is all there is to wait for.
+    GUFO_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  } else if (host_logits != nullptr) {
     GUFO_CUDA_TRY(cudaMemcpyAsync(host_logits, d->logits, static_cast<size_t>(count) * d->c.vocab * 4,
                                   cudaMemcpyDeviceToHost, ctx->stream));
     if (kernel_step) {

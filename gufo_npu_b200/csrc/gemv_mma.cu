@@ -441,8 +441,8 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     __syncthreads();
     gather(my_tiles - 1);
   }
-  if (a.peer_out.world > 0) {
-    PeerSignal(a.peer_out);
+  if (a.peer_out.world > 0 && a.peer_out.slot >= 0) {
+    PeerSignal(a.peer_out);   // slot < 0: copies that nobody waits on by flag (a host mirror)
   }
 }
 

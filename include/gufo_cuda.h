@@ -604,10 +604,14 @@ int gufo_cuda_decoder_destroy(gufo_cuda_decoder* decoder);
 /* A fresh sequence: Mixer::NewState (src/models/qwen35/decoder.cpp:144-159). */
 int gufo_cuda_decoder_reset(gufo_cuda_decoder* decoder);
 /* Decoder::Step (src/models/qwen35/decoder.cpp:478-528): runs `token` at the
- * current position, advances the state, and copies the vocab logits to
- * host_logits (may be NULL to leave them on the device). Returns
- * GUFO_CUDA_BAD_ARGUMENT for a token outside [0, vocab) and GUFO_CUDA_TOO_LARGE
- * when the attention cache is full. */
+ * current position, advances the state, and leaves the vocab logits in
+ * host_logits (may be NULL to leave them on the device only). Pageable memory
+ * gets a copy after the step. Pinned memory that the device can address
+ * (cudaHostAlloc, cudaHostRegister; 16-byte aligned) is written by the LM
+ * head's own stores while that kernel runs, once the step replays as a graph:
+ * pass the same buffer step after step (a new buffer costs a graph capture).
+ * Returns GUFO_CUDA_BAD_ARGUMENT for a token outside [0, vocab) and
+ * GUFO_CUDA_TOO_LARGE when the attention cache is full. */
 int gufo_cuda_decoder_step(gufo_cuda_decoder* decoder, int token,
                            float* host_logits);
 /* NpuDecoder::Step(tokens, count, state, logits)

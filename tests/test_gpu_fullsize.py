@@ -163,3 +163,23 @@ def test_attention_device_matches_cpu_restatement(ctx, heads, kv_heads, head_dim
         got_k = keys[pos].cpu().numpy().astype(np.float32)
         assert np.allclose(got_k, keys_h[pos].astype(np.float32), rtol=2e-3, atol=1e-4), pos
         assert np.array_equal(values[pos].cpu().numpy().view(np.uint16), values_h[pos].view(np.uint16)), pos
+
+
+def test_logits_into_pinned_memory_equal_copied_logits(ctx):
+    """gufo_cuda_decoder_step with a pinned host buffer: once the step replays as a graph, the LM
+    head writes the caller's buffer itself and no copy follows; the logits are those of a decoder
+    whose logits are copied down, bit for bit, also after the caller switches buffers."""
+    cfg = synth.ModelConfig(**G.DENSE)
+    tensors = synth.build_model(cfg, G.DENSE_SEED)
+    proj = CudaProjections(ctx, cfg, tensors)
+    copied = CudaDecoder(proj, tensors, max_positions=32, use_graph=True)
+    direct = CudaDecoder(proj, tensors, max_positions=32, use_graph=True)
+    pinned = [torch.empty(cfg.vocab, dtype=torch.float32).pin_memory() for _ in range(2)]
+    for i, tok in enumerate((3, 99, 7, 250, 11, 400, 42, 17, 301, 5)):
+        want = copied.Step(tok)
+        buf = pinned[0] if i < 6 else pinned[1]
+        buf.fill_(float("nan"))
+        got = direct.Step(tok, buf.numpy())
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), i
+    copied.close()
+    direct.close()
