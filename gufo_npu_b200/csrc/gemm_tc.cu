@@ -158,6 +158,7 @@ struct TcGemmArgs {
   int blocks_per_unit;     // K range of one unit of work
   int ksplit;
   int total_units;         // tiles * ksplit, dealt round-robin to the thread blocks
+  int tile_rows;           // weight rows per tile: a multiple of 16 up to kTileRows (the MMA's N)
   const uint8_t* xh;       // activation tile images [blocks * 4][128][64] fp16, swizzled
   const float* unscale;    // [128]: factor that undoes the row's power-of-two scale
   int tokens;
@@ -330,7 +331,7 @@ __device__ __forceinline__ Unit LocateUnit(const TcGemmArgs& a, int u) {
       unit.part = p + 1;
     }
   }
-  unit.row0 = tile * kTileRows;
+  unit.row0 = tile * a.tile_rows;
   unit.first_block = unit.split * a.blocks_per_unit;
   unit.blocks = min(a.blocks_per_unit, a.blocks - unit.first_block);   // >= 1 by construction
   return unit;
@@ -411,7 +412,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
     // between the loader warps; consecutive lanes take consecutive chunks -------
     const int which = warp - kLoaderWarp;
     constexpr int kChunksPerRow = Q::kRowBytes / 16;
-    constexpr int kChunks = kTileRows * kChunksPerRow;
+    const int kChunks = a.tile_rows * kChunksPerRow;
     int i = 0;   // blocks requested so far
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const Unit unit = LocateUnit(a, u);
@@ -458,7 +459,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
   } else if (warp == kMmaWarp) {
     // ---- MMA issue ---------------------------------------------------------
     // kind::f16, fp32 accumulate, fp16 A and B, both K-major, N = 256, M = 128.
-    const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(kTileRows >> 3) << 17) |
+    const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(a.tile_rows >> 3) << 17) |
                            (static_cast<uint32_t>(kTokenRows >> 4) << 24);
     int ws = 0, xs = 0;
     uint32_t w_phase = 0, x_phase = 0;
@@ -522,7 +523,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
       // A quarter without tokens is skipped (uniform over the warp, as
       // tcgen05.ld requires).
       if (quarter < a.tokens) {
-        for (int col0 = 0; col0 < kTileRows; col0 += 16) {
+        for (int col0 = 0; col0 < a.tile_rows; col0 += 16) {
           float v[16];
           TmemLoad16(tmem + (static_cast<uint32_t>(quarter * 32) << 16) + buffer * kTileRows + col0, v);
           if (live) {
@@ -557,6 +558,7 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
     // Tile g = 4 * block + t of the thread block's stream lands in buffer g % stages.
     const int r = threadIdx.x & (kTileRows - 1);
     const int half = threadIdx.x / kTileRows;
+    const bool active = r < a.tile_rows;   // rows past the tile's height: the barriers only
     int i = 0;   // blocks done so far
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
       const Unit unit = LocateUnit(a, u);
@@ -593,9 +595,11 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
   #pragma unroll
             for (int c = 0; c < 4; ++c) {
               // Chunk c: values 8c .. 8c + 7 of the low sub-block; chunk 4 + c: of the high one.
-              const uint4 eight = half == 0 ? EightWeights<false>(words[2 * c], words[2 * c + 1], scale2, constant2)
-                                            : EightWeights<true>(words[2 * c], words[2 * c + 1], scale2, constant2);
-              *reinterpret_cast<uint4*>(tile_row + (((4 * half + c) ^ (r & 7)) << 4)) = eight;
+              if (active) {
+                const uint4 eight = half == 0 ? EightWeights<false>(words[2 * c], words[2 * c + 1], scale2, constant2)
+                                              : EightWeights<true>(words[2 * c], words[2 * c + 1], scale2, constant2);
+                *reinterpret_cast<uint4*>(tile_row + (((4 * half + c) ^ (r & 7)) << 4)) = eight;
+              }
             }
             // Make the generic-proxy stores visible to the tensor core's reads; one
             // lane then arrives for the warp.
@@ -647,8 +651,10 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
                 const uint32_t b0 = shift <= 4 ? (qh[2 * k] << (4 - shift)) : (qh[2 * k] >> (shift - 4));
                 const uint32_t b1 = shift <= 4 ? (qh[2 * k + 1] << (4 - shift)) : (qh[2 * k + 1] >> (shift - 4));
                 const float sc = scale(4 * tt + 2 * half + (k >> 1));
-                *reinterpret_cast<uint4*>(tile_row + (((4 * half + k) ^ (r & 7)) << 4)) =
-                    EightCodes(n0 | (b0 & 0x30303030u), n1 | (b1 & 0x30303030u), sc);
+                if (active) {
+                  *reinterpret_cast<uint4*>(tile_row + (((4 * half + k) ^ (r & 7)) << 4)) =
+                      EightCodes(n0 | (b0 & 0x30303030u), n1 | (b1 & 0x30303030u), sc);
+                }
               }
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
               __syncwarp();
@@ -838,18 +844,43 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
     }
     return best;
   };
+  // Weight rows per tile for a group of parts: the height (a multiple of 16, up
+  // to 256) with the least modelled time over the persistent thread blocks. A
+  // unit's time falls with its rows until the tensor core's share (it spends as
+  // long on a narrow tile as on a wide one) takes over at about half height.
+  auto tiles_of = [&](const std::vector<int>& group, int tile_rows) {
+    int tiles = 0;
+    for (int p : group) {
+      tiles += (base.parts[p].rows + tile_rows - 1) / tile_rows;
+    }
+    return tiles;
+  };
+  auto tile_rows_for = [&](const std::vector<int>& group) {
+    int best = kTileRows;
+    double best_cost = 1e30;
+    for (int tr = kTileRows; tr >= 64; tr -= 16) {
+      const int tiles = tiles_of(group, tr);
+      const int rounds = (tiles + ctx->sm_count - 1) / ctx->sm_count;
+      const double unit = tr / static_cast<double>(kTileRows);
+      const double cost = rounds * (unit > 0.55 ? unit : 0.55);
+      if (cost < best_cost - 1e-9) {
+        best_cost = cost;
+        best = tr;
+      }
+    }
+    return best;
+  };
   for (int t0 = 0; t0 < tokens; t0 += kTcMaxTokens) {
     const int m = tokens - t0 < kTcMaxTokens ? tokens - t0 : kTcMaxTokens;
     const size_t image_bytes = static_cast<size_t>(blocks) * 4 * kXTileBytes;
     // Worst case for the partial sums: every part split into blocks / 2 ranges.
     size_t partial_floats = 0;
     for (const std::vector<int>& group : groups) {
-      int tiles = 0;
       size_t rows = 0;
       for (int p : group) {
-        tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
         rows += base.parts[p].rows;
       }
+      const int tiles = tiles_of(group, tile_rows_for(group));
       const int ksplit = splits_for(tiles, m);
       if (ksplit > 1) {
         const size_t need = static_cast<size_t>(ksplit) * m * rows;
@@ -877,10 +908,8 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
       args.unscale = unscale;
       args.tokens = m;
       args.error = reinterpret_cast<int*>(ctx->tc_scratch);
-      int tiles = 0;
-      for (int p : group) {
-        tiles += (base.parts[p].rows + kTileRows - 1) / kTileRows;
-      }
+      args.tile_rows = tile_rows_for(group);
+      const int tiles = tiles_of(group, args.tile_rows);
       args.ksplit = splits_for(tiles, m);
       args.blocks_per_unit = (blocks + args.ksplit - 1) / args.ksplit;
       float* next_partial = partial;
@@ -890,7 +919,7 @@ int LaunchGemmTc(gufo_cuda_ctx* ctx, const GemvArgs& base, int tokens) {
         to.w = part.data;
         to.rows = part.rows;
         to.row_bytes = part.row_bytes;
-        to.tiles = (part.rows + kTileRows - 1) / kTileRows;
+        to.tiles = (part.rows + args.tile_rows - 1) / args.tile_rows;
         if (args.ksplit == 1) {
           to.out = base.y + static_cast<size_t>(t0) * base.y_stride + part.out_offset;
           to.out_stride = base.y_stride;
