@@ -154,6 +154,8 @@ struct FastGemvArgs {
   // slabs r, r + ksplit, ... and the partial sums meet in block 0's shared
   // memory. Set by the launcher for matrices with few rows.
   int ksplit;
+  int tiles_each;         // set by the launcher: with ksplit == 1 block b multiplies tiles_each tiles,
+  int tiles_more;         //   one more if b < tiles_more
   // Grouped launches (the routed experts of a MoE layer): the parts are stacks
   // of `rows`-row matrices, group g multiplies matrix group_ids[g] of every
   // part (a negative id skips the group) with its own input and output. The

@@ -86,6 +86,16 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   // Where the blocks of a cluster leave their sums for block 0: [2][8][16][TOKENS].
   __shared__ float peers[2 * 8 * 16 * TOKENS];
   __shared__ __align__(8) uint64_t landed[kMaxStages];   // a slab's bytes have arrived
+  // The barriers need no kernel argument: set up first, while the arguments' first
+  // reads (constant-cache misses) are under way. A barrier takes eight arrivals.
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int s = 0; s < kStages; ++s) {
+      MbarInit(SharedAddress(&landed[s]), kFastWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   const ImageLayout l = MakeImageLayout(TOKENS, a.cols, S::kGroup);
   const int blocks = a.cols / kSuperBlock;
   const int slabs_per_tile = (blocks + 7) / 8;
@@ -114,12 +124,25 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   const bool grouped = a.group_ids != nullptr;
   const int row_tiles = grouped ? tiles_per_group * a.groups : tiles_per_group;
   // With ksplit > 1 a cluster of ksplit blocks shares each tile.
+  // (No division here: a block's first slabs cannot be requested before these
+  // are known, and nothing hides a chain of integer divisions at a kernel's start.
+  // A cluster launch has one cluster per tile; the launcher divides the rest.)
   const int ks = a.ksplit > 1 ? a.ksplit : 1;
-  const int rank = static_cast<int>(blockIdx.x) % ks;
-  const int slot = static_cast<int>(blockIdx.x) / ks;
-  const int stride = static_cast<int>(gridDim.x) / ks;
-  const int my_tiles = (row_tiles - slot + stride - 1) / stride;
-  const int slabs_mine = (slabs_per_tile - rank + ks - 1) / ks;
+  int rank = 0;
+  int slot = static_cast<int>(blockIdx.x);
+  int stride = static_cast<int>(gridDim.x);
+  int my_tiles = a.tiles_each + (slot < a.tiles_more ? 1 : 0);
+  int slabs_mine = slabs_per_tile;
+  if (ks > 1) {
+    asm("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm("mov.u32 %0, %%clusterid.x;" : "=r"(slot));
+    stride = row_tiles;
+    my_tiles = 1;
+    slabs_mine = 0;
+    for (int s = rank; s < slabs_per_tile; s += ks) {
+      ++slabs_mine;
+    }
+  }
   const int my_slabs = my_tiles * slabs_mine;
   // A grouped launch has one block per tile; the block's group picks the
   // matrix of each part, the input and the output.
@@ -141,46 +164,54 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
     LocateTile(a, grouped ? slot - group * units_per_group + (n & 1) * units_per_group : slot + n * stride, part,
                local);
   };
-  if (threadIdx.x == 0) {
-#pragma unroll
-    for (int s = 0; s < kStages; ++s) {
-      MbarInit(SharedAddress(&landed[s]), 1);
-    }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  if constexpr (S::kZeros) {
-    for (int i = threadIdx.x * 16; i < l.plane_stride; i += kFastThreads * 16) {
-      *reinterpret_cast<uint4*>(zeros + i) = make_uint4(0u, 0u, 0u, 0u);
-    }
-  }
   __syncthreads();
 
-  // Brings slab q of this block (slab s of tile n) into ring slot q % kStages:
-  // one bulk copy per row by the calling warp's sixteen low lanes.
+  // Brings slabs of this block into their ring slots (slab q into q % kStages);
+  // (n, s) = tile and own-slab index of slab q. A barrier takes eight arrivals.
+  // Ahead of the first multiplication every warp requests rows 2 * warp and
+  // 2 * warp + 1 of each of the `count` first slabs, a bulk copy per row and lane
+  // (one warp issuing a slab's sixteen copies spends about a thousand cycles in
+  // that instruction, which here nothing hides); later one warp requests a whole
+  // slab while the others multiply.
   const uint32_t ring_base = SharedAddress(ring);
-  auto issue = [&](int q, int n, int s) {
+  auto request = [&](int q, int n, int s, int r, bool announce, int rows_announced) {
+    const int slab = rank + s * ks;
     int bytes;
     if constexpr (kQ4) {
-      bytes = min(8, blocks - s * 8) * kQ4KBytes;
+      bytes = min(8, blocks - slab * 8) * kQ4KBytes;
     } else {
       // The row's last slab runs to the (16-byte padded) end of the row.
-      bytes = min(S::kDataBytes, a.row_bytes - s * S::kDataBytes);
+      bytes = min(S::kDataBytes, a.row_bytes - slab * S::kDataBytes);
     }
-    const uint32_t bar = SharedAddress(&landed[q % kStages]);
-    if (lane == 0) {
-      MbarArriveExpectTx(bar, 16u * static_cast<uint32_t>(bytes));
+    const int at = q % kStages;
+    const uint32_t bar = SharedAddress(&landed[at]);
+    if (announce) {
+      MbarArriveExpectTx(bar, static_cast<uint32_t>(rows_announced * bytes));
     }
-    __syncwarp();
+    __syncwarp(__activemask());
+    int part, local;
+    locate(n, &part, &local);
+    // Rows past the end repeat the last row; their sums are never stored.
+    const int row = min(local * 16 + r, a.parts[part].rows - 1);
+    const uint8_t* src = a.parts[part].w +
+                         (matrix * a.parts[part].rows + static_cast<size_t>(row)) * a.row_bytes +
+                         static_cast<size_t>(slab) * S::kDataBytes;
+    BulkCopy(ring_base + at * S::kBytes + r * S::kRowBytes, src, static_cast<uint32_t>(bytes), bar);
+  };
+  auto issue_first = [&](int count) {
+    const int mine = lane >> 1;   // which of the slabs this lane requests from
+    if (mine < count) {
+      int n = 0, s = mine;
+      while (s >= slabs_mine) {
+        s -= slabs_mine;
+        ++n;
+      }
+      request(mine, n, s, 2 * warp + (lane & 1), (lane & 1) == 0, 2);
+    }
+  };
+  auto issue = [&](int q, int n, int s) {
     if (lane < 16) {
-      int part, local;
-      locate(n, &part, &local);
-      // Rows past the end repeat the last row; their sums are never stored.
-      const int row = min(local * 16 + lane, a.parts[part].rows - 1);
-      const uint8_t* src = a.parts[part].w +
-                           (matrix * a.parts[part].rows + static_cast<size_t>(row)) * a.row_bytes +
-                           static_cast<size_t>(s) * S::kDataBytes;
-      BulkCopy(ring_base + (q % kStages) * S::kBytes + lane * S::kRowBytes, src, static_cast<uint32_t>(bytes), bar);
+      request(q, n, s, lane, lane < kFastWarps, 2);
     }
   };
   // (tile, own-slab index) of the next slab to request; every thread keeps it.
@@ -198,13 +229,17 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   // before, for the slab kStages - 1 on.
   constexpr bool kEarly = TOKENS == 1;
   constexpr int kAhead = kEarly ? kStages : kStages - 1;
-#pragma unroll
-  for (int q = 0; q < kAhead; ++q) {
-    if (q < my_slabs) {
-      if (warp == q) {
-        issue(q, req_n, rank + req_s * ks);
-      }
+  {
+    const int first = min(kAhead, my_slabs);
+    issue_first(first);
+    for (int q = 0; q < first; ++q) {
       advance();
+    }
+  }
+  if constexpr (S::kZeros) {
+    // Read only after the image's barrier below.
+    for (int i = threadIdx.x * 16; i < l.plane_stride; i += kFastThreads * 16) {
+      *reinterpret_cast<uint4*>(zeros + i) = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   float norm_ahead[8];
@@ -332,7 +367,7 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
       __syncthreads();
       if (q + kAhead < my_slabs) {
         if (warp == (q & 7)) {
-          issue(q + kAhead, req_n, rank + req_s * ks);
+          issue(q + kAhead, req_n, req_s);
         }
         advance();
       }
@@ -522,6 +557,12 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
     // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
     PlanFastGrid(GemvMma<TYPE, TOKENS, PER_SM>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit,
                  &grid);
+  }
+  {
+    // Tiles per block (ksplit == 1): block b takes tiles b, b + grid, ...
+    const int total = row_tiles * (args.group_ids != nullptr ? args.groups : 1);
+    launch.tiles_each = total / grid;
+    launch.tiles_more = total % grid;
   }
   GUFO_CUDA_TRY(LaunchOverlapped(GemvMma<TYPE, TOKENS, PER_SM>, dim3(grid), dim3(kFastThreads), smem, ctx->stream,
                                  launch.ksplit, launch));
