@@ -65,20 +65,23 @@ struct Slab<GUFO_CUDA_Q6_K> {
 constexpr int kMaxStages = 3;
 constexpr int kExchange = 2;
 
-template <int TYPE, int TOKENS>
+// ONE: every block of the launch multiplies a single slab, so the ring is one
+// slot (a third or half of the shared memory: more blocks fit an SM, which lets a
+// cluster of three split a three-slab row where two-slot blocks allowed two).
+template <int TYPE, int TOKENS, bool ONE = false>
 size_t SharedBytes(int cols) {
   const ImageLayout l = MakeImageLayout(TOKENS, cols, Slab<TYPE>::kGroup);
   return static_cast<size_t>(l.bytes) + (Slab<TYPE>::kZeros ? l.plane_stride : 0) +
          static_cast<size_t>(kExchange) * kFastWarps * 16 * TOKENS * 4 +
-         static_cast<size_t>(Slab<TYPE>::kStages) * Slab<TYPE>::kBytes;
+         static_cast<size_t>(ONE ? 1 : Slab<TYPE>::kStages) * Slab<TYPE>::kBytes;
 }
 
-template <int TYPE, int TOKENS, int PER_SM>
+template <int TYPE, int TOKENS, int PER_SM, bool ONE = false>
 __global__ void __launch_bounds__(kFastThreads, PER_SM)
 GemvMma(const __grid_constant__ FastGemvArgs a) {
   using S = Slab<TYPE>;
   constexpr bool kQ4 = TYPE == GUFO_CUDA_Q4_K;
-  constexpr int kStages = S::kStages;
+  constexpr int kStages = ONE ? 1 : S::kStages;
   constexpr int kNCols = TOKENS * kLimbs;
   constexpr int kNB = (kNCols + 7) / 8;
   constexpr int kTileFloats = 16 * TOKENS;   // per warp in an exchange buffer: row sums per token
@@ -228,7 +231,7 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
   // 7 % slower with it): the barrier comes first and frees the slot of the slab
   // before, for the slab kStages - 1 on.
   constexpr bool kEarly = TOKENS == 1;
-  constexpr int kAhead = kEarly ? kStages : kStages - 1;
+  constexpr int kAhead = kEarly || ONE ? kStages : kStages - 1;
   {
     const int first = min(kAhead, my_slabs);
     issue_first(first);
@@ -482,12 +485,12 @@ GemvMma(const __grid_constant__ FastGemvArgs a) {
 }
 
 // Lets the kernel use all the shared memory a block may have (once per device).
-template <int TYPE, int TOKENS, int PER_SM>
+template <int TYPE, int TOKENS, int PER_SM, bool ONE = false>
 int Configure(const gufo_cuda_ctx* ctx) {
   static bool configured[16] = {};
   if (!configured[ctx->device & 15]) {
-    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemvMma<TYPE, TOKENS, PER_SM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kFastMaxShared));
+    GUFO_CUDA_TRY(cudaFuncSetAttribute(GemvMma<TYPE, TOKENS, PER_SM, ONE>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, kFastMaxShared));
     configured[ctx->device & 15] = true;
   }
   return GUFO_CUDA_OK;
@@ -557,6 +560,29 @@ int LaunchVariant(gufo_cuda_ctx* ctx, const FastGemvArgs& args) {
     // Few rows and several slabs per tile: split the tiles' slabs over a cluster.
     PlanFastGrid(GemvMma<TYPE, TOKENS, PER_SM>, ctx->device, kFastThreads, smem, row_tiles, slabs, &launch.ksplit,
                  &grid);
+    if constexpr (TOKENS <= 2) {
+      // Rows of two to four slabs whose (tile, slab) pairs do not all get a block
+      // above: the one-slab form is smaller and may hold them (a 2048 x 6144 Q6_K
+      // product: clusters of three blocks with one slab each instead of two blocks
+      // with two and one). Only then: every further kernel that alternates with
+      // the others in a decode step costs instruction-cache misses at each start
+      // (the same launches ran 0.4 us slower when products that gain no wider
+      // split went to this form too).
+      if (slabs >= 2 && slabs <= 4 && launch.ksplit < slabs) {
+        const size_t smem_one = SharedBytes<TYPE, TOKENS, true>(args.cols);
+        auto* one = GemvMma<TYPE, TOKENS, PER_SM, true>;
+        if (Configure<TYPE, TOKENS, PER_SM, true>(ctx) == GUFO_CUDA_OK &&
+            row_tiles * slabs <= ResidentBlocks(one, ctx->device, kFastThreads, smem_one, slabs)) {
+          launch.ksplit = slabs;
+          launch.tiles_each = 1;
+          launch.tiles_more = 0;
+          GUFO_CUDA_TRY(LaunchOverlapped(one, dim3(row_tiles * slabs), dim3(kFastThreads), smem_one, ctx->stream,
+                                         slabs, launch));
+          ctx->launches.fetch_add(1);
+          return GUFO_CUDA_OK;
+        }
+      }
+    }
   }
   {
     // Tiles per block (ksplit == 1): block b takes tiles b, b + grid, ...
