@@ -83,8 +83,10 @@ struct Quant<GUFO_CUDA_Q4_K> {
 
 template <>
 struct Quant<GUFO_CUDA_Q6_K> {
-  // ql 128 | qh 64 | scales 16 | the 16 bytes that hold the slab's d values.
-  static constexpr int kRowBytes = 224;
+  // ql 128 | qh 64 | scales 16 | the 16 bytes that hold the slab's d values | 16
+  // unused: rows 240 bytes apart, so that the 16-byte reads of eight consecutive
+  // rows fall into different banks (224 put rows r and r + 4 into the same).
+  static constexpr int kRowBytes = 240;
   static constexpr int kWStages = 2, kXStages = 2, kRawStages = 2;
   static constexpr int kLoaders = 6;
   // The planar device arrangement (Q6KBlockAt): a slab of n blocks stores
@@ -422,15 +424,44 @@ GemmTc(const __grid_constant__ TcGemmArgs a) {
         const uint32_t phase = (i / kRawStages) & 1u;
         BoundedWait(raw_empty(s), phase ^ 1u, abort_flag, a.error, 1);
         const uint32_t to = base + Smem::kRaw + s * kRawBytes;
+        if constexpr (TYPE == GUFO_CUDA_Q4_K) {
 #pragma unroll 6
-        for (int c = which * 32 + lane; c < kChunks; c += 32 * Q::kLoaders) {
-          const int r = c / kChunksPerRow;
-          const int chunk = c - r * kChunksPerRow;
-          // Rows past the end repeat the last row; their sums are never stored.
-          const int row = min(unit.row0 + r, part.rows - 1);
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to + c * 16),
-                       "l"(Q::Source(part.w + static_cast<size_t>(row) * part.row_bytes, a.blocks,
-                                     unit.first_block + b, chunk)) : "memory");
+          for (int c = which * 32 + lane; c < kChunks; c += 32 * Q::kLoaders) {
+            const int r = c / kChunksPerRow;
+            const int chunk = c - r * kChunksPerRow;
+            // Rows past the end repeat the last row; their sums are never stored.
+            const int row = min(unit.row0 + r, part.rows - 1);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to + c * 16),
+                         "l"(Q::Source(part.w + static_cast<size_t>(row) * part.row_bytes, a.blocks,
+                                       unit.first_block + b, chunk)) : "memory");
+          }
+        } else {
+          // Plane by plane (ql: 8 chunks a row, qh: 4, scales: 1, the slab's d values: 1),
+          // so that a warp's lanes never part ways over which plane a chunk is in and the
+          // offsets of a plane are computed once a block.
+          const int block = unit.first_block + b;
+          const int slab = block / kQ6KSlabBlocks;
+          const int j = block - slab * kQ6KSlabBlocks;
+          const int left = a.blocks - slab * kQ6KSlabBlocks;
+          const int n = left < kQ6KSlabBlocks ? left : kQ6KSlabBlocks;
+          const uint8_t* from = part.w + static_cast<size_t>(slab) * kQ6KSlabBlocks * kQ6KBytes;
+          const int last = part.rows - 1 - unit.row0;
+          auto plane = [&](int src_at, int dst_at, int shift) {
+            // 1 << shift chunks a row.
+            const int items = a.tile_rows << shift;
+#pragma unroll 4
+            for (int c = which * 32 + lane; c < items; c += 32 * Q::kLoaders) {
+              const int r = c >> shift;
+              const int chunk = c & ((1 << shift) - 1);
+              const int row = unit.row0 + min(r, last);
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to + r * Q::kRowBytes + dst_at + 16 * chunk),
+                           "l"(from + static_cast<size_t>(row) * part.row_bytes + src_at + 16 * chunk) : "memory");
+            }
+          };
+          plane(128 * j, 0, 3);
+          plane(128 * n + 64 * j, 128, 2);
+          plane(192 * n + 16 * j, 192, 0);
+          plane(208 * n, 208, 0);
         }
         // Arrives on the stage's barrier once this thread's copies have landed.
         asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(raw_full(s)) : "memory");
