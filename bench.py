@@ -614,9 +614,8 @@ def probe_moe(ctx, stream, dev, gen) -> None:
         def enqueue():
             for r in range(rounds):
                 ctx.route_device(logits[r], experts + 1, tokens, experts, k, chosen, weights, scale)
-                ctx.expert_ffn_device(handles[r % banks], chosen, tokens * k, x, hidden, ffn, act, rows_out,
-                                      pairs_per_input=k)
-                ctx.moe_combine_device(shared, scale, weights, rows_out, tokens, k, hidden, y)
+                ctx.moe_ffn_device(handles[r % banks], chosen, weights, scale, tokens, k, x, hidden, shared, ffn, act,
+                                   rows_out, y)
         us = graph_us(stream, enqueue) / rounds
         algorithmic = tokens * k * per_expert
         out["results"].append({"tokens": tokens, "us": us, "GB/s": algorithmic / us / 1e3,

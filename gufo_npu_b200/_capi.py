@@ -164,6 +164,9 @@ SIGNATURES = {
                                          C.c_void_p, C.c_void_p]),
     "gufo_cuda_expert_ffn_device": (C.c_int, [C.c_void_p, C.POINTER(ExpertBank), C.c_void_p, C.c_int, C.c_void_p,
                                               C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "gufo_cuda_moe_ffn_device": (C.c_int, [C.c_void_p, C.POINTER(ExpertBank), C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p]),
     "gufo_cuda_moe_combine_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                                C.c_int, C.c_int, C.c_void_p]),
     "gufo_cuda_decoder_create": (C.c_int, [C.c_void_p, C.POINTER(DecoderConfig), C.POINTER(DecoderWeights),

@@ -227,6 +227,14 @@ class Context:
                                                          C.c_void_p(_ptr(ffn)),
                                                          C.c_void_p(_ptr(act)), C.c_void_p(_ptr(y))))
 
+    def moe_ffn_device(self, bank: "_capi.ExpertBank", ids, weights, scale, tokens: int, k: int, x, x_stride: int,
+                       shared, ffn, act, expert_out, out) -> None:
+        """out[t] = shared[t] * scale[t] + the weighted sum of token t's k experts' FFN (device tensors)."""
+        self._check(self.lib.gufo_cuda_moe_ffn_device(
+            self.handle, C.byref(bank), C.c_void_p(_ptr(ids)), C.c_void_p(_ptr(weights)), C.c_void_p(_ptr(scale)),
+            tokens, k, C.c_void_p(_ptr(x)), x_stride, C.c_void_p(_ptr(shared)), C.c_void_p(_ptr(ffn)),
+            C.c_void_p(_ptr(act)), C.c_void_p(_ptr(expert_out)), C.c_void_p(_ptr(out))))
+
     def moe_combine_device(self, shared, scale, weights, expert_out, tokens: int, k: int, hidden: int, out) -> None:
         self._check(self.lib.gufo_cuda_moe_combine_device(self.handle, C.c_void_p(_ptr(shared)),
                                                           C.c_void_p(_ptr(scale)), C.c_void_p(_ptr(weights)),
@@ -531,6 +539,11 @@ class CudaMoe:
         if tokens > self.max_tokens:
             raise ValueError("CudaMoe: more tokens than max_tokens")
         self.route(layer, normed, tokens)
+        if self.expert_range is None:
+            c = self.config
+            self.ctx.moe_ffn_device(self.banks[layer], self.chosen, self.weights, self.scale, tokens, c.experts_used,
+                                    normed, c.hidden, shared, self.ffn, self.act, self.expert_out, out)
+            return
         self.experts(layer, normed, tokens)
         self.combine(shared, tokens, out)
 

@@ -643,10 +643,8 @@ int EnqueueStep(gufo_cuda_decoder* d, int parity, bool want_logits, int tokens, 
       GUFO_STEP_TRY(LaunchGemv(ctx, router, tokens));
       GUFO_STEP_TRY(EnqueueRoute(ctx, d->router, c.experts + 1, tokens, c.experts, c.experts_used, d->chosen,
                                  d->route_weights, d->shared_scale));
-      GUFO_STEP_TRY(EnqueueExpertFfn(ctx, l.bank, d->chosen, tokens * c.experts_used, d->normed, c.hidden,
-                                     c.experts_used, d->expert_ffn, d->expert_act, d->expert_out));
-      GUFO_STEP_TRY(EnqueueMoeCombine(ctx, d->out, d->shared_scale, d->route_weights, d->expert_out, tokens,
-                                      c.experts_used, c.hidden, d->out));
+      GUFO_STEP_TRY(EnqueueMoeFfn(ctx, l.bank, d->chosen, d->route_weights, d->shared_scale, tokens, c.experts_used,
+                                  d->normed, c.hidden, d->out, d->expert_ffn, d->expert_act, d->expert_out, d->out));
     }
     Mark(d, GUFO_CUDA_TIMELINE_FFN_DOWN);
     pending = d->out;

@@ -198,6 +198,300 @@ int BuildExpertBank(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank& bank, Exper
   return GUFO_CUDA_OK;
 }
 
+namespace {
+
+// The grouped product of narrow Q4_K matrices (1, 2 or 4 blocks of 256 values a
+// row: an expert's down projection, 2048 x 512 here) with one fp32 input per
+// group. The 16-row x 8-block tiles of the fast GEMV leave six of eight warps
+// idle on such rows and pay an input conversion per tile; here sixteen lanes
+// take a block of a row (a lane: eight bytes of codes, i.e. eight values each of
+// the sub-blocks 2c and 2c + 1, with the sixteen inputs they meet held in
+// registers for all of the warp's rows), dequantize as the reference does
+// (w = d * sc * q - dmin * m, DequantQ4_K, src/core/quant.cpp:64-96) and reduce
+// over the row's lanes. `x` is plain, or [gate | up] per group when `swiglu`.
+struct NarrowArgs {
+  const uint8_t* w;      // experts stacked along the rows
+  int rows;              // of one expert
+  int row_bytes;
+  const int* ids;        // [groups], < 0: nothing to do
+  const float* x;
+  int x_stride;          // floats between the groups' inputs
+  int x_div;             // groups per input
+  int swiglu;
+  float* y;
+  int y_stride;          // floats between the groups' outputs
+};
+
+constexpr int kNarrowPasses = 8;   // rows (or row pairs) a warp multiplies, loads issued together
+
+__device__ __forceinline__ float NarrowSilu(float v) { return v * (1.0f / (1.0f + expf(-v))); }
+
+template <int BLOCKS>
+__global__ void __launch_bounds__(256)
+NarrowGroupedQ4K(const __grid_constant__ NarrowArgs a) {
+  constexpr int kSlots = 16 * BLOCKS;                       // lane slots a row
+  constexpr int kPer = kSlots > 32 ? kSlots / 32 : 1;       // slots a lane
+  constexpr int kRowsAtOnce = kSlots < 32 ? 32 / kSlots : 1;
+  constexpr int kWarpRows = kNarrowPasses * kRowsAtOnce;
+  GridLaunchDependents();
+  GridDependencyWait();   // the ids and the inputs come from earlier kernels
+  const int group = blockIdx.y;
+  const int id = a.ids[group];
+  if (id < 0) {
+    return;
+  }
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int first = (blockIdx.x * 8 + warp) * kWarpRows;
+  const uint8_t* matrix = a.w + static_cast<size_t>(id) * a.rows * a.row_bytes;
+  const float* x = a.x + static_cast<size_t>(group / (a.x_div > 1 ? a.x_div : 1)) * a.x_stride;
+  const int cols = 256 * BLOCKS;
+  // This lane's slots: block b, 32-byte chunk c of its codes, eight-byte part p.
+  int at[kPer];       // byte offset of the block in the row
+  int part[kPer];     // offset of the eight code bytes behind the block's 16-byte head
+  int pair[kPer];     // c: sub-blocks 2c (low nibbles) and 2c + 1 (high)
+  float lo[kPer][8], hi[kPer][8], lo_sum[kPer], hi_sum[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int slot = (lane + 32 * j) % kSlots;
+    const int b = slot >> 4;
+    const int c = (slot >> 2) & 3;
+    const int p = slot & 3;
+    at[j] = b * kQ4KBytes;
+    part[j] = 32 * c + 8 * p;
+    pair[j] = c;
+    const int col = 256 * b + 64 * c + 8 * p;
+    lo_sum[j] = hi_sum[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (a.swiglu) {
+        lo[j][i] = NarrowSilu(x[col + i]) * x[cols + col + i];
+        hi[j][i] = NarrowSilu(x[col + 32 + i]) * x[cols + col + 32 + i];
+      } else {
+        lo[j][i] = x[col + i];
+        hi[j][i] = x[col + 32 + i];
+      }
+      lo_sum[j] += lo[j][i];
+      hi_sum[j] += hi[j][i];
+    }
+  }
+  const int sub = kRowsAtOnce > 1 ? lane / kSlots : 0;   // which of the rows taken at once
+  uint4 head[kNarrowPasses][kPer];
+  uint2 codes[kNarrowPasses][kPer];
+#pragma unroll
+  for (int r = 0; r < kNarrowPasses; ++r) {
+    // Rows past the end repeat the last row; their sums are not stored.
+    const int row = min(first + r * kRowsAtOnce + sub, a.rows - 1);
+    const uint8_t* from = matrix + static_cast<size_t>(row) * a.row_bytes;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      head[r][j] = *reinterpret_cast<const uint4*>(from + at[j]);
+      codes[r][j] = *reinterpret_cast<const uint2*>(from + at[j] + 16 + part[j]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kNarrowPasses; ++r) {
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const float d = HalfBitsToFloat(static_cast<uint16_t>(head[r][j].x & 0xFFFF));
+      const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head[r][j].x >> 16));
+      int sc_lo, m_lo, sc_hi, m_hi;
+      ScaleMinK4(2 * pair[j], head[r][j].y, head[r][j].z, head[r][j].w, &sc_lo, &m_lo);
+      ScaleMinK4(2 * pair[j] + 1, head[r][j].y, head[r][j].z, head[r][j].w, &sc_hi, &m_hi);
+      float dot_lo = 0.f, dot_hi = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t word = i < 4 ? codes[r][j].x : codes[r][j].y;
+        const uint32_t byte = (word >> (8 * (i & 3))) & 0xFFu;
+        dot_lo = fmaf(static_cast<float>(byte & 15u), lo[j][i], dot_lo);
+        dot_hi = fmaf(static_cast<float>(byte >> 4), hi[j][i], dot_hi);
+      }
+      sum += d * (static_cast<float>(sc_lo) * dot_lo + static_cast<float>(sc_hi) * dot_hi) -
+             dmin * (static_cast<float>(m_lo) * lo_sum[j] + static_cast<float>(m_hi) * hi_sum[j]);
+    }
+#pragma unroll
+    for (int o = kSlots < 32 ? kSlots / 2 : 16; o > 0; o >>= 1) {
+      sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);
+    }
+    const int row = first + r * kRowsAtOnce + sub;
+    if ((lane % (kSlots < 32 ? kSlots : 32)) == 0 && row < a.rows) {
+      a.y[static_cast<size_t>(group) * a.y_stride + row] = sum;
+    }
+  }
+}
+
+template <int BLOCKS>
+int LaunchNarrow(gufo_cuda_ctx* ctx, const NarrowArgs& args, int groups) {
+  constexpr int kSlots = 16 * BLOCKS;
+  constexpr int kBlockRows = 8 * kNarrowPasses * (kSlots < 32 ? 32 / kSlots : 1);
+  GUFO_CUDA_TRY(LaunchOverlapped(NarrowGroupedQ4K<BLOCKS>, dim3((args.rows + kBlockRows - 1) / kBlockRows, groups),
+                                 dim3(256), 0, ctx->stream, 1, args));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+// Whether the narrow kernel takes a grouped product of one Q4_K part.
+bool NarrowFits(const GemvArgs& g) {
+  const int blocks = g.cols / kSuperBlock;
+  return g.nparts == 1 && g.parts[0].type == GUFO_CUDA_Q4_K && g.cols % kSuperBlock == 0 &&
+         (blocks == 1 || blocks == 2 || blocks == 4);
+}
+
+int LaunchNarrowGrouped(gufo_cuda_ctx* ctx, const GemvArgs& g, bool swiglu) {
+  NarrowArgs args{};
+  args.w = g.parts[0].data;
+  args.rows = g.parts[0].rows;
+  args.row_bytes = g.parts[0].row_bytes;
+  args.ids = g.group_ids;
+  args.x = g.x;
+  args.x_stride = g.x_group_stride;
+  args.x_div = g.x_group_div;
+  args.swiglu = swiglu ? 1 : 0;
+  args.y = g.y + g.parts[0].out_offset;
+  args.y_stride = g.y_group_stride;
+  switch (g.cols / kSuperBlock) {
+    case 1: return LaunchNarrow<1>(ctx, args, g.groups);
+    case 2: return LaunchNarrow<2>(ctx, args, g.groups);
+    default: return LaunchNarrow<4>(ctx, args, g.groups);
+  }
+}
+
+// The down product of a token's k (<= 8) chosen experts and Decoder::MoeFfn's
+// weighted sum in one launch (decoder.cpp:541-556): out[t][row] = shared[t][row] *
+// scale[t] + the sum, in slot order, of weights[t][s] * (row of expert ids[t][s]
+// times act[t][s]). A warp takes a row (BLOCKS = 1: two rows) of all k experts at
+// once: k row loads in flight, the k activated inputs of the token in shared
+// memory. A slot with ids < 0 adds nothing.
+struct NarrowCombineArgs {
+  const uint8_t* w;
+  int rows;
+  int row_bytes;
+  const int* ids;          // [tokens][k]
+  const float* weights;    // [tokens][k]
+  const float* scale;      // [tokens]
+  const float* shared;     // [tokens][rows]
+  const float* act;        // [tokens][k][256 * BLOCKS]
+  int k;
+  float* out;              // [tokens][rows]; may be shared
+};
+
+constexpr int kCombineSlots = 8;
+
+template <int BLOCKS>
+__global__ void __launch_bounds__(256)
+NarrowCombineQ4K(const __grid_constant__ NarrowCombineArgs a) {
+  constexpr int kSlots = 16 * BLOCKS;
+  constexpr int kPer = kSlots > 32 ? kSlots / 32 : 1;
+  constexpr int kRowsAtOnce = kSlots < 32 ? 32 / kSlots : 1;
+  constexpr int kCols = 256 * BLOCKS;
+  __shared__ __align__(16) float xs[kCombineSlots][kCols];
+  GridLaunchDependents();
+  GridDependencyWait();
+  const int token = blockIdx.y;
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int sub = kRowsAtOnce > 1 ? lane / kSlots : 0;
+  const int row = (blockIdx.x * 8 + warp) * kRowsAtOnce + sub;
+  const int load_row = min(row, a.rows - 1);
+  int at[kPer], part[kPer], pair[kPer], col[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int slot = (lane + 32 * j) % kSlots;
+    const int b = slot >> 4;
+    const int c = (slot >> 2) & 3;
+    const int p = slot & 3;
+    at[j] = b * kQ4KBytes;
+    part[j] = 32 * c + 8 * p;
+    pair[j] = c;
+    col[j] = 256 * b + 64 * c + 8 * p;
+  }
+  // The k rows first (they come from HBM), then the inputs.
+  uint4 head[kCombineSlots][kPer];
+  uint2 codes[kCombineSlots][kPer];
+  int id[kCombineSlots];
+#pragma unroll
+  for (int s = 0; s < kCombineSlots; ++s) {
+    id[s] = s < a.k ? a.ids[token * a.k + s] : -1;
+    if (id[s] >= 0) {
+      const uint8_t* from = a.w + (static_cast<size_t>(id[s]) * a.rows + load_row) * a.row_bytes;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        head[s][j] = *reinterpret_cast<const uint4*>(from + at[j]);
+        codes[s][j] = *reinterpret_cast<const uint2*>(from + at[j] + 16 + part[j]);
+      }
+    }
+  }
+  for (int i = threadIdx.x * 4; i < a.k * kCols; i += 256 * 4) {
+    const int s = i / kCols;
+    *reinterpret_cast<float4*>(&xs[s][i - s * kCols]) =
+        *reinterpret_cast<const float4*>(a.act + (static_cast<size_t>(token) * a.k + s) * kCols + (i - s * kCols));
+  }
+  __syncthreads();
+  float sum[kCombineSlots];
+#pragma unroll
+  for (int s = 0; s < kCombineSlots; ++s) {
+    sum[s] = 0.f;
+    if (id[s] >= 0) {
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const float4 l0 = *reinterpret_cast<const float4*>(&xs[s][col[j]]);
+        const float4 l1 = *reinterpret_cast<const float4*>(&xs[s][col[j] + 4]);
+        const float4 h0 = *reinterpret_cast<const float4*>(&xs[s][col[j] + 32]);
+        const float4 h1 = *reinterpret_cast<const float4*>(&xs[s][col[j] + 36]);
+        const float lo[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+        const float hi[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+        const float d = HalfBitsToFloat(static_cast<uint16_t>(head[s][j].x & 0xFFFF));
+        const float dmin = HalfBitsToFloat(static_cast<uint16_t>(head[s][j].x >> 16));
+        int sc_lo, m_lo, sc_hi, m_hi;
+        ScaleMinK4(2 * pair[j], head[s][j].y, head[s][j].z, head[s][j].w, &sc_lo, &m_lo);
+        ScaleMinK4(2 * pair[j] + 1, head[s][j].y, head[s][j].z, head[s][j].w, &sc_hi, &m_hi);
+        float dot_lo = 0.f, dot_hi = 0.f, lo_sum = 0.f, hi_sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t word = i < 4 ? codes[s][j].x : codes[s][j].y;
+          const uint32_t byte = (word >> (8 * (i & 3))) & 0xFFu;
+          dot_lo = fmaf(static_cast<float>(byte & 15u), lo[i], dot_lo);
+          dot_hi = fmaf(static_cast<float>(byte >> 4), hi[i], dot_hi);
+          lo_sum += lo[i];
+          hi_sum += hi[i];
+        }
+        sum[s] += d * (static_cast<float>(sc_lo) * dot_lo + static_cast<float>(sc_hi) * dot_hi) -
+                  dmin * (static_cast<float>(m_lo) * lo_sum + static_cast<float>(m_hi) * hi_sum);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = kSlots < 32 ? kSlots / 2 : 16; o > 0; o >>= 1) {
+#pragma unroll
+    for (int s = 0; s < kCombineSlots; ++s) {
+      sum[s] += __shfl_xor_sync(0xFFFFFFFFu, sum[s], o);
+    }
+  }
+  if ((lane % (kSlots < 32 ? kSlots : 32)) == 0 && row < a.rows) {
+    const size_t at_out = static_cast<size_t>(token) * a.rows + row;
+    float v = a.shared[at_out] * a.scale[token];
+#pragma unroll
+    for (int s = 0; s < kCombineSlots; ++s) {
+      if (s < a.k && id[s] >= 0) {
+        v = fmaf(a.weights[token * a.k + s], sum[s], v);
+      }
+    }
+    a.out[at_out] = v;
+  }
+}
+
+template <int BLOCKS>
+int LaunchNarrowCombine(gufo_cuda_ctx* ctx, const NarrowCombineArgs& args, int tokens) {
+  constexpr int kBlockRows = 8 * (16 * BLOCKS < 32 ? 32 / (16 * BLOCKS) : 1);
+  GUFO_CUDA_TRY(LaunchOverlapped(NarrowCombineQ4K<BLOCKS>, dim3((args.rows + kBlockRows - 1) / kBlockRows, tokens),
+                                 dim3(256), 0, ctx->stream, 1, args));
+  ctx->launches.fetch_add(1);
+  return GUFO_CUDA_OK;
+}
+
+}  // namespace
+
 int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, int pairs, const float* x,
                      int x_stride, int pairs_per_input, float* ffn, float* act, float* y) {
   if (pairs <= 0 || ids == nullptr || x == nullptr || ffn == nullptr || y == nullptr) {
@@ -227,7 +521,8 @@ int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids,
     }
     down.x = act;
     down.x_group_stride = bank.expert_ffn;
-    return LaunchGemvGrouped(ctx, down, kProloguePlain, nullptr);
+    return NarrowFits(down) ? LaunchNarrowGrouped(ctx, down, false)
+                            : LaunchGemvGrouped(ctx, down, kProloguePlain, nullptr);
   }
   int rc = LaunchGemvGrouped(ctx, in, kProloguePlain, nullptr);
   if (rc != GUFO_CUDA_OK) {
@@ -235,7 +530,8 @@ int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids,
   }
   down.x = ffn;
   down.x_group_stride = 2 * bank.expert_ffn;
-  return LaunchGemvGrouped(ctx, down, kPrologueSwiGlu, act);
+  return NarrowFits(down) ? LaunchNarrowGrouped(ctx, down, true)
+                          : LaunchGemvGrouped(ctx, down, kPrologueSwiGlu, act);
 }
 
 int EnqueueMoeCombine(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,
@@ -247,6 +543,50 @@ int EnqueueMoeCombine(gufo_cuda_ctx* ctx, const float* shared, const float* scal
                                  shared, scale, weights, expert_out, k, hidden, out));
   ctx->launches.fetch_add(1);
   return GUFO_CUDA_OK;
+}
+
+int EnqueueMoeFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, const float* weights,
+                  const float* scale, int tokens, int k, const float* x, int x_stride, const float* shared,
+                  float* ffn, float* act, float* expert_out, float* out) {
+  if (tokens <= 0 || k <= 0 || ids == nullptr || weights == nullptr || scale == nullptr || x == nullptr ||
+      shared == nullptr || ffn == nullptr || act == nullptr || expert_out == nullptr || out == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "moe ffn: null pointer or no tokens");
+  }
+  GemvArgs in = bank.in;
+  in.x = x;
+  in.y = act;
+  in.group_ids = ids;
+  in.groups = tokens * k;
+  in.x_group_stride = x_stride;
+  in.x_group_div = k;
+  in.y_group_stride = bank.expert_ffn;
+  GemvArgs down = bank.down;
+  const int blocks = down.cols / kSuperBlock;
+  if (k <= kCombineSlots && NarrowFits(down) && blocks <= 2 && GroupedSwiGluInProduct(ctx, in)) {
+    // Two launches: gate / up with the SwiGLU in its epilogue, then the down rows
+    // of a token's experts with the weighted sum.
+    const int rc = LaunchGemvGrouped(ctx, in, kProloguePlain, nullptr, true);
+    if (rc != GUFO_CUDA_OK) {
+      return rc;
+    }
+    NarrowCombineArgs args{};
+    args.w = down.parts[0].data;
+    args.rows = down.parts[0].rows;
+    args.row_bytes = down.parts[0].row_bytes;
+    args.ids = ids;
+    args.weights = weights;
+    args.scale = scale;
+    args.shared = shared;
+    args.act = act;
+    args.k = k;
+    args.out = out;
+    return blocks == 1 ? LaunchNarrowCombine<1>(ctx, args, tokens) : LaunchNarrowCombine<2>(ctx, args, tokens);
+  }
+  const int rc = EnqueueExpertFfn(ctx, bank, ids, tokens * k, x, x_stride, k, ffn, act, expert_out);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  return EnqueueMoeCombine(ctx, shared, scale, weights, expert_out, tokens, k, bank.hidden, out);
 }
 
 }  // namespace gufo
@@ -291,6 +631,27 @@ int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank*
     return Fail(GUFO_CUDA_BAD_ARGUMENT, "expert ffn: pairs_per_input is at least 1");
   }
   return gufo::EnqueueExpertFfn(ctx, built, ids, pairs, x, static_cast<int>(x_stride), pairs_per_input, ffn, act, y);
+}
+
+int gufo_cuda_moe_ffn_device(gufo_cuda_ctx* ctx, const gufo_cuda_expert_bank* bank, const int* ids,
+                             const float* weights, const float* scale, int tokens, int k, const float* x,
+                             int64_t x_stride, const float* shared, float* ffn, float* act, float* expert_out,
+                             float* out) {
+  if (ctx == nullptr || bank == nullptr) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "moe ffn: null pointer");
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  GUFO_CUDA_TRY(cudaSetDevice(ctx->device));
+  gufo::ExpertBank built;
+  const int rc = gufo::BuildExpertBank(ctx, *bank, &built);
+  if (rc != GUFO_CUDA_OK) {
+    return rc;
+  }
+  if (x_stride != 0 && x_stride < bank->hidden) {
+    return Fail(GUFO_CUDA_BAD_ARGUMENT, "moe ffn: x_stride is 0 (shared input) or at least hidden");
+  }
+  return gufo::EnqueueMoeFfn(ctx, built, ids, weights, scale, tokens, k, x, static_cast<int>(x_stride), shared, ffn,
+                             act, expert_out, out);
 }
 
 int gufo_cuda_moe_combine_device(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,

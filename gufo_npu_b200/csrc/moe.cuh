@@ -30,4 +30,13 @@ int EnqueueExpertFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids,
 int EnqueueMoeCombine(gufo_cuda_ctx* ctx, const float* shared, const float* scale, const float* weights,
                       const float* expert_out, int tokens, int k, int hidden, float* out);
 
+// Decoder::MoeFfn behind the router: out[t] = shared[t] * scale[t] + the weighted
+// sum of the k chosen experts' FFN of x_t (x_t = x + t * x_stride). Two launches
+// where the bank's shapes allow (Q4_K, expert_ffn 256 or 512, k <= 8): the gate /
+// up product with its SwiGLU, and the down rows with the weighted sum; otherwise
+// EnqueueExpertFfn and EnqueueMoeCombine through `ffn` and `expert_out`.
+int EnqueueMoeFfn(gufo_cuda_ctx* ctx, const ExpertBank& bank, const int* ids, const float* weights,
+                  const float* scale, int tokens, int k, const float* x, int x_stride, const float* shared,
+                  float* ffn, float* act, float* expert_out, float* out);
+
 }  // namespace gufo

@@ -438,6 +438,24 @@ int gufo_cuda_expert_ffn_device(gufo_cuda_ctx* ctx,
                                 int64_t x_stride, int pairs_per_input,
                                 float* ffn, float* act, float* y);
 
+/* Decoder::MoeFfn behind the router (decoder.cpp:535-557) in one call: out[t] =
+ * shared[t] * scale[t] + sum over slots s, in slot order, of weights[t][s] *
+ * y(t, s), y(t, s) the FFN of expert ids[t][s] applied to x_t = x + t *
+ * x_stride; a slot with ids < 0 adds nothing. Equal to
+ * gufo_cuda_expert_ffn_device (pairs = tokens * k, pairs_per_input = k) followed
+ * by gufo_cuda_moe_combine_device up to the rounding of the row sums' order;
+ * for Q4_K banks with expert_ffn 256 or 512 and k <= 8 it runs as two launches
+ * (gate / up with the SwiGLU; the down rows of a token's experts with the
+ * weighted sum) and touches neither ffn nor expert_out. Scratch as for
+ * gufo_cuda_expert_ffn_device plus expert_out [tokens][k][hidden]. out may be
+ * shared. */
+int gufo_cuda_moe_ffn_device(gufo_cuda_ctx* ctx,
+                             const gufo_cuda_expert_bank* bank, const int* ids,
+                             const float* weights, const float* scale,
+                             int tokens, int k, const float* x, int64_t x_stride,
+                             const float* shared, float* ffn, float* act,
+                             float* expert_out, float* out);
+
 /* out[t] = shared[t] * scale[t] + sum over slots, in slot order, of
  * weights[t][slot] * expert_out[t][slot] (decoder.cpp:541-556). out may be
  * shared. */

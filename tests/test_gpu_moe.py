@@ -247,3 +247,46 @@ def test_config4_shaped_experts(ctx, oracle):
         assert rel_l2(got[slot], want) <= GEMV_TOL, slot
     for m in mats.values():
         ctx.matrix_free(m)
+
+
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_moe_ffn_in_one_call_equals_expert_ffn_then_combine(ctx, tokens):
+    """gufo_cuda_moe_ffn_device (config-4 shapes: the down rows of a token's experts and the
+    weighted sum in one launch) against gufo_cuda_expert_ffn_device + gufo_cuda_moe_combine_device
+    on the same routing, one slot of the second token's ids set to -1 (adds nothing)."""
+    hidden, ef, experts, k = 2048, 512, 32, 8
+    dev = torch.device("cuda:0")
+    gen = torch.Generator().manual_seed(41)
+    mats = {}
+    for name, rows, cols in (("gate", ef, hidden), ("up", ef, hidden), ("down", hidden, ef)):
+        w = torch.randn(experts * rows, cols, generator=gen) * 0.02
+        raw = Q.quantize(Q.GGML_Q4_K, w).numpy()
+        mats[name] = ctx.matrix_upload(Q.GGML_Q4_K, raw, experts * rows, cols)
+    bank = _capi.ExpertBank(mats["gate"], mats["up"], mats["down"], experts, ef, hidden)
+    logits = torch.from_numpy(G.normal(42, tokens, experts + 1)).to(dev)
+    chosen = torch.empty(tokens, k, dtype=torch.int32, device=dev)
+    weights = torch.empty(tokens, k, device=dev)
+    scale = torch.empty(tokens, device=dev)
+    ctx.route_device(logits, experts + 1, tokens, experts, k, chosen, weights, scale)
+    ctx.synchronize()
+    if tokens > 1:
+        chosen[1, 2] = -1
+        torch.cuda.synchronize()
+    x = torch.from_numpy(G.normal(43, tokens, hidden)).to(dev)
+    shared = torch.from_numpy(G.normal(44, tokens, hidden)).to(dev)
+    ffn = torch.empty(tokens * k, 2 * ef, device=dev)
+    act = torch.empty(tokens * k, ef, device=dev)
+    rows_out = torch.zeros(tokens, k, hidden, device=dev)   # a skipped pair's rows stay zero
+    want = torch.empty(tokens, hidden, device=dev)
+    ctx.expert_ffn_device(bank, chosen, tokens * k, x, hidden, ffn, act, rows_out, pairs_per_input=k)
+    ctx.moe_combine_device(shared, scale, weights, rows_out, tokens, k, hidden, want)
+    got = torch.empty(tokens, hidden, device=dev)
+    ctx.moe_ffn_device(bank, chosen, weights, scale, tokens, k, x, hidden, shared, ffn, act, rows_out, got)
+    ctx.synchronize()
+    assert rel_l2(got.cpu().numpy(), want.cpu().numpy()) <= 1e-6
+    # In place over the shared expert's output, as the decoder calls it.
+    ctx.moe_ffn_device(bank, chosen, weights, scale, tokens, k, x, hidden, shared, ffn, act, rows_out, shared)
+    ctx.synchronize()
+    assert rel_l2(shared.cpu().numpy(), want.cpu().numpy()) <= 1e-6
+    for m in mats.values():
+        ctx.matrix_free(m)
