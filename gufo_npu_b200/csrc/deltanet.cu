@@ -62,7 +62,7 @@ struct DeltaShared {
   float v[kMaxHeadDim];
   float y[kMaxHeadDim];
   float gate[2];                              // decay, beta
-  float scratch[2 * (2 * kDeltaThreads / 32)];
+  float scratch[5 * (2 * kDeltaThreads / 32)];   // up to five sums a warp (BlockSum5)
 };
 
 // A warp's tile of COLS (8 or 16) adjacent columns of a head's state: a lane
@@ -248,6 +248,33 @@ __device__ __forceinline__ void BlockSum2(float& a, float& b, DeltaShared& sh, i
   }
 }
 
+// The same for five values (the decode step's one reduction ahead of the delta
+// rule: the input's sum of squares, the two gate dots, the q and k norms).
+__device__ __forceinline__ void BlockSum5(float (&v)[5], DeltaShared& sh, int warps) {
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    v[i] = WarpSum(v[i]);
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      sh.scratch[5 * (threadIdx.x >> 5) + i] = v[i];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 5; ++i) {
+    v[i] = 0.f;
+  }
+  for (int w = 0; w < warps; ++w) {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      v[i] += sh.scratch[5 * w + i];
+    }
+  }
+}
+
 // Mixer::Linear for one (sequence, value head). grid = (value_heads,
 // sequences), 2 * dk threads: thread t < dk owns channel t of the head's q and k
 // and output t of the epilogue, thread dk + t channel t of v; warp w owns columns
@@ -376,7 +403,6 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   if (lower) {
     tb.cur = x[ch_b];
   }
-  float alpha, beta;
   if (gate_rows) {
     // The head's alpha and beta rows against the normed input, one float4 per
     // thread and pass (GgufProjections serves these F32 rows through its own
@@ -393,24 +419,14 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
       const int i = tid + j * threads;
       x_ahead[j] = i < g.cols / 4 ? xa[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    float inv = 1.0f;
-    if (g.norm_w != nullptr) {
-      float sq = 0.f;
-#pragma unroll
-      for (int j = 0; j < kGateAhead; ++j) {
-        const float4 xv = x_ahead[j];
-        sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
-      }
-      for (int i = tid + kGateAhead * threads; i < g.cols / 4; i += threads) {
-        const float4 xv = xa[i];
-        sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
-      }
-      inv = 1.0f / sqrtf(BlockSum(sq, sh, warps) / static_cast<float>(g.cols) + g.eps);
-    }
-    float pa = 0.f, pb = 0.f;
+    // One pass and one block-wide reduction: with norm weights the dots are taken
+    // against x * w and scaled by the norm's 1 / rms afterwards (a scalar), so the
+    // sum of squares, both dots and the q / k norms below reduce together.
+    float sq = 0.f, pa = 0.f, pb = 0.f;
     auto pass = [&](float4 xv, const float4& nw, const float4& av, const float4& bv) {
       if (g.norm_w != nullptr) {
-        xv = make_float4(xv.x * inv * nw.x, xv.y * inv * nw.y, xv.z * inv * nw.z, xv.w * inv * nw.w);
+        sq += xv.x * xv.x + xv.y * xv.y + xv.z * xv.z + xv.w * xv.w;
+        xv = make_float4(xv.x * nw.x, xv.y * nw.y, xv.z * nw.z, xv.w * nw.w);
       }
       pa += av.x * xv.x + av.y * xv.y + av.z * xv.z + av.w * xv.w;
       pb += bv.x * xv.x + bv.y * xv.y + bv.z * xv.z + bv.w * xv.w;
@@ -426,35 +442,53 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
     for (int i = tid + kGateAhead * threads; i < g.cols / 4; i += threads) {
       pass(xa[i], g.norm_w != nullptr ? reinterpret_cast<const float4*>(g.norm_w)[i] : one4, wa[i], wb[i]);
     }
-    BlockSum2(pa, pb, sh, warps);
-    alpha = pa;
-    beta = pb;
+    float qv = 0.f, kv = 0.f;
+    if (lower) {
+      qv = conv(ch_a, ta, head < hk);
+      kv = conv(ch_b, tb, head < hk);
+    } else {
+      sh.v[ch] = conv(ch_a, ta, true);
+    }
+    float five[5] = {sq, pa, pb, qv * qv, kv * kv};
+    BlockSum5(five, sh, warps);
+    const float inv = g.norm_w != nullptr ? 1.0f / sqrtf(five[0] / static_cast<float>(g.cols) + g.eps) : 1.0f;
+    const float alpha = five[1] * inv, beta = five[2] * inv;
+    // The two gates by two threads of the upper half.
+    if (tid == dk) {
+      sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
+    }
+    if (tid == (dk >= 64 ? dk + 32 : dk)) {
+      sh.gate[1] = Sigmoid(beta);
+    }
+    // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
+    if (lower) {
+      sh.q[ch] = qv * ((1.0f / sqrtf(five[3] + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
+      sh.k[ch] = kv * (1.0f / sqrtf(five[4] + 1e-6f));
+    }
   } else {
     const float* gates = x + channels + value_dim;  // alpha | beta follow z
-    alpha = gates[head];
-    beta = gates[hv + head];
-  }
-  // The two gates by two threads of the upper half, while the lower half convolves.
-  if (tid == dk) {
-    sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
-  }
-  if (tid == (dk >= 64 ? dk + 32 : dk)) {
-    sh.gate[1] = Sigmoid(beta);
-  }
-  float qq = 0.f, kk = 0.f, qv = 0.f, kv = 0.f;
-  if (lower) {
-    qv = conv(ch_a, ta, head < hk);
-    kv = conv(ch_b, tb, head < hk);
-    qq = qv * qv;
-    kk = kv * kv;
-  } else {
-    sh.v[ch] = conv(ch_a, ta, true);
-  }
-  // L2 norms (+1e-6 under the root); q also takes 1/sqrt(dk).
-  BlockSum2(qq, kk, sh, warps);
-  if (lower) {
-    sh.q[ch] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
-    sh.k[ch] = kv * (1.0f / sqrtf(kk + 1e-6f));
+    const float alpha = gates[head];
+    const float beta = gates[hv + head];
+    if (tid == dk) {
+      sh.gate[0] = expf(ssm_a * Softplus(alpha + dt_bias));
+    }
+    if (tid == (dk >= 64 ? dk + 32 : dk)) {
+      sh.gate[1] = Sigmoid(beta);
+    }
+    float qq = 0.f, kk = 0.f, qv = 0.f, kv = 0.f;
+    if (lower) {
+      qv = conv(ch_a, ta, head < hk);
+      kv = conv(ch_b, tb, head < hk);
+      qq = qv * qv;
+      kk = kv * kv;
+    } else {
+      sh.v[ch] = conv(ch_a, ta, true);
+    }
+    BlockSum2(qq, kk, sh, warps);
+    if (lower) {
+      sh.q[ch] = qv * ((1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(static_cast<float>(dk))));
+      sh.k[ch] = kv * (1.0f / sqrtf(kk + 1e-6f));
+    }
   }
   __syncthreads();
 
