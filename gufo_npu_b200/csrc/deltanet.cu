@@ -106,10 +106,11 @@ __device__ __forceinline__ float4 NarrowColumnSum(float4 v) {
 }
 
 // The delta rule on this warp's column tile. sh.q, sh.k, sh.v and sh.gate are
-// ready. Writes S' to dst and the tile's outputs to sh.y (no barrier).
+// ready. Writes S' to dst and the tile's outputs to sh.y (no barrier); with
+// `squares`, lane 0 also leaves the sum of the squares of the tile's outputs there.
 template <int COLS>
 __device__ __forceinline__ void NarrowDeltaTile(NarrowTile<COLS>& tile, float* __restrict__ dst, int dk,
-                                                int tile_index, DeltaShared& sh) {
+                                                int tile_index, DeltaShared& sh, float* squares = nullptr) {
   using T = NarrowTile<COLS>;
   const int lane = threadIdx.x & 31;
   const int col = tile_index * COLS + 4 * (lane % T::kGroups);
@@ -160,6 +161,17 @@ __device__ __forceinline__ void NarrowDeltaTile(NarrowTile<COLS>& tile, float* _
   y = NarrowColumnSum<COLS>(y);
   if (ig == 0) {
     *reinterpret_cast<float4*>(&sh.y[col]) = y;
+  }
+  if (squares != nullptr) {
+    // Lanes 0 .. kGroups - 1 hold the tile's COLS outputs.
+    float sq = ig == 0 ? y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w : 0.f;
+#pragma unroll
+    for (int o = T::kGroups / 2; o > 0; o >>= 1) {
+      sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+    }
+    if (lane == 0) {
+      *squares = sq;
+    }
   }
 }
 
@@ -493,11 +505,16 @@ DeltaNetLinearKernel(const __grid_constant__ LinearArgs args) {
   __syncthreads();
 
   float* dst = (seq.ssm_out != nullptr ? seq.ssm_out : seq.ssm) + state_at;
-  NarrowDeltaTile(state_tile, dst, dk, tid >> 5, sh);
-  // Gated RMSNorm over the head's dk outputs: RMS(o) * w * silu(z).
+  // (The scratch's last readers passed the barrier above.)
+  NarrowDeltaTile(state_tile, dst, dk, tid >> 5, sh, &sh.scratch[tid >> 5]);
+  // Gated RMSNorm over the head's dk outputs: RMS(o) * w * silu(z); the warps'
+  // tiles left their outputs' squares, so one barrier serves both.
   __syncthreads();
   const float o = lower ? sh.y[ch] : 0.f;
-  const float total = BlockSum(o * o, sh, warps);
+  float total = 0.f;
+  for (int w = 0; w < warps; ++w) {
+    total += sh.scratch[w];
+  }
   if (lower) {
     const float inv = 1.0f / sqrtf(total / static_cast<float>(dk) + args.rms_eps);
     seq.y[head * dk + ch] = o * inv * norm_w * Silu(z);
