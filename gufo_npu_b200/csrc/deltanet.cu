@@ -227,21 +227,6 @@ __device__ __forceinline__ float Softplus(float x) {
   return x > 20.0f ? x : log1pf(expf(x));
 }
 
-// Block-wide sum of one value per thread; result to every thread.
-__device__ __forceinline__ float BlockSum(float v, DeltaShared& sh, int warps) {
-  v = WarpSum(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) {
-    sh.scratch[threadIdx.x >> 5] = v;
-  }
-  __syncthreads();
-  float total = 0.f;
-  for (int w = 0; w < warps; ++w) {
-    total += sh.scratch[w];
-  }
-  return total;
-}
-
 // Block-wide sums of two values per thread at once; results to every thread.
 __device__ __forceinline__ void BlockSum2(float& a, float& b, DeltaShared& sh, int warps) {
   a = WarpSum(a);
